@@ -1,0 +1,117 @@
+// Python bindings: torch tensors in, raw pointers + current CUDA stream out to
+// the C launchers declared in dsb_api.h.  No kernels here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "dsb_api.h"
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_bf16_2d(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2 && t.scalar_type() == torch::kBFloat16 &&
+                  t.stride(1) == 1,
+              name, ": expected a 2-D bf16 CUDA tensor with unit inner stride");
+  TORCH_CHECK(t.stride(0) % 8 == 0 && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0, name,
+              ": row stride must be a multiple of 8 elements and the base 16-byte aligned");
+}
+const float* opt_f32(const c10::optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->is_contiguous());
+  return t->data_ptr<float>();
+}
+float* opt_f32_mut(c10::optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->is_contiguous());
+  return t->data_ptr<float>();
+}
+DsbGate to_gate(const std::vector<double>& g) {
+  TORCH_CHECK(g.size() == 8, "gate: expected 8 numbers");
+  DsbGate d;
+  d.kind = static_cast<int>(g[0]);
+  d.sharpness = g[1]; d.act_threshold = g[2]; d.act_cutoff = g[3]; d.epsilon = g[4];
+  d.max_intensity = g[5]; d.clip_max = g[6]; d.dead_threshold = g[7];
+  return d;
+}
+
+// C (=|+=) alpha * row_scale * op(A) . op(B)^T + bias.
+//   a_mn == false: A is [M,K];  a_mn == true: A is stored [K,M]
+//   b_mn == false: B is [N,K];  b_mn == true: B is stored [K,N]
+void gemm(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn, Tensor& C, bool accumulate,
+          double alpha, c10::optional<Tensor> row_scale, c10::optional<Tensor> bias,
+          int64_t block_n, Tensor& status) {
+  check_bf16_2d(A, "A");
+  check_bf16_2d(B, "B");
+  const c10::cuda::CUDAGuard guard(A.device());
+  const int64_t M = a_mn ? A.size(1) : A.size(0);
+  const int64_t K = a_mn ? A.size(0) : A.size(1);
+  const int64_t N = b_mn ? B.size(1) : B.size(0);
+  TORCH_CHECK((b_mn ? B.size(0) : B.size(1)) == K, "gemm: K mismatch");
+  TORCH_CHECK(C.is_cuda() && C.dim() == 2 && C.size(0) == M && C.size(1) == N && C.stride(1) == 1,
+              "gemm: bad C");
+  const bool c_bf16 = C.scalar_type() == torch::kBFloat16;
+  TORCH_CHECK(c_bf16 || C.scalar_type() == torch::kFloat32, "gemm: C must be bf16 or fp32");
+  TORCH_CHECK(!(accumulate && c_bf16), "gemm: accumulate needs an fp32 C");
+  int rc = dsb_gemm_bf16(A.data_ptr(), a_mn, A.stride(0), B.data_ptr(), b_mn, B.stride(0), M, N, K,
+                         C.data_ptr(), C.stride(0), c_bf16, accumulate, alpha, opt_f32(row_scale),
+                         opt_f32(bias), block_n, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_gemm_bf16 failed with code ", rc);
+}
+
+void srw_fwd_gate(const Tensor& h, const Tensor& emb, const Tensor& x, const Tensor& read,
+                  Tensor& p_out, const Tensor& tau, const Tensor& inv_sigma, Tensor& den_sum,
+                  c10::optional<Tensor> gate_sum, c10::optional<Tensor> alive,
+                  c10::optional<Tensor> unit_mask, std::vector<double> gate, Tensor& status) {
+  check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(x, "x");
+  check_bf16_2d(read, "read"); check_bf16_2d(p_out, "p_out");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = x.size(0), D = x.size(1), U = emb.size(0), r = emb.size(1);
+  TORCH_CHECK(h.size(0) == T && h.size(1) == r && read.size(0) == U && read.size(1) == D);
+  TORCH_CHECK(p_out.size(0) == T && p_out.size(1) >= U);
+  DsbGate g = to_gate(gate);
+  unsigned char* alive_p = nullptr;
+  if (alive.has_value() && alive->defined()) {
+    TORCH_CHECK(alive->scalar_type() == torch::kUInt8 && alive->numel() >= U);
+    alive_p = alive->data_ptr<unsigned char>();
+  }
+  int rc = dsb_srw_fwd_gate(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0), x.data_ptr(),
+                            x.stride(0), read.data_ptr(), read.stride(0), T, U, r, D,
+                            p_out.data_ptr(), p_out.stride(0), tau.data_ptr<float>(),
+                            inv_sigma.data_ptr<float>(), den_sum.data_ptr<float>(),
+                            opt_f32_mut(gate_sum), alive_p, opt_f32(unit_mask), &g,
+                            status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_fwd_gate failed with code ", rc);
+}
+
+void srw_bwd_gate(const Tensor& h, const Tensor& emb, const Tensor& x, const Tensor& read,
+                  const Tensor& dy, const Tensor& write, Tensor& p_out, Tensor& dxr_out,
+                  Tensor& ds_out, const Tensor& tau, const Tensor& inv_sigma, const Tensor& dden,
+                  Tensor& dtau_sum, Tensor& dsz_sum, std::vector<double> gate, Tensor& status) {
+  check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(x, "x");
+  check_bf16_2d(read, "read"); check_bf16_2d(dy, "dy"); check_bf16_2d(write, "write");
+  check_bf16_2d(p_out, "p_out"); check_bf16_2d(dxr_out, "dxr_out"); check_bf16_2d(ds_out, "ds_out");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = x.size(0), D = x.size(1), U = emb.size(0), r = emb.size(1);
+  TORCH_CHECK(p_out.stride(0) == dxr_out.stride(0) && p_out.stride(0) == ds_out.stride(0));
+  DsbGate g = to_gate(gate);
+  int rc = dsb_srw_bwd_gate(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0), x.data_ptr(),
+                            x.stride(0), read.data_ptr(), read.stride(0), dy.data_ptr(),
+                            dy.stride(0), write.data_ptr(), write.stride(0), T, U, r, D,
+                            p_out.data_ptr(), dxr_out.data_ptr(), ds_out.data_ptr(),
+                            p_out.stride(0), tau.data_ptr<float>(), inv_sigma.data_ptr<float>(),
+                            dden.data_ptr<float>(), dtau_sum.data_ptr<float>(),
+                            dsz_sum.data_ptr<float>(), &g, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_bwd_gate failed with code ", rc);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("srw_fwd_gate", &srw_fwd_gate);
+  m.def("srw_bwd_gate", &srw_bwd_gate);
+}

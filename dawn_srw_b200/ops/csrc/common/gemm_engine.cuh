@@ -1,0 +1,236 @@
+// Persistent, warp-specialised tcgen05 GEMM engine for sm_100a.
+//
+// One CTA per SM, 192 threads:
+//   warps 0-3  epilogue   (warp w owns TMEM lanes 32w..32w+31 = tile rows)
+//   warp  4    TMA producer (one lane issues cp.async.bulk.tensor loads)
+//   warp  5    MMA issuer   (one lane issues tcgen05.mma; also owns TMEM alloc)
+//
+// A tile is 128 rows x BN columns of up to kMaxSeg independent products
+//   acc[s.acc] (+)= A_s[128, K_s] . B_s[BN, K_s]^T        (bf16 in, fp32 in TMEM)
+// Each operand is either K-major (stored [rows][K]) or MN-major (stored
+// [K][rows]); both arrive through 128-byte-swizzled TMA boxes and are consumed
+// in place by the tensor core through shared-memory descriptors.  Out-of-range
+// rows / K are zero-filled by TMA, so M, N, K need not be tile multiples.
+//
+// Accumulators live in TMEM (512 columns).  When two accumulator sets fit
+// (kNumAcc * BN * 2 <= 512) the epilogue of tile i overlaps the MMAs of tile
+// i+1.  The epilogue is a policy class (see the .cu files) that reads the
+// accumulators with tcgen05.ld and writes whatever the fused op needs.
+//
+// Every mbarrier wait is bounded.  When one runs out the CTA raises its abort
+// flag, all roles leave their loops, TMEM is freed and `status` gets
+// kStatusWaitTimeout; the host checks it after the launch.
+#pragma once
+#include "ptx.cuh"
+
+namespace dsb {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int kMaxSeg = 3;
+constexpr int kNumThreads = 192;
+constexpr int kTmemCols = 512;
+
+struct GemmSeg {
+  int k_tiles;  // ceil(K / 64)
+  int acc;      // which accumulator this product adds into
+  int a_mn;     // 1: A stored [K][M] (MN-major)
+  int b_mn;     // 1: B stored [K][N] (MN-major)
+};
+
+template <class EpiParams>
+struct alignas(64) GemmParams {
+  CUtensorMap tma_a[kMaxSeg];
+  CUtensorMap tma_b[kMaxSeg];
+  GemmSeg seg[kMaxSeg];
+  int n_seg;
+  int M, N;
+  int m_tiles, n_tiles;
+  int n_fastest;  // tile raster: 1 = consecutive tiles walk N first
+  int* status;    // device word, set non-zero on failure
+  EpiParams epi;
+};
+
+template <int BN>
+struct EngineSmem {
+  static constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KB
+  static constexpr int kBBytes = BN * kBlockK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBudget = 200 * 1024;
+  static constexpr int kStages = (kBudget / kStageBytes) > 8 ? 8 : (kBudget / kStageBytes);
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kTotalBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+// Epilogue policy contract:
+//   static constexpr int kNumAcc;
+//   struct Params;
+//   __device__ static void run(const Params&, int m0, int n0, int M, int N,
+//                              uint32_t tmem_acc0 /*lane bits set*/, int warp, int lane);
+// tmem address of accumulator a, column c:  tmem_acc0 + a * BN + c.
+
+template <int BN, class Epi>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
+  using Smem = EngineSmem<BN>;
+  constexpr int kNumAcc = Epi::kNumAcc;
+  constexpr int kAccCols = kNumAcc * BN;
+  constexpr int kNumBuf = (2 * kAccCols <= kTmemCols) ? 2 : 1;
+  static_assert(kAccCols <= kTmemCols, "accumulators exceed TMEM");
+  constexpr int kStages = Smem::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kTileBytes);
+  uint64_t* full_bar = bars;                       // [kStages]
+  uint64_t* empty_bar = bars + kStages;            // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;         // [kNumBuf]
+  uint64_t* acc_empty = bars + 2 * kStages + 2;    // [kNumBuf]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < kNumBuf; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    for (int s = 0; s < p.n_seg; ++s) {
+      tma_prefetch_desc(&p.tma_a[s]);
+      tma_prefetch_desc(&p.tma_b[s]);
+    }
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
+        const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
+        const int m0 = mt * kBlockM, n0 = nt * BN;
+        for (int s = 0; s < p.n_seg && ok; ++s) {
+          const GemmSeg sg = p.seg[s];
+          for (int kt = 0; kt < sg.k_tiles; ++kt) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+            uint8_t* sa = smem + stage * Smem::kStageBytes;
+            uint8_t* sb = sa + Smem::kABytes;
+            mbar_expect_tx(&full_bar[stage], Smem::kStageBytes);
+            const int k0 = kt * kBlockK;
+            if (sg.a_mn) {
+              tma_load_2d(sa, &p.tma_a[s], &full_bar[stage], m0, k0);
+              tma_load_2d(sa + 8192, &p.tma_a[s], &full_bar[stage], m0 + 64, k0);
+            } else {
+              tma_load_2d(sa, &p.tma_a[s], &full_bar[stage], k0, m0);
+            }
+            if (sg.b_mn) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &p.tma_b[s], &full_bar[stage], n0 + 64 * j, k0);
+            } else {
+              tma_load_2d(sb, &p.tma_b[s], &full_bar[stage], k0, n0);
+            }
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it % kNumBuf;
+        const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
+        if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t acc_base = tmem_base + buf * kAccCols;
+        uint32_t started = 0;  // bit a set once accumulator a holds data for this tile
+        for (int s = 0; s < p.n_seg && ok; ++s) {
+          const GemmSeg sg = p.seg[s];
+          const uint32_t idesc = umma_idesc_bf16(kBlockM, BN, sg.a_mn, sg.b_mn);
+          const uint32_t a_lbo = sg.a_mn ? 8192u : 16u, a_step = sg.a_mn ? 2048u : 32u;
+          const uint32_t b_lbo = sg.b_mn ? 8192u : 16u, b_step = sg.b_mn ? 2048u : 32u;
+          const uint32_t d_tmem = acc_base + sg.acc * BN;
+          for (int kt = 0; kt < sg.k_tiles; ++kt) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * Smem::kStageBytes);
+            const uint32_t sb = sa + Smem::kABytes;
+#pragma unroll
+            for (int kk = 0; kk < kBlockK / 16; ++kk) {
+              const uint64_t ad = umma_desc(sa + kk * a_step, a_lbo, 1024);
+              const uint64_t bd = umma_desc(sb + kk * b_step, b_lbo, 1024);
+              mma_bf16_ss(d_tmem, ad, bd, idesc, (started >> sg.acc) & 1u);
+              started |= 1u << sg.acc;
+            }
+            mma_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+          }
+        }
+        if (ok) mma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
+      const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
+      const int buf = it % kNumBuf;
+      const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
+      if (!mbar_wait(&acc_full[buf], use & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t acc0 = tmem_base + buf * kAccCols + (static_cast<uint32_t>(warp * 32) << 16);
+      Epi::template run<BN>(p.epi, mt * kBlockM, nt * BN, p.M, p.N, acc0, warp, lane);
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, kStatusWaitTimeout);
+    // give copies / MMAs that may still be in flight time to land before the
+    // shared memory and TMEM they target are released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace dsb

@@ -1,0 +1,48 @@
+// C ABI of the dawn_srw_b200 CUDA library.  All pointers are device pointers
+// unless noted; every launcher is asynchronous on `stream` and returns 0 on a
+// successful launch (non-zero: host-side argument / launch error).  Kernels
+// report device-side failures (bounded waits that ran out) through the int
+// `status` word the caller passes (0 = ok).
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct DsbGate {
+  int kind;  // 0: clip(relu(s-tau),0,clip_max)  1: z*Phi(z), z=(s-tau)/sigma  2: two-stage
+  float sharpness, act_threshold, act_cutoff, epsilon, max_intensity, clip_max, dead_threshold;
+} DsbGate;
+
+// C[M,N] (=|+=) alpha * row_scale[m] * (A . B^T)[m,n] + bias[n]
+//   A: a_mn == 0 -> stored [M][K] (lda >= K);  a_mn == 1 -> stored [K][M] (lda >= M)
+//   B: b_mn == 0 -> stored [N][K];             b_mn == 1 -> stored [K][N]
+//   bf16 operands, fp32 accumulation; C is bf16 (c_is_bf16) or fp32.
+//   Leading dimensions must be multiples of 8 elements, bases 16-byte aligned.
+int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void* B, int b_mn, long long ldb,
+                  int M, int N, int K, void* C, long long ldc, int c_is_bf16, int accumulate,
+                  float alpha, const float* row_scale, const float* bias, int block_n,
+                  int* status, cudaStream_t stream);
+
+// SRW forward gate kernel: p[T,U] = gate(h.emb^T; tau, 1/sigma) * (x.read^T),
+// den_sum[T] += sum_U den_term.  gate_sum / alive / unit_mask may be null.
+int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, long long lde, const void* x,
+                     long long ldx, const void* read, long long ldr, int T, int U, int r, int D,
+                     void* p_out, long long ldp, const float* tau, const float* inv_sigma,
+                     float* den_sum, float* gate_sum, unsigned char* alive,
+                     const float* unit_mask, const DsbGate* gate /*host*/, int* status,
+                     cudaStream_t stream);
+
+// SRW backward gate kernel: recomputes S and XR, adds DP = dy.write^T, writes
+// p, dxr = DP*g and ds (all bf16 [T, ld_out]) and accumulates dtau_sum / dsz_sum.
+int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, long long lde, const void* x,
+                     long long ldx, const void* read, long long ldr, const void* dy,
+                     long long lddy, const void* write, long long ldw, int T, int U, int r, int D,
+                     void* p_out, void* dxr_out, void* ds_out, long long ld_out, const float* tau,
+                     const float* inv_sigma, const float* dden, float* dtau_sum, float* dsz_sum,
+                     const DsbGate* gate /*host*/, int* status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
