@@ -17,6 +17,12 @@
 // i+1.  The epilogue is a policy class (see the .cu files) that reads the
 // accumulators with tcgen05.ld and writes whatever the fused op needs.
 //
+// Epilogues never store to global memory from registers (a thread owns a row,
+// so a warp's store would touch 32 different lines).  Each warp stages its
+// 32-row slab in 128-byte-swizzled shared memory and one lane issues a TMA
+// bulk store (or reduce-add, for gradient accumulation); the hardware clips
+// rows / columns outside the tensor.
+//
 // Every mbarrier wait is bounded.  When one runs out the CTA raises its abort
 // flag, all roles leave their loops, TMEM is freed and `status` gets
 // kStatusWaitTimeout; the host checks it after the launch.
@@ -42,6 +48,7 @@ template <class EpiParams>
 struct alignas(64) GemmParams {
   CUtensorMap tma_a[kMaxSeg];
   CUtensorMap tma_b[kMaxSeg];
+  CUtensorMap tma_out[kMaxSeg];  // epilogue outputs: box = 128 bytes x 32 rows, 128B swizzle
   GemmSeg seg[kMaxSeg];
   int n_seg;
   int M, N;
@@ -51,28 +58,68 @@ struct alignas(64) GemmParams {
   EpiParams epi;
 };
 
-template <int BN>
+constexpr int kOutBufBytes = 4096;  // one staged slab: 32 rows x 128 bytes
+
+template <int BN, int kOutBufsPerWarp>
 struct EngineSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KB
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBudget = 200 * 1024;
+  static constexpr int kOutBytes = 4 * kOutBufsPerWarp * kOutBufBytes;
+  static constexpr int kMaxSmem = 227 * 1024;
+  static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 256 /*barriers*/;
   static constexpr int kStages = (kBudget / kStageBytes) > 8 ? 8 : (kBudget / kStageBytes);
   static constexpr int kTileBytes = kStages * kStageBytes;
-  static constexpr int kTotalBytes = kTileBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int kTotalBytes = kTileBytes + kOutBytes + 1024 + 256;
+  static_assert(kStages >= 2, "not enough shared memory for a pipeline");
+};
+
+// Per-warp staging of epilogue output slabs (32 rows x 128 bytes each).
+// Thread `lane` owns row `lane`; 16-byte chunk c of its row lives at
+// lane*128 + ((c ^ (lane & 7)) << 4), the layout a 128B-swizzled TMA box reads.
+struct WarpStager {
+  uint32_t base;  // shared address of this warp's first buffer
+  int lane;
+  __device__ __forceinline__ uint32_t buf(int i) const { return base + i * kOutBufBytes; }
+  // Block until at most `kPending` of this warp's bulk stores still read smem.
+  template <int kPending>
+  __device__ __forceinline__ void wait_free() const {
+    if (lane == 0) bulk_wait_read<kPending>();
+    __syncwarp();
+  }
+  __device__ __forceinline__ void put(uint32_t buf_addr, int chunk, uint32_t a, uint32_t b,
+                                      uint32_t c, uint32_t d) const {
+    st_shared_v4(buf_addr + lane * 128 + ((chunk ^ (lane & 7)) << 4), a, b, c, d);
+  }
+  // Make the staged slab visible to the async proxy and store it at
+  // (c0, r0).  Always commits a group so waits can count slabs.
+  __device__ __forceinline__ void flush(const CUtensorMap* map, uint32_t buf_addr, int c0, int r0,
+                                        bool reduce_add, bool issue) const {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (issue) {
+        if (reduce_add) tma_reduce_add_2d(map, buf_addr, c0, r0);
+        else tma_store_2d(map, buf_addr, c0, r0);
+      }
+      bulk_commit();
+    }
+  }
 };
 
 // Epilogue policy contract:
 //   static constexpr int kNumAcc;
 //   struct Params;
-//   __device__ static void run(const Params&, int m0, int n0, int M, int N,
+//   static constexpr int kOutBufs;   // staging buffers per warp
+//   __device__ static void run(const Params&, const CUtensorMap* out_maps, WarpStager&,
+//                              int m0, int n0, int M, int N,
 //                              uint32_t tmem_acc0 /*lane bits set*/, int warp, int lane);
 // tmem address of accumulator a, column c:  tmem_acc0 + a * BN + c.
 
 template <int BN, class Epi>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
-  using Smem = EngineSmem<BN>;
+  using Smem = EngineSmem<BN, Epi::kOutBufs>;
   constexpr int kNumAcc = Epi::kNumAcc;
   constexpr int kAccCols = kNumAcc * BN;
   constexpr int kNumBuf = (2 * kAccCols <= kTmemCols) ? 2 : 1;
@@ -82,7 +129,8 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::kTileBytes);
+  uint8_t* out_stage = smem + Smem::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Smem::kOutBytes);
   uint64_t* full_bar = bars;                       // [kStages]
   uint64_t* empty_bar = bars + kStages;            // [kStages]
   uint64_t* acc_full = bars + 2 * kStages;         // [kNumBuf]
@@ -110,6 +158,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       tma_prefetch_desc(&p.tma_a[s]);
       tma_prefetch_desc(&p.tma_b[s]);
     }
+  }
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < Epi::kNumOut; ++s) tma_prefetch_desc(&p.tma_out[s]);
   }
   if (warp == 5) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -201,6 +252,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     // ------------------------------------------------------------ epilogue
     int it = 0;
     bool ok = true;
+    WarpStager stager{smem_u32(out_stage + warp * Epi::kOutBufs * kOutBufBytes), lane};
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
       const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
@@ -209,10 +261,12 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const uint32_t acc0 = tmem_base + buf * kAccCols + (static_cast<uint32_t>(warp * 32) << 16);
-      Epi::template run<BN>(p.epi, mt * kBlockM, nt * BN, p.M, p.N, acc0, warp, lane);
+      Epi::template run<BN>(p.epi, p.tma_out, stager, mt * kBlockM, nt * BN, p.M, p.N, acc0,
+                            warp, lane);
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);
     }
+    if (lane == 0) bulk_wait<0>();  // all of this warp's bulk stores have landed
   }
 
   // ---------------------------------------------------------------- teardown

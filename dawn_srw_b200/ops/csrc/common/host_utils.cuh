@@ -45,6 +45,25 @@ inline int make_tmap_bf16(CUtensorMap* map, const void* ptr, uint64_t inner, uin
   return r == CUDA_SUCCESS ? 0 : 3;
 }
 
+// Output tensor map for the epilogue stagers: a row-major [rows, cols] matrix
+// of bf16 (elem_bytes 2) or fp32 (4); box = 128 bytes x 32 rows, 128B swizzle.
+inline int make_out_tmap(CUtensorMap* map, void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                         int elem_bytes) {
+  auto enc = tensor_map_encoder();
+  if (enc == nullptr) return 1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || ((ld * elem_bytes) & 15) != 0) return 2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                   2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 3;
+}
+
 inline int sm_count() {
   static int n = 0;
   if (n == 0) {

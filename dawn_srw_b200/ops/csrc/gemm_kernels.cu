@@ -25,18 +25,42 @@ struct GateConsts {
   float sharp, thr, cut, eps, max_int, clip_max, dead_thr;
 };
 
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;  // rcp(+inf) = 0, no slow path
+}
+
+// Phi(z) = 0.5 (1 + erf(z / sqrt 2)) for z > 0 and the N(0,1) density, sharing
+// one exponential.  erf uses the 5-term rational form 1 - poly(t) e^{-x^2},
+// t = 1 / (1 + 0.3275911 x) (absolute error 1.5e-7), which is branch-free.
+__device__ __forceinline__ void phi_pdf(float z, float& phi, float& pdf) {
+  const float e = __expf(-0.5f * z * z);
+  const float t = rcp_approx(fmaf(0.3275911f * 0.70710678f, z, 1.f));
+  float poly = fmaf(t, 1.061405429f, -1.453152027f);
+  poly = fmaf(t, poly, 1.421413741f);
+  poly = fmaf(t, poly, -0.284496736f);
+  poly = fmaf(t, poly, 0.254829592f);
+  poly *= t;
+  phi = fmaf(-0.5f * poly, e, 1.f);
+  pdf = 0.39894228f * e;
+}
+
+template <int KIND>
 __device__ __forceinline__ void gate_fwd(const GateConsts& gc, float s, float tau, float isg,
                                          float& g, float& dterm) {
-  if (gc.kind == 0) {
+  if constexpr (KIND == 0) {
     g = fminf(fmaxf(s - tau, 0.f), gc.clip_max);
     dterm = g;
-  } else if (gc.kind == 1) {
-    const float z = (s - tau) * isg;
-    g = z > 0.f ? z * 0.5f * (1.f + erff(z * 0.70710678f)) : 0.f;
+  } else if constexpr (KIND == 1) {
+    const float z = fmaxf((s - tau) * isg, 0.f);
+    float phi, pdf;
+    phi_pdf(z, phi, pdf);
+    g = z * phi;  // z == 0 gives exactly 0
     dterm = g;
   } else {
     const float m = s - tau - gc.thr;
-    const float act = 1.f / (1.f + __expf(-gc.sharp * m));
+    const float act = rcp_approx(1.f + __expf(-gc.sharp * m));
     const float inten = gc.eps + fminf(fmaxf(m - gc.cut, 0.f), gc.max_int);
     g = act * inten;
     dterm = inten;
@@ -45,29 +69,26 @@ __device__ __forceinline__ void gate_fwd(const GateConsts& gc, float s, float ta
 
 // Returns g; ds = d loss / d s through the gate given dg (grad on the gate
 // value) and dden (grad on the denominator term); dsz = ds * z (v4.0.1 only).
+template <int KIND>
 __device__ __forceinline__ float gate_bwd(const GateConsts& gc, float s, float tau, float isg,
                                           float dg, float dden, float& ds, float& dsz) {
   float g;
   dsz = 0.f;
-  if (gc.kind == 0) {
+  if constexpr (KIND == 0) {
     const float raw = s - tau;
     g = fminf(fmaxf(raw, 0.f), gc.clip_max);
     ds = (raw > 0.f && raw < gc.clip_max) ? (dg + dden) : 0.f;
-  } else if (gc.kind == 1) {
-    const float z = (s - tau) * isg;
-    if (z > 0.f) {
-      const float phi = 0.5f * (1.f + erff(z * 0.70710678f));
-      const float pdf = 0.39894228f * __expf(-0.5f * z * z);
-      g = z * phi;
-      ds = (dg + dden) * (phi + z * pdf) * isg;
-      dsz = ds * z;
-    } else {
-      g = 0.f;
-      ds = 0.f;
-    }
+  } else if constexpr (KIND == 1) {
+    const float zr = (s - tau) * isg;
+    const float z = fmaxf(zr, 0.f);
+    float phi, pdf;
+    phi_pdf(z, phi, pdf);
+    g = z * phi;
+    ds = zr > 0.f ? (dg + dden) * fmaf(z, pdf, phi) * isg : 0.f;
+    dsz = ds * z;
   } else {
     const float m = s - tau - gc.thr;
-    const float act = 1.f / (1.f + __expf(-gc.sharp * m));
+    const float act = rcp_approx(1.f + __expf(-gc.sharp * m));
     const float amr = m - gc.cut;
     const float inten = gc.eps + fminf(fmaxf(amr, 0.f), gc.max_int);
     g = act * inten;
@@ -77,121 +98,159 @@ __device__ __forceinline__ float gate_bwd(const GateConsts& gc, float s, float t
   return g;
 }
 
-__device__ __forceinline__ void store_bf16_row(__nv_bfloat16* dst, const float* v, int n_valid,
-                                               int n) {
-  // dst: start of this thread's n-element run; n_valid of them are in range.
-  if (n_valid >= n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+// Stage 32 fp32 values of this thread's row as bf16 into chunks
+// [chunk0, chunk0+4) of a 64-column bf16 slab.
+__device__ __forceinline__ void stage_bf16_32(const WarpStager& st, uint32_t buf, int chunk0,
+                                              const float* v) {
 #pragma unroll
-    for (int j = 0; j < n; j += 8)
-      st_global_v4(dst + j, pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                   pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-  } else {
-    for (int j = 0; j < n; ++j)
-      if (j < n_valid) dst[j] = __float2bfloat16(v[j]);
-  }
+  for (int q = 0; q < 4; ++q)
+    st.put(buf, chunk0 + q, pack_bf16x2(v[8 * q], v[8 * q + 1]),
+           pack_bf16x2(v[8 * q + 2], v[8 * q + 3]), pack_bf16x2(v[8 * q + 4], v[8 * q + 5]),
+           pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+}
+__device__ __forceinline__ void stage_bf16_16(const WarpStager& st, uint32_t buf, int chunk0,
+                                              const float* v) {
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+    st.put(buf, chunk0 + q, pack_bf16x2(v[8 * q], v[8 * q + 1]),
+           pack_bf16x2(v[8 * q + 2], v[8 * q + 3]), pack_bf16x2(v[8 * q + 4], v[8 * q + 5]),
+           pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
 }
 
 // --------------------------------------------------------- plain epilogue
 struct PlainEpi {
   static constexpr int kNumAcc = 1;
+  static constexpr int kNumOut = 1;
+  static constexpr int kOutBufs = 2;
   struct Params {
-    void* out;
-    long long ldc;
     float alpha;
     const float* row_scale;  // optional [M]
     const float* bias;       // optional [N]
     int out_bf16;            // 1: bf16 output, 0: fp32
-    int accumulate;          // 1: out += result (fp32 output only)
+    int accumulate;          // 1: out += result (fp32 output only; TMA reduce-add)
+    int dbg;                 // profiling toggle: 1 = skip the stores
   };
   template <int BN>
-  __device__ static void run(const Params& p, int m0, int n0, int M, int N, uint32_t acc0,
-                             int warp, int lane) {
-    const int row = m0 + warp * 32 + lane;
-    const bool row_ok = row < M;
-    const float scale = p.alpha * ((row_ok && p.row_scale) ? p.row_scale[row] : 1.f);
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
+                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+    const int r0 = m0 + warp * 32;
+    if (r0 >= M) return;  // whole 32-row slab is outside the matrix (warp-uniform)
+    const int row = r0 + lane;
+    const float scale = p.alpha * ((row < M && p.row_scale) ? p.row_scale[row] : 1.f);
+    int slab = 0;
+    if (p.out_bf16) {
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
-      const int col0 = n0 + c;
-      if (col0 >= N) break;
-      float v[32];
-      tmem_ld32(acc0 + c, v);
-      tmem_ld_wait();
-      if (!row_ok) continue;
-      const int nv = min(32, N - col0);
+      for (int c = 0; c < BN; c += 64, ++slab) {
+        const int col0 = n0 + c;
+        if (col0 >= N) break;
+        st.wait_free<1>();
+        const uint32_t buf = st.buf(slab & 1);
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        v[j] *= scale;
-        if (p.bias != nullptr && j < nv) v[j] += p.bias[col0 + j];
-      }
-      if (p.out_bf16) {
-        store_bf16_row(reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.ldc + col0, v, nv, 32);
-      } else {
-        float* o = reinterpret_cast<float*>(p.out) + row * p.ldc + col0;
-        if (nv == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-          float4* o4 = reinterpret_cast<float4*>(o);
+        for (int half = 0; half < 2; ++half) {
+          float v[32];
+          tmem_ld32(acc0 + c + 32 * half, v);
+          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            float4 t = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            if (p.accumulate) {
-              const float4 old = o4[j];
-              t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
+          for (int j = 0; j < 32; ++j) {
+            v[j] *= scale;
+            if (p.bias != nullptr) {
+              const int col = col0 + 32 * half + j;
+              if (col < N) v[j] += p.bias[col];
             }
-            o4[j] = t;
           }
-        } else {
-          for (int j = 0; j < nv; ++j) o[j] = p.accumulate ? o[j] + v[j] : v[j];
+          stage_bf16_32(st, buf, 4 * half, v);
         }
+        st.flush(&maps[0], buf, col0, r0, false, !(p.dbg & 1));
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32, ++slab) {
+        const int col0 = n0 + c;
+        if (col0 >= N) break;
+        st.wait_free<1>();
+        const uint32_t buf = st.buf(slab & 1);
+        float v[32];
+        tmem_ld32(acc0 + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          v[j] *= scale;
+          if (p.bias != nullptr) {
+            const int col = col0 + j;
+            if (col < N) v[j] += p.bias[col];
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          st.put(buf, q, __float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
+                 __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+        st.flush(&maps[0], buf, col0, r0, p.accumulate != 0, !(p.dbg & 1));
       }
     }
   }
 };
 
 // ------------------------------------------------------ forward gate epilogue
+struct FwdGateParams {
+  const float* tau;        // [T]
+  const float* inv_sigma;  // [T]
+  float* den_sum;          // [T] += sum_U den_term
+  float* gate_sum;         // optional [T] += sum_U g
+  unsigned char* alive;    // optional [U]: 1 if any token gates the unit >= dead_thr
+  const float* unit_mask;  // optional [U] multiplier on the gate (ablation)
+  GateConsts gc;
+};
+template <int KIND>
 struct FwdGateEpi {
   static constexpr int kNumAcc = 2;
-  struct Params {
-    __nv_bfloat16* p_out;  // [T, ldp]
-    long long ldp;
-    const float* tau;        // [T]
-    const float* inv_sigma;  // [T]
-    float* den_sum;          // [T] += sum_U den_term
-    float* gate_sum;         // optional [T] += sum_U g
-    unsigned char* alive;    // optional [U]: 1 if any token gates the unit >= dead_thr
-    const float* unit_mask;  // optional [U] multiplier on the gate (ablation)
-    GateConsts gc;
-  };
+  static constexpr int kNumOut = 1;
+  static constexpr int kOutBufs = 2;
+  using Params = FwdGateParams;
   template <int BN>
-  __device__ static void run(const Params& p, int m0, int n0, int M, int N, uint32_t acc0,
-                             int warp, int lane) {
-    const int row = m0 + warp * 32 + lane;
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
+                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+    const int r0 = m0 + warp * 32;
+    if (r0 >= M) return;
+    const int row = r0 + lane;
     const bool row_ok = row < M;
     const float tau = row_ok ? p.tau[row] : 0.f;
     const float isg = row_ok ? p.inv_sigma[row] : 1.f;
     float den_acc = 0.f, g_acc = 0.f;
+    int slab = 0;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
+    for (int c = 0; c < BN; c += 64, ++slab) {
       const int col0 = n0 + c;
       if (col0 >= N) break;
-      float s[32], xr[32];
-      tmem_ld32(acc0 + c, s);
-      tmem_ld32(acc0 + BN + c, xr);
-      tmem_ld_wait();
-      const int nv = min(32, N - col0);
+      st.wait_free<1>();
+      const uint32_t buf = st.buf(slab & 1);
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        float s[32], xr[32];
+        tmem_ld32(acc0 + c + 32 * half, s);
+        tmem_ld32(acc0 + BN + c + 32 * half, xr);
+        tmem_ld_wait();
+        const int nv = N - (col0 + 32 * half);  // columns of this half inside the pool
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float g, dt;
-        gate_fwd(p.gc, s[j], tau, isg, g, dt);
-        if (j >= nv || !row_ok) { g = 0.f; dt = 0.f; }
-        if (p.unit_mask != nullptr && j < nv) { const float um = p.unit_mask[col0 + j]; g *= um; dt *= um; }
-        den_acc += dt;
-        g_acc += g;
-        if (p.alive != nullptr) {
-          const unsigned b = __ballot_sync(0xffffffffu, g >= p.gc.dead_thr);
-          if (lane == 0 && b != 0u && j < nv) p.alive[col0 + j] = 1;
+        for (int j = 0; j < 32; ++j) {
+          float g, dt;
+          gate_fwd<KIND>(p.gc, s[j], tau, isg, g, dt);
+          if (j >= nv || !row_ok) { g = 0.f; dt = 0.f; }
+          if (p.unit_mask != nullptr && j < nv) {
+            const float um = p.unit_mask[col0 + 32 * half + j];
+            g *= um;
+            dt *= um;
+          }
+          den_acc += dt;
+          g_acc += g;
+          if (p.alive != nullptr) {
+            const unsigned b = __ballot_sync(0xffffffffu, g >= p.gc.dead_thr);
+            if (lane == 0 && b != 0u && j < nv) p.alive[col0 + 32 * half + j] = 1;
+          }
+          s[j] = g * xr[j];
         }
-        s[j] = g * xr[j];
+        stage_bf16_32(st, buf, 4 * half, s);
       }
-      if (row_ok) store_bf16_row(p.p_out + row * p.ldp + col0, s, nv, 32);
+      st.flush(&maps[0], buf, col0, r0, false, true);
     }
     if (row_ok) {
       atomicAdd(p.den_sum + row, den_acc);
@@ -201,61 +260,71 @@ struct FwdGateEpi {
 };
 
 // ----------------------------------------------------- backward gate epilogue
+struct BwdGateParams {
+  const float* tau;        // [T]
+  const float* inv_sigma;  // [T]
+  const float* dden;       // [T] grad on sum_U den_term
+  float* dtau_sum;         // [T] += -sum_U ds
+  float* dsz_sum;          // [T] += sum_U ds * z     (v4.0.1)
+  GateConsts gc;
+};
+template <int KIND>
 struct BwdGateEpi {
   static constexpr int kNumAcc = 3;
-  struct Params {
-    __nv_bfloat16* p_out;    // [T, ld]  g * xr
-    __nv_bfloat16* dxr_out;  // [T, ld]  dp * g
-    __nv_bfloat16* ds_out;   // [T, ld]  d loss / d score through the gate
-    long long ld;
-    const float* tau;        // [T]
-    const float* inv_sigma;  // [T]
-    const float* dden;       // [T] grad on sum_U den_term
-    float* dtau_sum;         // [T] += -sum_U ds
-    float* dsz_sum;          // [T] += sum_U ds * z     (v4.0.1)
-    GateConsts gc;
-  };
+  static constexpr int kNumOut = 3;   // p, dxr, ds
+  static constexpr int kOutBufs = 6;  // three outputs, double-buffered
+  using Params = BwdGateParams;
   template <int BN>
-  __device__ static void run(const Params& p, int m0, int n0, int M, int N, uint32_t acc0,
-                             int warp, int lane) {
-    const int row = m0 + warp * 32 + lane;
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
+                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+    const int r0 = m0 + warp * 32;
+    if (r0 >= M) return;
+    const int row = r0 + lane;
     const bool row_ok = row < M;
     const float tau = row_ok ? p.tau[row] : 0.f;
     const float isg = row_ok ? p.inv_sigma[row] : 1.f;
     const float dden = row_ok ? p.dden[row] : 0.f;
     float dtau_acc = 0.f, dsz_acc = 0.f;
+    int slab = 0;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 16) {
+    for (int c = 0; c < BN; c += 64, ++slab) {
       const int col0 = n0 + c;
       if (col0 >= N) break;
-      float s[16], xr[16], dp[16];
-      tmem_ld16(acc0 + c, s);
-      tmem_ld16(acc0 + BN + c, xr);
-      tmem_ld16(acc0 + 2 * BN + c, dp);
-      tmem_ld_wait();
-      const int nv = min(16, N - col0);
+      st.wait_free<3>();  // the slab before last has been read out of its three buffers
+      const uint32_t b_p = st.buf(3 * (slab & 1));
+      const uint32_t b_dxr = st.buf(3 * (slab & 1) + 1);
+      const uint32_t b_ds = st.buf(3 * (slab & 1) + 2);
+#pragma unroll 1
+      for (int q = 0; q < 4; ++q) {
+        float s[16], xr[16], dp[16];
+        tmem_ld16(acc0 + c + 16 * q, s);
+        tmem_ld16(acc0 + BN + c + 16 * q, xr);
+        tmem_ld16(acc0 + 2 * BN + c + 16 * q, dp);
+        tmem_ld_wait();
+        const int nv = N - (col0 + 16 * q);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        float ds, dsz;
-        const float g = gate_bwd(p.gc, s[j], tau, isg, dp[j] * xr[j], dden, ds, dsz);
-        if (j >= nv || !row_ok) { ds = 0.f; dsz = 0.f; }
-        dtau_acc -= ds;
-        dsz_acc += dsz;
-        s[j] = ds;
-        const float pv = g * xr[j];
-        dp[j] = dp[j] * g;  // dxr
-        xr[j] = pv;         // p
+        for (int j = 0; j < 16; ++j) {
+          float ds, dsz;
+          const float g = gate_bwd<KIND>(p.gc, s[j], tau, isg, dp[j] * xr[j], dden, ds, dsz);
+          if (j >= nv || !row_ok) { ds = 0.f; dsz = 0.f; }
+          dtau_acc -= ds;
+          dsz_acc += dsz;
+          s[j] = ds;
+          const float pv = g * xr[j];
+          dp[j] = dp[j] * g;  // dxr
+          xr[j] = pv;         // p
+        }
+        stage_bf16_16(st, b_p, 2 * q, xr);
+        stage_bf16_16(st, b_dxr, 2 * q, dp);
+        stage_bf16_16(st, b_ds, 2 * q, s);
       }
-      if (row_ok) {
-        const long long off = row * p.ld + col0;
-        store_bf16_row(p.p_out + off, xr, nv, 16);
-        store_bf16_row(p.dxr_out + off, dp, nv, 16);
-        store_bf16_row(p.ds_out + off, s, nv, 16);
-      }
+      st.flush(&maps[0], b_p, col0, r0, false, true);
+      st.flush(&maps[1], b_dxr, col0, r0, false, true);
+      st.flush(&maps[2], b_ds, col0, r0, false, true);
     }
     if (row_ok) {
       atomicAdd(p.dtau_sum + row, dtau_acc);
-      if (p.gc.kind == 1) atomicAdd(p.dsz_sum + row, dsz_acc);
+      if (KIND == 1) atomicAdd(p.dsz_sum + row, dsz_acc);
     }
   }
 };
@@ -275,7 +344,7 @@ static int fill_operand(CUtensorMap* map, const OperandDesc& o, long long rows, 
 
 template <int BN, class Epi>
 static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
-  using Smem = EngineSmem<BN>;
+  using Smem = EngineSmem<BN, Epi::kOutBufs>;
   auto kern = gemm_engine_kernel<BN, Epi>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -305,7 +374,7 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   GemmParams<PlainEpi::Params> gp;
   memset(&gp, 0, sizeof(gp));
-  const int BN = block_n == 128 ? 128 : 256;
+  const int BN = (block_n & 0xffff) == 128 ? 128 : 256;
   int rc = fill_operand(&gp.tma_a[0], {A, a_mn, lda}, M, K, kBlockM);
   if (rc) return 100 + rc;
   rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, BN);
@@ -315,7 +384,9 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   gp.M = M;
   gp.N = N;
   gp.status = status;
-  gp.epi = {C, ldc, alpha, row_scale, bias, c_is_bf16, accumulate};
+  rc = make_out_tmap(&gp.tma_out[0], C, M, N, ldc, c_is_bf16 ? 2 : 4);
+  if (rc) return 300 + rc;
+  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, block_n >> 16};
   return BN == 128 ? launch_engine<128, PlainEpi>(gp, stream)
                    : launch_engine<256, PlainEpi>(gp, stream);
 }
@@ -333,7 +404,7 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
                                 const DsbGate* gate, int* status, cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   constexpr int BN = 128;
-  GemmParams<FwdGateEpi::Params> gp;
+  GemmParams<FwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, BN);
@@ -346,9 +417,12 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
   gp.M = T;
   gp.N = U;
   gp.status = status;
-  gp.epi = {reinterpret_cast<__nv_bfloat16*>(p_out), ldp, tau, inv_sigma, den_sum, gate_sum,
-            alive, unit_mask, make_gc(gate)};
-  return launch_engine<BN, FwdGateEpi>(gp, stream);
+  rc = make_out_tmap(&gp.tma_out[0], p_out, T, U, ldp, 2);
+  if (rc) return 300 + rc;
+  gp.epi = {tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, make_gc(gate)};
+  if (gate->kind == 0) return launch_engine<BN, FwdGateEpi<0>>(gp, stream);
+  if (gate->kind == 1) return launch_engine<BN, FwdGateEpi<1>>(gp, stream);
+  return launch_engine<BN, FwdGateEpi<2>>(gp, stream);
 }
 
 extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, long long lde,
@@ -361,7 +435,7 @@ extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, l
                                 cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   constexpr int BN = 128;
-  GemmParams<BwdGateEpi::Params> gp;
+  GemmParams<BwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, BN);
@@ -377,8 +451,12 @@ extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, l
   gp.M = T;
   gp.N = U;
   gp.status = status;
-  gp.epi = {reinterpret_cast<__nv_bfloat16*>(p_out), reinterpret_cast<__nv_bfloat16*>(dxr_out),
-            reinterpret_cast<__nv_bfloat16*>(ds_out), ld_out, tau, inv_sigma, dden, dtau_sum,
-            dsz_sum, make_gc(gate)};
-  return launch_engine<BN, BwdGateEpi>(gp, stream);
+  rc = make_out_tmap(&gp.tma_out[0], p_out, T, U, ld_out, 2);
+  rc |= make_out_tmap(&gp.tma_out[1], dxr_out, T, U, ld_out, 2);
+  rc |= make_out_tmap(&gp.tma_out[2], ds_out, T, U, ld_out, 2);
+  if (rc) return 300 + rc;
+  gp.epi = {tau, inv_sigma, dden, dtau_sum, dsz_sum, make_gc(gate)};
+  if (gate->kind == 0) return launch_engine<BN, BwdGateEpi<0>>(gp, stream);
+  if (gate->kind == 1) return launch_engine<BN, BwdGateEpi<1>>(gp, stream);
+  return launch_engine<BN, BwdGateEpi<2>>(gp, stream);
 }

@@ -1,0 +1,484 @@
+"""sm_100a backend: autograd wrappers around the hand-written kernels.
+
+SRW pool op, one route (reference math: models/dawn_spatial_v41_exp.py:352-637;
+the reference gets its backward from autodiff and recomputes per chunk):
+
+  prepare (once per step, shared by all layers)
+      emb_c/read_c/write_c = bf16(optionally row-normalised pool tensors)
+      G = emb_c^T emb_c  [r,r],  e_sum = sum_u emb_c[u]      (fp32)
+  per call
+      mu    = h . e_sum / U            E[s^2] = h G h^T / U      (no pass over [T,U])
+      sigma = sqrt(E[s^2] - mu^2) + 1e-8 ;  tau = mu + tau_off * sigma
+      kernel A (tcgen05):  S = h.emb^T, XR = x.read^T in TMEM; epilogue
+                           p = gate(S) * XR -> bf16 [T,U];  den_sum[T]
+      kernel B (tcgen05):  raw_out = p . write     [T,D]
+      out = raw_out / max(den_sum, 1)
+  backward
+      kernel C (tcgen05):  S, XR, DP = dy.write^T in TMEM; epilogue writes
+                           p, dxr = DP*g, ds and the per-token sums for tau, sigma
+      five plain tcgen05 GEMMs: dwrite += p^T dy, dread += dxr^T x, demb += ds^T h
+                           (TMA reduce-add into fp32 buffers shared by all layers),
+                           dx = dxr . read, dh = ds . emb
+
+The per-token score mean and variance over the pool are quadratic forms in
+``h`` (sum_u (h.e_u)^2 = h (E^T E) h^T), so the reference's first pass over all
+scores collapses to one r x r Gram matrix per step; its gradient reaches ``emb``
+through G.  The per-unit mean score used by the load-balance and dead-unit
+terms is likewise ``emb . mean_t(h)``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import build as _build
+from . import reference as R
+from .backend import ParallelCtx, PreparedPool
+from .gates import GATE_GELU_Z, GateSpec
+from .srw_ref import SRWResult, srw_pool_ref
+from ..parallel import collectives as C
+
+_EXT = None
+_STATUS = {}
+
+
+def ext():
+    """The compiled extension; building or importing it must succeed on a GPU box."""
+    global _EXT
+    if _EXT is None:
+        _EXT = _build.load()
+    return _EXT
+
+
+def status_word(device) -> torch.Tensor:
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_status(device=None) -> None:
+    """Raise if any kernel since the last check reported a device-side failure
+    (a bounded wait that ran out).  Synchronises the device."""
+    for key, st in list(_STATUS.items()):
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            raise RuntimeError(f"dawn_srw_b200 kernel reported status {code} on cuda:{key} "
+                               "(1 = barrier wait timed out, 3 = peer wait timed out)")
+
+
+def _gate_list(spec: GateSpec) -> List[float]:
+    return [spec.kind, spec.sharpness, spec.activation_threshold, spec.activation_cutoff,
+            spec.epsilon, spec.max_intensity, spec.clip_max, spec.dead_threshold]
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+def gemm(a, a_mn, b, b_mn, *, out=None, out_dtype=torch.float32, accumulate=False, alpha=1.0,
+         row_scale=None, bias=None, block_n: Optional[int] = None):
+    """out[M,N] (=|+=) alpha * row_scale * A.B^T + bias on the tcgen05 engine.
+    a_mn / b_mn: the operand is stored transposed ([K, rows])."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        ld = _round_up(N, 8)
+        buf = torch.empty(M, ld, dtype=out_dtype, device=a.device)
+        out = buf[:, :N] if ld != N else buf
+    if block_n is None:
+        block_n = 128 if N <= 128 else 256
+    ext().gemm(a, a_mn, b, b_mn, out, accumulate, float(alpha), row_scale, bias, block_n,
+               status_word(a.device))
+    return out
+
+
+def _bf16_2d(t: torch.Tensor) -> torch.Tensor:
+    """bf16, unit inner stride, 16-byte aligned rows."""
+    if t.dtype != torch.bfloat16:
+        t = t.to(torch.bfloat16)
+    if t.stride(-1) != 1 or t.stride(0) % 8 != 0 or t.data_ptr() % 16 != 0:
+        t = t.contiguous()
+        if t.shape[1] % 8 != 0:
+            buf = torch.zeros(t.shape[0], _round_up(t.shape[1], 8), dtype=t.dtype, device=t.device)
+            buf[:, :t.shape[1]] = t
+            t = buf[:, :t.shape[1]]
+    return t
+
+
+# ---------------------------------------------------------------------------
+# dense layer:  y = x W^T + b   (W is [out, in])
+class _LinearFn(torch.autograd.Function):
+    """``w`` is the fp32 master weight (receives an fp32 gradient); ``w_bf`` is
+    its bf16 compute copy, made once per optimizer step."""
+    @staticmethod
+    def forward(ctx, x, w, bias, w_bf, out_dtype):
+        xb = _bf16_2d(x)
+        ctx.save_for_backward(xb, w_bf)
+        ctx.has_bias = bias is not None
+        ctx.x_dtype = x.dtype
+        return gemm(xb, False, w_bf, False, out_dtype=out_dtype, bias=bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xb, w_bf = ctx.saved_tensors
+        dyb = _bf16_2d(dy)
+        dx = gemm(dyb, False, w_bf, True, out_dtype=ctx.x_dtype) if ctx.needs_input_grad[0] else None
+        dw = gemm(dyb, True, xb, True, out_dtype=torch.float32)           # dy^T . x
+        db = dy.float().sum(0) if ctx.has_bias else None
+        return dx, dw, db, None, None
+
+
+# ---------------------------------------------------------------------------
+class CudaPool(PreparedPool):
+    pass
+
+
+class _PoolPrepFn(torch.autograd.Function):
+    """Once per forward: bf16 (row-normalised) pool copies, the Gram matrix and
+    column sum of emb, and zeroed fp32 gradient accumulators that every SRW call
+    of the step adds into.  Its backward runs after all of them (they depend on
+    ``anchor``) and chains the accumulated gradients through the normalisation."""
+
+    @staticmethod
+    def forward(ctx, emb, read, write, holder, normalize, n_valid):
+        ctx.normalize = normalize
+        ctx.holder = holder
+        U = n_valid
+
+        def prep(w):
+            if normalize:
+                nrm = torch.linalg.vector_norm(w, dim=-1, keepdim=True) + 1e-8
+                return (w / nrm).to(torch.bfloat16), nrm
+            return w.to(torch.bfloat16), None
+        emb_c, n_e = prep(emb)
+        read_c, n_r = prep(read)
+        write_c, n_w = prep(write)
+        ef = emb_c[:U].float()
+        gram = ef.t() @ ef
+        esum = ef.sum(0)
+        holder.emb, holder.read, holder.write = emb_c, read_c, write_c
+        if any(ctx.needs_input_grad[:3]):
+            holder.g_emb = torch.zeros_like(emb, dtype=torch.float32)
+            holder.g_read = torch.zeros_like(read, dtype=torch.float32)
+            holder.g_write = torch.zeros_like(write, dtype=torch.float32)
+        ctx.save_for_backward(emb, read, write, n_e, n_r, n_w)
+        ctx.U = U
+        anchor = torch.zeros(1, device=emb.device)
+        return anchor, gram, esum
+
+    @staticmethod
+    def backward(ctx, d_anchor, d_gram, d_esum):
+        emb, read, write, n_e, n_r, n_w = ctx.saved_tensors
+        hd = ctx.holder
+        U = ctx.U
+        g_emb, g_read, g_write = hd.g_emb, hd.g_read, hd.g_write
+        ef = hd.emb[:U].float()
+        if d_gram is not None:
+            g_emb[:U] += ef @ (d_gram + d_gram.t())
+        if d_esum is not None:
+            g_emb[:U] += d_esum.unsqueeze(0)
+
+        def chain(g, w, nrm):
+            if not ctx.normalize:
+                return g
+            n = w / nrm
+            return (g - n * (n * g).sum(-1, keepdim=True)) / nrm
+        out = (chain(g_emb, emb, n_e), chain(g_read, read, n_r), chain(g_write, write, n_w))
+        hd.g_emb = hd.g_read = hd.g_write = None
+        return out + (None, None, None)
+
+
+class _PoolMatVecFn(torch.autograd.Function):
+    """m[u] = emb_c[u] . v  (per-unit mean score).  The emb gradient is added
+    into the pool's shared accumulator."""
+    @staticmethod
+    def forward(ctx, v, anchor, holder, U):
+        ctx.holder, ctx.U = holder, U
+        ctx.save_for_backward(v)
+        return holder.emb[:U].float() @ v
+
+    @staticmethod
+    def backward(ctx, dm):
+        (v,) = ctx.saved_tensors
+        hd, U = ctx.holder, ctx.U
+        hd.g_emb[:U].addr_(dm, v)
+        return hd.emb[:U].float().t() @ dm, torch.zeros_like(dm[:1]), None, None
+
+
+class _SRWRouteFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_bf, h_bf, tau, inv_sd, anchor, holder, spec, U, alive, unit_mask):
+        e = ext()
+        st = status_word(x_bf.device)
+        T, D = x_bf.shape
+        Up = _round_up(U, 8)
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=x_bf.device)
+        den = torch.zeros(T, dtype=torch.float32, device=x_bf.device)
+        gl = _gate_list(spec)
+        e.srw_fwd_gate(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, tau, inv_sd, den, None,
+                       alive, unit_mask, gl, st)
+        raw = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32)
+        ctx.save_for_backward(x_bf, h_bf, tau, inv_sd)
+        ctx.holder, ctx.spec, ctx.U = holder, spec, U
+        return raw, den
+
+    @staticmethod
+    def backward(ctx, d_raw, d_den):
+        x_bf, h_bf, tau, inv_sd = ctx.saved_tensors
+        hd, spec, U = ctx.holder, ctx.spec, ctx.U
+        e = ext()
+        dev = x_bf.device
+        st = status_word(dev)
+        T, D = x_bf.shape
+        Up = _round_up(U, 8)
+        dy = _bf16_2d(d_raw)
+        d_den = d_den.contiguous().float() if d_den is not None else torch.zeros(T, device=dev)
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+        dxr = torch.empty_like(p)
+        ds = torch.empty_like(p)
+        dtau = torch.zeros(T, dtype=torch.float32, device=dev)
+        dsz = torch.zeros(T, dtype=torch.float32, device=dev)
+        emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
+        e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den, dtau, dsz,
+                       _gate_list(spec), st)
+        pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
+        gemm(pv, True, dy, True, out=hd.g_write[:U], accumulate=True)       # p^T dy
+        gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
+        gemm(dsv, True, h_bf, True, out=hd.g_emb[:U], accumulate=True)      # ds^T h
+        dx = gemm(dxrv, False, read, True, out_dtype=torch.bfloat16)        # dxr . read
+        dh = gemm(dsv, False, emb, True, out_dtype=torch.bfloat16)          # ds . emb
+        d_isd = dsz / (inv_sd * inv_sd) if spec.kind == GATE_GELU_Z else None
+        return dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None, None
+
+
+# ---------------------------------------------------------------------------
+class _LMHeadCEFn(torch.autograd.Function):
+    """Tied-embedding cross entropy without keeping [T, V] logits: logits are
+    produced chunk by chunk on the tcgen05 engine, reduced to (lse, label
+    logit, argmax) and recomputed in backward."""
+    CHUNK = 8192
+
+    @staticmethod
+    def forward(ctx, x, emb, labels, emb_bf):
+        T = x.shape[0]
+        xb = _bf16_2d(x)
+        lse = torch.empty(T, dtype=torch.float32, device=x.device)
+        lab = torch.empty(T, dtype=torch.float32, device=x.device)
+        pred = torch.empty(T, dtype=torch.long, device=x.device)
+        safe = labels.clamp(min=0)
+        for a in range(0, T, _LMHeadCEFn.CHUNK):
+            b = min(a + _LMHeadCEFn.CHUNK, T)
+            lg = gemm(xb[a:b], False, emb_bf, False, out_dtype=torch.float32)
+            lse[a:b] = torch.logsumexp(lg, dim=-1)
+            lab[a:b] = lg.gather(-1, safe[a:b, None]).squeeze(-1)
+            pred[a:b] = lg.argmax(-1)
+        ctx.save_for_backward(xb, emb_bf, labels, lse)
+        ctx.x_dtype = x.dtype
+        ctx.mark_non_differentiable(pred)
+        return lse - lab, pred
+
+    @staticmethod
+    def backward(ctx, d_nll, _d_pred):
+        xb, emb_bf, labels, lse = ctx.saved_tensors
+        T = xb.shape[0]
+        V = emb_bf.shape[0]
+        dx = torch.empty(T, xb.shape[1], dtype=ctx.x_dtype, device=xb.device)
+        demb = torch.zeros(V, emb_bf.shape[1], dtype=torch.float32, device=xb.device)
+        safe = labels.clamp(min=0)
+        for a in range(0, T, _LMHeadCEFn.CHUNK):
+            b = min(a + _LMHeadCEFn.CHUNK, T)
+            lg = gemm(xb[a:b], False, emb_bf, False, out_dtype=torch.float32)
+            dl = torch.exp(lg - lse[a:b, None])
+            dl.scatter_add_(-1, safe[a:b, None], -torch.ones_like(dl[:, :1]))
+            dl = _bf16_2d(dl * d_nll[a:b, None])
+            gemm(dl, False, emb_bf, True, out=dx[a:b])                         # dl . E
+            gemm(dl, True, xb[a:b], True, out=demb, accumulate=True)           # dl^T x
+        return dx, demb, None, None
+
+
+# ---------------------------------------------------------------------------
+def fused_adamw(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps, wd, bc1, bc2):
+    """Multi-tensor AdamW step with the clip factor applied on the fly
+    (``clip_scale`` is a device scalar so no host sync is needed)."""
+    e = ext()
+    if hasattr(e, "adamw_multi"):
+        e.adamw_multi(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps, wd, bc1, bc2)
+        return
+    g = torch._foreach_mul(grads, clip_scale)
+    torch._foreach_mul_(exp_avg, b1)
+    torch._foreach_add_(exp_avg, g, alpha=1.0 - b1)
+    torch._foreach_mul_(exp_avg_sq, b2)
+    torch._foreach_addcmul_(exp_avg_sq, g, g, value=1.0 - b2)
+    den = torch._foreach_div(exp_avg_sq, bc2)
+    torch._foreach_sqrt_(den)
+    torch._foreach_add_(den, eps)
+    upd = torch._foreach_div(exp_avg, bc1)
+    torch._foreach_div_(upd, den)
+    if wd != 0.0:
+        torch._foreach_add_(upd, params, alpha=wd)
+    torch._foreach_add_(params, upd, alpha=-lr)
+
+
+# ---------------------------------------------------------------------------
+class CudaBackend:
+    name = "sm100a"
+    compute_dtype = torch.bfloat16
+
+    def __init__(self, diag_chunk: int = 12500):
+        ext()
+        self.diag_chunk = diag_chunk
+        self._wcache = {}
+
+    # ---- dense ops -----------------------------------------------------
+    def _w(self, w):
+        """bf16 compute copy of a master weight, refreshed when the weight changes."""
+        key = id(w)
+        hit = self._wcache.get(key)
+        if hit is None or hit[0] != w._version or hit[1].device != w.device:
+            hit = (w._version, w.detach().to(torch.bfloat16))
+            self._wcache[key] = hit
+        return hit[1]
+
+    def layer_norm(self, x, w, b):
+        return F.layer_norm(x.float(), (x.shape[-1],), w, b, 1e-6)
+
+    def linear(self, x, w, b=None):
+        n = w.shape[0]
+        if n % 8 != 0:       # tiny heads (tau): keep them in fp32 on the library path
+            return F.linear(x.float(), w, b)
+        return _LinearFn.apply(x, w, b, self._w(w), torch.float32)
+
+    def embed(self, ids, tok, pos):
+        return R.embed(ids, tok, pos)
+
+    def dropout(self, x, p, training):
+        return R.dropout(x, p, training)
+
+    def attention(self, q, k, v, dropout_p, training):
+        o = F.scaled_dot_product_attention(q.bfloat16(), k.bfloat16(), v.bfloat16(),
+                                           dropout_p=dropout_p if training else 0.0, is_causal=True)
+        return o.float()
+
+    def lm_head_ce(self, x, tok_emb, labels):
+        B, S, D = x.shape
+        sx = x[:, :-1, :].reshape(-1, D)
+        sl = labels[:, 1:].reshape(-1).long()
+        valid = sl != -100
+        nll, pred = _LMHeadCEFn.apply(sx, tok_emb, sl, self._w(tok_emb))
+        per_tok = (nll * valid).reshape(B, S - 1)
+        loss = per_tok.sum() / (valid.sum() + 1e-8)
+        correct = ((pred == sl) & valid).sum()
+        return loss, per_tok, correct, valid.sum(), valid.reshape(B, S - 1)
+
+    def logits(self, x, tok_emb):
+        shp = x.shape
+        lg = gemm(_bf16_2d(x.reshape(-1, shp[-1])), False, self._w(tok_emb), False,
+                  out_dtype=torch.float32)
+        return lg.reshape(*shp[:-1], -1)
+
+    def diversity(self, tensors):
+        return R.pool_diversity(tensors)
+
+    # ---- SRW pool op ---------------------------------------------------
+    def prepare_pool(self, emb, read, write, spec: GateSpec, pctx: Optional[ParallelCtx] = None):
+        pctx = pctx or ParallelCtx()
+        U = pctx.n_valid if pctx.n_valid is not None else emb.shape[0]
+        pool = CudaPool(None, None, None)
+        anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, pool, spec.normalize_pool, U)
+        gram = C.reduce_from_shards(gram, pctx.shard_group)
+        esum = C.reduce_from_shards(esum, pctx.shard_group)
+        pool.extra = {"anchor": anchor, "gram": gram, "esum": esum, "U": U}
+        return pool
+
+    def srw(self, x, h, tau_off, pool: CudaPool, spec: GateSpec, *,
+            pctx: Optional[ParallelCtx] = None, want_diag: bool = True,
+            return_gates: bool = False, unit_mask=None) -> SRWResult:
+        pctx = pctx or ParallelCtx()
+        if return_gates:
+            return self._srw_library(x, h, tau_off, pool, spec, pctx, True, True, unit_mask)
+        ex = pool.extra
+        U, anchor = ex["U"], ex["anchor"]
+        nsh = C.group_size(pctx.shard_group)
+        U_tot = pctx.n_total if pctx.n_total is not None else U * nsh
+        seq = bool(pctx.seq_sharded and nsh > 1)
+        if seq:
+            x = C.gather_tokens(x, pctx.shard_group)
+            h = C.gather_tokens(h, pctx.shard_group)
+            tau_off = C.gather_tokens(tau_off, pctx.shard_group)
+        elif nsh > 1:
+            x = C.copy_to_shards(x, pctx.shard_group)
+            h = C.copy_to_shards(h, pctx.shard_group)
+            tau_off = C.copy_to_shards(tau_off, pctx.shard_group)
+        T, Rr, r = h.shape
+        x_bf = _bf16_2d(x)
+        h_bf3 = h.to(torch.bfloat16)
+        hf = h_bf3.float()
+        mu = hf @ (ex["esum"] / U_tot)                                     # [T,R]
+        m2 = ((hf @ ex["gram"]) * hf).sum(-1) / U_tot
+        sd = torch.sqrt((m2 - mu * mu).clamp_min(0.0)) + 1e-8
+        tau = mu + tau_off * sd
+        inv_sd = 1.0 / sd
+        # per-unit mean score over the local tokens and routes -> LB / dead statistics
+        hbar = hf.mean(dim=(0, 1))
+        m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
+        ns_sum = C.reduce_from_shards(C.mean_over_group(m_u.sum(), pctx.dp_group), pctx.shard_group)
+        ns_sq = C.reduce_from_shards(C.mean_over_group((m_u * m_u).sum(), pctx.dp_group),
+                                     pctx.shard_group)
+        mean_score = ns_sum / U_tot
+        var_score = ns_sq / U_tot - mean_score ** 2
+        lb = var_score / (mean_score ** 2 + var_score + 1e-2)
+        alive = None
+        if spec.has_dead_penalty:
+            alive = torch.zeros(U, dtype=torch.uint8, device=x.device)
+        um = None if unit_mask is None else unit_mask[:U].float().contiguous()
+        outs, dens = [], []
+        for ri in range(Rr):
+            h_r = _bf16_2d(h_bf3[:, ri])
+            raw, den = _SRWRouteFn.apply(x_bf, h_r, tau[:, ri].contiguous(),
+                                         inv_sd[:, ri].contiguous(), anchor, pool, spec, U, alive, um)
+            outs.append(raw)
+            dens.append(den)
+        raw = torch.stack(outs, dim=1)                                     # [T,R,D]
+        den_sum = C.reduce_from_shards(torch.stack(dens, dim=1), pctx.shard_group)
+        den = den_sum.clamp(min=1.0)
+        out = raw / den.unsqueeze(-1)
+        if seq:
+            out = C.scatter_tokens_sum(out.to(torch.bfloat16), pctx.shard_group).float()
+            r_, n_ = C.group_rank(pctx.shard_group), out.shape[0]
+            den = den[r_ * n_:(r_ + 1) * n_]
+        elif nsh > 1:
+            out = C.reduce_from_shards(out.to(torch.bfloat16), pctx.shard_group).float()
+        dead_pen = x.new_zeros(())
+        dead_cnt = x.new_zeros(())
+        if spec.has_dead_penalty:
+            al = C.all_reduce_nograd(alive.float(), pctx.dp_group, "max")
+            dead = (al < 0.5).float()
+            ms = C.mean_over_group(m_u, pctx.dp_group)
+            dead_pen = C.reduce_from_shards((torch.relu(-ms) * dead).sum(), pctx.shard_group)
+            dead_cnt = dead.sum()
+        diag = {}
+        if want_diag:
+            with torch.no_grad():
+                lib = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec,
+                                        ParallelCtx(pctx.shard_group, pctx.dp_group, pctx.n_total,
+                                                    pctx.n_valid, False), True, False, unit_mask)
+                diag = lib.diag
+        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den)
+
+    def _srw_library(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask):
+        """The same op through torch matmuls (diagnostics / gate dumps only)."""
+        return srw_pool_ref(x, h, tau_off, pool.emb, pool.read, pool.write, spec,
+                            compute_dtype=torch.bfloat16, chunk_size=self.diag_chunk,
+                            n_valid=pctx.n_valid, n_total=pctx.n_total,
+                            shard_group=pctx.shard_group, dp_group=pctx.dp_group,
+                            unit_mask=unit_mask, want_diag=want_diag, return_gates=return_gates,
+                            seq_sharded=pctx.seq_sharded)
+
+    def finish_step(self):
+        check_status()
