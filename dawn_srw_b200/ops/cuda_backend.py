@@ -43,6 +43,12 @@ from ..parallel import collectives as C
 
 _EXT = None
 _STATUS = {}
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched by this process."""
+    return _LAUNCHES
 
 
 def ext():
@@ -93,6 +99,8 @@ def gemm(a, a_mn, b, b_mn, *, out=None, out_dtype=torch.float32, accumulate=Fals
         out = buf[:, :N] if ld != N else buf
     if block_n is None:
         block_n = 128 if N <= 128 else 256
+    global _LAUNCHES
+    _LAUNCHES += 1
     ext().gemm(a, a_mn, b, b_mn, out, accumulate, float(alpha), row_scale, bias, block_n,
                status_word(a.device))
     return out
@@ -221,6 +229,8 @@ class _SRWRouteFn(torch.autograd.Function):
         p = torch.empty(T, Up, dtype=torch.bfloat16, device=x_bf.device)
         den = torch.zeros(T, dtype=torch.float32, device=x_bf.device)
         gl = _gate_list(spec)
+        global _LAUNCHES
+        _LAUNCHES += 1
         e.srw_fwd_gate(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, tau, inv_sd, den, None,
                        alive, unit_mask, gl, st)
         raw = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32)
@@ -245,6 +255,8 @@ class _SRWRouteFn(torch.autograd.Function):
         dtau = torch.zeros(T, dtype=torch.float32, device=dev)
         dsz = torch.zeros(T, dtype=torch.float32, device=dev)
         emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
+        global _LAUNCHES
+        _LAUNCHES += 1
         e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den, dtau, dsz,
                        _gate_list(spec), st)
         pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
@@ -391,8 +403,8 @@ class CudaBackend:
         U = pctx.n_valid if pctx.n_valid is not None else emb.shape[0]
         pool = CudaPool(None, None, None)
         anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, pool, spec.normalize_pool, U)
-        gram = C.reduce_from_shards(gram, pctx.shard_group)
-        esum = C.reduce_from_shards(esum, pctx.shard_group)
+        gram = C.sum_over_shards(gram, pctx.shard_group)
+        esum = C.sum_over_shards(esum, pctx.shard_group)
         pool.extra = {"anchor": anchor, "gram": gram, "esum": esum, "U": U}
         return pool
 
@@ -411,10 +423,6 @@ class CudaBackend:
             x = C.gather_tokens(x, pctx.shard_group)
             h = C.gather_tokens(h, pctx.shard_group)
             tau_off = C.gather_tokens(tau_off, pctx.shard_group)
-        elif nsh > 1:
-            x = C.copy_to_shards(x, pctx.shard_group)
-            h = C.copy_to_shards(h, pctx.shard_group)
-            tau_off = C.copy_to_shards(tau_off, pctx.shard_group)
         T, Rr, r = h.shape
         x_bf = _bf16_2d(x)
         h_bf3 = h.to(torch.bfloat16)
@@ -427,8 +435,8 @@ class CudaBackend:
         # per-unit mean score over the local tokens and routes -> LB / dead statistics
         hbar = hf.mean(dim=(0, 1))
         m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
-        ns_sum = C.reduce_from_shards(C.mean_over_group(m_u.sum(), pctx.dp_group), pctx.shard_group)
-        ns_sq = C.reduce_from_shards(C.mean_over_group((m_u * m_u).sum(), pctx.dp_group),
+        ns_sum = C.sum_over_shards(C.mean_over_group(m_u.sum(), pctx.dp_group), pctx.shard_group)
+        ns_sq = C.sum_over_shards(C.mean_over_group((m_u * m_u).sum(), pctx.dp_group),
                                      pctx.shard_group)
         mean_score = ns_sum / U_tot
         var_score = ns_sq / U_tot - mean_score ** 2
@@ -445,7 +453,7 @@ class CudaBackend:
             outs.append(raw)
             dens.append(den)
         raw = torch.stack(outs, dim=1)                                     # [T,R,D]
-        den_sum = C.reduce_from_shards(torch.stack(dens, dim=1), pctx.shard_group)
+        den_sum = C.sum_over_shards(torch.stack(dens, dim=1), pctx.shard_group)
         den = den_sum.clamp(min=1.0)
         out = raw / den.unsqueeze(-1)
         if seq:
@@ -453,14 +461,14 @@ class CudaBackend:
             r_, n_ = C.group_rank(pctx.shard_group), out.shape[0]
             den = den[r_ * n_:(r_ + 1) * n_]
         elif nsh > 1:
-            out = C.reduce_from_shards(out.to(torch.bfloat16), pctx.shard_group).float()
+            out = C.sum_over_shards(out.to(torch.bfloat16), pctx.shard_group).float()
         dead_pen = x.new_zeros(())
         dead_cnt = x.new_zeros(())
         if spec.has_dead_penalty:
             al = C.all_reduce_nograd(alive.float(), pctx.dp_group, "max")
             dead = (al < 0.5).float()
             ms = C.mean_over_group(m_u, pctx.dp_group)
-            dead_pen = C.reduce_from_shards((torch.relu(-ms) * dead).sum(), pctx.shard_group)
+            dead_pen = C.sum_over_shards((torch.relu(-ms) * dead).sum(), pctx.shard_group)
             dead_cnt = dead.sum()
         diag = {}
         if want_diag:

@@ -19,6 +19,13 @@ v3.9.4 models/dawn_spatial_v394_exp.py:180-260):
 Units may be sharded over ``shard_group`` (each rank holds ``U_local`` rows of
 emb/read/write); per-token sums are all-reduced.  ``n_valid`` marks how many
 local rows are real: trailing rows are padding and contribute nothing.
+
+Gradient convention for multi-rank runs: every rank's loss is one term of the
+objective ``mean_r L_r`` and every collective back-propagates with its true
+transpose (all-reduce <-> all-reduce, all-gather <-> reduce-scatter), exactly
+like ``psum`` inside the reference's ``shard_map``.  A rank's parameter
+gradients are therefore partial sums; ``parallel/grad_sync.py`` adds them over
+the ranks that hold a copy and divides by the world size.
 """
 from __future__ import annotations
 
@@ -84,10 +91,8 @@ def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
         h = C.gather_tokens(h, shard_group)
         tau_off = C.gather_tokens(tau_off, shard_group)
         T = h.shape[0]
-    else:
-        x = C.copy_to_shards(x, shard_group)
-        h = C.copy_to_shards(h, shard_group)
-        tau_off = C.copy_to_shards(tau_off, shard_group)
+    # without sequence sharding every rank of the group holds its own (equal)
+    # copy of x/h/tau_off and uses it as is
     cs = U_loc if not chunk_size else min(chunk_size, U_loc)
     bounds = [(a, min(a + cs, U_loc)) for a in range(0, U_loc, cs)]
     f32 = torch.float32
@@ -110,8 +115,10 @@ def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
              if use_checkpoint else _stats(hq, emb[a:b]))
         s1, s2, s3, s4 = s1 + o[0], s2 + o[1], s3 + o[2].detach(), s4 + o[3].detach()
         ns_sum, ns_sq = ns_sum + o[4], ns_sq + o[5]
-    s1 = C.reduce_from_shards(s1, shard_group)
-    s2 = C.reduce_from_shards(s2, shard_group)
+    # the statistics feed each rank's own gates, so their cotangents differ per
+    # rank and are summed in backward
+    s1 = C.sum_over_shards(s1, shard_group)
+    s2 = C.sum_over_shards(s2, shard_group)
     mu = s1 / U_tot
     sd = torch.sqrt(s2 / U_tot - mu * mu) + 1e-8
     tau = mu + tau_off.unsqueeze(-1) * sd
@@ -119,8 +126,8 @@ def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
     # shard and then averaged over data shards (reference :476-483).
     ns_sum = C.mean_over_group(ns_sum, dp_group)
     ns_sq = C.mean_over_group(ns_sq, dp_group)
-    ns_sum = C.reduce_from_shards(ns_sum, shard_group)
-    ns_sq = C.reduce_from_shards(ns_sq, shard_group)
+    ns_sum = C.sum_over_shards(ns_sum, shard_group)
+    ns_sq = C.sum_over_shards(ns_sq, shard_group)
     mean_score = ns_sum / U_tot
     var_score = ns_sq / U_tot - mean_score ** 2
     lb = var_score / (mean_score ** 2 + var_score + 1e-2)
@@ -195,8 +202,8 @@ def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
                     acc["active"] += (aux["raw"] > 0).float().sum(-1, keepdim=True)
                 acc["glogg"] += (gd * torch.log(gd + 1e-8)).sum(-1, keepdim=True)
 
-    gsum = C.reduce_from_shards(acc["gsum"], shard_group)
-    den_sum = C.reduce_from_shards(acc["den"], shard_group)
+    gsum = C.sum_over_shards(acc["gsum"], shard_group)
+    den_sum = C.sum_over_shards(acc["den"], shard_group)   # divides each rank's own partial output
     den = den_sum.clamp(min=1.0)
     out = raw_out / den
     if seq_sharded:
@@ -205,8 +212,8 @@ def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
         den = den[r_ * n_:(r_ + 1) * n_]
     elif nsh > 1:
         # the cross-shard sum carries bf16 partials when computing in bf16
-        out = C.reduce_from_shards(out.to(compute_dtype), shard_group).float()
-    dead_pen = C.reduce_from_shards(dead_pen, shard_group)
+        out = C.sum_over_shards(out.to(compute_dtype), shard_group).float()
+    dead_pen = C.sum_over_shards(dead_pen, shard_group)
 
     diag: Dict[str, torch.Tensor] = {}
     if want_diag:

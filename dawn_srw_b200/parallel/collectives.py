@@ -2,12 +2,17 @@
 CPU ranks).  These are the *library* data plane: the control plane, the
 baseline every fused kernel is compared with, and the path CPU-rank tests use.
 
-Conjugate pairs (forward / backward):
+Every rank's loss is treated as one term of the objective ``mean_r L_r`` and
+each collective back-propagates with its true transpose (forward / backward):
 
-* ``copy_to_shards``      identity / all-reduce   (replicated input of a sharded op)
-* ``reduce_from_shards``  all-reduce / identity   (partial sums -> replicated)
+* ``sum_over_shards``     all-reduce / all-reduce
 * ``gather_tokens``       all-gather(dim 0) / reduce-scatter(dim 0)
 * ``scatter_tokens_sum``  reduce-scatter(dim 0) / all-gather(dim 0)
+* ``mean_over_group``     mean / mean
+
+``copy_to_shards`` / ``reduce_from_shards`` (identity <-> all-reduce) are the
+Megatron-style pair for groups that compute one loss redundantly; the model
+code does not use them, they are kept for experiments.
 
 The reference expresses the same algebra as ``lax.psum`` inside ``shard_map``
 (reference: models/dawn_spatial_v41_exp.py:455-458, 579-586).
@@ -54,6 +59,21 @@ class _ReduceFromShards(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
+        return g, None
+
+
+class _SumOverShards(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        y = x.contiguous().clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
         return g, None
 
 
@@ -114,6 +134,10 @@ def copy_to_shards(x, group):
 
 def reduce_from_shards(x, group):
     return x if group_size(group) == 1 else _ReduceFromShards.apply(x, group)
+
+
+def sum_over_shards(x, group):
+    return x if group_size(group) == 1 else _SumOverShards.apply(x, group)
 
 
 def gather_tokens(x, group):

@@ -1,0 +1,132 @@
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from dawn_srw_b200.data.loaders import BinDataLoader, BinDataset, ShardedBinDataset, SyntheticDataset
+from dawn_srw_b200.models.dawn import DAWN
+from dawn_srw_b200.train import checkpoint as ck
+from dawn_srw_b200.train.optimizer import DawnAdamW
+from dawn_srw_b200.utils import flax_convert as fc
+
+
+def test_bin_dataset_and_loader_slices(tmp_path):
+    toks = np.arange(10 * 8 + 3, dtype=np.uint16)
+    p = tmp_path / "t.bin"
+    toks.tofile(p)
+    ds = BinDataset(str(p), 8)
+    assert len(ds) == 10
+    a = BinDataLoader(ds, 4, batch_index=0, batch_replicas=2, pin=False)
+    b = BinDataLoader(ds, 4, batch_index=1, batch_replicas=2, pin=False)
+    assert len(a) == 2
+    ia, _ = a.batch(1)
+    ib, mb = b.batch(1)
+    assert ia[0, 0] == 4 * 8 and ib[0, 0] == 6 * 8 and ia.shape == (2, 8) and int(mb.sum()) == 16
+    a.reset(1)
+    assert len(list(a)) == 1 and len(list(a)) == 2      # reset applies to the next pass only
+    with pytest.raises(ValueError):
+        BinDataLoader(ds, 5, batch_replicas=2)
+
+
+def test_sharded_dataset_crosses_shard_boundaries(tmp_path):
+    seq = 4
+    shards = []
+    start = 0
+    for i, n in enumerate((3, 5, 2)):
+        arr = np.arange(start, start + n * seq, dtype=np.uint16)
+        path = tmp_path / f"d_{i:03d}.bin"
+        arr.tofile(path)
+        shards.append({"path": path.name, "sequences": n, "tokens": n * seq})
+        start += n * seq
+    (tmp_path / "_meta.json").write_text(json.dumps({"shards": shards, "vocab_size": 99, "num_shards": 3}))
+    ds = ShardedBinDataset(str(tmp_path), seq)
+    assert len(ds) == 10 and ds.vocab_size == 99
+    rows = ds.rows(2, 9)
+    assert np.array_equal(rows.flatten(), np.arange(2 * seq, 9 * seq))
+
+
+def test_synthetic_rows_depend_only_on_index():
+    ds = SyntheticDataset(32, 16, 1000, seed=3)
+    assert np.array_equal(ds.rows(4, 6)[1], ds.rows(5, 6)[0])
+    assert ds.rows(0, 4).max() < 1000
+
+
+def _tiny():
+    return DAWN(vocab_size=50, d_model=16, n_layers=1, n_heads=2, max_seq_len=8, d_route=4, n_qk=8,
+                n_v=8, n_know=12)
+
+
+def test_checkpoint_roundtrip_retention_and_latest(tmp_path):
+    m = _tiny()
+    opt = DawnAdamW(m.named_parameters(), lr=1e-3, fused=False)
+    run = ck.new_run_dir(str(tmp_path), "spatial-r1-v4.1")
+    kw = dict(epoch=0, step_in_epoch=0, steps_per_epoch=10, best_val_loss=1.0, config={}, training_config={})
+    for s in (10, 20, 30, 40):
+        ck.save_checkpoint(os.path.join(run, f"checkpoint_step{s}.pt"), m, opt, step=s, **kw)
+    ck.save_checkpoint(os.path.join(run, "best_model.pt"), m, opt, step=20, **kw)
+    ck.save_checkpoint(os.path.join(run, "checkpoint_epoch0.pt"), m, opt, step=25, **kw)
+    ck.cleanup_old(run, keep_last=3)
+    left = sorted(os.path.basename(f) for f in ck.list_checkpoints(run))
+    assert left == ["best_model.pt", "checkpoint_epoch0.pt", "checkpoint_step20.pt",
+                    "checkpoint_step30.pt", "checkpoint_step40.pt"]
+    run_dir, latest = ck.find_latest(str(tmp_path))
+    assert os.path.basename(latest) == "checkpoint_step40.pt"   # highest step, not best_model
+    m2 = _tiny()
+    with torch.no_grad():
+        for p in m2.parameters():
+            p.add_(1.0)
+    blob = ck.load_checkpoint(latest, m2, None)
+    assert blob["step"] == 40
+    for a, b in zip(m.parameters(), m2.parameters()):
+        assert torch.equal(a, b)
+
+
+def test_corrupt_checkpoint_raises(tmp_path):
+    m = _tiny()
+    path = ck.save_checkpoint(str(tmp_path / "checkpoint_step1.pt"), m, None, epoch=0, step=1,
+                              step_in_epoch=1, steps_per_epoch=1, best_val_loss=0.0, config={},
+                              training_config={})
+    data = bytearray(open(path, "rb").read())
+    open(path, "wb").write(bytes(data[: len(data) // 2]))
+    with pytest.raises(RuntimeError):
+        ck.load_checkpoint(path, _tiny(), None)
+
+
+def test_flax_msgpack_roundtrip_and_name_mapping(tmp_path):
+    m = _tiny()
+    sd = m.state_dict()
+    path = str(tmp_path / "c.flax")
+    fc.save_flax_checkpoint(path, sd, epoch=1, step=7, config={"d_model": 16})
+    raw = fc.msgpack_restore(open(path, "rb").read())
+    params = raw["params"]
+    assert params["router"]["proj_attn"]["kernel"].shape == (16, 12)          # [in, out]
+    assert params["block_0"]["attn"]["expand_O"]["kernel"].shape == (16, 16)
+    assert params["block_0"]["norm1"]["scale"].shape == (16,)
+    assert params["token_emb"]["embedding"].shape == (50, 16)
+    assert params["neuron_pool"]["know_write"].shape == (12, 16)
+    back = fc.load_flax_checkpoint(path)
+    assert back["step"] == 7 and set(back["state_dict"]) == set(sd)
+    for k in sd:
+        assert torch.allclose(back["state_dict"][k], sd[k]), k
+    # device-replicated checkpoints carry a leading singleton axis
+    params["neuron_pool"]["qk_emb"] = params["neuron_pool"]["qk_emb"][None]
+    sd2 = fc.flax_params_to_state_dict(params)
+    assert sd2["neuron_pool.qk_emb"].shape == sd["neuron_pool.qk_emb"].shape
+
+
+def test_shard_consolidation(tmp_path):
+    from dawn_srw_b200.parallel.topology import PoolShard
+    full = _tiny()
+    paths = []
+    for i in range(2):
+        m = DAWN(vocab_size=50, d_model=16, n_layers=1, n_heads=2, max_seq_len=8, d_route=4, n_qk=8,
+                 n_v=8, n_know=12, pool_shard=PoolShard(i, 2))
+        paths.append(ck.save_checkpoint(str(tmp_path / "checkpoint_step3.pt"), m, None, epoch=0, step=3,
+                                        step_in_epoch=3, steps_per_epoch=9, best_val_loss=0.0, config={},
+                                        training_config={}, shard_index=i, shard_count=2))
+    out = ck.consolidate(paths, {"qk": 8, "v": 8, "know": 12}, str(tmp_path / "full.pt"))
+    blob = torch.load(out, weights_only=False)
+    for k, v in full.state_dict().items():
+        assert torch.equal(blob["params"][k], v), k

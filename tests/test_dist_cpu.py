@@ -1,0 +1,165 @@
+"""Multi-rank logic on CPU ranks (gloo): sharded results equal the single-rank
+result, host-side consensus protocols behave."""
+import os
+
+import pytest
+import torch
+
+from helpers import run_ranks, tiny_config
+
+KW = dict(vocab_size=120, d_model=32, n_layers=2, n_heads=4, max_seq_len=16, d_route=8, n_qk=21,
+          n_v=30, n_know=50, dropout_rate=0.0, router_dropout=0.0)
+
+
+def _single(version, ids):
+    from dawn_srw_b200.models.dawn import DAWN
+    m = DAWN(**KW, model_version=version, seed=5)
+    r = m(ids, labels=ids, want_diag=True)
+    (r["loss"] + 0.1 * r["aux_loss"] + 0.05 * r["dead_penalty"]).backward()
+    return m, r
+
+
+def _sharded_worker(rank, world, version, seq_sharded):
+    import torch.distributed as dist
+    from dawn_srw_b200.models.dawn import DAWN
+    from dawn_srw_b200.parallel.topology import init_topology
+    topo = init_topology(pool_shards=world, seq_shard=seq_sharded, backend="gloo")
+    torch.manual_seed(0)
+    ids = torch.randint(0, 120, (4, 16))
+    m = DAWN(**KW, model_version=version, seed=5, pool_shard=topo.pool_shard)
+    m.set_parallel(shard_group=topo.shard_group, dp_group=None, seq_sharded=topo.seq_shard)
+    local = ids[rank * 2:(rank + 1) * 2] if seq_sharded else ids
+    r = m(local, labels=local, want_diag=True)
+    (r["loss"] + 0.1 * r["aux_loss"] + 0.05 * r["dead_penalty"]).backward()
+    g = {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+    return {"loss": float(r["loss"]), "aux": float(r["aux_loss"]), "dead": float(r["dead_penalty"]),
+            "active": float(r["know_active"]), "grads": g, "n_valid": m.neuron_pool.n_valid("qk")}
+
+
+@pytest.mark.parametrize("version", ["spatial-r1-v4.0.1", "spatial-r1-v4.1"])
+def test_pool_sharding_matches_single_rank(version):
+    torch.manual_seed(0)
+    ids = torch.randint(0, 120, (4, 16))
+    m, r = _single(version, ids)
+    outs = run_ranks(_sharded_worker, 2, version, False)
+    assert sum(o["n_valid"] for o in outs) == 21            # 21 units over 2 ranks: 16 + 5 (padded)
+    for o in outs:
+        assert abs(o["loss"] - float(r["loss"])) < 1e-5
+        assert abs(o["aux"] - float(r["aux_loss"])) < 1e-5
+        assert abs(o["dead"] - float(r["dead_penalty"])) < 1e-5
+        assert abs(o["active"] - float(r["know_active"])) < 1e-6
+    full = {n: p.grad for n, p in m.named_parameters()}
+    # objective = mean of the (here identical) per-rank losses; collectives use
+    # true transposes, so replicated-parameter gradients are summed / world ...
+    for n in ("router.proj_know.weight", "layers.0.attn.expand_O.weight", "token_emb.weight",
+              "router.tau_attn.bias", "layers.1.norm2.weight"):
+        got = (outs[0]["grads"][n] + outs[1]["grads"][n]) / 2
+        assert torch.allclose(got, full[n], atol=2e-5), n
+    # ... and rank k's pool rows hold world x the gradient of its units
+    from dawn_srw_b200.parallel.topology import PoolShard
+    for name, n_units in (("qk", 21), ("know", 50)):
+        for kind in ("emb", "read", "write"):
+            for k in range(2):
+                lo, hi, _ = PoolShard(k, 2).slice_of(n_units)
+                got = outs[k]["grads"][f"neuron_pool.{name}_{kind}"][: hi - lo] / 2
+                assert torch.allclose(got, full[f"neuron_pool.{name}_{kind}"][lo:hi], atol=2e-5), (name, kind, k)
+
+
+def test_sequence_sharding_matches_single_rank():
+    version = "spatial-r1-v4.0.1"
+    torch.manual_seed(0)
+    ids = torch.randint(0, 120, (4, 16))
+    m, r = _single(version, ids)
+    outs = run_ranks(_sharded_worker, 2, version, True)
+    # each rank's loss is the mean over its own sequences; equal token counts -> mean of means
+    assert abs(sum(o["loss"] for o in outs) / 2 - float(r["loss"])) < 1e-5
+    full = {n: p.grad for n, p in m.named_parameters()}
+    from dawn_srw_b200.parallel.topology import PoolShard
+    # objective = mean of per-rank losses: replicated grads sum over ranks / world,
+    # pool grads are already summed over the shard group -> / world
+    for n in ("router.proj_know.weight", "router.proj_attn.bias", "token_emb.weight",
+              "layers.0.attn.expand_O.weight"):
+        assert torch.allclose((outs[0]["grads"][n] + outs[1]["grads"][n]) / 2, full[n], atol=2e-5), n
+    for kind in ("emb", "read", "write"):
+        for k in range(2):
+            lo, hi, _ = PoolShard(k, 2).slice_of(50)
+            got = outs[k]["grads"][f"neuron_pool.know_{kind}"][: hi - lo] / 2
+            assert torch.allclose(got, full[f"neuron_pool.know_{kind}"][lo:hi], atol=2e-5), (kind, k)
+
+
+def _dp_trainer_worker(rank, world, pool_shards, seq_shard):
+    from dawn_srw_b200.parallel.topology import init_topology
+    from dawn_srw_b200.train.trainer import Trainer
+    topo = init_topology(pool_shards=pool_shards, seq_shard=seq_shard, backend="gloo")
+    cfg = tiny_config(version="spatial-r1-v4.0.1", max_steps=3, diversity_weight=0.0)
+    tr = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10)
+    for i in range(3):
+        ids, mask = tr.train_loader.batch(i)
+        m = tr.train_step(ids, mask)
+    sd = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    return {"sd": sd, "gn": float(m["grad_norm"])}
+
+
+def _dp_grad_worker(rank, world):
+    """One forward/backward on this rank's half of the batch, then GradSync."""
+    from dawn_srw_b200.parallel.grad_sync import GradSync
+    from dawn_srw_b200.parallel.topology import init_topology
+    from dawn_srw_b200.train.trainer import Trainer
+    topo = init_topology(backend="gloo")
+    cfg = tiny_config(version="spatial-r1-v4.0.1", diversity_weight=0.0, load_balance_weight=0.0)
+    tr = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10)
+    ids, mask = tr.train_loader.batch(0)
+    r = tr.model(ids.long(), labels=ids.long(), want_diag=False)
+    r["loss"].backward()
+    named = list(tr.model.named_parameters())
+    grads = GradSync(topo).reduce(named, [p.grad for _, p in named])
+    return {n: g for (n, _), g in zip(named, grads)}
+
+
+def test_data_parallel_gradients_match_single_process():
+    from dawn_srw_b200.train.trainer import Trainer
+    cfg = tiny_config(version="spatial-r1-v4.0.1", diversity_weight=0.0, load_balance_weight=0.0)
+    ref = Trainer(cfg, device=torch.device("cpu"), total_steps=10)
+    ids, mask = ref.train_loader.batch(0)
+    ref.model(ids.long(), labels=ids.long(), want_diag=False)["loss"].backward()
+    outs = run_ranks(_dp_grad_worker, 2)
+    for n, p in ref.model.named_parameters():
+        assert torch.allclose(outs[0][n], p.grad, atol=1e-6), n
+        assert torch.equal(outs[0][n], outs[1][n]), n
+
+
+def test_data_parallel_training_keeps_replicas_identical():
+    outs = run_ranks(_dp_trainer_worker, 2, 1, False)
+    for n in outs[0]["sd"]:
+        assert torch.equal(outs[0]["sd"][n], outs[1]["sd"][n]), n
+    assert outs[0]["gn"] == outs[1]["gn"]
+
+
+def test_pool_and_sequence_sharded_training_runs_and_agrees_across_ranks():
+    outs = run_ranks(_dp_trainer_worker, 2, 2, True)
+    for n in ("router.proj_know.weight", "token_emb.weight", "layers.1.norm2.weight"):
+        assert torch.allclose(outs[0]["sd"][n], outs[1]["sd"][n], atol=1e-6), n
+    assert abs(outs[0]["gn"] - outs[1]["gn"]) < 1e-5
+
+
+def _consensus_worker(rank, world):
+    from dawn_srw_b200.parallel.topology import init_topology
+    from dawn_srw_b200.train.trainer import Trainer
+    topo = init_topology(backend="gloo")
+    tr = Trainer(tiny_config(), topo=topo, device=torch.device("cpu"), build_data=True)
+    if rank == 1:
+        tr.preempt_requested = True        # only one rank got the signal
+    agreed = tr.preemption_consensus()
+    tr.global_step = 7 if rank == 0 else 8
+    try:
+        tr.check_step_consistency()
+        mismatch = False
+    except RuntimeError:
+        mismatch = True
+    return agreed, mismatch
+
+
+def test_preemption_consensus_and_step_check():
+    outs = run_ranks(_consensus_worker, 2)
+    assert all(a for a, _ in outs)          # every rank leaves the loop together
+    assert all(m for _, m in outs)          # a split resume is detected on every rank

@@ -1,0 +1,102 @@
+import pytest
+import torch
+
+from dawn_srw_b200.ops.gates import GateSpec, gate_backward, gate_forward, gate_spec_for
+from dawn_srw_b200.ops.srw_ref import prepare_pool_ref, srw_pool_ref
+
+VERSIONS = ["spatial-r1-v3.9.4", "spatial-r1-v4.0.1", "spatial-r1-v4.1"]
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+def test_manual_gate_backward_matches_autograd(kind):
+    torch.manual_seed(kind)
+    spec = GateSpec(kind=kind, sharpness=20.0)   # softer sigmoid keeps fp64 autograd comparable
+    s = torch.randn(7, 2, 33, dtype=torch.float64, requires_grad=True)
+    tau = (torch.randn(7, 2, 1, dtype=torch.float64) * 0.3).requires_grad_(True)
+    sd = (torch.rand(7, 2, 1, dtype=torch.float64) + 0.5).requires_grad_(True)
+    g, dterm, _ = gate_forward(spec, s, tau, sd)
+    dg = torch.randn_like(g)
+    dden = torch.randn(7, 2, 1, dtype=torch.float64)
+    (g * dg).sum().add((dterm * dden).sum()).backward()
+    ds, dtau, dsig_z = gate_backward(spec, s.detach(), tau.detach(), sd.detach(), dg, dden)
+    assert torch.allclose(ds, s.grad, atol=1e-9)
+    assert torch.allclose(dtau, tau.grad, atol=1e-9)
+    if kind == 1:   # d sigma = sum(ds * -z) = dsig_z with z = (s - tau) / sigma
+        assert torch.allclose(dsig_z, sd.grad, atol=1e-9)
+
+
+def _inputs(T=12, R=2, U=50, r=8, D=16, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    return rn(T, D), rn(T, R, r), rn(T, R) * 0.3 - 0.3, rn(U, r), rn(U, D), rn(U, D)
+
+
+@pytest.mark.parametrize("version", VERSIONS)
+def test_chunked_equals_dense(version):
+    spec = gate_spec_for(version)
+    x, h, off, emb, read, write = _inputs()
+    e, r_, w = prepare_pool_ref(emb, read, write, spec, torch.float32)
+    a = srw_pool_ref(x, h, off, e, r_, w, spec)
+    b = srw_pool_ref(x, h, off, e, r_, w, spec, chunk_size=7, use_checkpoint=True)
+    assert torch.allclose(a.out, b.out, atol=1e-5)
+    assert torch.allclose(a.lb, b.lb, atol=1e-6)
+    for k in a.diag:
+        assert torch.allclose(a.diag[k], b.diag[k], atol=1e-4), k
+
+
+@pytest.mark.parametrize("version", VERSIONS)
+def test_padding_rows_contribute_nothing(version):
+    spec = gate_spec_for(version)
+    x, h, off, emb, read, write = _inputs(U=37)
+    e, r_, w = prepare_pool_ref(emb, read, write, spec, torch.float32)
+    a = srw_pool_ref(x, h, off, e, r_, w, spec)
+    pad = lambda t: torch.cat([t, torch.randn(11, t.shape[1])])
+    b = srw_pool_ref(x, h, off, pad(e), pad(r_), pad(w), spec, n_valid=37, n_total=37)
+    assert torch.allclose(a.out, b.out, atol=1e-6)
+    assert torch.allclose(a.lb, b.lb) and torch.allclose(a.dead_penalty, b.dead_penalty)
+    assert torch.allclose(a.diag["active_n_mean"], b.diag["active_n_mean"])
+
+
+def test_paired_routes_equal_two_single_routes():
+    spec = gate_spec_for("spatial-r1-v4.0.1")
+    x, h, off, emb, read, write = _inputs()
+    e, r_, w = prepare_pool_ref(emb, read, write, spec, torch.float32)
+    both = srw_pool_ref(x, h, off, e, r_, w, spec, want_diag=False)
+    for i in range(2):
+        one = srw_pool_ref(x, h[:, i:i + 1], off[:, i:i + 1], e, r_, w, spec, want_diag=False)
+        assert torch.allclose(both.out[:, i], one.out[:, 0], atol=1e-6)
+
+
+def test_output_formula_v41():
+    """out = ((g * xr) @ write) / max(sum intensity, 1)."""
+    spec = gate_spec_for("spatial-r1-v4.1")
+    x, h, off, emb, read, write = _inputs(R=1)
+    res = srw_pool_ref(x, h, off, emb, read, write, spec, return_gates=True)
+    s = h[:, 0] @ emb.t()
+    mu, sd = s.mean(-1, keepdim=True), s.std(-1, unbiased=False, keepdim=True) + 1e-8
+    m = s - (mu + off * sd) - 0.5
+    act = torch.sigmoid(500 * m)
+    inten = 1e-4 + (m - 0.01).clamp(0, 10)
+    want = ((act * inten) * (x @ read.t())) @ write / inten.sum(-1, keepdim=True).clamp(min=1)
+    assert torch.allclose(res.out[:, 0], want, atol=1e-5)
+    assert torch.allclose(res.gates[:, 0], act * inten, atol=1e-6)
+
+
+def test_unit_mask_zeroes_units():
+    spec = gate_spec_for("spatial-r1-v4.0.1")
+    x, h, off, emb, read, write = _inputs(R=1)
+    e, r_, w = prepare_pool_ref(emb, read, write, spec, torch.float32)
+    mask = torch.ones(50)
+    mask[::2] = 0
+    a = srw_pool_ref(x, h, off, e, r_, w, spec, unit_mask=mask, return_gates=True)
+    assert float(a.gates[..., ::2].abs().max()) == 0.0
+
+
+def test_dead_penalty_has_gradient():
+    spec = gate_spec_for("spatial-r1-v4.1")
+    x, h, off, emb, read, write = _inputs(R=1)
+    emb = emb.clone().requires_grad_(True)
+    res = srw_pool_ref(x, h, off + 5.0, emb, read, write, spec)   # tau far up: everything dead
+    assert float(res.diag["dead_count"]) > 0
+    res.dead_penalty.backward()
+    assert emb.grad is not None and float(emb.grad.abs().sum()) > 0

@@ -1,0 +1,104 @@
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from dawn_srw_b200.train import checkpoint as ck
+from dawn_srw_b200.train.logging import ANALYSIS_KEYS, TRAIN_KEYS
+from dawn_srw_b200.train.trainer import NonFiniteLoss, Trainer
+
+from helpers import tiny_config
+
+
+def _params(tr):
+    return {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+
+
+def test_resume_is_deterministic(tmp_path):
+    """8 steps in one go == 4 steps, checkpoint, new process state, 4 more."""
+    cfg = tiny_config(max_steps=8, checkpoint_interval=4, dead_penalty_weight=0.05)
+    a = Trainer(cfg, run_dir=str(tmp_path / "a"), total_steps=8)
+    os.makedirs(a.run_dir, exist_ok=True)
+    a.fit()
+    cfg_b = tiny_config(max_steps=4, checkpoint_interval=4, dead_penalty_weight=0.05)
+    b = Trainer(cfg_b, run_dir=str(tmp_path / "b"), total_steps=8)
+    os.makedirs(b.run_dir, exist_ok=True)
+    b.fit()
+    cfg_c = tiny_config(max_steps=8, checkpoint_interval=4, dead_penalty_weight=0.05)
+    c = Trainer(cfg_c, run_dir=str(tmp_path / "b"), total_steps=8)
+    c.resume(os.path.join(str(tmp_path / "b"), "checkpoint_step4.pt"))
+    assert c.global_step == 4 and c.step_in_epoch == 4 and c.optimizer.count == 4
+    c.fit()
+    pa, pc = _params(a), _params(c)
+    for n in pa:
+        assert torch.allclose(pa[n], pc[n], atol=1e-7), n
+
+
+def test_jsonl_schema(tmp_path):
+    cfg = tiny_config(max_steps=4, log_interval=2, log_analysis_multiplier=2, val_interval=4,
+                      dead_penalty_weight=0.05, exploration_weight=1e-3, exploration_warmup_steps=0)
+    run = str(tmp_path / "r")
+    os.makedirs(run)
+    Trainer(cfg, run_dir=run).fit()
+    recs = [json.loads(l) for f in os.listdir(run) if f.startswith("metrics_")
+            for l in open(os.path.join(run, f))]
+    types = {r["type"] for r in recs}
+    assert {"train", "train_analysis", "val"} <= types
+    tr = next(r for r in recs if r["type"] == "train")
+    missing = [k for k in TRAIN_KEYS + ["step", "epoch", "steps_per_sec", "elapsed", "timestamp",
+                                        "per_layer_attn_out_norm", "per_layer_know_out_norm"]
+               if k not in tr]
+    assert not missing, missing
+    an = next(r for r in recs if r["type"] == "train_analysis")
+    missing = [k for k in ANALYSIS_KEYS if k not in an]
+    assert not missing, missing
+    v = next(r for r in recs if r["type"] == "val")
+    assert {"step", "epoch", "val_loss", "val_acc", "timestamp"} <= set(v)
+    assert os.path.exists(os.path.join(run, "config.json"))
+    cfgj = json.load(open(os.path.join(run, "config.json")))
+    assert set(cfgj) == {"model", "training"}
+
+
+def test_non_finite_loss_stops_training(tmp_path):
+    cfg = tiny_config(max_steps=3)
+    tr = Trainer(cfg, run_dir=None)
+    with torch.no_grad():
+        tr.model.token_emb.weight.fill_(float("nan"))
+    with pytest.raises(NonFiniteLoss):
+        tr.fit()
+
+
+def test_loss_decreases_on_a_fixed_batch():
+    cfg = tiny_config(lr=3e-3, diversity_weight=0.0)
+    tr = Trainer(cfg, total_steps=1000)
+    ids, mask = tr.train_loader.batch(0)
+    first = float(tr.train_step(ids, mask)["ce_loss"])
+    for _ in range(30):
+        last = float(tr.train_step(ids, mask)["ce_loss"])
+    assert last < first - 0.3
+
+
+def test_sigterm_flag_writes_emergency_checkpoint(tmp_path):
+    cfg = tiny_config(max_steps=50)
+    run = str(tmp_path / "r")
+    os.makedirs(run)
+    tr = Trainer(cfg, run_dir=run)
+    orig = tr.train_step
+
+    def step_then_flag(*a, **k):
+        out = orig(*a, **k)
+        if tr.global_step == 3:
+            tr.preempt_requested = True       # what the SIGTERM handler does
+        return out
+    tr.train_step = step_then_flag
+    tr.fit()
+    assert tr.global_step == 10               # the flag is polled every 10 steps
+    assert os.path.exists(os.path.join(run, "emergency_step10.pt"))
+
+
+def test_baseline_model_trains(tmp_path):
+    cfg = tiny_config(version="baseline", max_steps=2)
+    out = Trainer(cfg).fit()
+    assert math.isfinite(out["total_loss"])
