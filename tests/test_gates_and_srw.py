@@ -100,3 +100,45 @@ def test_dead_penalty_has_gradient():
     assert float(res.diag["dead_count"]) > 0
     res.dead_penalty.backward()
     assert emb.grad is not None and float(emb.grad.abs().sum()) > 0
+
+
+@pytest.mark.parametrize("normalize", [False, True])
+def test_gram_statistics_and_their_gradient(normalize):
+    """mean_U(s) and mean_U(s^2) as quadratic forms in h (the CUDA backend's
+    replacement for the first pass over all scores), and the gradient that
+    reaches emb through the Gram matrix and the pool preparation."""
+    from dawn_srw_b200.ops.backend import PreparedPool
+    from dawn_srw_b200.ops.cuda_backend import _PoolPrepFn
+    torch.manual_seed(1)
+    U, r, D, T = 40, 8, 12, 9
+    emb = torch.randn(U, r, requires_grad=True)
+    read = torch.randn(U, D, requires_grad=True)
+    write = torch.randn(U, D, requires_grad=True)
+    h = torch.randn(T, r).bfloat16().float().requires_grad_(True)
+    holder = PreparedPool(None, None, None)
+    anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, holder, normalize, U)
+    mu = h @ (esum / U)
+    m2 = ((h @ gram) * h).sum(-1) / U
+    w1, w2 = torch.randn(T), torch.randn(T)
+    # pool gradients that the SRW calls of a step would have accumulated
+    acc = [torch.randn(U, r), torch.randn(U, D), torch.randn(U, D)]
+    holder.g_emb += acc[0]; holder.g_read += acc[1]; holder.g_write += acc[2]
+    ((mu * w1).sum() + (m2 * w2).sum() + anchor.sum() * 0).backward()
+    got = [emb.grad.clone(), read.grad.clone(), write.grad.clone(), h.grad.clone()]
+
+    # oracle: the same quantities straight from the scores, bf16 cast with a
+    # straight-through gradient
+    emb2, read2, write2 = (t.detach().clone().requires_grad_(True) for t in (emb, read, write))
+    h2 = h.detach().clone().requires_grad_(True)
+
+    def prep(w):
+        n = w / (torch.linalg.vector_norm(w, dim=-1, keepdim=True) + 1e-8) if normalize else w
+        return n + (n.bfloat16().float() - n).detach()
+    e_c, r_c, w_c = prep(emb2), prep(read2), prep(write2)
+    s = h2 @ e_c.t()
+    loss = (s.mean(-1) * w1).sum() + ((s * s).mean(-1) * w2).sum()
+    loss = loss + (e_c * acc[0]).sum() + (r_c * acc[1]).sum() + (w_c * acc[2]).sum()
+    loss.backward()
+    assert torch.allclose(mu, s.mean(-1), atol=1e-5) and torch.allclose(m2, (s * s).mean(-1), atol=1e-5)
+    for a, b in zip(got, (emb2.grad, read2.grad, write2.grad, h2.grad)):
+        assert torch.allclose(a, b, atol=2e-5), float((a - b).abs().max())
