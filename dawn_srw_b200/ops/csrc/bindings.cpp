@@ -108,10 +108,40 @@ void srw_bwd_gate(const Tensor& h, const Tensor& emb, const Tensor& x, const Ten
   TORCH_CHECK(rc == 0, "dsb_srw_bwd_gate failed with code ", rc);
 }
 
+void srw_forward(const Tensor& h, const Tensor& emb, const Tensor& x, const Tensor& read,
+                 const Tensor& write, const Tensor& tau, const Tensor& inv_sigma, Tensor& p_scratch,
+                 Tensor& raw_out, Tensor& den_sum, c10::optional<Tensor> alive,
+                 c10::optional<Tensor> unit_mask, std::vector<double> gate, Tensor& status) {
+  check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(x, "x");
+  check_bf16_2d(read, "read"); check_bf16_2d(write, "write"); check_bf16_2d(p_scratch, "p_scratch");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = x.size(0), D = x.size(1), U = emb.size(0), r = emb.size(1);
+  TORCH_CHECK(h.size(0) == T && h.size(1) == r && read.size(0) == U && read.size(1) == D &&
+              write.size(0) == U && write.size(1) == D);
+  TORCH_CHECK(p_scratch.size(0) >= T && p_scratch.stride(0) >= U);
+  TORCH_CHECK(raw_out.scalar_type() == torch::kFloat32 && raw_out.size(0) == T &&
+              raw_out.size(1) == D && raw_out.stride(1) == 1);
+  TORCH_CHECK(den_sum.scalar_type() == torch::kFloat32 && den_sum.numel() >= T);
+  DsbGate g = to_gate(gate);
+  unsigned char* alive_p = nullptr;
+  if (alive.has_value() && alive->defined()) {
+    TORCH_CHECK(alive->scalar_type() == torch::kUInt8 && alive->numel() >= U);
+    alive_p = alive->data_ptr<unsigned char>();
+  }
+  int rc = dsb_srw_forward(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0), x.data_ptr(),
+                           x.stride(0), read.data_ptr(), read.stride(0), write.data_ptr(),
+                           write.stride(0), T, U, r, D, tau.data_ptr<float>(),
+                           inv_sigma.data_ptr<float>(), p_scratch.data_ptr(), p_scratch.stride(0),
+                           raw_out.data_ptr<float>(), raw_out.stride(0), den_sum.data_ptr<float>(),
+                           alive_p, opt_f32(unit_mask), &g, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_forward failed with code ", rc);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("srw_fwd_gate", &srw_fwd_gate);
   m.def("srw_bwd_gate", &srw_bwd_gate);
+  m.def("srw_forward", &srw_forward);
 }

@@ -43,6 +43,17 @@ int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, long long ld
                      const float* inv_sigma, const float* dden, float* dtau_sum, float* dsz_sum,
                      const DsbGate* gate /*host*/, int* status, cudaStream_t stream);
 
+// One route of the SRW forward op (gate kernel + write GEMM).  `p_scratch` is
+// caller-provided scratch: bf16 [T, ldp] with ldp >= U and ldp % 8 == 0; its
+// contents on return are unspecified.  den_sum[T] is cleared and filled here;
+// raw_out is fp32 [T, ldo].  alive / unit_mask may be null.
+int dsb_srw_forward(const void* h, long long ldh, const void* emb, long long lde, const void* x,
+                    long long ldx, const void* read, long long ldr, const void* write,
+                    long long ldw, int T, int U, int r, int D, const float* tau,
+                    const float* inv_sigma, void* p_scratch, long long ldp, float* raw_out,
+                    long long ldo, float* den_sum, unsigned char* alive, const float* unit_mask,
+                    const DsbGate* gate /*host*/, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

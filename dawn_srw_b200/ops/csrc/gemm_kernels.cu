@@ -460,3 +460,24 @@ extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, l
   if (gate->kind == 1) return launch_engine<BN, BwdGateEpi<1>>(gp, stream);
   return launch_engine<BN, BwdGateEpi<2>>(gp, stream);
 }
+
+// One route of the SRW forward op: p = gate(h.emb^T) * (x.read^T) into the
+// caller's scratch buffer, then raw_out = p . write.  den_sum is cleared here
+// and receives sum_U den_term.
+extern "C" int dsb_srw_forward(const void* h, long long ldh, const void* emb, long long lde,
+                               const void* x, long long ldx, const void* read, long long ldr,
+                               const void* write, long long ldw, int T, int U, int r, int D,
+                               const float* tau, const float* inv_sigma, void* p_scratch,
+                               long long ldp, float* raw_out, long long ldo, float* den_sum,
+                               unsigned char* alive, const float* unit_mask, const DsbGate* gate,
+                               int* status, cudaStream_t stream) {
+  if (T <= 0 || U <= 0) return 0;
+  if (ldp < U || (ldp & 7) != 0) return 400;
+  if (cudaMemsetAsync(den_sum, 0, sizeof(float) * T, stream) != cudaSuccess) return 401;
+  int rc = dsb_srw_fwd_gate(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_scratch, ldp, tau,
+                            inv_sigma, den_sum, nullptr, alive, unit_mask, gate, status, stream);
+  if (rc) return rc;
+  // raw_out[T,D] = p[T,U] . write[U,D]   (write is the MN-major B operand)
+  return dsb_gemm_bf16(p_scratch, 0, ldp, write, 1, ldw, T, D, U, raw_out, ldo, 0, 0, 1.0f,
+                       nullptr, nullptr, 256, status, stream);
+}

@@ -226,14 +226,13 @@ class _SRWRouteFn(torch.autograd.Function):
         st = status_word(x_bf.device)
         T, D = x_bf.shape
         Up = _round_up(U, 8)
-        p = torch.empty(T, Up, dtype=torch.bfloat16, device=x_bf.device)
-        den = torch.zeros(T, dtype=torch.float32, device=x_bf.device)
-        gl = _gate_list(spec)
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=x_bf.device)    # scratch
+        den = torch.empty(T, dtype=torch.float32, device=x_bf.device)
+        raw = torch.empty(T, D, dtype=torch.float32, device=x_bf.device)
         global _LAUNCHES
-        _LAUNCHES += 1
-        e.srw_fwd_gate(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, tau, inv_sd, den, None,
-                       alive, unit_mask, gl, st)
-        raw = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32)
+        _LAUNCHES += 2
+        e.srw_forward(h_bf, holder.emb[:U], x_bf, holder.read[:U], holder.write[:U], tau, inv_sd,
+                      p, raw, den, alive, unit_mask, _gate_list(spec), st)
         ctx.save_for_backward(x_bf, h_bf, tau, inv_sd)
         ctx.holder, ctx.spec, ctx.U = holder, spec, U
         return raw, den
