@@ -1,9 +1,11 @@
 // Persistent, warp-specialised tcgen05 GEMM engine for sm_100a.
 //
-// One CTA per SM, 192 threads:
-//   warps 0-3  epilogue   (warp w owns TMEM lanes 32w..32w+31 = tile rows)
-//   warp  4    TMA producer (one lane issues cp.async.bulk.tensor loads)
-//   warp  5    MMA issuer   (one lane issues tcgen05.mma; also owns TMEM alloc)
+// One CTA per SM, (E + 2) warps where E = Epi::kEpiWarps is 4 or 8:
+//   warps 0..E-1  epilogue  (warp w reads TMEM lanes 32(w%4)..32(w%4)+31 = tile rows;
+//                            with E = 8, warps w and w+4 split the tile's columns, which
+//                            gives every scheduler two warps to hide ALU latency with)
+//   warp  E       TMA producer (one lane issues cp.async.bulk.tensor loads)
+//   warp  E+1     MMA issuer   (one lane issues tcgen05.mma; also owns TMEM alloc)
 //
 // A tile is 128 rows x BN columns of up to kMaxSeg independent products
 //   acc[s.acc] (+)= A_s[128, K_s] . B_s[BN, K_s]^T        (bf16 in, fp32 in TMEM)
@@ -34,7 +36,6 @@ namespace dsb {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int kMaxSeg = 3;
-constexpr int kNumThreads = 192;
 constexpr int kTmemCols = 512;
 
 struct GemmSeg {
@@ -60,12 +61,12 @@ struct alignas(64) GemmParams {
 
 constexpr int kOutBufBytes = 4096;  // one staged slab: 32 rows x 128 bytes
 
-template <int BN, int kOutBufsPerWarp>
+template <int BN, int kOutBufsPerWarp, int kEpiWarps = 4>
 struct EngineSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KB
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kOutBytes = 4 * kOutBufsPerWarp * kOutBufBytes;
+  static constexpr int kOutBytes = kEpiWarps * kOutBufsPerWarp * kOutBufBytes;
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 256 /*barriers*/;
   static constexpr int kStages = (kBudget / kStageBytes) > 8 ? 8 : (kBudget / kStageBytes);
@@ -110,16 +111,23 @@ struct WarpStager {
 // Epilogue policy contract:
 //   static constexpr int kNumAcc;
 //   struct Params;
-//   static constexpr int kOutBufs;   // staging buffers per warp
+//   static constexpr int kNumOut;    // output tensor maps used
+//   static constexpr int kOutBufs;   // staging buffers per epilogue warp
+//   static constexpr int kEpiWarps;  // 4 or 8
 //   __device__ static void run(const Params&, const CUtensorMap* out_maps, WarpStager&,
 //                              int m0, int n0, int M, int N,
 //                              uint32_t tmem_acc0 /*lane bits set*/, int warp, int lane);
+// `warp` is the epilogue warp index (0..kEpiWarps-1); its rows are
+// m0 + 32*(warp%4) + lane and, with 8 warps, its columns the (warp/4)-th half.
 // tmem address of accumulator a, column c:  tmem_acc0 + a * BN + c.
 
 template <int BN, class Epi>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__((Epi::kEpiWarps + 2) * 32, 1)
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
-  using Smem = EngineSmem<BN, Epi::kOutBufs>;
+  using Smem = EngineSmem<BN, Epi::kOutBufs, Epi::kEpiWarps>;
+  constexpr int kEpiWarps = Epi::kEpiWarps;
+  constexpr int kTmaWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
+  static_assert(kEpiWarps == 4 || kEpiWarps == 8, "4 or 8 epilogue warps");
   constexpr int kNumAcc = Epi::kNumAcc;
   constexpr int kAccCols = kNumAcc * BN;
   constexpr int kNumBuf = (2 * kAccCols <= kTmemCols) ? 2 : 1;
@@ -148,12 +156,12 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     }
     for (int i = 0; i < kNumBuf; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 128);
+      mbar_init(&acc_empty[i], kEpiWarps * 32);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     for (int s = 0; s < p.n_seg; ++s) {
       tma_prefetch_desc(&p.tma_a[s]);
       tma_prefetch_desc(&p.tma_b[s]);
@@ -162,7 +170,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   if (warp == 0 && lane == 0) {
     for (int s = 0; s < Epi::kNumOut; ++s) tma_prefetch_desc(&p.tma_out[s]);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -173,7 +181,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
 
   const int total_tiles = p.m_tiles * p.n_tiles;
 
-  if (warp == 4) {
+  if (warp == kTmaWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       int stage = 0;
@@ -209,13 +217,14 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      const uint32_t smem_base = smem_u32(smem);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         const int buf = it % kNumBuf;
         const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
@@ -226,20 +235,25 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         for (int s = 0; s < p.n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
           const uint32_t idesc = umma_idesc_bf16(kBlockM, BN, sg.a_mn, sg.b_mn);
-          const uint32_t a_lbo = sg.a_mn ? 8192u : 16u, a_step = sg.a_mn ? 2048u : 32u;
-          const uint32_t b_lbo = sg.b_mn ? 8192u : 16u, b_step = sg.b_mn ? 2048u : 32u;
+          // descriptors for stage 0; a stage / k-slice only moves the 14-bit
+          // address field, so the hot loop just adds to the low word
+          const uint64_t a_base = umma_desc(smem_base, sg.a_mn ? 8192u : 16u, 1024);
+          const uint64_t b_base = umma_desc(smem_base + Smem::kABytes, sg.b_mn ? 8192u : 16u, 1024);
+          const uint64_t a_inc = (sg.a_mn ? 2048u : 32u) >> 4, b_inc = (sg.b_mn ? 2048u : 32u) >> 4;
           const uint32_t d_tmem = acc_base + sg.acc * BN;
+          uint32_t accum = (started >> sg.acc) & 1u;
+          started |= 1u << sg.acc;
           for (int kt = 0; kt < sg.k_tiles; ++kt) {
             if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = smem_u32(smem + stage * Smem::kStageBytes);
-            const uint32_t sb = sa + Smem::kABytes;
+            const uint64_t so = static_cast<uint64_t>((stage * Smem::kStageBytes) >> 4);
+            uint64_t ad = a_base + so, bd = b_base + so;
 #pragma unroll
             for (int kk = 0; kk < kBlockK / 16; ++kk) {
-              const uint64_t ad = umma_desc(sa + kk * a_step, a_lbo, 1024);
-              const uint64_t bd = umma_desc(sb + kk * b_step, b_lbo, 1024);
-              mma_bf16_ss(d_tmem, ad, bd, idesc, (started >> sg.acc) & 1u);
-              started |= 1u << sg.acc;
+              mma_bf16_ss(d_tmem, ad, bd, idesc, accum);
+              accum = 1u;
+              ad += a_inc;
+              bd += b_inc;
             }
             mma_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
             if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -260,7 +274,8 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t acc0 = tmem_base + buf * kAccCols + (static_cast<uint32_t>(warp * 32) << 16);
+      const uint32_t acc0 =
+          tmem_base + buf * kAccCols + (static_cast<uint32_t>((warp & 3) * 32) << 16);
       Epi::template run<BN>(p.epi, p.tma_out, stager, mt * kBlockM, nt * BN, p.M, p.N, acc0,
                             warp, lane);
       tc_fence_before();
@@ -281,7 +296,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     while (clock64() - t0 < 2000000LL) { }
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }

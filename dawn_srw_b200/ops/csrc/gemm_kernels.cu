@@ -122,6 +122,7 @@ struct PlainEpi {
   static constexpr int kNumAcc = 1;
   static constexpr int kNumOut = 1;
   static constexpr int kOutBufs = 2;
+  static constexpr int kEpiWarps = 4;
   struct Params {
     float alpha;
     const float* row_scale;  // optional [M]
@@ -151,9 +152,10 @@ struct PlainEpi {
           tmem_ld32(acc0 + c + 32 * half, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] *= scale;
-            if (p.bias != nullptr) {
+          for (int j = 0; j < 32; ++j) v[j] *= scale;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
               const int col = col0 + 32 * half + j;
               if (col < N) v[j] += p.bias[col];
             }
@@ -173,9 +175,10 @@ struct PlainEpi {
         tmem_ld32(acc0 + c, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          v[j] *= scale;
-          if (p.bias != nullptr) {
+        for (int j = 0; j < 32; ++j) v[j] *= scale;
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
             const int col = col0 + j;
             if (col < N) v[j] += p.bias[col];
           }
@@ -191,6 +194,8 @@ struct PlainEpi {
 };
 
 // ------------------------------------------------------ forward gate epilogue
+// Eight epilogue warps: warp w handles rows 32(w%4).. of the tile and the
+// (w/4)-th 64-column half, i.e. exactly one staged slab per tile.
 struct FwdGateParams {
   const float* tau;        // [T]
   const float* inv_sigma;  // [T]
@@ -204,54 +209,70 @@ template <int KIND>
 struct FwdGateEpi {
   static constexpr int kNumAcc = 2;
   static constexpr int kNumOut = 1;
-  static constexpr int kOutBufs = 2;
+  static constexpr int kOutBufs = 1;
+  static constexpr int kEpiWarps = 8;
   using Params = FwdGateParams;
-  template <int BN>
-  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
-                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
-    const int r0 = m0 + warp * 32;
-    if (r0 >= M) return;
-    const int row = r0 + lane;
-    const bool row_ok = row < M;
-    const float tau = row_ok ? p.tau[row] : 0.f;
-    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
-    float den_acc = 0.f, g_acc = 0.f;
-    int slab = 0;
+
+  // kGeneral: column tail, unit mask or alive flags are in play for this slab.
+  template <int BN, bool kGeneral>
+  __device__ static __forceinline__ void slab(const Params& p, uint32_t buf, const WarpStager& st,
+                                              uint32_t acc, int col0, int N, bool row_ok,
+                                              float tau, float isg, float& den_acc, float& g_acc,
+                                              int lane) {
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 64, ++slab) {
-      const int col0 = n0 + c;
-      if (col0 >= N) break;
-      st.wait_free<1>();
-      const uint32_t buf = st.buf(slab & 1);
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
-        float s[32], xr[32];
-        tmem_ld32(acc0 + c + 32 * half, s);
-        tmem_ld32(acc0 + BN + c + 32 * half, xr);
-        tmem_ld_wait();
-        const int nv = N - (col0 + 32 * half);  // columns of this half inside the pool
+    for (int half = 0; half < 2; ++half) {
+      float s[32], xr[32];
+      tmem_ld32(acc + 32 * half, s);
+      tmem_ld32(acc + BN + 32 * half, xr);
+      tmem_ld_wait();
+      const int cbase = col0 + 32 * half;
+      unsigned alive_bits = 0u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float g, dt;
-          gate_fwd<KIND>(p.gc, s[j], tau, isg, g, dt);
-          if (j >= nv || !row_ok) { g = 0.f; dt = 0.f; }
-          if (p.unit_mask != nullptr && j < nv) {
-            const float um = p.unit_mask[col0 + 32 * half + j];
+      for (int j = 0; j < 32; ++j) {
+        float g, dt;
+        gate_fwd<KIND>(p.gc, s[j], tau, isg, g, dt);
+        if (kGeneral) {
+          if (cbase + j >= N) { g = 0.f; dt = 0.f; }
+          if (p.unit_mask != nullptr && cbase + j < N) {
+            const float um = p.unit_mask[cbase + j];
             g *= um;
             dt *= um;
           }
-          den_acc += dt;
-          g_acc += g;
-          if (p.alive != nullptr) {
-            const unsigned b = __ballot_sync(0xffffffffu, g >= p.gc.dead_thr);
-            if (lane == 0 && b != 0u && j < nv) p.alive[col0 + 32 * half + j] = 1;
-          }
-          s[j] = g * xr[j];
+          if (row_ok && g >= p.gc.dead_thr) alive_bits |= 1u << j;
         }
-        stage_bf16_32(st, buf, 4 * half, s);
+        den_acc += dt;
+        g_acc += g;
+        s[j] = g * xr[j];
       }
-      st.flush(&maps[0], buf, col0, r0, false, true);
+      if (kGeneral && p.alive != nullptr) {
+        const unsigned any = __reduce_or_sync(0xffffffffu, alive_bits);  // OR over the 32 rows
+        if (((any >> lane) & 1u) && cbase + lane < N) p.alive[cbase + lane] = 1;
+      }
+      stage_bf16_32(st, buf, 4 * half, s);
     }
+  }
+
+  template <int BN>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
+                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+    static_assert(BN == 128, "one 64-column slab per warp");
+    const int r0 = m0 + (warp & 3) * 32;
+    const int c = (warp >> 2) * 64;
+    const int col0 = n0 + c;
+    if (r0 >= M || col0 >= N) return;  // warp-uniform
+    const int row = r0 + lane;
+    const bool row_ok = row < M;
+    // rows past M hold zero accumulators; their results are clipped by the
+    // store and never reach den_sum, so they need no masking
+    const float tau = row_ok ? p.tau[row] : 0.f;
+    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
+    float den_acc = 0.f, g_acc = 0.f;
+    st.wait_free<0>();
+    const uint32_t buf = st.buf(0);
+    const bool general = (col0 + 64 > N) || p.unit_mask != nullptr || p.alive != nullptr;
+    if (general) slab<BN, true>(p, buf, st, acc0 + c, col0, N, row_ok, tau, isg, den_acc, g_acc, lane);
+    else slab<BN, false>(p, buf, st, acc0 + c, col0, N, row_ok, tau, isg, den_acc, g_acc, lane);
+    st.flush(&maps[0], buf, col0, r0, false, true);
     if (row_ok) {
       atomicAdd(p.den_sum + row, den_acc);
       if (p.gate_sum != nullptr) atomicAdd(p.gate_sum + row, g_acc);
@@ -272,56 +293,53 @@ template <int KIND>
 struct BwdGateEpi {
   static constexpr int kNumAcc = 3;
   static constexpr int kNumOut = 3;   // p, dxr, ds
-  static constexpr int kOutBufs = 6;  // three outputs, double-buffered
+  static constexpr int kOutBufs = 3;  // one staged slab per output per warp per tile
+  static constexpr int kEpiWarps = 8;
   using Params = BwdGateParams;
   template <int BN>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
                              int n0, int M, int N, uint32_t acc0, int warp, int lane) {
-    const int r0 = m0 + warp * 32;
-    if (r0 >= M) return;
+    static_assert(BN == 128, "one 64-column slab per warp");
+    const int r0 = m0 + (warp & 3) * 32;
+    const int c = (warp >> 2) * 64;
+    const int col0 = n0 + c;
+    if (r0 >= M || col0 >= N) return;
     const int row = r0 + lane;
     const bool row_ok = row < M;
     const float tau = row_ok ? p.tau[row] : 0.f;
     const float isg = row_ok ? p.inv_sigma[row] : 1.f;
     const float dden = row_ok ? p.dden[row] : 0.f;
+    const bool tail = col0 + 64 > N;
     float dtau_acc = 0.f, dsz_acc = 0.f;
-    int slab = 0;
+    st.wait_free<0>();
+    const uint32_t b_p = st.buf(0), b_dxr = st.buf(1), b_ds = st.buf(2);
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 64, ++slab) {
-      const int col0 = n0 + c;
-      if (col0 >= N) break;
-      st.wait_free<3>();  // the slab before last has been read out of its three buffers
-      const uint32_t b_p = st.buf(3 * (slab & 1));
-      const uint32_t b_dxr = st.buf(3 * (slab & 1) + 1);
-      const uint32_t b_ds = st.buf(3 * (slab & 1) + 2);
-#pragma unroll 1
-      for (int q = 0; q < 4; ++q) {
-        float s[16], xr[16], dp[16];
-        tmem_ld16(acc0 + c + 16 * q, s);
-        tmem_ld16(acc0 + BN + c + 16 * q, xr);
-        tmem_ld16(acc0 + 2 * BN + c + 16 * q, dp);
-        tmem_ld_wait();
-        const int nv = N - (col0 + 16 * q);
+    for (int q = 0; q < 4; ++q) {
+      float s[16], xr[16], dp[16];
+      tmem_ld16(acc0 + c + 16 * q, s);
+      tmem_ld16(acc0 + BN + c + 16 * q, xr);
+      tmem_ld16(acc0 + 2 * BN + c + 16 * q, dp);
+      tmem_ld_wait();
+      const int nv = tail ? N - (col0 + 16 * q) : 16;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float ds, dsz;
-          const float g = gate_bwd<KIND>(p.gc, s[j], tau, isg, dp[j] * xr[j], dden, ds, dsz);
-          if (j >= nv || !row_ok) { ds = 0.f; dsz = 0.f; }
-          dtau_acc -= ds;
-          dsz_acc += dsz;
-          s[j] = ds;
-          const float pv = g * xr[j];
-          dp[j] = dp[j] * g;  // dxr
-          xr[j] = pv;         // p
-        }
-        stage_bf16_16(st, b_p, 2 * q, xr);
-        stage_bf16_16(st, b_dxr, 2 * q, dp);
-        stage_bf16_16(st, b_ds, 2 * q, s);
+      for (int j = 0; j < 16; ++j) {
+        float ds, dsz;
+        const float g = gate_bwd<KIND>(p.gc, s[j], tau, isg, dp[j] * xr[j], dden, ds, dsz);
+        if (j >= nv) { ds = 0.f; dsz = 0.f; }
+        dtau_acc -= ds;
+        dsz_acc += dsz;
+        s[j] = ds;
+        const float pv = g * xr[j];
+        dp[j] = dp[j] * g;  // dxr
+        xr[j] = pv;         // p
       }
-      st.flush(&maps[0], b_p, col0, r0, false, true);
-      st.flush(&maps[1], b_dxr, col0, r0, false, true);
-      st.flush(&maps[2], b_ds, col0, r0, false, true);
+      stage_bf16_16(st, b_p, 2 * q, xr);
+      stage_bf16_16(st, b_dxr, 2 * q, dp);
+      stage_bf16_16(st, b_ds, 2 * q, s);
     }
+    st.flush(&maps[0], b_p, col0, r0, false, true);
+    st.flush(&maps[1], b_dxr, col0, r0, false, true);
+    st.flush(&maps[2], b_ds, col0, r0, false, true);
     if (row_ok) {
       atomicAdd(p.dtau_sum + row, dtau_acc);
       if (KIND == 1) atomicAdd(p.dsz_sum + row, dsz_acc);
@@ -344,7 +362,7 @@ static int fill_operand(CUtensorMap* map, const OperandDesc& o, long long rows, 
 
 template <int BN, class Epi>
 static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
-  using Smem = EngineSmem<BN, Epi::kOutBufs>;
+  using Smem = EngineSmem<BN, Epi::kOutBufs, Epi::kEpiWarps>;
   auto kern = gemm_engine_kernel<BN, Epi>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -359,7 +377,7 @@ static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stre
   const long long total = static_cast<long long>(gp.m_tiles) * gp.n_tiles;
   if (total <= 0) return 0;
   const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
-  kern<<<grid, kNumThreads, Smem::kTotalBytes, stream>>>(gp);
+  kern<<<grid, (Epi::kEpiWarps + 2) * 32, Smem::kTotalBytes, stream>>>(gp);
   return cudaGetLastError() == cudaSuccess ? 0 : 11;
 }
 
