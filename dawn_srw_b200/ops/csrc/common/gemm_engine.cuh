@@ -55,6 +55,7 @@ struct alignas(64) GemmParams {
   int M, N;
   int m_tiles, n_tiles;
   int n_fastest;  // tile raster: 1 = consecutive tiles walk N first
+  int dbg;        // profiling only: 1 = no loads, MMAs run on whatever is in shared memory
   int* status;    // device word, set non-zero on failure
   EpiParams epi;
 };
@@ -121,10 +122,18 @@ struct WarpStager {
 // m0 + 32*(warp%4) + lane and, with 8 warps, its columns the (warp/4)-th half.
 // tmem address of accumulator a, column c:  tmem_acc0 + a * BN + c.
 
-template <int BN, class Epi>
+template <int BN, class Epi, int kCtas>
 __global__ void __launch_bounds__((Epi::kEpiWarps + 2) * 32, 1)
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
-  using Smem = EngineSmem<BN, Epi::kOutBufs, Epi::kEpiWarps>;
+  // kCtas == 2: the CTA pair of a 2-CTA cluster shares a 256-row tile.  Each CTA
+  // stages its own 128 rows of A and BN/2 rows of B; the leader CTA (cluster
+  // rank 0) issues tcgen05.mma.cta_group::2 for both.  All TMA loads count
+  // their bytes on the leader's `full` barrier; MMA completion is multicast to
+  // both CTAs' `empty` / `acc_full` barriers; both CTAs' epilogue warps arrive
+  // on the leader's `acc_empty`.
+  static_assert(kCtas == 1 || kCtas == 2, "1 or 2 CTAs per tile");
+  constexpr int kBRows = BN / kCtas;  // rows of B this CTA stages
+  using Smem = EngineSmem<kBRows, Epi::kOutBufs, Epi::kEpiWarps>;
   constexpr int kEpiWarps = Epi::kEpiWarps;
   constexpr int kTmaWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "4 or 8 epilogue warps");
@@ -133,6 +142,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   constexpr int kNumBuf = (2 * kAccCols <= kTmemCols) ? 2 : 1;
   static_assert(kAccCols <= kTmemCols, "accumulators exceed TMEM");
   constexpr int kStages = Smem::kStages;
+  constexpr int kTileM = kBlockM * kCtas;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -148,6 +158,10 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = (kCtas == 2) ? cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  const int tile_stride = gridDim.x / kCtas;
+  const int first_tile = blockIdx.x / kCtas;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -156,7 +170,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     }
     for (int i = 0; i < kNumBuf; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], kEpiWarps * 32);
+      mbar_init(&acc_empty[i], kCtas * kEpiWarps);   // one elected arrive per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -171,11 +185,12 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     for (int s = 0; s < Epi::kNumOut; ++s) tma_prefetch_desc(&p.tma_out[s]);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if (kCtas == 2) { tmem_alloc_pair(tmem_slot, kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
   }
   tc_fence_before();
   __syncthreads();
+  if (kCtas == 2) cluster_sync_all();   // peer barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -183,34 +198,54 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
 
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
+    if (lane == 0 && !(p.dbg & 1)) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
         const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
         const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
-        const int m0 = mt * kBlockM, n0 = nt * BN;
+        const int m0 = mt * kTileM + static_cast<int>(rank) * kBlockM;
+        const int n0 = nt * BN + static_cast<int>(rank) * kBRows;
         for (int s = 0; s < p.n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
           for (int kt = 0; kt < sg.k_tiles; ++kt) {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
             uint8_t* sa = smem + stage * Smem::kStageBytes;
             uint8_t* sb = sa + Smem::kABytes;
-            mbar_expect_tx(&full_bar[stage], Smem::kStageBytes);
             const int k0 = kt * kBlockK;
-            if (sg.a_mn) {
-              tma_load_2d(sa, &p.tma_a[s], &full_bar[stage], m0, k0);
-              tma_load_2d(sa + 8192, &p.tma_a[s], &full_bar[stage], m0 + 64, k0);
-            } else {
-              tma_load_2d(sa, &p.tma_a[s], &full_bar[stage], k0, m0);
-            }
-            if (sg.b_mn) {
+            if (kCtas == 1) {
+              mbar_expect_tx(&full_bar[stage], Smem::kStageBytes);
+              if (sg.a_mn) {
+                tma_load_2d(sa, &p.tma_a[s], &full_bar[stage], m0, k0);
+                tma_load_2d(sa + 8192, &p.tma_a[s], &full_bar[stage], m0 + 64, k0);
+              } else {
+                tma_load_2d(sa, &p.tma_a[s], &full_bar[stage], k0, m0);
+              }
+              if (sg.b_mn) {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_2d(sb + j * 8192, &p.tma_b[s], &full_bar[stage], n0 + 64 * j, k0);
+                for (int j = 0; j < kBRows / 64; ++j)
+                  tma_load_2d(sb + j * 8192, &p.tma_b[s], &full_bar[stage], n0 + 64 * j, k0);
+              } else {
+                tma_load_2d(sb, &p.tma_b[s], &full_bar[stage], k0, n0);
+              }
             } else {
-              tma_load_2d(sb, &p.tma_b[s], &full_bar[stage], k0, n0);
+              // bytes of both CTAs are counted on the leader's barrier
+              if (leader) mbar_expect_tx(&full_bar[stage], 2 * Smem::kStageBytes);
+              const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
+              if (sg.a_mn) {
+                tma_load_2d_pair(sa, &p.tma_a[s], fb, m0, k0);
+                tma_load_2d_pair(sa + 8192, &p.tma_a[s], fb, m0 + 64, k0);
+              } else {
+                tma_load_2d_pair(sa, &p.tma_a[s], fb, k0, m0);
+              }
+              if (sg.b_mn) {
+#pragma unroll
+                for (int j = 0; j < kBRows / 64; ++j)
+                  tma_load_2d_pair(sb + j * 8192, &p.tma_b[s], fb, n0 + 64 * j, k0);
+              } else {
+                tma_load_2d_pair(sb, &p.tma_b[s], fb, k0, n0);
+              }
             }
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
@@ -219,13 +254,13 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     }
   } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
         const int buf = it % kNumBuf;
         const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
         if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -234,7 +269,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         uint32_t started = 0;  // bit a set once accumulator a holds data for this tile
         for (int s = 0; s < p.n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
-          const uint32_t idesc = umma_idesc_bf16(kBlockM, BN, sg.a_mn, sg.b_mn);
+          const uint32_t idesc = umma_idesc_bf16(kTileM, BN, sg.a_mn, sg.b_mn);
           // descriptors for stage 0; a stage / k-slice only moves the 14-bit
           // address field, so the hot loop just adds to the low word
           const uint64_t a_base = umma_desc(smem_base, sg.a_mn ? 8192u : 16u, 1024);
@@ -244,22 +279,32 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
           uint32_t accum = (started >> sg.acc) & 1u;
           started |= 1u << sg.acc;
           for (int kt = 0; kt < sg.k_tiles; ++kt) {
-            if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
-            tc_fence_after();
+            if (!(p.dbg & 1)) {
+              if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+            }
             const uint64_t so = static_cast<uint64_t>((stage * Smem::kStageBytes) >> 4);
             uint64_t ad = a_base + so, bd = b_base + so;
 #pragma unroll
             for (int kk = 0; kk < kBlockK / 16; ++kk) {
-              mma_bf16_ss(d_tmem, ad, bd, idesc, accum);
+              if (kCtas == 2) mma_bf16_ss_pair(d_tmem, ad, bd, idesc, accum);
+              else mma_bf16_ss(d_tmem, ad, bd, idesc, accum);
               accum = 1u;
               ad += a_inc;
               bd += b_inc;
             }
-            mma_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
+            // frees the smem stage (in both CTAs) when the MMAs retire
+            if (!(p.dbg & 1)) {
+              if (kCtas == 2) mma_commit_pair(&empty_bar[stage]);
+              else mma_commit(&empty_bar[stage]);
+            }
             if (++stage == kStages) { stage = 0; phase ^= 1; }
           }
         }
-        if (ok) mma_commit(&acc_full[buf]);
+        if (ok) {
+          if (kCtas == 2) mma_commit_pair(&acc_full[buf]);
+          else mma_commit(&acc_full[buf]);
+        }
       }
     }
   } else {
@@ -267,7 +312,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     int it = 0;
     bool ok = true;
     WarpStager stager{smem_u32(out_stage + warp * Epi::kOutBufs * kOutBufBytes), lane};
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
       const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
       const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
       const int buf = it % kNumBuf;
@@ -276,10 +321,14 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       tc_fence_after();
       const uint32_t acc0 =
           tmem_base + buf * kAccCols + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-      Epi::template run<BN>(p.epi, p.tma_out, stager, mt * kBlockM, nt * BN, p.M, p.N, acc0,
-                            warp, lane);
+      Epi::template run<BN>(p.epi, p.tma_out, stager, mt * kTileM + static_cast<int>(rank) * kBlockM,
+                            nt * BN, p.M, p.N, acc0, warp, lane);
       tc_fence_before();
-      mbar_arrive(&acc_empty[buf]);
+      __syncwarp();
+      if (lane == 0) {
+        if (kCtas == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[buf]), 0));
+        else mbar_arrive(&acc_empty[buf]);
+      }
     }
     if (lane == 0) bulk_wait<0>();  // all of this warp's bulk stores have landed
   }
@@ -296,9 +345,11 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     while (clock64() - t0 < 2000000LL) { }
     __syncthreads();
   }
+  if (kCtas == 2) cluster_sync_all();   // neither CTA leaves while its peer may still signal it
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (kCtas == 2) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -13,6 +13,9 @@
 //   that flow to tau and sigma.
 // The reference computes the same quantities chunk by chunk in XLA
 // (models/dawn_spatial_v41_exp.py:485-586) and derives the backward by autodiff.
+#include <stdlib.h>
+#include <string.h>
+
 #include "common/gemm_engine.cuh"
 #include "common/host_utils.cuh"
 #include "dsb_api.h"
@@ -354,16 +357,18 @@ struct OperandDesc {
   long long ld;    // elements between stored rows
 };
 
+static bool use_cta_pairs();
 static int fill_operand(CUtensorMap* map, const OperandDesc& o, long long rows, long long K,
                         int box_rows) {
   if (o.mn_major) return make_tmap_bf16(map, o.ptr, rows, K, o.ld, 64, 64);
   return make_tmap_bf16(map, o.ptr, K, rows, o.ld, 64, box_rows);
 }
 
-template <int BN, class Epi>
-static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
-  using Smem = EngineSmem<BN, Epi::kOutBufs, Epi::kEpiWarps>;
-  auto kern = gemm_engine_kernel<BN, Epi>;
+// kCtas == 2 launches 2-CTA clusters (one SM pair per 256-row tile).
+template <int BN, class Epi, int kCtas>
+static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
+  using Smem = EngineSmem<BN / kCtas, Epi::kOutBufs, Epi::kEpiWarps>;
+  auto kern = gemm_engine_kernel<BN, Epi, kCtas>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -371,14 +376,47 @@ static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stre
       return 10;
     attr_set = true;
   }
-  gp.m_tiles = (gp.M + kBlockM - 1) / kBlockM;
+  gp.m_tiles = (gp.M + kBlockM * kCtas - 1) / (kBlockM * kCtas);
   gp.n_tiles = (gp.N + BN - 1) / BN;
   gp.n_fastest = gp.n_tiles <= gp.m_tiles ? 1 : 0;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("DSB_DBG"); dbg = e ? atoi(e) : 0; }
+    gp.dbg = dbg;
+  }
   const long long total = static_cast<long long>(gp.m_tiles) * gp.n_tiles;
   if (total <= 0) return 0;
-  const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
-  kern<<<grid, (Epi::kEpiWarps + 2) * 32, Smem::kTotalBytes, stream>>>(gp);
-  return cudaGetLastError() == cudaSuccess ? 0 : 11;
+  const int units = sm_count() / kCtas;
+  const int grid = kCtas * static_cast<int>(total < units ? total : units);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3((Epi::kEpiWarps + 2) * 32);
+  cfg.dynamicSmemBytes = Smem::kTotalBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, gp) == cudaSuccess ? 0 : 11;
+}
+
+// Environment switch DSB_CTA_PAIRS=0 falls back to single-CTA tiles (profiling).
+static bool use_cta_pairs() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DSB_CTA_PAIRS");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <int BN, class Epi>
+static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
+  if (use_cta_pairs()) return launch_engine_impl<BN, Epi, 2>(gp, stream);
+  return launch_engine_impl<BN, Epi, 1>(gp, stream);
 }
 
 }  // namespace dsb
@@ -395,7 +433,7 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   const int BN = (block_n & 0xffff) == 128 ? 128 : 256;
   int rc = fill_operand(&gp.tma_a[0], {A, a_mn, lda}, M, K, kBlockM);
   if (rc) return 100 + rc;
-  rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, BN);
+  rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, use_cta_pairs() ? BN / 2 : BN);
   if (rc) return 200 + rc;
   gp.seg[0] = {(K + kBlockK - 1) / kBlockK, 0, a_mn, b_mn};
   gp.n_seg = 1;
@@ -424,10 +462,11 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
   constexpr int BN = 128;
   GemmParams<FwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
+  const int brows = use_cta_pairs() ? BN / 2 : BN;
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
-  rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, BN);
+  rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
   rc |= fill_operand(&gp.tma_a[1], {x, 0, ldx}, T, D, kBlockM);
-  rc |= fill_operand(&gp.tma_b[1], {read, 0, ldr}, U, D, BN);
+  rc |= fill_operand(&gp.tma_b[1], {read, 0, ldr}, U, D, brows);
   if (rc) return 100 + rc;
   gp.seg[0] = {(r + kBlockK - 1) / kBlockK, 0, 0, 0};
   gp.seg[1] = {(D + kBlockK - 1) / kBlockK, 1, 0, 0};
@@ -455,12 +494,13 @@ extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, l
   constexpr int BN = 128;
   GemmParams<BwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
+  const int brows = use_cta_pairs() ? BN / 2 : BN;
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
-  rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, BN);
+  rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
   rc |= fill_operand(&gp.tma_a[1], {x, 0, ldx}, T, D, kBlockM);
-  rc |= fill_operand(&gp.tma_b[1], {read, 0, ldr}, U, D, BN);
+  rc |= fill_operand(&gp.tma_b[1], {read, 0, ldr}, U, D, brows);
   rc |= fill_operand(&gp.tma_a[2], {dy, 0, lddy}, T, D, kBlockM);
-  rc |= fill_operand(&gp.tma_b[2], {write, 0, ldw}, U, D, BN);
+  rc |= fill_operand(&gp.tma_b[2], {write, 0, ldw}, U, D, brows);
   if (rc) return 100 + rc;
   gp.seg[0] = {(r + kBlockK - 1) / kBlockK, 0, 0, 0};
   gp.seg[1] = {(D + kBlockK - 1) / kBlockK, 1, 0, 0};
