@@ -29,6 +29,8 @@
 // flag, all roles leave their loops, TMEM is freed and `status` gets
 // kStatusWaitTimeout; the host checks it after the launch.
 #pragma once
+#include <type_traits>
+
 #include "ptx.cuh"
 
 namespace dsb {
@@ -254,12 +256,52 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     }
   } else if (warp == kMmaWarp) {
     // ---------------------------------------------------------- MMA issuer
+    // One thread feeds the tensor pipe, which queues only about one
+    // instruction ahead, so everything between two tcgen05.mma must be cheap:
+    // descriptor increments are compile-time constants (the loop body is
+    // instantiated per operand layout) and the barrier wait has a one-
+    // instruction fast path.
     if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
+      const bool no_loads = (p.dbg & 1) != 0;
+      const int n_seg = p.n_seg;
+      auto issue_seg = [&](auto a_mn_c, auto b_mn_c, const int k_tiles, const uint32_t d_tmem,
+                           uint32_t accum) {
+        constexpr bool kAmn = decltype(a_mn_c)::value, kBmn = decltype(b_mn_c)::value;
+        constexpr uint32_t kAInc = (kAmn ? 2048u : 32u) >> 4, kBInc = (kBmn ? 2048u : 32u) >> 4;
+        const uint32_t idesc = umma_idesc_bf16(kTileM, BN, kAmn, kBmn);
+        const uint64_t a_base = umma_desc(smem_base, kAmn ? 8192u : 16u, 1024);
+        const uint64_t b_base = umma_desc(smem_base + Smem::kABytes, kBmn ? 8192u : 16u, 1024);
+#pragma unroll 1
+        for (int kt = 0; kt < k_tiles; ++kt) {
+          if (!no_loads) {
+            if (!mbar_try_wait(&full_bar[stage], phase) &&
+                !mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; return; }
+            tc_fence_after();
+          }
+          const uint64_t so = static_cast<uint64_t>(static_cast<uint32_t>(stage) *
+                                                    (Smem::kStageBytes >> 4));
+          const uint64_t ad = a_base + so, bd = b_base + so;
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / 16; ++kk) {
+            if (kCtas == 2) mma_bf16_ss_pair(d_tmem, ad + kk * kAInc, bd + kk * kBInc, idesc, accum);
+            else mma_bf16_ss(d_tmem, ad + kk * kAInc, bd + kk * kBInc, idesc, accum);
+            accum = 1u;
+          }
+          if (!no_loads) {
+            // frees the smem stage (in both CTAs) when the MMAs retire
+            if (kCtas == 2) mma_commit_pair(&empty_bar[stage]);
+            else mma_commit(&empty_bar[stage]);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      };
+      using T_ = std::true_type;
+      using F_ = std::false_type;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
         const int buf = it % kNumBuf;
         const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
@@ -267,39 +309,15 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         tc_fence_after();
         const uint32_t acc_base = tmem_base + buf * kAccCols;
         uint32_t started = 0;  // bit a set once accumulator a holds data for this tile
-        for (int s = 0; s < p.n_seg && ok; ++s) {
+        for (int s = 0; s < n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
-          const uint32_t idesc = umma_idesc_bf16(kTileM, BN, sg.a_mn, sg.b_mn);
-          // descriptors for stage 0; a stage / k-slice only moves the 14-bit
-          // address field, so the hot loop just adds to the low word
-          const uint64_t a_base = umma_desc(smem_base, sg.a_mn ? 8192u : 16u, 1024);
-          const uint64_t b_base = umma_desc(smem_base + Smem::kABytes, sg.b_mn ? 8192u : 16u, 1024);
-          const uint64_t a_inc = (sg.a_mn ? 2048u : 32u) >> 4, b_inc = (sg.b_mn ? 2048u : 32u) >> 4;
           const uint32_t d_tmem = acc_base + sg.acc * BN;
-          uint32_t accum = (started >> sg.acc) & 1u;
+          const uint32_t accum = (started >> sg.acc) & 1u;
           started |= 1u << sg.acc;
-          for (int kt = 0; kt < sg.k_tiles; ++kt) {
-            if (!(p.dbg & 1)) {
-              if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
-              tc_fence_after();
-            }
-            const uint64_t so = static_cast<uint64_t>((stage * Smem::kStageBytes) >> 4);
-            uint64_t ad = a_base + so, bd = b_base + so;
-#pragma unroll
-            for (int kk = 0; kk < kBlockK / 16; ++kk) {
-              if (kCtas == 2) mma_bf16_ss_pair(d_tmem, ad, bd, idesc, accum);
-              else mma_bf16_ss(d_tmem, ad, bd, idesc, accum);
-              accum = 1u;
-              ad += a_inc;
-              bd += b_inc;
-            }
-            // frees the smem stage (in both CTAs) when the MMAs retire
-            if (!(p.dbg & 1)) {
-              if (kCtas == 2) mma_commit_pair(&empty_bar[stage]);
-              else mma_commit(&empty_bar[stage]);
-            }
-            if (++stage == kStages) { stage = 0; phase ^= 1; }
-          }
+          if (!sg.a_mn && !sg.b_mn) issue_seg(F_{}, F_{}, sg.k_tiles, d_tmem, accum);
+          else if (!sg.a_mn && sg.b_mn) issue_seg(F_{}, T_{}, sg.k_tiles, d_tmem, accum);
+          else if (sg.a_mn && !sg.b_mn) issue_seg(T_{}, F_{}, sg.k_tiles, d_tmem, accum);
+          else issue_seg(T_{}, T_{}, sg.k_tiles, d_tmem, accum);
         }
         if (ok) {
           if (kCtas == 2) mma_commit_pair(&acc_full[buf]);

@@ -55,6 +55,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   long long t0 = 0;
   for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (it > 4) __nanosleep(64);  // long waits poll gently: shared memory feeds the tensor core
     if ((it & 0xff) == 0xff) {
       if (*abort_flag) return false;
       long long now = clock64();
