@@ -137,6 +137,36 @@ void srw_forward(const Tensor& h, const Tensor& emb, const Tensor& x, const Tens
   TORCH_CHECK(rc == 0, "dsb_srw_forward failed with code ", rc);
 }
 
+// Fused GEMM -> reduce-scatter.  `out_ptrs`: data pointers of every rank's
+// [rows_per_rank, N] fp32 buffer (index = rank), as integers.
+void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
+                  std::vector<int64_t> out_ptrs, int64_t rows_per_rank, int64_t ldc, double alpha,
+                  c10::optional<Tensor> row_scale, Tensor& status) {
+  check_bf16_2d(A, "A");
+  check_bf16_2d(B, "B");
+  const c10::cuda::CUDAGuard guard(A.device());
+  const int64_t M = a_mn ? A.size(1) : A.size(0);
+  const int64_t K = a_mn ? A.size(0) : A.size(1);
+  const int64_t N = b_mn ? B.size(1) : B.size(0);
+  std::vector<void*> outs;
+  for (auto p : out_ptrs) outs.push_back(reinterpret_cast<void*>(p));
+  int rc = dsb_gemm_bf16_scatter(A.data_ptr(), a_mn, A.stride(0), B.data_ptr(), b_mn, B.stride(0),
+                                 M, N, K, outs.data(), static_cast<int>(outs.size()),
+                                 rows_per_rank, ldc, alpha, opt_f32(row_scale),
+                                 status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_gemm_bf16_scatter failed with code ", rc);
+}
+
+void peer_barrier(const Tensor& pads_dev, int64_t rank, int64_t world, int64_t epoch,
+                  int64_t slot_base, Tensor& status, int64_t wait_cycles) {
+  TORCH_CHECK(pads_dev.is_cuda() && pads_dev.scalar_type() == torch::kInt64);
+  const c10::cuda::CUDAGuard guard(pads_dev.device());
+  int rc = dsb_peer_barrier(reinterpret_cast<unsigned int* const*>(pads_dev.data_ptr<int64_t>()),
+                            rank, world, static_cast<unsigned int>(epoch), slot_base,
+                            status.data_ptr<int>(), wait_cycles, cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_peer_barrier failed with code ", rc);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -144,4 +174,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_fwd_gate", &srw_fwd_gate);
   m.def("srw_bwd_gate", &srw_bwd_gate);
   m.def("srw_forward", &srw_forward);
+  m.def("gemm_scatter", &gemm_scatter);
+  m.def("peer_barrier", &peer_barrier);
 }

@@ -38,6 +38,7 @@ namespace dsb {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int kMaxSeg = 3;
+constexpr int kMaxOut = 8;   // output tensor maps (one per owner rank for scattered outputs)
 constexpr int kTmemCols = 512;
 
 struct GemmSeg {
@@ -51,7 +52,7 @@ template <class EpiParams>
 struct alignas(64) GemmParams {
   CUtensorMap tma_a[kMaxSeg];
   CUtensorMap tma_b[kMaxSeg];
-  CUtensorMap tma_out[kMaxSeg];  // epilogue outputs: box = 128 bytes x 32 rows, 128B swizzle
+  CUtensorMap tma_out[kMaxOut];  // epilogue outputs: box = 128 bytes x 32 rows, 128B swizzle
   GemmSeg seg[kMaxSeg];
   int n_seg;
   int M, N;

@@ -54,6 +54,20 @@ int dsb_srw_forward(const void* h, long long ldh, const void* emb, long long lde
                     long long ldo, float* den_sum, unsigned char* alive, const float* unit_mask,
                     const DsbGate* gate /*host*/, int* status, cudaStream_t stream);
 
+// GEMM with the reduce-scatter fused into its epilogue (see gemm_kernels.cu).
+// `outs` is a HOST array of n_ranks device pointers (peer pointers included).
+int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                          long long ldb, int M, int N, int K, void* const* outs, int n_ranks,
+                          int rows_per_rank, long long ldc, float alpha, const float* row_scale,
+                          int* status, cudaStream_t stream);
+
+// Bounded cross-GPU barrier over symmetric signal pads.  `pads_dev` is a DEVICE
+// array of `world` pointers to the ranks' pads (uint32); slots
+// [slot_base, slot_base + world) of every pad belong to this barrier stream.
+// `epoch` must increase by one per call.  wait_cycles <= 0 selects the default.
+int dsb_peer_barrier(unsigned int* const* pads_dev, int rank, int world, unsigned int epoch,
+                     int slot_base, int* status, long long wait_cycles, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -123,7 +123,7 @@ __device__ __forceinline__ void stage_bf16_16(const WarpStager& st, uint32_t buf
 // --------------------------------------------------------- plain epilogue
 struct PlainEpi {
   static constexpr int kNumAcc = 1;
-  static constexpr int kNumOut = 1;
+  static constexpr int kNumOut = 1;   // (kMaxOut maps when scattering; they are not prefetched)
   static constexpr int kOutBufs = 2;
   static constexpr int kEpiWarps = 4;
   struct Params {
@@ -133,6 +133,10 @@ struct PlainEpi {
     int out_bf16;            // 1: bf16 output, 0: fp32
     int accumulate;          // 1: out += result (fp32 output only; TMA reduce-add)
     int dbg;                 // profiling toggle: 1 = skip the stores
+    // Fused reduce-scatter: when > 0, global row R of the result belongs to rank
+    // R / scatter_rows and is reduce-added (fp32) into that rank's buffer
+    // (tensor map index = owner rank; peer memory for the other ranks).
+    int scatter_rows;
   };
   template <int BN>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
@@ -190,7 +194,12 @@ struct PlainEpi {
         for (int q = 0; q < 8; ++q)
           st.put(buf, q, __float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
                  __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
-        st.flush(&maps[0], buf, col0, r0, p.accumulate != 0, !(p.dbg & 1));
+        if (p.scatter_rows > 0) {
+          const int owner = r0 / p.scatter_rows;
+          st.flush(&maps[owner], buf, col0, r0 - owner * p.scatter_rows, true, true);
+        } else {
+          st.flush(&maps[0], buf, col0, r0, p.accumulate != 0, !(p.dbg & 1));
+        }
       }
     }
   }
@@ -442,7 +451,7 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   gp.status = status;
   rc = make_out_tmap(&gp.tma_out[0], C, M, N, ldc, c_is_bf16 ? 2 : 4);
   if (rc) return 300 + rc;
-  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, block_n >> 16};
+  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, block_n >> 16, 0};
   return BN == 128 ? launch_engine<128, PlainEpi>(gp, stream)
                    : launch_engine<256, PlainEpi>(gp, stream);
 }
@@ -538,4 +547,39 @@ extern "C" int dsb_srw_forward(const void* h, long long ldh, const void* emb, lo
   // raw_out[T,D] = p[T,U] . write[U,D]   (write is the MN-major B operand)
   return dsb_gemm_bf16(p_scratch, 0, ldp, write, 1, ldw, T, D, U, raw_out, ldo, 0, 0, 1.0f,
                        nullptr, nullptr, 256, status, stream);
+}
+
+// GEMM with a fused reduce-scatter over `n_ranks` GPUs: this rank's product
+// A.B^T [M, N] (M = n_ranks * rows_per_rank) is row-scaled and reduce-added
+// (fp32, TMA reduce over NVLink) straight from the epilogue into the owner
+// rank's buffer outs[j] ([rows_per_rank, N] fp32, ldc elements between rows).
+// The buffers must have been zeroed on every rank before any rank launches,
+// and read only after every rank's kernel has finished (see parallel/symm.py).
+extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, const void* B,
+                                     int b_mn, long long ldb, int M, int N, int K,
+                                     void* const* outs, int n_ranks, int rows_per_rank,
+                                     long long ldc, float alpha, const float* row_scale,
+                                     int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (n_ranks < 1 || n_ranks > kMaxOut || rows_per_rank % 32 != 0 ||
+      static_cast<long long>(n_ranks) * rows_per_rank != M)
+    return 500;
+  GemmParams<PlainEpi::Params> gp;
+  memset(&gp, 0, sizeof(gp));
+  constexpr int BN = 256;
+  int rc = fill_operand(&gp.tma_a[0], {A, a_mn, lda}, M, K, kBlockM);
+  if (rc) return 100 + rc;
+  rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, use_cta_pairs() ? BN / 2 : BN);
+  if (rc) return 200 + rc;
+  for (int j = 0; j < n_ranks; ++j) {
+    rc = make_out_tmap(&gp.tma_out[j], outs[j], rows_per_rank, N, ldc, 4);
+    if (rc) return 300 + rc;
+  }
+  gp.seg[0] = {(K + kBlockK - 1) / kBlockK, 0, a_mn, b_mn};
+  gp.n_seg = 1;
+  gp.M = M;
+  gp.N = N;
+  gp.status = status;
+  gp.epi = {alpha, row_scale, nullptr, 0, 1, 0, rows_per_rank};
+  return launch_engine<BN, PlainEpi>(gp, stream);
 }

@@ -1,0 +1,115 @@
+"""Kernels that talk over NVLink, on 2 GPUs of one box (skipped with fewer).
+Child processes, NCCL only for set-up, NVLS off."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _spawn(fn, world, *args):
+    import torch.multiprocessing as mp
+    from helpers import free_port
+    port = free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_child, args=(fn, r, world, port, q, args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = {}
+    try:
+        for _ in range(world):
+            r, status, val = q.get(timeout=300)
+            if status != "ok":
+                raise RuntimeError(f"rank {r} failed:\n{val}")
+            out[r] = val
+    finally:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.terminate()
+    return [out[r] for r in range(world)]
+
+
+def _child(fn, rank, world, port, q, args):
+    import traceback
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    try:
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+        val = fn(rank, world, *args)
+        torch.cuda.synchronize()
+        dist.barrier()
+        q.put((rank, "ok", val))
+        dist.destroy_process_group()
+    except Exception:
+        q.put((rank, "err", traceback.format_exc()))
+
+
+def _barrier_and_scatter(rank, world):
+    import torch.distributed as dist
+    from dawn_srw_b200.ops import cuda_backend as CB
+    from dawn_srw_b200.parallel.symm import SymmWorkspace
+    dev = torch.device("cuda", rank)
+    ws = SymmWorkspace(None, dev)
+    for _ in range(5):
+        ws.barrier()
+    torch.cuda.synchronize()
+    CB.check_status()
+    # fused GEMM -> reduce-scatter against NCCL reduce_scatter of the same products
+    rows, N, K = 256, 520, 384
+    M = rows * world
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    A = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    B = torch.randn(N, K, device=dev, generator=g).bfloat16()
+    rs = torch.rand(M, device=dev, generator=g) + 0.5
+    out = ws.alloc("rs_out", (rows, N), torch.float32)
+    res = []
+    for it in range(2):                       # twice: buffers are reused across calls
+        out.local.zero_()
+        ws.barrier()                          # every rank has zeroed its buffer
+        CB.ext().gemm_scatter(A, False, B, False, out.ptrs, rows, N, 1.0, rs, CB.status_word(dev))
+        ws.barrier()                          # every rank's adds have landed
+        torch.cuda.synchronize()
+        res.append(out.local.clone())
+    CB.check_status()
+    full = (A.float() @ B.float().t()) * rs[:, None]
+    ref = torch.empty(rows, N, device=dev)
+    dist.reduce_scatter_tensor(ref, full.contiguous())
+    err = max(((r - ref).norm() / ref.norm()).item() for r in res)
+    return err
+
+
+def test_peer_barrier_and_fused_gemm_reduce_scatter():
+    _need(2)
+    errs = _spawn(_barrier_and_scatter, 2)
+    assert max(errs) < 1e-5, errs
+
+
+def test_peer_barrier_times_out_when_a_peer_never_arrives():
+    """One GPU plays a two-rank world in which the other rank's flag is never
+    written: the wait runs out, the status word reports it, the context lives."""
+    _need(1)
+    from dawn_srw_b200.ops import cuda_backend as CB
+    dev = torch.device("cuda", 0)
+    pad0 = torch.zeros(64, dtype=torch.int32, device=dev)
+    pad1 = torch.zeros(64, dtype=torch.int32, device=dev)      # stands in for the absent peer's pad
+    pads = torch.tensor([pad0.data_ptr(), pad1.data_ptr()], dtype=torch.int64, device=dev)
+    st = CB.status_word(dev)
+    st.zero_()
+    CB.ext().peer_barrier(pads, 0, 2, 1, 0, st, 20_000_000)     # ~10 ms budget
+    torch.cuda.synchronize()
+    assert int(st.item()) == 3
+    with pytest.raises(RuntimeError):
+        CB.check_status()
+    assert int(st.item()) == 0                                  # cleared; the GPU is still usable
+    x = torch.ones(4, device=dev)
+    assert float((x + 1).sum()) == 8.0
