@@ -4,6 +4,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstring>
+#include <vector>
+
 #include "dsb_api.h"
 
 namespace {
@@ -137,6 +140,78 @@ void srw_forward(const Tensor& h, const Tensor& emb, const Tensor& x, const Tens
   TORCH_CHECK(rc == 0, "dsb_srw_forward failed with code ", rc);
 }
 
+struct GatherHolder {
+  std::vector<std::vector<const void*>> ptrs;
+  DsbGather g;
+};
+// tensors: list of (peer pointer list, ld, cols) in the order x, h [, dy]
+void fill_gather(GatherHolder& gh, const std::vector<std::vector<int64_t>>& ptr_lists,
+                 const std::vector<int64_t>& lds, const std::vector<int64_t>& cols, int64_t my_rank,
+                 int64_t rows_per_rank, Tensor& ready, int64_t epoch) {
+  memset(&gh.g, 0, sizeof(gh.g));
+  gh.ptrs.resize(ptr_lists.size());
+  gh.g.n_tensors = static_cast<int>(ptr_lists.size());
+  gh.g.n_ranks = static_cast<int>(ptr_lists[0].size());
+  gh.g.my_rank = static_cast<int>(my_rank);
+  gh.g.rows_per_rank = static_cast<int>(rows_per_rank);
+  for (size_t t = 0; t < ptr_lists.size(); ++t) {
+    for (auto p : ptr_lists[t]) gh.ptrs[t].push_back(reinterpret_cast<const void*>(p));
+    gh.g.bufs[t] = gh.ptrs[t].data();
+    gh.g.ld[t] = lds[t];
+    gh.g.cols[t] = static_cast<int>(cols[t]);
+  }
+  TORCH_CHECK(ready.is_cuda() && ready.scalar_type() == torch::kInt32);
+  gh.g.ready = reinterpret_cast<unsigned int*>(ready.data_ptr<int>());
+  gh.g.epoch = static_cast<unsigned int>(epoch);
+}
+
+void srw_fwd_gate_gather(const Tensor& h_full, const Tensor& emb, const Tensor& x_full,
+                         const Tensor& read, Tensor& p_out, const Tensor& tau,
+                         const Tensor& inv_sigma, Tensor& den_sum, std::vector<double> gate,
+                         Tensor& status, std::vector<std::vector<int64_t>> ptr_lists,
+                         int64_t my_rank, int64_t rows_per_rank, Tensor& ready, int64_t epoch) {
+  check_bf16_2d(h_full, "h_full"); check_bf16_2d(emb, "emb"); check_bf16_2d(x_full, "x_full");
+  check_bf16_2d(read, "read"); check_bf16_2d(p_out, "p_out");
+  const c10::cuda::CUDAGuard guard(x_full.device());
+  const int T = x_full.size(0), D = x_full.size(1), U = emb.size(0), r = emb.size(1);
+  DsbGate g = to_gate(gate);
+  GatherHolder gh;
+  fill_gather(gh, ptr_lists, {x_full.stride(0), h_full.stride(0)}, {D, r}, my_rank, rows_per_rank,
+              ready, epoch);
+  int rc = dsb_srw_fwd_gate_gather(h_full.data_ptr(), h_full.stride(0), emb.data_ptr(),
+                                   emb.stride(0), x_full.data_ptr(), x_full.stride(0),
+                                   read.data_ptr(), read.stride(0), T, U, r, D, p_out.data_ptr(),
+                                   p_out.stride(0), tau.data_ptr<float>(),
+                                   inv_sigma.data_ptr<float>(), den_sum.data_ptr<float>(), nullptr,
+                                   nullptr, nullptr, &g, &gh.g, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_fwd_gate_gather failed with code ", rc);
+}
+
+void srw_bwd_gate_gather(const Tensor& h_full, const Tensor& emb, const Tensor& x_full,
+                         const Tensor& read, const Tensor& dy_full, const Tensor& write,
+                         Tensor& p_out, Tensor& dxr_out, Tensor& ds_out, const Tensor& tau,
+                         const Tensor& inv_sigma, const Tensor& dden, Tensor& dtau_sum,
+                         Tensor& dsz_sum, std::vector<double> gate, Tensor& status,
+                         std::vector<std::vector<int64_t>> ptr_lists, int64_t my_rank,
+                         int64_t rows_per_rank, Tensor& ready, int64_t epoch) {
+  check_bf16_2d(h_full, "h_full"); check_bf16_2d(x_full, "x_full"); check_bf16_2d(dy_full, "dy_full");
+  check_bf16_2d(p_out, "p_out"); check_bf16_2d(dxr_out, "dxr_out"); check_bf16_2d(ds_out, "ds_out");
+  const c10::cuda::CUDAGuard guard(x_full.device());
+  const int T = x_full.size(0), D = x_full.size(1), U = emb.size(0), r = emb.size(1);
+  DsbGate g = to_gate(gate);
+  GatherHolder gh;
+  fill_gather(gh, ptr_lists, {x_full.stride(0), h_full.stride(0), dy_full.stride(0)}, {D, r, D},
+              my_rank, rows_per_rank, ready, epoch);
+  int rc = dsb_srw_bwd_gate_gather(
+      h_full.data_ptr(), h_full.stride(0), emb.data_ptr(), emb.stride(0), x_full.data_ptr(),
+      x_full.stride(0), read.data_ptr(), read.stride(0), dy_full.data_ptr(), dy_full.stride(0),
+      write.data_ptr(), write.stride(0), T, U, r, D, p_out.data_ptr(), dxr_out.data_ptr(),
+      ds_out.data_ptr(), p_out.stride(0), tau.data_ptr<float>(), inv_sigma.data_ptr<float>(),
+      dden.data_ptr<float>(), dtau_sum.data_ptr<float>(), dsz_sum.data_ptr<float>(), &g, &gh.g,
+      status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_bwd_gate_gather failed with code ", rc);
+}
+
 // Fused GEMM -> reduce-scatter.  `out_ptrs`: data pointers of every rank's
 // [rows_per_rank, N] fp32 buffer (index = rank), as integers.
 void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
@@ -175,5 +250,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_bwd_gate", &srw_bwd_gate);
   m.def("srw_forward", &srw_forward);
   m.def("gemm_scatter", &gemm_scatter);
+  m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
+  m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);
   m.def("peer_barrier", &peer_barrier);
 }

@@ -48,6 +48,27 @@ struct GemmSeg {
   int b_mn;     // 1: B stored [K][N] (MN-major)
 };
 
+// Fused all-gather: the A operands of a token-sharded op live in per-rank
+// "full" buffers [n_ranks * rows_per_rank, cols] in symmetric memory; every
+// rank has written only its own row block.  A gather warp in each CTA pulls
+// the other ranks' row blocks (TMA load from the peer's buffer -> shared
+// memory -> TMA store into the local buffer), then publishes a per-128-row
+// ready flag; tiles that need those rows wait for the flag (bounded).  Tiles on
+// this rank's own rows are scheduled first, so the transfer overlaps the math.
+constexpr int kMaxGatherTensors = 3;
+constexpr int kMaxRanks = 8;
+struct alignas(64) GatherParams {
+  CUtensorMap src[kMaxGatherTensors][kMaxRanks];  // rank j's full buffer (peer memory)
+  CUtensorMap dst[kMaxGatherTensors];             // this rank's full buffer
+  int cols[kMaxGatherTensors];
+  int n_tensors;
+  int n_ranks;        // <= 1 disables the gather
+  int my_rank;
+  int rows_per_rank;  // multiple of 128
+  unsigned int* ready;  // [total_rows / 128] flags in local memory, compared with `epoch`
+  unsigned int epoch;
+};
+
 template <class EpiParams>
 struct alignas(64) GemmParams {
   CUtensorMap tma_a[kMaxSeg];
@@ -59,18 +80,22 @@ struct alignas(64) GemmParams {
   int m_tiles, n_tiles;
   int n_fastest;  // tile raster: 1 = consecutive tiles walk N first
   int dbg;        // profiling only: 1 = no loads, MMAs run on whatever is in shared memory
+  int m_rot;      // tile rows are visited starting from this m-tile (own rows first)
+  GatherParams gather;
   int* status;    // device word, set non-zero on failure
   EpiParams epi;
 };
 
 constexpr int kOutBufBytes = 4096;  // one staged slab: 32 rows x 128 bytes
 
-template <int BN, int kOutBufsPerWarp, int kEpiWarps = 4>
+constexpr int kGatherPieceBytes = 128 * 64 * 2;   // 128 rows x 64 bf16
+template <int BN, int kOutBufsPerWarp, int kEpiWarps = 4, bool kGather = false>
 struct EngineSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KB
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kOutBytes = kEpiWarps * kOutBufsPerWarp * kOutBufBytes;
+  static constexpr int kGatherBytes = kGather ? 2 * kGatherPieceBytes : 0;
+  static constexpr int kOutBytes = kEpiWarps * kOutBufsPerWarp * kOutBufBytes + kGatherBytes;
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 256 /*barriers*/;
   static constexpr int kStages = (kBudget / kStageBytes) > 8 ? 8 : (kBudget / kStageBytes);
@@ -125,8 +150,8 @@ struct WarpStager {
 // m0 + 32*(warp%4) + lane and, with 8 warps, its columns the (warp/4)-th half.
 // tmem address of accumulator a, column c:  tmem_acc0 + a * BN + c.
 
-template <int BN, class Epi, int kCtas>
-__global__ void __launch_bounds__((Epi::kEpiWarps + 2) * 32, 1)
+template <int BN, class Epi, int kCtas, bool kGather = false>
+__global__ void __launch_bounds__((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32, 1)
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   // kCtas == 2: the CTA pair of a 2-CTA cluster shares a 256-row tile.  Each CTA
   // stages its own 128 rows of A and BN/2 rows of B; the leader CTA (cluster
@@ -136,9 +161,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   // on the leader's `acc_empty`.
   static_assert(kCtas == 1 || kCtas == 2, "1 or 2 CTAs per tile");
   constexpr int kBRows = BN / kCtas;  // rows of B this CTA stages
-  using Smem = EngineSmem<kBRows, Epi::kOutBufs, Epi::kEpiWarps>;
+  using Smem = EngineSmem<kBRows, Epi::kOutBufs, Epi::kEpiWarps, kGather>;
   constexpr int kEpiWarps = Epi::kEpiWarps;
-  constexpr int kTmaWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1;
+  constexpr int kTmaWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kGatherWarp = kEpiWarps + 2;
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "4 or 8 epilogue warps");
   constexpr int kNumAcc = Epi::kNumAcc;
   constexpr int kAccCols = kNumAcc * BN;
@@ -158,6 +183,8 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   uint64_t* acc_empty = bars + 2 * kStages + 2;    // [kNumBuf]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* gather_bar = bars + 2 * kStages + 6;   // [2]
+  uint8_t* gather_buf = out_stage + kEpiWarps * Epi::kOutBufs * kOutBufBytes;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -175,6 +202,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], kCtas * kEpiWarps);   // one elected arrive per epilogue warp
     }
+    if (kGather) { mbar_init(&gather_bar[0], 1); mbar_init(&gather_bar[1], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -206,10 +234,18 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
-        const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
+        int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
         const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
+        mt += p.m_rot;
+        if (mt >= p.m_tiles) mt -= p.m_tiles;
         const int m0 = mt * kTileM + static_cast<int>(rank) * kBlockM;
         const int n0 = nt * BN + static_cast<int>(rank) * kBRows;
+        if (kGather && p.gather.n_ranks > 1 && m0 < p.M &&
+            m0 / p.gather.rows_per_rank != p.gather.my_rank) {
+          // rows of another rank: wait until the gather warps have landed them here
+          if (!flag_wait_ge(p.gather.ready + m0 / 128, p.gather.epoch, abort_flag)) { ok = false; break; }
+          fence_proxy_async_global();
+        }
         for (int s = 0; s < p.n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
           for (int kt = 0; kt < sg.k_tiles; ++kt) {
@@ -326,14 +362,49 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         }
       }
     }
+  } else if (kGather && warp == kGatherWarp) {
+    // -------------------------------------------------------------- gather
+    const GatherParams& g = p.gather;
+    if (lane == 0 && g.n_ranks > 1) {
+      const int cpr = g.rows_per_rank / 128;               // 128-row chunks per rank
+      const int remote = (g.n_ranks - 1) * cpr;
+      int slot = 0;
+      uint32_t ph[2] = {0u, 0u};
+      bool ok = true;
+      for (int rc = blockIdx.x; rc < remote && ok; rc += gridDim.x) {
+        // nearer ranks first; every rank starts with a different peer
+        const int owner = (g.my_rank + 1 + rc / cpr) % g.n_ranks;
+        const int grow = owner * g.rows_per_rank + (rc % cpr) * 128;
+        for (int t = 0; t < g.n_tensors && ok; ++t) {
+          for (int c0 = 0; c0 < g.cols[t]; c0 += 64) {
+            bulk_wait_read<1>();   // the store that last used this bounce buffer has read it
+            uint8_t* b = gather_buf + slot * kGatherPieceBytes;
+            mbar_expect_tx(&gather_bar[slot], kGatherPieceBytes);
+            tma_load_2d(b, &g.src[t][owner], &gather_bar[slot], c0, grow);
+            if (!mbar_wait(&gather_bar[slot], ph[slot], abort_flag)) { ok = false; break; }
+            ph[slot] ^= 1u;
+            tma_store_2d(&g.dst[t], smem_u32(b), c0, grow);
+            bulk_commit();
+            slot ^= 1;
+          }
+        }
+        if (!ok) break;
+        bulk_wait<0>();            // the whole chunk is in local memory
+        __threadfence();
+        flag_store_release(g.ready + grow / 128, g.epoch);
+      }
+      bulk_wait<0>();
+    }
   } else {
     // ------------------------------------------------------------ epilogue
     int it = 0;
     bool ok = true;
     WarpStager stager{smem_u32(out_stage + warp * Epi::kOutBufs * kOutBufBytes), lane};
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
-      const int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
+      int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
       const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
+      mt += p.m_rot;
+      if (mt >= p.m_tiles) mt -= p.m_tiles;
       const int buf = it % kNumBuf;
       const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
       if (!mbar_wait(&acc_full[buf], use & 1, abort_flag)) { ok = false; break; }

@@ -75,6 +75,35 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+// ------------------------------------------------------------- flag words
+__device__ __forceinline__ void flag_store_release(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait until *p >= v (wrap-safe).  Same abort protocol as mbar_wait.
+__device__ __forceinline__ bool flag_wait_ge(const unsigned int* p, unsigned int v,
+                                             volatile int* abort_flag) {
+  long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    unsigned int cur;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(p) : "memory");
+    if (static_cast<int>(cur - v) >= 0) return true;
+    __nanosleep(100);
+    if ((it & 0x3f) == 0x3f) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

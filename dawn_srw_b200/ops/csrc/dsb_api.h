@@ -15,6 +15,23 @@ typedef struct DsbGate {
   float sharpness, act_threshold, act_cutoff, epsilon, max_intensity, clip_max, dead_threshold;
 } DsbGate;
 
+// Fused all-gather of the token operands of a gate kernel over `n_ranks` GPUs.
+// Tensor t (0: x, 1: h, 2: dy) lives on every rank in a "full" bf16 buffer
+// [n_ranks * rows_per_rank, cols[t]] (ld[t] elements between rows) of which
+// the rank has filled only its own row block; bufs[t] is a HOST array with the
+// n_ranks device pointers of those buffers (peer pointers for other ranks).
+// The kernel pulls the missing row blocks into bufs[t][my_rank] while it
+// computes.  `ready` is local device memory with one uint32 per 128 rows and
+// `epoch` must be larger than any value used before on that array.
+typedef struct DsbGather {
+  int n_ranks, my_rank, rows_per_rank, n_tensors;
+  const void* const* bufs[3];
+  long long ld[3];
+  int cols[3];
+  unsigned int* ready;
+  unsigned int epoch;
+} DsbGather;
+
 // C[M,N] (=|+=) alpha * row_scale[m] * (A . B^T)[m,n] + bias[n]
 //   A: a_mn == 0 -> stored [M][K] (lda >= K);  a_mn == 1 -> stored [K][M] (lda >= M)
 //   B: b_mn == 0 -> stored [N][K];             b_mn == 1 -> stored [K][N]
@@ -42,6 +59,23 @@ int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, long long ld
                      void* p_out, void* dxr_out, void* ds_out, long long ld_out, const float* tau,
                      const float* inv_sigma, const float* dden, float* dtau_sum, float* dsz_sum,
                      const DsbGate* gate /*host*/, int* status, cudaStream_t stream);
+
+// Gate kernels with the all-gather fused in (gather may be null: plain kernel).
+// h / x (/ dy) must then be this rank's full buffers.
+int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void* emb, long long lde,
+                            const void* x, long long ldx, const void* read, long long ldr, int T,
+                            int U, int r, int D, void* p_out, long long ldp, const float* tau,
+                            const float* inv_sigma, float* den_sum, float* gate_sum,
+                            unsigned char* alive, const float* unit_mask, const DsbGate* gate,
+                            const DsbGather* gather /*host*/, int* status, cudaStream_t stream);
+int dsb_srw_bwd_gate_gather(const void* h, long long ldh, const void* emb, long long lde,
+                            const void* x, long long ldx, const void* read, long long ldr,
+                            const void* dy, long long lddy, const void* write, long long ldw,
+                            int T, int U, int r, int D, void* p_out, void* dxr_out, void* ds_out,
+                            long long ld_out, const float* tau, const float* inv_sigma,
+                            const float* dden, float* dtau_sum, float* dsz_sum,
+                            const DsbGate* gate, const DsbGather* gather /*host*/, int* status,
+                            cudaStream_t stream);
 
 // One route of the SRW forward op (gate kernel + write GEMM).  `p_scratch` is
 // caller-provided scratch: bf16 [T, ldp] with ldp >= U and ldp % 8 == 0; its

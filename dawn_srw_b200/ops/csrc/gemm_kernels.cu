@@ -374,10 +374,10 @@ static int fill_operand(CUtensorMap* map, const OperandDesc& o, long long rows, 
 }
 
 // kCtas == 2 launches 2-CTA clusters (one SM pair per 256-row tile).
-template <int BN, class Epi, int kCtas>
+template <int BN, class Epi, int kCtas, bool kGather = false>
 static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
-  using Smem = EngineSmem<BN / kCtas, Epi::kOutBufs, Epi::kEpiWarps>;
-  auto kern = gemm_engine_kernel<BN, Epi, kCtas>;
+  using Smem = EngineSmem<BN / kCtas, Epi::kOutBufs, Epi::kEpiWarps, kGather>;
+  auto kern = gemm_engine_kernel<BN, Epi, kCtas, kGather>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -399,7 +399,7 @@ static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t
   const int grid = kCtas * static_cast<int>(total < units ? total : units);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((Epi::kEpiWarps + 2) * 32);
+  cfg.blockDim = dim3((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32);
   cfg.dynamicSmemBytes = Smem::kTotalBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -426,6 +426,39 @@ template <int BN, class Epi>
 static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
   if (use_cta_pairs()) return launch_engine_impl<BN, Epi, 2>(gp, stream);
   return launch_engine_impl<BN, Epi, 1>(gp, stream);
+}
+
+// Gate kernels with the all-gather of their token operands fused in (CTA pairs only).
+template <int BN, class Epi>
+static int launch_engine_gather(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
+  return launch_engine_impl<BN, Epi, 2, true>(gp, stream);
+}
+
+static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int* m_rot) {
+  memset(g, 0, sizeof(*g));
+  *m_rot = 0;
+  if (d == nullptr || d->n_ranks <= 1) return 0;
+  if (d->n_ranks > kMaxRanks || d->n_tensors < 1 || d->n_tensors > kMaxGatherTensors ||
+      d->rows_per_rank % 256 != 0 || d->n_ranks * d->rows_per_rank != total_rows ||
+      d->ready == nullptr)
+    return 700;
+  g->n_tensors = d->n_tensors;
+  g->n_ranks = d->n_ranks;
+  g->my_rank = d->my_rank;
+  g->rows_per_rank = d->rows_per_rank;
+  g->ready = d->ready;
+  g->epoch = d->epoch;
+  for (int t = 0; t < d->n_tensors; ++t) {
+    if (d->cols[t] % 64 != 0) return 701;
+    g->cols[t] = d->cols[t];
+    for (int j = 0; j < d->n_ranks; ++j) {
+      int rc = make_tmap_bf16(&g->src[t][j], d->bufs[t][j], d->cols[t], total_rows, d->ld[t], 64, 128);
+      if (rc) return 710 + rc;
+    }
+    g->dst[t] = g->src[t][d->my_rank];
+  }
+  *m_rot = d->my_rank * d->rows_per_rank / (2 * kBlockM);
+  return 0;
 }
 
 }  // namespace dsb
@@ -467,6 +500,19 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
                                 const float* tau, const float* inv_sigma, float* den_sum,
                                 float* gate_sum, unsigned char* alive, const float* unit_mask,
                                 const DsbGate* gate, int* status, cudaStream_t stream) {
+  return dsb_srw_fwd_gate_gather(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, tau,
+                                 inv_sigma, den_sum, gate_sum, alive, unit_mask, gate, nullptr,
+                                 status, stream);
+}
+
+extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void* emb,
+                                       long long lde, const void* x, long long ldx,
+                                       const void* read, long long ldr, int T, int U, int r, int D,
+                                       void* p_out, long long ldp, const float* tau,
+                                       const float* inv_sigma, float* den_sum, float* gate_sum,
+                                       unsigned char* alive, const float* unit_mask,
+                                       const DsbGate* gate, const DsbGather* gather, int* status,
+                                       cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   constexpr int BN = 128;
   GemmParams<FwdGateParams> gp;
@@ -486,6 +532,15 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
   rc = make_out_tmap(&gp.tma_out[0], p_out, T, U, ldp, 2);
   if (rc) return 300 + rc;
   gp.epi = {tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, make_gc(gate)};
+  const bool fused = gather != nullptr && gather->n_ranks > 1;
+  if (fused) {
+    if (!use_cta_pairs()) return 702;
+    rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
+    if (rc) return rc;
+    if (gate->kind == 0) return launch_engine_gather<BN, FwdGateEpi<0>>(gp, stream);
+    if (gate->kind == 1) return launch_engine_gather<BN, FwdGateEpi<1>>(gp, stream);
+    return launch_engine_gather<BN, FwdGateEpi<2>>(gp, stream);
+  }
   if (gate->kind == 0) return launch_engine<BN, FwdGateEpi<0>>(gp, stream);
   if (gate->kind == 1) return launch_engine<BN, FwdGateEpi<1>>(gp, stream);
   return launch_engine<BN, FwdGateEpi<2>>(gp, stream);
@@ -499,6 +554,20 @@ extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, l
                                 const float* inv_sigma, const float* dden, float* dtau_sum,
                                 float* dsz_sum, const DsbGate* gate, int* status,
                                 cudaStream_t stream) {
+  return dsb_srw_bwd_gate_gather(h, ldh, emb, lde, x, ldx, read, ldr, dy, lddy, write, ldw, T, U, r,
+                                 D, p_out, dxr_out, ds_out, ld_out, tau, inv_sigma, dden, dtau_sum,
+                                 dsz_sum, gate, nullptr, status, stream);
+}
+
+extern "C" int dsb_srw_bwd_gate_gather(const void* h, long long ldh, const void* emb,
+                                       long long lde, const void* x, long long ldx,
+                                       const void* read, long long ldr, const void* dy,
+                                       long long lddy, const void* write, long long ldw, int T,
+                                       int U, int r, int D, void* p_out, void* dxr_out,
+                                       void* ds_out, long long ld_out, const float* tau,
+                                       const float* inv_sigma, const float* dden, float* dtau_sum,
+                                       float* dsz_sum, const DsbGate* gate,
+                                       const DsbGather* gather, int* status, cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   constexpr int BN = 128;
   GemmParams<BwdGateParams> gp;
@@ -523,6 +592,14 @@ extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, l
   rc |= make_out_tmap(&gp.tma_out[2], ds_out, T, U, ld_out, 2);
   if (rc) return 300 + rc;
   gp.epi = {tau, inv_sigma, dden, dtau_sum, dsz_sum, make_gc(gate)};
+  if (gather != nullptr && gather->n_ranks > 1) {
+    if (!use_cta_pairs()) return 702;
+    rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
+    if (rc) return rc;
+    if (gate->kind == 0) return launch_engine_gather<BN, BwdGateEpi<0>>(gp, stream);
+    if (gate->kind == 1) return launch_engine_gather<BN, BwdGateEpi<1>>(gp, stream);
+    return launch_engine_gather<BN, BwdGateEpi<2>>(gp, stream);
+  }
   if (gate->kind == 0) return launch_engine<BN, BwdGateEpi<0>>(gp, stream);
   if (gate->kind == 1) return launch_engine<BN, BwdGateEpi<1>>(gp, stream);
   return launch_engine<BN, BwdGateEpi<2>>(gp, stream);

@@ -341,10 +341,12 @@ class CudaBackend:
     name = "sm100a"
     compute_dtype = torch.bfloat16
 
-    def __init__(self, diag_chunk: int = 12500):
+    def __init__(self, diag_chunk: int = 12500, fused_comm: bool = True):
         ext()
         self.diag_chunk = diag_chunk
         self._wcache = {}
+        self.fused_comm = fused_comm     # in-kernel all-gather / reduce-scatter when sharded
+        self._comm = {}
 
     # ---- dense ops -----------------------------------------------------
     def _w(self, w):
@@ -418,6 +420,10 @@ class CudaBackend:
         nsh = C.group_size(pctx.shard_group)
         U_tot = pctx.n_total if pctx.n_total is not None else U * nsh
         seq = bool(pctx.seq_sharded and nsh > 1)
+        if seq and self.fused_comm and unit_mask is None and not spec.has_dead_penalty \
+                and x.shape[0] % 256 == 0 and x.shape[1] % 64 == 0 and h.shape[-1] % 64 == 0 \
+                and nsh <= 8:
+            return self._srw_fused_sharded(x, h, tau_off, pool, spec, pctx, want_diag)
         if seq:
             x = C.gather_tokens(x, pctx.shard_group)
             h = C.gather_tokens(h, pctx.shard_group)
@@ -475,6 +481,55 @@ class CudaBackend:
                 lib = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec,
                                         ParallelCtx(pctx.shard_group, pctx.dp_group, pctx.n_total,
                                                     pctx.n_valid, False), True, False, unit_mask)
+                diag = lib.diag
+        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den)
+
+    def _srw_fused_sharded(self, x, h, tau_off, pool, spec, pctx, want_diag):
+        """Sequence- and pool-sharded route through the kernels with fused
+        collectives (parallel/fused_srw.py).  x/h/tau_off hold this rank's tokens."""
+        from ..parallel.fused_srw import FusedShardComm, _SRWRouteGatherFn
+        ex = pool.extra
+        U, anchor = ex["U"], ex["anchor"]
+        grp = pctx.shard_group
+        nsh = C.group_size(grp)
+        U_tot = pctx.n_total if pctx.n_total is not None else U * nsh
+        Tl, Rr, r = h.shape
+        key = (id(grp), Tl, x.shape[1], r)
+        comm = self._comm.get(key)
+        if comm is None:
+            comm = self._comm[key] = FusedShardComm(grp, x.device, Tl, x.shape[1], r)
+        x_bf = _bf16_2d(x)
+        h_bf3 = h.to(torch.bfloat16)
+        hf = h_bf3.float()
+        mu = hf @ (ex["esum"] / U_tot)
+        m2 = ((hf @ ex["gram"]) * hf).sum(-1) / U_tot
+        sd = torch.sqrt((m2 - mu * mu).clamp_min(0.0)) + 1e-8
+        tau = mu + tau_off * sd                                           # [Tl,R]
+        inv_sd = 1.0 / sd
+        # per-unit mean score over ALL tokens of the group (they share one batch)
+        hbar = C.sum_over_shards(hf.sum(dim=(0, 1)), grp) / float(Tl * nsh * Rr)
+        m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
+        ns_sum = C.sum_over_shards(C.mean_over_group(m_u.sum(), pctx.dp_group), grp)
+        ns_sq = C.sum_over_shards(C.mean_over_group((m_u * m_u).sum(), pctx.dp_group), grp)
+        mean_score = ns_sum / U_tot
+        var_score = ns_sq / U_tot - mean_score ** 2
+        lb = var_score / (mean_score ** 2 + var_score + 1e-2)
+        outs, dens = [], []
+        for ri in range(Rr):
+            tau_f = C.gather_tokens(tau[:, ri].contiguous(), grp)
+            isd_f = C.gather_tokens(inv_sd[:, ri].contiguous(), grp)
+            o, d = _SRWRouteGatherFn.apply(x_bf, _bf16_2d(h_bf3[:, ri]), tau_f, isd_f, anchor, pool,
+                                           spec, U, comm)
+            outs.append(o)
+            dens.append(d[comm.rows])
+        out = torch.stack(outs, dim=1)                                    # [Tl,R,D], normalised
+        den = torch.stack(dens, dim=1).clamp(min=1.0)
+        dead_pen = x.new_zeros(())     # gates with a dead-unit penalty take the NCCL path
+        diag = {}
+        if want_diag:
+            with torch.no_grad():
+                lib = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec, pctx,
+                                        True, False, None)
                 diag = lib.diag
         return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den)
 

@@ -1,0 +1,147 @@
+"""Sequence-sharded, pool-sharded SRW route with the collectives inside the kernels.
+
+Layout (8 GPUs = one shard group): rank k stores ``U/8`` units of every pool and
+``T/8`` tokens of the activations.  One SRW route then is
+
+  forward
+    1. each rank writes its bf16 ``x``/``h`` rows into its slice of the
+       symmetric "full" buffers; bounded barrier;
+    2. gate kernel with the all-gather fused in: gather warps pull the other
+       ranks' row blocks over NVLink (TMA from peer memory) into the local full
+       buffer while tcgen05 tiles on this rank's own tokens already run;
+       writes ``p = gate * xr`` for all tokens x local units and the partial
+       ``sum_U den_term`` per token;
+    3. the per-token denominators are summed over ranks (``[T]`` fp32, NCCL);
+    4. write GEMM with the reduce-scatter fused into its epilogue: each 32-row
+       slab of ``(p . write) / den`` is TMA-reduce-added (fp32) into the owner
+       rank's ``[T/8, D]`` buffer, locally or over NVLink.
+  backward mirrors it: ``dy`` rows are gathered by the backward gate kernel
+  together with ``x`` and ``h``; ``dx`` and ``dh`` leave through the same fused
+  reduce-scatter epilogue; pool gradients stay on the rank that owns the units.
+
+Against the reference's layout (activations replicated over the unit axis and a
+bf16 all-reduce of the output, models/dawn_spatial_v41_exp.py:579-586) this
+halves the output traffic and removes the redundant LayerNorm / router /
+attention work across the group.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+import torch.distributed as dist
+
+from ..ops.gates import GATE_GELU_Z
+from .symm import SymmWorkspace
+
+
+class FusedShardComm:
+    """Symmetric buffers + counters shared by all fused SRW calls of a model."""
+
+    def __init__(self, group, device, t_local: int, d_model: int, d_route: int):
+        self.ws = SymmWorkspace(group, device)
+        self.group = self.ws.group
+        self.rank, self.world = self.ws.rank, self.ws.world
+        if t_local % 256 != 0:
+            raise ValueError(f"tokens per rank ({t_local}) must be a multiple of 256 for the fused path")
+        self.t_local, self.t_total = t_local, t_local * self.world
+        bf, f32 = torch.bfloat16, torch.float32
+        T = self.t_total
+        self.xfull = [self.ws.alloc(f"xfull{i}", (T, d_model), bf) for i in range(2)]
+        self.hfull = [self.ws.alloc(f"hfull{i}", (T, d_route), bf) for i in range(2)]
+        self.dyfull = [self.ws.alloc(f"dyfull{i}", (T, d_model), bf) for i in range(2)]
+        self.out_rs = self.ws.alloc("out_rs", (t_local, d_model), f32)
+        self.dx_rs = self.ws.alloc("dx_rs", (t_local, d_model), f32)
+        self.dh_rs = self.ws.alloc("dh_rs", (t_local, d_route), f32)
+        self.ready = torch.zeros(T // 128, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.parity = 0
+        self.rows = slice(self.rank * t_local, (self.rank + 1) * t_local)
+
+    def next_buffers(self):
+        self.parity ^= 1
+        return self.parity
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
+class _SRWRouteGatherFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_bf, h_bf, tau_full, inv_sd_full, anchor, holder, spec, U, comm):
+        from ..ops import cuda_backend as CB
+        e, dev = CB.ext(), x_bf.device
+        st = CB.status_word(dev)
+        c: FusedShardComm = comm
+        T, Tl, D = c.t_total, c.t_local, x_bf.shape[1]
+        Up = CB._round_up(U, 8)
+        b = c.next_buffers()
+        xf, hf = c.xfull[b], c.hfull[b]
+        xf.local[c.rows].copy_(x_bf)
+        hf.local[c.rows].copy_(h_bf)
+        c.ws.barrier()                                   # every rank's rows are in place
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+        den = torch.zeros(T, dtype=torch.float32, device=dev)
+        gl = CB._gate_list(spec)
+        CB._LAUNCHES += 2
+        e.srw_fwd_gate_gather(hf.local, holder.emb[:U], xf.local, holder.read[:U], p, tau_full,
+                              inv_sd_full, den, gl, st, [xf.ptrs, hf.ptrs], c.rank, Tl, c.ready,
+                              c.next_epoch())
+        dist.all_reduce(den, group=c.group)              # [T] fp32
+        inv_den = 1.0 / den.clamp(min=1.0)
+        c.out_rs.local.zero_()
+        c.ws.barrier()                                   # every rank's target is zeroed
+        e.gemm_scatter(p[:, :U], False, holder.write[:U], True, c.out_rs.ptrs, Tl, D, 1.0, inv_den, st)
+        c.ws.barrier()                                   # every rank's contributions have landed
+        out = c.out_rs.local.clone()
+        ctx.save_for_backward(x_bf, h_bf, tau_full, inv_sd_full, den, out)
+        ctx.holder, ctx.spec, ctx.U, ctx.comm = holder, spec, U, c
+        ctx.mark_non_differentiable(den)
+        return out, den
+
+    @staticmethod
+    def backward(ctx, d_out, _d_den):
+        from ..ops import cuda_backend as CB
+        x_bf, h_bf, tau_full, inv_sd_full, den, out = ctx.saved_tensors
+        hd, spec, U, c = ctx.holder, ctx.spec, ctx.U, ctx.comm
+        e, dev = CB.ext(), x_bf.device
+        st = CB.status_word(dev)
+        T, Tl, D, r = c.t_total, c.t_local, x_bf.shape[1], h_bf.shape[1]
+        Up = CB._round_up(U, 8)
+        den_l = den[c.rows]
+        inv_den_l = 1.0 / den_l.clamp(min=1.0)
+        d_out = d_out.float()
+        b = c.next_buffers()
+        xf, hf, dyf = c.xfull[b], c.hfull[b], c.dyfull[b]
+        xf.local[c.rows].copy_(x_bf)
+        hf.local[c.rows].copy_(h_bf)
+        dyf.local[c.rows].copy_(d_out * inv_den_l[:, None])
+        dden_l = -(d_out * out).sum(-1) * inv_den_l * (den_l > 1.0)
+        dden = torch.empty(T, dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(dden, dden_l.contiguous(), group=c.group)
+        c.ws.barrier()
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+        dxr, ds = torch.empty_like(p), torch.empty_like(p)
+        dtau = torch.zeros(T, dtype=torch.float32, device=dev)
+        dsz = torch.zeros(T, dtype=torch.float32, device=dev)
+        emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
+        CB._LAUNCHES += 1
+        e.srw_bwd_gate_gather(hf.local, emb, xf.local, read, dyf.local, write, p, dxr, ds, tau_full,
+                              inv_sd_full, dden, dtau, dsz, CB._gate_list(spec), st,
+                              [xf.ptrs, hf.ptrs, dyf.ptrs], c.rank, Tl, c.ready, c.next_epoch())
+        pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
+        CB.gemm(pv, True, dyf.local, True, out=hd.g_write[:U], accumulate=True)      # p^T dy
+        CB.gemm(dxrv, True, xf.local, True, out=hd.g_read[:U], accumulate=True)      # dxr^T x
+        CB.gemm(dsv, True, hf.local, True, out=hd.g_emb[:U], accumulate=True)        # ds^T h
+        c.dx_rs.local.zero_()
+        c.dh_rs.local.zero_()
+        c.ws.barrier()
+        CB._LAUNCHES += 2
+        e.gemm_scatter(dxrv, False, read, True, c.dx_rs.ptrs, Tl, D, 1.0, None, st)   # dxr . read
+        e.gemm_scatter(dsv, False, emb, True, c.dh_rs.ptrs, Tl, r, 1.0, None, st)     # ds . emb
+        c.ws.barrier()
+        dx = c.dx_rs.local.to(torch.bfloat16)
+        dh = c.dh_rs.local.to(torch.bfloat16)
+        d_isd = dsz / (inv_sd_full * inv_sd_full) if spec.kind == GATE_GELU_Z else None
+        return dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None

@@ -94,6 +94,57 @@ def test_peer_barrier_and_fused_gemm_reduce_scatter():
     assert max(errs) < 1e-5, errs
 
 
+def _fused_vs_nccl(rank, world, version):
+    """One sequence+pool-sharded SRW op: in-kernel collectives vs NCCL collectives."""
+    from dawn_srw_b200.ops import cuda_backend as CB
+    from dawn_srw_b200.ops.backend import ParallelCtx
+    from dawn_srw_b200.ops.gates import gate_spec_for
+    from dawn_srw_b200.parallel.topology import PoolShard
+    import torch.distributed as dist
+    dev = torch.device("cuda", rank)
+    spec = gate_spec_for(version)
+    Tl, R, U, r, D = 512, 2, 300, 64, 128
+    g = torch.Generator(device=dev).manual_seed(7)             # same full tensors on every rank
+    rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+    nz = torch.nn.functional.normalize
+    emb_f, read_f, write_f = nz(rn(U, r), dim=-1), nz(rn(U, D), dim=-1), nz(rn(U, D), dim=-1)
+    x_f, h_f, off_f, w_f = rn(world * Tl, D), rn(world * Tl, R, r), rn(world * Tl, R) * 0.3 - 0.3, rn(world * Tl, R, D)
+    sh = PoolShard(rank, world)
+    lo, hi, padded = sh.slice_of(U)
+
+    def local_pool(t):
+        out = torch.zeros(padded, t.shape[1], device=dev)
+        out[: hi - lo] = t[lo:hi]
+        return out
+    rows = slice(rank * Tl, (rank + 1) * Tl)
+    pctx = ParallelCtx(shard_group=dist.group.WORLD, dp_group=None, n_total=U, n_valid=hi - lo,
+                       seq_sharded=True)
+    res = {}
+    for name, fused in (("nccl", False), ("fused", True)):
+        be = CB.CudaBackend(fused_comm=fused)
+        ps = [t.clone().requires_grad_(True) for t in
+              (local_pool(emb_f), local_pool(read_f), local_pool(write_f), x_f[rows], h_f[rows], off_f[rows])]
+        pool = be.prepare_pool(ps[0], ps[1], ps[2], spec, pctx)
+        out = be.srw(ps[3], ps[4], ps[5], pool, spec, pctx=pctx, want_diag=False)
+        ((out.out * w_f[rows]).sum() + 3.0 * out.lb).backward()
+        torch.cuda.synchronize()
+        res[name] = [out.out.detach(), out.lb.detach(), out.den.detach()] + [p.grad.clone() for p in ps]
+    CB.check_status()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+    names = ["out", "lb", "den", "demb", "dread", "dwrite", "dx", "dh", "doff"]
+    return {n: rel(a, b) for n, a, b in zip(names, res["fused"], res["nccl"])}
+
+
+@pytest.mark.parametrize("version", ["spatial-r1-v4.0.1", "spatial-r1-v3.9.4"])
+def test_fused_all_gather_and_reduce_scatter_match_nccl_path(version):
+    _need(2)
+    outs = _spawn(_fused_vs_nccl, 2, version)
+    for o in outs:
+        for k, v in o.items():
+            # same kernels and math; differences: fp32 (fused) vs bf16 (NCCL) partial sums
+            assert v < 2e-2, (k, v, o)
+
+
 def test_peer_barrier_times_out_when_a_peer_never_arrives():
     """One GPU plays a two-rank world in which the other rank's flag is never
     written: the wait runs out, the status word reports it, the context lives."""
