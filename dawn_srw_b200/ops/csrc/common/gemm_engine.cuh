@@ -81,6 +81,8 @@ struct alignas(64) GemmParams {
   int n_fastest;  // tile raster: 1 = consecutive tiles walk N first
   int dbg;        // profiling only: 1 = no loads, MMAs run on whatever is in shared memory
   int m_rot;      // tile rows are visited starting from this m-tile (own rows first)
+  int k_splits;   // > 1: the K range of segment 0 is cut into this many tiles that all
+                  // reduce-add into the same output (accumulating fp32 epilogues only)
   GatherParams gather;
   int* status;    // device word, set non-zero on failure
   EpiParams epi;
@@ -225,7 +227,11 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int mn_tiles = p.m_tiles * p.n_tiles;
+  const int k_splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int total_tiles = mn_tiles * k_splits;
+  // k-tiles of segment 0 handled by one split (the last split may get fewer)
+  const int kt_per_split = (p.seg[0].k_tiles + k_splits - 1) / k_splits;
 
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------ producer
@@ -234,8 +240,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
-        int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
-        const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
+        const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
+        int mt = p.n_fastest ? t2 / p.n_tiles : t2 % p.m_tiles;
+        const int nt = p.n_fastest ? t2 % p.n_tiles : t2 / p.m_tiles;
         mt += p.m_rot;
         if (mt >= p.m_tiles) mt -= p.m_tiles;
         const int m0 = mt * kTileM + static_cast<int>(rank) * kBlockM;
@@ -248,7 +255,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         }
         for (int s = 0; s < p.n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
-          for (int kt = 0; kt < sg.k_tiles; ++kt) {
+          const int kt_lo = k_splits > 1 ? ks * kt_per_split : 0;
+          const int kt_hi = k_splits > 1 ? min(sg.k_tiles, kt_lo + kt_per_split) : sg.k_tiles;
+          for (int kt = kt_lo; kt < kt_hi; ++kt) {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
             uint8_t* sa = smem + stage * Smem::kStageBytes;
             uint8_t* sb = sa + Smem::kABytes;
@@ -351,10 +360,16 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
           const uint32_t d_tmem = acc_base + sg.acc * BN;
           const uint32_t accum = (started >> sg.acc) & 1u;
           started |= 1u << sg.acc;
-          if (!sg.a_mn && !sg.b_mn) issue_seg(F_{}, F_{}, sg.k_tiles, d_tmem, accum);
-          else if (!sg.a_mn && sg.b_mn) issue_seg(F_{}, T_{}, sg.k_tiles, d_tmem, accum);
-          else if (sg.a_mn && !sg.b_mn) issue_seg(T_{}, F_{}, sg.k_tiles, d_tmem, accum);
-          else issue_seg(T_{}, T_{}, sg.k_tiles, d_tmem, accum);
+          int nk = sg.k_tiles;
+          if (k_splits > 1) {
+            const int ks = tile / mn_tiles;
+            nk = min(sg.k_tiles, (ks + 1) * kt_per_split) - ks * kt_per_split;
+            if (nk < 0) nk = 0;
+          }
+          if (!sg.a_mn && !sg.b_mn) issue_seg(F_{}, F_{}, nk, d_tmem, accum);
+          else if (!sg.a_mn && sg.b_mn) issue_seg(F_{}, T_{}, nk, d_tmem, accum);
+          else if (sg.a_mn && !sg.b_mn) issue_seg(T_{}, F_{}, nk, d_tmem, accum);
+          else issue_seg(T_{}, T_{}, nk, d_tmem, accum);
         }
         if (ok) {
           if (kCtas == 2) mma_commit_pair(&acc_full[buf]);
@@ -401,8 +416,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     bool ok = true;
     WarpStager stager{smem_u32(out_stage + warp * Epi::kOutBufs * kOutBufBytes), lane};
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
-      int mt = p.n_fastest ? tile / p.n_tiles : tile % p.m_tiles;
-      const int nt = p.n_fastest ? tile % p.n_tiles : tile / p.m_tiles;
+      const int t2 = tile % mn_tiles;
+      int mt = p.n_fastest ? t2 / p.n_tiles : t2 % p.m_tiles;
+      const int nt = p.n_fastest ? t2 % p.n_tiles : t2 / p.m_tiles;
       mt += p.m_rot;
       if (mt >= p.m_tiles) mt -= p.m_tiles;
       const int buf = it % kNumBuf;

@@ -485,6 +485,20 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   rc = make_out_tmap(&gp.tma_out[0], C, M, N, ldc, c_is_bf16 ? 2 : 4);
   if (rc) return 300 + rc;
   gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, block_n >> 16, 0};
+  if (accumulate && !c_is_bf16 && bias == nullptr) {
+    // few output tiles but a long K (pool gradients of a small unit shard): cut K so
+    // that every SM pair has work; the splits meet in the fp32 reduce-add epilogue
+    const int tm = use_cta_pairs() ? 2 * kBlockM : kBlockM;
+    const long long tiles = static_cast<long long>((M + tm - 1) / tm) * ((N + BN - 1) / BN);
+    const int units = sm_count() / (use_cta_pairs() ? 2 : 1);
+    const int k_tiles = gp.seg[0].k_tiles;
+    if (tiles < 2 * units && k_tiles >= 64) {
+      int want = static_cast<int>((3 * units + tiles - 1) / tiles);
+      const int max_by_k = k_tiles / 32;
+      if (want > max_by_k) want = max_by_k;
+      if (want > 1) gp.k_splits = want;
+    }
+  }
   return BN == 128 ? launch_engine<128, PlainEpi>(gp, stream)
                    : launch_engine<256, PlainEpi>(gp, stream);
 }

@@ -50,9 +50,15 @@ class FusedShardComm:
         self.xfull = [self.ws.alloc(f"xfull{i}", (T, d_model), bf) for i in range(2)]
         self.hfull = [self.ws.alloc(f"hfull{i}", (T, d_route), bf) for i in range(2)]
         self.dyfull = [self.ws.alloc(f"dyfull{i}", (T, d_model), bf) for i in range(2)]
-        self.out_rs = self.ws.alloc("out_rs", (t_local, d_model), f32)
-        self.dx_rs = self.ws.alloc("dx_rs", (t_local, d_model), f32)
-        self.dh_rs = self.ws.alloc("dh_rs", (t_local, d_route), f32)
+        # reduce-scatter targets, two of each: a buffer is cleared right after it has been
+        # consumed and next used two ops later, with at least two barriers in between, so
+        # no peer can add into it before it is zero (no "everyone has zeroed" barrier)
+        self.out_rs = [self.ws.alloc(f"out_rs{i}", (t_local, d_model), f32) for i in range(2)]
+        self.dx_rs = [self.ws.alloc(f"dx_rs{i}", (t_local, d_model), f32) for i in range(2)]
+        self.dh_rs = [self.ws.alloc(f"dh_rs{i}", (t_local, d_route), f32) for i in range(2)]
+        for b_ in self.out_rs + self.dx_rs + self.dh_rs:
+            b_.local.zero_()
+        self._rs_parity = {"out": 0, "dx": 0}
         self.ready = torch.zeros(T // 128, dtype=torch.int32, device=device)
         self.epoch = 0
         self.parity = 0
@@ -61,6 +67,10 @@ class FusedShardComm:
     def next_buffers(self):
         self.parity ^= 1
         return self.parity
+
+    def next_rs(self, which: str) -> int:
+        self._rs_parity[which] ^= 1
+        return self._rs_parity[which]
 
     def next_epoch(self) -> int:
         self.epoch += 1
@@ -90,11 +100,11 @@ class _SRWRouteGatherFn(torch.autograd.Function):
                               c.next_epoch())
         dist.all_reduce(den, group=c.group)              # [T] fp32
         inv_den = 1.0 / den.clamp(min=1.0)
-        c.out_rs.local.zero_()
-        c.ws.barrier()                                   # every rank's target is zeroed
-        e.gemm_scatter(p[:, :U], False, holder.write[:U], True, c.out_rs.ptrs, Tl, D, 1.0, inv_den, st)
+        tgt = c.out_rs[c.next_rs("out")]
+        e.gemm_scatter(p[:, :U], False, holder.write[:U], True, tgt.ptrs, Tl, D, 1.0, inv_den, st)
         c.ws.barrier()                                   # every rank's contributions have landed
-        out = c.out_rs.local.clone()
+        out = tgt.local.clone()
+        tgt.local.zero_()                                # ready for its next use, two ops from now
         ctx.save_for_backward(x_bf, h_bf, tau_full, inv_sd_full, den, out)
         ctx.holder, ctx.spec, ctx.U, ctx.comm = holder, spec, U, c
         ctx.mark_non_differentiable(den)
@@ -134,14 +144,15 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         CB.gemm(pv, True, dyf.local, True, out=hd.g_write[:U], accumulate=True)      # p^T dy
         CB.gemm(dxrv, True, xf.local, True, out=hd.g_read[:U], accumulate=True)      # dxr^T x
         CB.gemm(dsv, True, hf.local, True, out=hd.g_emb[:U], accumulate=True)        # ds^T h
-        c.dx_rs.local.zero_()
-        c.dh_rs.local.zero_()
-        c.ws.barrier()
+        bi = c.next_rs("dx")
+        dxt, dht = c.dx_rs[bi], c.dh_rs[bi]
         CB._LAUNCHES += 2
-        e.gemm_scatter(dxrv, False, read, True, c.dx_rs.ptrs, Tl, D, 1.0, None, st)   # dxr . read
-        e.gemm_scatter(dsv, False, emb, True, c.dh_rs.ptrs, Tl, r, 1.0, None, st)     # ds . emb
+        e.gemm_scatter(dxrv, False, read, True, dxt.ptrs, Tl, D, 1.0, None, st)       # dxr . read
+        e.gemm_scatter(dsv, False, emb, True, dht.ptrs, Tl, r, 1.0, None, st)         # ds . emb
         c.ws.barrier()
-        dx = c.dx_rs.local.to(torch.bfloat16)
-        dh = c.dh_rs.local.to(torch.bfloat16)
+        dx = dxt.local.to(torch.bfloat16)
+        dh = dht.local.to(torch.bfloat16)
+        dxt.local.zero_()
+        dht.local.zero_()
         d_isd = dsz / (inv_sd_full * inv_sd_full) if spec.kind == GATE_GELU_Z else None
         return dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None

@@ -49,6 +49,12 @@ def test_gemm_epilogue_options(cb):
     # a second accumulation into the same buffer adds again
     cb.gemm(A, False, B, False, out=acc, accumulate=True)
     assert _rel(acc, 2 * (A.float() @ B.float().t()) + 1.0) < 1e-5
+    # few output tiles with a long K: the launcher cuts K and the splits meet in the reduce-add
+    A2 = torch.randn(8192, 304, device=dev).bfloat16()      # stored [K, M]
+    B2 = torch.randn(8192, 264, device=dev).bfloat16()      # stored [K, N]
+    acc2 = torch.full((304, 264), 0.5, device=dev)
+    cb.gemm(A2, True, B2, True, out=acc2, accumulate=True)
+    assert _rel(acc2, A2.float().t() @ B2.float() + 0.5) < 1e-5
     cb.check_status()
 
 
