@@ -47,6 +47,9 @@ def parse():
     ap.add_argument("--batch-per-gpu", type=int, default=0, help="sequences per GPU per step")
     ap.add_argument("--parallelism", default="pool", choices=["pool", "dp"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile", metavar="FILE",
+                    help="after the timed runs, profile one more step with torch.profiler and "
+                         "write the per-kernel device-time table of rank 0 to FILE")
     return ap.parse_args()
 
 
@@ -210,6 +213,21 @@ def main():
         e2e_s = time.perf_counter() - t0
         h2d = sum(x.numel() * x.element_size() for x in host_batches[0])
         e2e = (e2e_s, h2d, 4)
+
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            trainer.train_step(*dev_batches[0])
+            torch.cuda.synchronize()
+        if topo.is_main:
+            rows = sorted(((e.key, e.device_time_total / 1e3, e.count) for e in prof.key_averages()
+                           if e.device_time_total > 0), key=lambda r: -r[1])
+            with open(args.profile, "w") as f:
+                f.write(f"# one training step, rank 0 of {world}; total device time "
+                        f"{sum(r[1] for r in rows):.1f} ms\n")
+                for k, t_ms, n in rows[:40]:
+                    f.write(f"{t_ms:10.2f} ms {n:6d}x  {k[:120]}\n")
 
     vals = torch.tensor([ms, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
     if world > 1:
