@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "dsb_api.h"
+#include "dsb_api_ops.h"
 
 namespace {
 
@@ -242,6 +243,83 @@ void peer_barrier(const Tensor& pads_dev, int64_t rank, int64_t world, int64_t e
   TORCH_CHECK(rc == 0, "dsb_peer_barrier failed with code ", rc);
 }
 
+std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kFloat32 && x.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = x.size(0), D = x.size(1);
+  auto y = torch::empty({T, D}, x.options().dtype(torch::kBFloat16));
+  auto mean = torch::empty({T}, x.options());
+  auto rstd = torch::empty({T}, x.options());
+  TORCH_CHECK(dsb_layernorm_fwd(x.data_ptr<float>(), w.data_ptr<float>(), b.data_ptr<float>(),
+                                y.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), T, D,
+                                eps, cur_stream()) == 0);
+  return {y, mean, rstd};
+}
+
+std::vector<Tensor> layernorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w,
+                                  const Tensor& mean, const Tensor& rstd) {
+  TORCH_CHECK(dy.scalar_type() == torch::kBFloat16 && dy.is_contiguous() && x.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = x.size(0), D = x.size(1);
+  auto dx = torch::empty_like(x);
+  auto dw = torch::zeros({D}, x.options());
+  auto db = torch::zeros({D}, x.options());
+  TORCH_CHECK(dsb_layernorm_bwd(dy.data_ptr(), x.data_ptr<float>(), w.data_ptr<float>(),
+                                mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                                dx.data_ptr<float>(), dw.data_ptr<float>(), db.data_ptr<float>(), T,
+                                D, cur_stream()) == 0);
+  return {dx, dw, db};
+}
+
+void ce_fwd(const Tensor& logits, const Tensor& labels, int64_t V, Tensor& lse, Tensor& lab,
+            Tensor& pred) {
+  TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 &&
+              labels.scalar_type() == torch::kInt64 && labels.is_contiguous());
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(dsb_ce_fwd(logits.data_ptr<float>(), logits.stride(0),
+                         reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                         logits.size(0), V, lse.data_ptr<float>(), lab.data_ptr<float>(),
+                         reinterpret_cast<long long*>(pred.data_ptr<int64_t>()), cur_stream()) == 0);
+}
+
+void ce_bwd(const Tensor& logits, const Tensor& labels, const Tensor& lse, const Tensor& scale,
+            int64_t V, Tensor& dl) {
+  TORCH_CHECK(logits.scalar_type() == torch::kFloat32 && logits.stride(1) == 1 &&
+              dl.scalar_type() == torch::kBFloat16 && dl.stride(1) == 1);
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(dsb_ce_bwd(logits.data_ptr<float>(), logits.stride(0),
+                         reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                         lse.data_ptr<float>(), scale.data_ptr<float>(), logits.size(0), V,
+                         dl.data_ptr(), dl.stride(0), cur_stream()) == 0);
+}
+
+void adamw_multi(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> exp_avg,
+                 std::vector<Tensor> exp_avg_sq, const Tensor& clip_scale, double lr, double b1,
+                 double b2, double eps, double wd, double bc1, double bc2) {
+  for (size_t i = 0; i < params.size(); ++i) {
+    auto& p = params[i];
+    TORCH_CHECK(p.is_cuda() && p.scalar_type() == torch::kFloat32 && p.is_contiguous() &&
+                grads[i].is_contiguous() && grads[i].scalar_type() == torch::kFloat32);
+    const c10::cuda::CUDAGuard guard(p.device());
+    TORCH_CHECK(dsb_adamw(p.data_ptr<float>(), grads[i].data_ptr<float>(),
+                          exp_avg[i].data_ptr<float>(), exp_avg_sq[i].data_ptr<float>(), p.numel(),
+                          clip_scale.data_ptr<float>(), lr, b1, b2, eps, wd, bc1, bc2,
+                          cur_stream()) == 0);
+  }
+}
+
+Tensor grad_sq_norm(std::vector<Tensor> grads) {
+  TORCH_CHECK(!grads.empty());
+  const c10::cuda::CUDAGuard guard(grads[0].device());
+  auto out = torch::zeros({}, grads[0].options().dtype(torch::kFloat32));
+  for (auto& g : grads) {
+    TORCH_CHECK(g.scalar_type() == torch::kFloat32 && g.is_contiguous());
+    TORCH_CHECK(dsb_sqnorm_accumulate(g.data_ptr<float>(), g.numel(), out.data_ptr<float>(),
+                                      cur_stream()) == 0);
+  }
+  return out;
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -250,6 +328,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_bwd_gate", &srw_bwd_gate);
   m.def("srw_forward", &srw_forward);
   m.def("gemm_scatter", &gemm_scatter);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("ce_fwd", &ce_fwd);
+  m.def("ce_bwd", &ce_bwd);
+  m.def("adamw_multi", &adamw_multi);
+  m.def("grad_sq_norm", &grad_sq_norm);
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
   m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);
   m.def("peer_barrier", &peer_barrier);

@@ -1,0 +1,33 @@
+// C ABI of the memory-bound kernels (see elementwise_kernels.cu).  Device
+// pointers; asynchronous on `stream`; return 0 on a successful launch.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// y = (x - mean) * rstd * w + b, eps inside the sqrt; x fp32 [T,D], y bf16 [T,D].
+int dsb_layernorm_fwd(const float* x, const float* w, const float* b, void* y_bf16, float* mean,
+                      float* rstd, int T, int D, float eps, cudaStream_t stream);
+// dx fp32 [T,D]; dw, db fp32 [D] are accumulated into (zero them first).
+int dsb_layernorm_bwd(const void* dy_bf16, const float* x, const float* w, const float* mean,
+                      const float* rstd, float* dx, float* dw, float* db, int T, int D,
+                      cudaStream_t stream);
+// Row statistics of fp32 logits [R, ld] with V valid columns: logsumexp, the
+// label's logit (labels < 0 read column 0) and the arg-max.
+int dsb_ce_fwd(const float* logits, long long ld, const long long* labels, int R, int V, float* lse,
+               float* label_logit, long long* argmax, cudaStream_t stream);
+// dl = scale[row] * (softmax - onehot) as bf16 [R, ldo] (columns V..ldo zeroed).
+int dsb_ce_bwd(const float* logits, long long ld, const long long* labels, const float* lse,
+               const float* scale, int R, int V, void* dl_bf16, long long ldo, cudaStream_t stream);
+// AdamW step on one tensor; the global-norm clip factor is read from device memory.
+int dsb_adamw(float* p, const float* g, float* m, float* v, long long n, const float* clip_scale,
+              float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+              cudaStream_t stream);
+// out[0] += sum(g^2)
+int dsb_sqnorm_accumulate(const float* g, long long n, float* out, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,255 @@
+// Memory-bound kernels around the GEMMs: LayerNorm forward/backward (bf16 out),
+// row-wise softmax cross-entropy statistics and gradient for the chunked tied
+// LM head, and the AdamW update with the clip factor read from device memory.
+// Reference math: LayerNorm eps 1e-6, population variance
+// (models/dawn_spatial_v41_exp.py:321-324); CE on shifted labels (:1642-1668);
+// optimizer chain (scripts/train_jax.py:2083-2089).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "dsb_api_ops.h"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per row.  x fp32 [T, D]; y bf16 [T, D]; mean/rstd fp32 [T].
+__global__ void ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                              const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                              float* __restrict__ mean, float* __restrict__ rstd, int T, int D,
+                              float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const float* xr = x + static_cast<size_t>(row) * D;
+  float s = 0.f;
+  for (int i = lane; i < D; i += 32) s += xr[i];
+  const float mu = warp_sum(s) / D;
+  float q = 0.f;
+  for (int i = lane; i < D; i += 32) { const float d = xr[i] - mu; q += d * d; }
+  const float rs = rsqrtf(warp_sum(q) / D + eps);
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * D;
+  for (int i = lane; i < D; i += 32) yr[i] = __float2bfloat16((xr[i] - mu) * rs * w[i] + b[i]);
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+}
+
+// dx fp32 [T, D]; dw/db fp32 [D] accumulated with atomics (must be zeroed).
+__global__ void ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                              const float* __restrict__ w, const float* __restrict__ mean,
+                              const float* __restrict__ rstd, float* __restrict__ dx,
+                              float* __restrict__ dw, float* __restrict__ db, int T, int D,
+                              int rows_per_block) {
+  extern __shared__ float sh[];  // [2 * D] partial dw, db of this block
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) sh[i] = 0.f;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const int row0 = blockIdx.x * rows_per_block;
+  for (int rr = warp; rr < rows_per_block; rr += nwarp) {
+    const int row = row0 + rr;
+    if (row >= T) break;
+    const float mu = mean[row], rs = rstd[row];
+    const float* xr = x + static_cast<size_t>(row) * D;
+    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * D;
+    float s1 = 0.f, s2 = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float g = __bfloat162float(dyr[i]) * w[i];
+      const float xh = (xr[i] - mu) * rs;
+      s1 += g;
+      s2 += g * xh;
+    }
+    s1 = warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    float* dxr = dx + static_cast<size_t>(row) * D;
+    for (int i = lane; i < D; i += 32) {
+      const float d = __bfloat162float(dyr[i]);
+      const float xh = (xr[i] - mu) * rs;
+      dxr[i] = rs * (d * w[i] - s1 - xh * s2);
+      atomicAdd(&sh[i], d * xh);
+      atomicAdd(&sh[D + i], d);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    atomicAdd(&dw[i], sh[i]);
+    atomicAdd(&db[i], sh[D + i]);
+  }
+}
+
+// One block per row of logits [R, ld] (fp32, V valid columns).
+__global__ void ce_fwd_kernel(const float* __restrict__ logits, long long ld,
+                              const long long* __restrict__ labels, int V, float* __restrict__ lse,
+                              float* __restrict__ label_logit, long long* __restrict__ argmax) {
+  const int row = blockIdx.x;
+  const float* lr = logits + row * ld;
+  float m = -FLT_MAX;
+  int mi = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = lr[i];
+    if (v > m) { m = v; mi = i; }
+  }
+  __shared__ float sm[32];
+  __shared__ int si[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+    if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+  }
+  if (lane == 0) { sm[warp] = m; si[warp] = mi; }
+  __syncthreads();
+  if (warp == 0) {
+    m = lane < nwarp ? sm[lane] : -FLT_MAX;
+    mi = lane < nwarp ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+      if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+    }
+    if (lane == 0) { sm[0] = m; si[0] = mi; }
+  }
+  __syncthreads();
+  m = sm[0];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) s += __expf(lr[i] - m);
+  s = warp_sum(s);
+  __shared__ float ss[32];
+  if (lane == 0) ss[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int k = 0; k < nwarp; ++k) t += ss[k];
+    lse[row] = m + logf(t);
+    long long lab = labels[row];
+    if (lab < 0) lab = 0;
+    label_logit[row] = lr[lab];
+    argmax[row] = si[0];
+  }
+}
+
+// dl[row, i] = scale[row] * (softmax(logits[row])[i] - [i == label]) as bf16 [R, ldo].
+__global__ void ce_bwd_kernel(const float* __restrict__ logits, long long ld,
+                              const long long* __restrict__ labels, const float* __restrict__ lse,
+                              const float* __restrict__ scale, int V, __nv_bfloat16* __restrict__ dl,
+                              long long ldo) {
+  const int row = blockIdx.x;
+  const float* lr = logits + row * ld;
+  __nv_bfloat16* dr = dl + row * ldo;
+  const float l = lse[row], sc = scale[row];
+  long long lab = labels[row];
+  if (lab < 0) lab = 0;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = __expf(lr[i] - l);
+    if (i == lab) v -= 1.f;
+    dr[i] = __float2bfloat16(v * sc);
+  }
+  for (long long i = V + threadIdx.x; i < ldo; i += blockDim.x) dr[i] = __float2bfloat16(0.f);
+}
+
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v, long long n,
+                             const float* __restrict__ clip_scale, float lr, float b1, float b2,
+                             float eps, float wd, float bc1, float bc2) {
+  const float cs = *clip_scale;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const float gi = g[i] * cs;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float pi = p[i];
+    const float upd = (mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * pi;
+    p[i] = pi - lr * upd;
+  }
+}
+
+// out[0] += sum(g^2)
+__global__ void sqnorm_kernel(const float* __restrict__ g, long long n, float* __restrict__ out) {
+  float s = 0.f;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += stride) {
+    const float v = g[i];
+    s += v * v;
+  }
+  s = warp_sum(s);
+  __shared__ float sh[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sh[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int k = 0; k < (blockDim.x >> 5); ++k) t += sh[k];
+    atomicAdd(out, t);
+  }
+}
+
+inline int grid_for(long long n, int block, int cap) {
+  long long g = (n + block - 1) / block;
+  return static_cast<int>(g < cap ? (g < 1 ? 1 : g) : cap);
+}
+
+}  // namespace
+
+extern "C" int dsb_layernorm_fwd(const float* x, const float* w, const float* b, void* y_bf16,
+                                 float* mean, float* rstd, int T, int D, float eps,
+                                 cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int warps = 8;
+  ln_fwd_kernel<<<(T + warps - 1) / warps, warps * 32, 0, stream>>>(
+      x, w, b, reinterpret_cast<__nv_bfloat16*>(y_bf16), mean, rstd, T, D, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_layernorm_bwd(const void* dy_bf16, const float* x, const float* w,
+                                 const float* mean, const float* rstd, float* dx, float* dw,
+                                 float* db, int T, int D, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const int rows_per_block = 64;
+  const int blocks = (T + rows_per_block - 1) / rows_per_block;
+  ln_bwd_kernel<<<blocks, 256, 2 * D * sizeof(float), stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy_bf16), x, w, mean, rstd, dx, dw, db, T, D,
+      rows_per_block);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_ce_fwd(const float* logits, long long ld, const long long* labels, int R, int V,
+                          float* lse, float* label_logit, long long* argmax, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  ce_fwd_kernel<<<R, 256, 0, stream>>>(logits, ld, labels, V, lse, label_logit, argmax);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_ce_bwd(const float* logits, long long ld, const long long* labels,
+                          const float* lse, const float* scale, int R, int V, void* dl_bf16,
+                          long long ldo, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  ce_bwd_kernel<<<R, 256, 0, stream>>>(logits, ld, labels, lse, scale, V,
+                                       reinterpret_cast<__nv_bfloat16*>(dl_bf16), ldo);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_adamw(float* p, const float* g, float* m, float* v, long long n,
+                         const float* clip_scale, float lr, float b1, float b2, float eps, float wd,
+                         float bc1, float bc2, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  adamw_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, stream>>>(p, g, m, v, n, clip_scale, lr, b1,
+                                                               b2, eps, wd, bc1, bc2);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_sqnorm_accumulate(const float* g, long long n, float* out,
+                                     cudaStream_t stream) {
+  if (n <= 0) return 0;
+  sqnorm_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(g, n, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}

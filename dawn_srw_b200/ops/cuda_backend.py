@@ -142,6 +142,26 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db, None, None
 
 
+class _LayerNormFn(torch.autograd.Function):
+    """LayerNorm (eps 1e-6, population variance) with bf16 output: the only
+    consumers of a normed activation are bf16 GEMM operands."""
+    @staticmethod
+    def forward(ctx, x, w, b):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).float().contiguous()
+        y, mean, rstd = ext().layernorm_fwd(x2, w, b, 1e-6)
+        ctx.save_for_backward(x2, w, mean, rstd)
+        ctx.shape, ctx.x_dtype = shp, x.dtype
+        return y.reshape(shp)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, mean, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(x2.shape).to(torch.bfloat16).contiguous()
+        dx, dw, db = ext().layernorm_bwd(dy2, x2, w, mean, rstd)
+        return dx.reshape(ctx.shape).to(ctx.x_dtype), dw, db
+
+
 # ---------------------------------------------------------------------------
 class CudaPool(PreparedPool):
     pass
@@ -283,12 +303,12 @@ class _LMHeadCEFn(torch.autograd.Function):
         lab = torch.empty(T, dtype=torch.float32, device=x.device)
         pred = torch.empty(T, dtype=torch.long, device=x.device)
         safe = labels.clamp(min=0)
+        V = emb_bf.shape[0]
+        e = ext()
         for a in range(0, T, _LMHeadCEFn.CHUNK):
             b = min(a + _LMHeadCEFn.CHUNK, T)
             lg = gemm(xb[a:b], False, emb_bf, False, out_dtype=torch.float32)
-            lse[a:b] = torch.logsumexp(lg, dim=-1)
-            lab[a:b] = lg.gather(-1, safe[a:b, None]).squeeze(-1)
-            pred[a:b] = lg.argmax(-1)
+            e.ce_fwd(lg, safe[a:b].contiguous(), V, lse[a:b], lab[a:b], pred[a:b])
         ctx.save_for_backward(xb, emb_bf, labels, lse)
         ctx.x_dtype = x.dtype
         ctx.mark_non_differentiable(pred)
@@ -302,12 +322,15 @@ class _LMHeadCEFn(torch.autograd.Function):
         dx = torch.empty(T, xb.shape[1], dtype=ctx.x_dtype, device=xb.device)
         demb = torch.zeros(V, emb_bf.shape[1], dtype=torch.float32, device=xb.device)
         safe = labels.clamp(min=0)
+        e = ext()
+        scale = d_nll.float().contiguous()
+        ldo = _round_up(V, 8)
         for a in range(0, T, _LMHeadCEFn.CHUNK):
             b = min(a + _LMHeadCEFn.CHUNK, T)
             lg = gemm(xb[a:b], False, emb_bf, False, out_dtype=torch.float32)
-            dl = torch.exp(lg - lse[a:b, None])
-            dl.scatter_add_(-1, safe[a:b, None], -torch.ones_like(dl[:, :1]))
-            dl = _bf16_2d(dl * d_nll[a:b, None])
+            dl_buf = torch.empty(b - a, ldo, dtype=torch.bfloat16, device=xb.device)
+            e.ce_bwd(lg, safe[a:b].contiguous(), lse[a:b], scale[a:b], V, dl_buf)
+            dl = dl_buf[:, :V]
             gemm(dl, False, emb_bf, True, out=dx[a:b])                         # dl . E
             gemm(dl, True, xb[a:b], True, out=demb, accumulate=True)           # dl^T x
         return dx, demb, None, None
@@ -318,8 +341,12 @@ def fused_adamw(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps,
     """Multi-tensor AdamW step with the clip factor applied on the fly
     (``clip_scale`` is a device scalar so no host sync is needed)."""
     e = ext()
-    if hasattr(e, "adamw_multi"):
-        e.adamw_multi(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps, wd, bc1, bc2)
+    if hasattr(e, "adamw_multi") and all(p.dtype == torch.float32 and p.is_contiguous() for p in params):
+        global _LAUNCHES
+        _LAUNCHES += len(params)
+        cs = clip_scale.detach().float().reshape(1).contiguous()
+        e.adamw_multi([p.data for p in params], [g.float().contiguous() for g in grads], exp_avg,
+                      exp_avg_sq, cs, lr, b1, b2, eps, wd, bc1, bc2)
         return
     g = torch._foreach_mul(grads, clip_scale)
     torch._foreach_mul_(exp_avg, b1)
@@ -334,6 +361,11 @@ def fused_adamw(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps,
     if wd != 0.0:
         torch._foreach_add_(upd, params, alpha=wd)
     torch._foreach_add_(params, upd, alpha=-lr)
+
+
+def grad_sq_norm(grads) -> torch.Tensor:
+    """sum of squares over a list of fp32 gradient tensors (one pass each)."""
+    return ext().grad_sq_norm([g.float().contiguous() for g in grads])
 
 
 # ---------------------------------------------------------------------------
@@ -359,7 +391,7 @@ class CudaBackend:
         return hit[1]
 
     def layer_norm(self, x, w, b):
-        return F.layer_norm(x.float(), (x.shape[-1],), w, b, 1e-6)
+        return _LayerNormFn.apply(x, w, b)
 
     def linear(self, x, w, b=None):
         n = w.shape[0]

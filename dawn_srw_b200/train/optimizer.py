@@ -116,8 +116,13 @@ class DawnAdamW:
             self._acc, self.micro = None, 0
         if self.grad_sync is not None:
             grads = self.grad_sync.reduce(self.named, grads)
-        sq = self.grad_sync.global_sq_norm(self.named, grads) if self.grad_sync is not None \
-            else torch.stack([g.float().square().sum() for g in grads]).sum()
+        if self.grad_sync is not None:
+            sq = self.grad_sync.global_sq_norm(self.named, grads)
+        elif self.fused:
+            from ..ops.cuda_backend import grad_sq_norm
+            sq = grad_sq_norm(grads)
+        else:
+            sq = torch.stack([g.float().square().sum() for g in grads]).sum()
         norm = sq.sqrt()
         self.last_grad_norm = norm
         clip_scale = self.clip_norm / torch.clamp(norm, min=self.clip_norm)

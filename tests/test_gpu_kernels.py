@@ -138,6 +138,63 @@ def test_srw_op_forward_backward_against_fp32_oracle(cb, version, dims):
     cb.check_status()
 
 
+def test_layernorm_kernel(cb):
+    from dawn_srw_b200.ops import reference as R
+    dev = torch.device("cuda")
+    for T, D in ((300, 384), (129, 1280)):
+        x = (torch.randn(T, D, device=dev) * 3 + 1).requires_grad_(True)
+        w = torch.randn(D, device=dev).requires_grad_(True)
+        b = torch.randn(D, device=dev).requires_grad_(True)
+        y = cb._LayerNormFn.apply(x, w, b)
+        assert y.dtype == torch.bfloat16
+        gy = torch.randn(T, D, device=dev).bfloat16()
+        y.backward(gy)
+        x2, w2, b2 = (t.detach().clone().requires_grad_(True) for t in (x, w, b))
+        y2 = R.layer_norm(x2, w2, b2)
+        y2.backward(gy.float())
+        assert _rel(y, y2) < 4e-3
+        assert _rel(x.grad, x2.grad) < 1e-4 and _rel(w.grad, w2.grad) < 1e-4 and _rel(b.grad, b2.grad) < 1e-4
+
+
+def test_lm_head_cross_entropy(cb):
+    from dawn_srw_b200.ops import reference as R
+    dev = torch.device("cuda")
+    be = cb.CudaBackend()
+    B, S, D, V = 3, 40, 128, 1003
+    x = torch.randn(B, S, D, device=dev).bfloat16().float().requires_grad_(True)
+    emb = (torch.randn(V, D, device=dev) * 0.1).bfloat16().float().requires_grad_(True)
+    labels = torch.randint(0, V, (B, S), device=dev)
+    labels[0, 5:9] = -100
+    loss, per_tok, correct, nvalid, vmask = be.lm_head_ce(x, emb, labels)
+    loss.backward()
+    x2, emb2 = x.detach().clone().requires_grad_(True), emb.detach().clone().requires_grad_(True)
+    l2, pt2, c2, n2, _ = R.lm_head_ce(x2, emb2, labels)
+    l2.backward()
+    assert abs(float(loss) - float(l2)) < 2e-3 and int(nvalid) == int(n2) and int(correct) == int(c2)
+    assert _rel(per_tok, pt2) < 2e-3
+    assert _rel(x.grad, x2.grad) < 1e-2 and _rel(emb.grad, emb2.grad) < 1e-2
+
+
+def test_fused_adamw_and_grad_norm(cb):
+    from dawn_srw_b200.train.optimizer import DawnAdamW
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    shapes = [(130, 70), (70,), (1000, 33)]
+    names = ["router.proj_know.weight", "router.proj_know.bias", "neuron_pool.know_read"]
+    pa = [torch.nn.Parameter(torch.randn(*s, device=dev)) for s in shapes]
+    pb = [torch.nn.Parameter(p.detach().clone()) for p in pa]
+    oa = DawnAdamW(list(zip(names, pa)), lr=1e-2, fused=True)
+    ob = DawnAdamW(list(zip(names, pb)), lr=1e-2, fused=False)
+    for _ in range(3):
+        gs = [torch.randn(*s, device=dev) * 2 for s in shapes]
+        for p, q, g in zip(pa, pb, gs):
+            p.grad, q.grad = g.clone(), g.clone()
+        oa.step(), ob.step()
+    assert abs(float(oa.last_grad_norm) - float(ob.last_grad_norm)) < 1e-3
+    for p, q in zip(pa, pb):
+        assert torch.allclose(p, q, atol=2e-6)
+
+
 def test_tiny_model_matches_reference_backend_and_trains(cb):
     from dawn_srw_b200.models.dawn import DAWN
     from dawn_srw_b200.ops.backend import ReferenceBackend
