@@ -99,10 +99,10 @@ struct EngineSmem {
   static constexpr int kGatherBytes = kGather ? 2 * kGatherPieceBytes : 0;
   static constexpr int kOutBytes = kEpiWarps * kOutBufsPerWarp * kOutBufBytes + kGatherBytes;
   static constexpr int kMaxSmem = 227 * 1024;
-  static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 256 /*barriers*/;
+  static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 512 /*barriers*/;
   static constexpr int kStages = (kBudget / kStageBytes) > 8 ? 8 : (kBudget / kStageBytes);
   static constexpr int kTileBytes = kStages * kStageBytes;
-  static constexpr int kTotalBytes = kTileBytes + kOutBytes + 1024 + 256;
+  static constexpr int kTotalBytes = kTileBytes + kOutBytes + 1024 + 512;
   static_assert(kStages >= 2, "not enough shared memory for a pipeline");
 };
 
@@ -139,18 +139,63 @@ struct WarpStager {
   }
 };
 
+// Accumulator hand-off between the MMA issuer and the epilogue warps.  Every
+// accumulator `a` of a tile has Epi::acc_bufs(a) TMEM buffers (1 or 2) and its
+// own full/empty barrier pair, so a policy can read (and free) one accumulator
+// while the tensor core still works on another one of the same tile, and an
+// accumulator with two buffers lets the next tile start while this tile's
+// epilogue runs.  Per tile every epilogue warp must wait() and release() each
+// accumulator exactly once (skip() does both without reading).
+template <int BN, class Epi, int kCtas>
+struct AccCtl {
+  uint64_t* full;    // [kNumAcc][2]
+  uint64_t* empty;   // [kNumAcc][2]
+  uint32_t tmem_lanes;  // TMEM base address with this warp's lane offset
+  int it;               // tiles processed so far by this CTA
+  int lane;
+  volatile int* abort_flag;
+  bool ok;
+
+  __device__ __forceinline__ static constexpr int col_off(int a) {
+    int c = 0;
+    for (int b = 0; b < a; ++b) c += Epi::acc_bufs(b) * BN;
+    return c;
+  }
+  // Wait until accumulator `a` of this tile is complete; returns its TMEM address.
+  __device__ __forceinline__ uint32_t wait(int a) {
+    const int nb = Epi::acc_bufs(a), j = it % nb;
+    const uint32_t use = static_cast<uint32_t>(it / nb);
+    if (ok && !mbar_wait(&full[a * 2 + j], use & 1, abort_flag)) ok = false;
+    tc_fence_after();
+    return tmem_lanes + col_off(a) + j * BN;
+  }
+  // This warp is done reading accumulator `a` of this tile.
+  __device__ __forceinline__ void release(int a) {
+    const int nb = Epi::acc_bufs(a), j = it % nb;
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      if (kCtas == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&empty[a * 2 + j]), 0));
+      else mbar_arrive(&empty[a * 2 + j]);
+    }
+  }
+  __device__ __forceinline__ void skip() {
+#pragma unroll
+    for (int a = 0; a < Epi::kNumAcc; ++a) { wait(a); release(a); }
+  }
+};
+
 // Epilogue policy contract:
 //   static constexpr int kNumAcc;
 //   struct Params;
 //   static constexpr int kNumOut;    // output tensor maps used
 //   static constexpr int kOutBufs;   // staging buffers per epilogue warp
 //   static constexpr int kEpiWarps;  // 4 or 8
+//   static constexpr int acc_bufs(int a);   // TMEM buffers of accumulator a (1 or 2)
 //   __device__ static void run(const Params&, const CUtensorMap* out_maps, WarpStager&,
-//                              int m0, int n0, int M, int N,
-//                              uint32_t tmem_acc0 /*lane bits set*/, int warp, int lane);
+//                              AccCtl&, int m0, int n0, int M, int N, int warp, int lane);
 // `warp` is the epilogue warp index (0..kEpiWarps-1); its rows are
 // m0 + 32*(warp%4) + lane and, with 8 warps, its columns the (warp/4)-th half.
-// tmem address of accumulator a, column c:  tmem_acc0 + a * BN + c.
 
 template <int BN, class Epi, int kCtas, bool kGather = false>
 __global__ void __launch_bounds__((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32, 1)
@@ -168,9 +213,8 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   constexpr int kTmaWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kGatherWarp = kEpiWarps + 2;
   static_assert(kEpiWarps == 4 || kEpiWarps == 8, "4 or 8 epilogue warps");
   constexpr int kNumAcc = Epi::kNumAcc;
-  constexpr int kAccCols = kNumAcc * BN;
-  constexpr int kNumBuf = (2 * kAccCols <= kTmemCols) ? 2 : 1;
-  static_assert(kAccCols <= kTmemCols, "accumulators exceed TMEM");
+  using Ctl = AccCtl<BN, Epi, kCtas>;
+  static_assert(Ctl::col_off(kNumAcc) <= kTmemCols, "accumulators exceed TMEM");
   constexpr int kStages = Smem::kStages;
   constexpr int kTileM = kBlockM * kCtas;
 
@@ -181,11 +225,11 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Smem::kOutBytes);
   uint64_t* full_bar = bars;                       // [kStages]
   uint64_t* empty_bar = bars + kStages;            // [kStages]
-  uint64_t* acc_full = bars + 2 * kStages;         // [kNumBuf]
-  uint64_t* acc_empty = bars + 2 * kStages + 2;    // [kNumBuf]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  uint64_t* acc_full = bars + 2 * kStages;         // [kMaxSeg][2]
+  uint64_t* acc_empty = bars + 2 * kStages + 6;    // [kMaxSeg][2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint64_t* gather_bar = bars + 2 * kStages + 6;   // [2]
+  uint64_t* gather_bar = bars + 2 * kStages + 14;  // [2]
   uint8_t* gather_buf = out_stage + kEpiWarps * Epi::kOutBufs * kOutBufBytes;
 
   const int warp = threadIdx.x >> 5;
@@ -200,7 +244,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
     }
-    for (int i = 0; i < kNumBuf; ++i) {
+    for (int i = 0; i < 2 * kMaxSeg; ++i) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], kCtas * kEpiWarps);   // one elected arrive per epilogue warp
     }
@@ -349,31 +393,28 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       using T_ = std::true_type;
       using F_ = std::false_type;
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
-        const int buf = it % kNumBuf;
-        const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
-        if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t acc_base = tmem_base + buf * kAccCols;
-        uint32_t started = 0;  // bit a set once accumulator a holds data for this tile
         for (int s = 0; s < n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
-          const uint32_t d_tmem = acc_base + sg.acc * BN;
-          const uint32_t accum = (started >> sg.acc) & 1u;
-          started |= 1u << sg.acc;
+          // one segment per accumulator: wait for its buffer, fill it, publish it
+          const int nb = Epi::acc_bufs(sg.acc), j = it % nb;
+          const uint32_t use = static_cast<uint32_t>(it / nb);
+          if (!mbar_wait(&acc_empty[sg.acc * 2 + j], (use & 1) ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + Ctl::col_off(sg.acc) + j * BN;
           int nk = sg.k_tiles;
           if (k_splits > 1) {
             const int ks = tile / mn_tiles;
             nk = min(sg.k_tiles, (ks + 1) * kt_per_split) - ks * kt_per_split;
             if (nk < 0) nk = 0;
           }
-          if (!sg.a_mn && !sg.b_mn) issue_seg(F_{}, F_{}, nk, d_tmem, accum);
-          else if (!sg.a_mn && sg.b_mn) issue_seg(F_{}, T_{}, nk, d_tmem, accum);
-          else if (sg.a_mn && !sg.b_mn) issue_seg(T_{}, F_{}, nk, d_tmem, accum);
-          else issue_seg(T_{}, T_{}, nk, d_tmem, accum);
-        }
-        if (ok) {
-          if (kCtas == 2) mma_commit_pair(&acc_full[buf]);
-          else mma_commit(&acc_full[buf]);
+          if (!sg.a_mn && !sg.b_mn) issue_seg(F_{}, F_{}, nk, d_tmem, 0u);
+          else if (!sg.a_mn && sg.b_mn) issue_seg(F_{}, T_{}, nk, d_tmem, 0u);
+          else if (sg.a_mn && !sg.b_mn) issue_seg(T_{}, F_{}, nk, d_tmem, 0u);
+          else issue_seg(T_{}, T_{}, nk, d_tmem, 0u);
+          if (ok) {
+            if (kCtas == 2) mma_commit_pair(&acc_full[sg.acc * 2 + j]);
+            else mma_commit(&acc_full[sg.acc * 2 + j]);
+          }
         }
       }
     }
@@ -421,20 +462,12 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       const int nt = p.n_fastest ? t2 % p.n_tiles : t2 / p.m_tiles;
       mt += p.m_rot;
       if (mt >= p.m_tiles) mt -= p.m_tiles;
-      const int buf = it % kNumBuf;
-      const uint32_t use = static_cast<uint32_t>(it / kNumBuf);
-      if (!mbar_wait(&acc_full[buf], use & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t acc0 =
-          tmem_base + buf * kAccCols + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-      Epi::template run<BN>(p.epi, p.tma_out, stager, mt * kTileM + static_cast<int>(rank) * kBlockM,
-                            nt * BN, p.M, p.N, acc0, warp, lane);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (kCtas == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[buf]), 0));
-        else mbar_arrive(&acc_empty[buf]);
-      }
+      Ctl ctl{acc_full, acc_empty, tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16), it,
+              lane, abort_flag, true};
+      Epi::template run<BN>(p.epi, p.tma_out, stager, ctl,
+                            mt * kTileM + static_cast<int>(rank) * kBlockM, nt * BN, p.M, p.N, warp,
+                            lane);
+      ok = ctl.ok;
     }
     if (lane == 0) bulk_wait<0>();  // all of this warp's bulk stores have landed
   }

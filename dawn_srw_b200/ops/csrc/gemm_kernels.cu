@@ -126,6 +126,7 @@ struct PlainEpi {
   static constexpr int kNumOut = 1;   // (kMaxOut maps when scattering; they are not prefetched)
   static constexpr int kOutBufs = 2;
   static constexpr int kEpiWarps = 4;
+  __host__ __device__ static constexpr int acc_bufs(int) { return 2; }
   struct Params {
     float alpha;
     const float* row_scale;  // optional [M]
@@ -138,11 +139,12 @@ struct PlainEpi {
     // (tensor map index = owner rank; peer memory for the other ranks).
     int scatter_rows;
   };
-  template <int BN>
-  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
-                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
     const int r0 = m0 + warp * 32;
-    if (r0 >= M) return;  // whole 32-row slab is outside the matrix (warp-uniform)
+    if (r0 >= M) { ctl.skip(); return; }  // whole 32-row slab is outside the matrix (warp-uniform)
+    const uint32_t acc0 = ctl.wait(0);
     const int row = r0 + lane;
     const float scale = p.alpha * ((row < M && p.row_scale) ? p.row_scale[row] : 1.f);
     int slab = 0;
@@ -202,6 +204,7 @@ struct PlainEpi {
         }
       }
     }
+    ctl.release(0);
   }
 };
 
@@ -223,19 +226,20 @@ struct FwdGateEpi {
   static constexpr int kNumOut = 1;
   static constexpr int kOutBufs = 1;
   static constexpr int kEpiWarps = 8;
+  __host__ __device__ static constexpr int acc_bufs(int) { return 2; }   // S and XR, two tiles in flight
   using Params = FwdGateParams;
 
   // kGeneral: column tail, unit mask or alive flags are in play for this slab.
   template <int BN, bool kGeneral>
   __device__ static __forceinline__ void slab(const Params& p, uint32_t buf, const WarpStager& st,
-                                              uint32_t acc, int col0, int N, bool row_ok,
-                                              float tau, float isg, float& den_acc, float& g_acc,
-                                              int lane) {
+                                              uint32_t acc_s, uint32_t acc_xr, int col0, int N,
+                                              bool row_ok, float tau, float isg, float& den_acc,
+                                              float& g_acc, int lane) {
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       float s[32], xr[32];
-      tmem_ld32(acc + 32 * half, s);
-      tmem_ld32(acc + BN + 32 * half, xr);
+      tmem_ld32(acc_s + 32 * half, s);
+      tmem_ld32(acc_xr + 32 * half, xr);
       tmem_ld_wait();
       const int cbase = col0 + 32 * half;
       unsigned alive_bits = 0u;
@@ -264,14 +268,14 @@ struct FwdGateEpi {
     }
   }
 
-  template <int BN>
-  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
-                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
     static_assert(BN == 128, "one 64-column slab per warp");
     const int r0 = m0 + (warp & 3) * 32;
     const int c = (warp >> 2) * 64;
     const int col0 = n0 + c;
-    if (r0 >= M || col0 >= N) return;  // warp-uniform
+    if (r0 >= M || col0 >= N) { ctl.skip(); return; }  // warp-uniform
     const int row = r0 + lane;
     const bool row_ok = row < M;
     // rows past M hold zero accumulators; their results are clipped by the
@@ -281,9 +285,12 @@ struct FwdGateEpi {
     float den_acc = 0.f, g_acc = 0.f;
     st.wait_free<0>();
     const uint32_t buf = st.buf(0);
+    const uint32_t acc_s = ctl.wait(0) + c, acc_xr = ctl.wait(1) + c;
     const bool general = (col0 + 64 > N) || p.unit_mask != nullptr || p.alive != nullptr;
-    if (general) slab<BN, true>(p, buf, st, acc0 + c, col0, N, row_ok, tau, isg, den_acc, g_acc, lane);
-    else slab<BN, false>(p, buf, st, acc0 + c, col0, N, row_ok, tau, isg, den_acc, g_acc, lane);
+    if (general) slab<BN, true>(p, buf, st, acc_s, acc_xr, col0, N, row_ok, tau, isg, den_acc, g_acc, lane);
+    else slab<BN, false>(p, buf, st, acc_s, acc_xr, col0, N, row_ok, tau, isg, den_acc, g_acc, lane);
+    ctl.release(0);
+    ctl.release(1);
     st.flush(&maps[0], buf, col0, r0, false, true);
     if (row_ok) {
       atomicAdd(p.den_sum + row, den_acc);
@@ -301,61 +308,135 @@ struct BwdGateParams {
   float* dsz_sum;          // [T] += sum_U ds * z     (v4.0.1)
   GateConsts gc;
 };
+// Backward gate coefficients from one score: returns g and writes A1, A2 with
+//   ds = A1 * (dp * xr) + A2 * dden        (dg = dp * xr)
+template <int KIND>
+__device__ __forceinline__ float gate_bwd_coeffs(const GateConsts& gc, float s, float tau,
+                                                 float isg, float& a1, float& a2) {
+  float g;
+  if constexpr (KIND == 0) {
+    const float raw = s - tau;
+    g = fminf(fmaxf(raw, 0.f), gc.clip_max);
+    a1 = (raw > 0.f && raw < gc.clip_max) ? 1.f : 0.f;
+    a2 = a1;
+  } else if constexpr (KIND == 1) {
+    const float zr = (s - tau) * isg;
+    const float z = fmaxf(zr, 0.f);
+    float phi, pdf;
+    phi_pdf(z, phi, pdf);
+    g = z * phi;
+    a1 = zr > 0.f ? fmaf(z, pdf, phi) * isg : 0.f;
+    a2 = a1;
+  } else {
+    const float m = s - tau - gc.thr;
+    const float act = rcp_approx(1.f + __expf(-gc.sharp * m));
+    const float amr = m - gc.cut;
+    const float inten = gc.eps + fminf(fmaxf(amr, 0.f), gc.max_int);
+    g = act * inten;
+    a2 = (amr > 0.f && amr < gc.max_int) ? 1.f : 0.f;
+    a1 = inten * gc.sharp * act * (1.f - act) + act * a2;
+  }
+  return g;
+}
+
+// Three accumulators per tile: S (one buffer), XR (two), DP (one) = 512 TMEM
+// columns.  Phase 1 turns S into per-element (g, A1[, A2]) held in registers as
+// bf16 and frees S; phase 2 combines them with XR and DP.  Because XR has two
+// buffers and S is freed early, the tensor core computes the next tile's S and
+// XR while this tile's phase 2 runs; only DP of the next tile waits for it.
 template <int KIND>
 struct BwdGateEpi {
   static constexpr int kNumAcc = 3;
   static constexpr int kNumOut = 3;   // p, dxr, ds
   static constexpr int kOutBufs = 3;  // one staged slab per output per warp per tile
   static constexpr int kEpiWarps = 8;
+  __host__ __device__ static constexpr int acc_bufs(int a) { return a == 1 ? 2 : 1; }
   using Params = BwdGateParams;
-  template <int BN>
-  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, int m0,
-                             int n0, int M, int N, uint32_t acc0, int warp, int lane) {
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
     static_assert(BN == 128, "one 64-column slab per warp");
     const int r0 = m0 + (warp & 3) * 32;
     const int c = (warp >> 2) * 64;
     const int col0 = n0 + c;
-    if (r0 >= M || col0 >= N) return;
+    if (r0 >= M || col0 >= N) { ctl.skip(); return; }
     const int row = r0 + lane;
     const bool row_ok = row < M;
     const float tau = row_ok ? p.tau[row] : 0.f;
     const float isg = row_ok ? p.inv_sigma[row] : 1.f;
     const float dden = row_ok ? p.dden[row] : 0.f;
     const bool tail = col0 + 64 > N;
-    float dtau_acc = 0.f, dsz_acc = 0.f;
+
+    // ---- phase 1: S -> (g, A1), two bf16 per register.  For the two-stage gate
+    // A2 (0 or 1) rides in the sign of g, which is never negative itself.
+    uint32_t st_g[32], st_a[32];
+    {
+      const uint32_t acc_s = ctl.wait(0) + c;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float s[16];
+        tmem_ld16(acc_s + 16 * q, s);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          float a1x, a2x, a1y, a2y;
+          float gx = gate_bwd_coeffs<KIND>(p.gc, s[j], tau, isg, a1x, a2x);
+          float gy = gate_bwd_coeffs<KIND>(p.gc, s[j + 1], tau, isg, a1y, a2y);
+          if (tail) {
+            const int col = col0 + 16 * q + j;
+            if (col >= N) { gx = 0.f; a1x = 0.f; a2x = 0.f; }
+            if (col + 1 >= N) { gy = 0.f; a1y = 0.f; a2y = 0.f; }
+          }
+          if constexpr (KIND == 2) {
+            if (a2x != 0.f) gx = -gx;
+            if (a2y != 0.f) gy = -gy;
+          }
+          st_g[8 * q + j / 2] = pack_bf16x2(gx, gy);
+          st_a[8 * q + j / 2] = pack_bf16x2(a1x, a1y);
+        }
+      }
+      ctl.release(0);
+    }
+
+    // ---- phase 2: XR and DP
+    float dtau_acc = 0.f;
     st.wait_free<0>();
     const uint32_t b_p = st.buf(0), b_dxr = st.buf(1), b_ds = st.buf(2);
-#pragma unroll 1
+    const uint32_t acc_xr = ctl.wait(1) + c, acc_dp = ctl.wait(2) + c;
+#pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float s[16], xr[16], dp[16];
-      tmem_ld16(acc0 + c + 16 * q, s);
-      tmem_ld16(acc0 + BN + c + 16 * q, xr);
-      tmem_ld16(acc0 + 2 * BN + c + 16 * q, dp);
+      float xr[16], dp[16], ds[16];
+      tmem_ld16(acc_xr + 16 * q, xr);
+      tmem_ld16(acc_dp + 16 * q, dp);
       tmem_ld_wait();
-      const int nv = tail ? N - (col0 + 16 * q) : 16;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        float ds, dsz;
-        const float g = gate_bwd<KIND>(p.gc, s[j], tau, isg, dp[j] * xr[j], dden, ds, dsz);
-        if (j >= nv) { ds = 0.f; dsz = 0.f; }
-        dtau_acc -= ds;
-        dsz_acc += dsz;
-        s[j] = ds;
+        const uint32_t wg = st_g[8 * q + j / 2], wa = st_a[8 * q + j / 2];
+        // bf16 -> fp32: the value sits in the upper half of the fp32 word
+        float g = __uint_as_float((j & 1) ? (wg & 0xffff0000u) : (wg << 16));
+        const float a1 = __uint_as_float((j & 1) ? (wa & 0xffff0000u) : (wa << 16));
+        float a2 = a1;
+        if constexpr (KIND == 2) {
+          a2 = g < 0.f ? 1.f : 0.f;
+          g = fabsf(g);
+        }
+        const float d = fmaf(a1, dp[j] * xr[j], a2 * dden);
+        dtau_acc -= d;
+        ds[j] = d;
         const float pv = g * xr[j];
         dp[j] = dp[j] * g;  // dxr
         xr[j] = pv;         // p
       }
       stage_bf16_16(st, b_p, 2 * q, xr);
       stage_bf16_16(st, b_dxr, 2 * q, dp);
-      stage_bf16_16(st, b_ds, 2 * q, s);
+      stage_bf16_16(st, b_ds, 2 * q, ds);
     }
+    ctl.release(1);
+    ctl.release(2);
     st.flush(&maps[0], b_p, col0, r0, false, true);
     st.flush(&maps[1], b_dxr, col0, r0, false, true);
     st.flush(&maps[2], b_ds, col0, r0, false, true);
-    if (row_ok) {
-      atomicAdd(p.dtau_sum + row, dtau_acc);
-      if (KIND == 1) atomicAdd(p.dsz_sum + row, dsz_acc);
-    }
+    if (row_ok) atomicAdd(p.dtau_sum + row, dtau_acc);
   }
 };
 

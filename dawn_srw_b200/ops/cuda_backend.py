@@ -283,9 +283,15 @@ class _SRWRouteFn(torch.autograd.Function):
         gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
         gemm(dsv, True, h_bf, True, out=hd.g_emb[:U], accumulate=True)      # ds^T h
         dx = gemm(dxrv, False, read, True, out_dtype=torch.bfloat16)        # dxr . read
-        dh = gemm(dsv, False, emb, True, out_dtype=torch.bfloat16)          # ds . emb
-        d_isd = dsz / (inv_sd * inv_sd) if spec.kind == GATE_GELU_Z else None
-        return dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None, None
+        dh32 = gemm(dsv, False, emb, True, out_dtype=torch.float32)         # ds . emb
+        d_isd = None
+        if spec.kind == GATE_GELU_Z:
+            # sum_u ds_u z_u = (1/sigma) (<h, ds.emb> + tau * dtau): the sigma path needs no
+            # reduction of its own in the kernel
+            dsz = inv_sd * ((h_bf.float() * dh32).sum(-1) + tau * dtau)
+            d_isd = dsz / (inv_sd * inv_sd)
+        return (dx, dh32.to(torch.bfloat16), dtau, d_isd, torch.zeros(1, device=dev), None, None,
+                None, None, None)
 
 
 # ---------------------------------------------------------------------------

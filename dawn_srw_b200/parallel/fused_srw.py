@@ -151,8 +151,18 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         e.gemm_scatter(dsv, False, emb, True, dht.ptrs, Tl, r, 1.0, None, st)         # ds . emb
         c.ws.barrier()
         dx = dxt.local.to(torch.bfloat16)
-        dh = dht.local.to(torch.bfloat16)
+        dh32 = dht.local.clone()
         dxt.local.zero_()
         dht.local.zero_()
-        d_isd = dsz / (inv_sd_full * inv_sd_full) if spec.kind == GATE_GELU_Z else None
-        return dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None
+        d_isd = None
+        if spec.kind == GATE_GELU_Z:
+            # sum_u ds_u z_u = (1/sigma)(<h, ds.emb> + tau * dtau), evaluated by the owner of
+            # each token on the fully reduced ds.emb and dtau; other rows contribute zero
+            dtau_l = torch.empty(Tl, dtype=torch.float32, device=dev)
+            dist.reduce_scatter_tensor(dtau_l, dtau, group=c.group)
+            isd_l, tau_l = inv_sd_full[c.rows], tau_full[c.rows]
+            dsz_l = isd_l * ((h_bf.float() * dh32).sum(-1) + tau_l * dtau_l)
+            d_isd = torch.zeros(T, dtype=torch.float32, device=dev)
+            d_isd[c.rows] = dsz_l / (isd_l * isd_l)
+        return (dx, dh32.to(torch.bfloat16), dtau, d_isd, torch.zeros(1, device=dev), None, None,
+                None, None)
