@@ -70,6 +70,8 @@ class TrainingConfig:
     diversity_weight: float = 0.1
     load_balance_weight: float = 2e-5
     tau_reg_weight: float = 0.0
+    entropy_weight: float = 0.0          # carried by the dense-baseline configs; no live loss term uses it
+    process_norm_weight: float = 0.0     # likewise
     dead_penalty_weight: float = 0.0
     dead_penalty_threshold: float = 0.01
     sharpness: float = 500.0

@@ -119,9 +119,8 @@ class Trainer:
                                   dp_group=self.topo.world_group if self.topo.world > 1 else None,
                                   backend=self.backend, want_stats=want_diag)
         total.backward()
-        updated = self.optimizer.step()
-        if updated:
-            self.optimizer.zero_grad()
+        self.optimizer.step()         # consumes this micro-step's gradients (it keeps its own sum)
+        self.optimizer.zero_grad()
         self.backend.finish_step()
         self.global_step += 1
         metrics: Dict[str, Any] = {"total_loss": total.detach()}

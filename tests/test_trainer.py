@@ -102,3 +102,24 @@ def test_baseline_model_trains(tmp_path):
     cfg = tiny_config(version="baseline", max_steps=2)
     out = Trainer(cfg).fit()
     assert math.isfinite(out["total_loss"])
+
+
+def test_gradient_accumulation_in_the_trainer():
+    """Two micro-steps on the same batch with accumulation 2 give the update of
+    one plain step on that batch (the mean of two equal gradients)."""
+    torch.manual_seed(0)
+    a = Trainer(tiny_config(gradient_accumulation_steps=2), total_steps=100)
+    b = Trainer(tiny_config(), total_steps=100)
+    b.model.load_state_dict(a.model.state_dict())
+    ids, mask = a.train_loader.batch(0)
+    before = _params(a)
+    a.train_step(ids, mask)
+    assert a.optimizer.count == 0
+    for n, p in _params(a).items():
+        assert torch.equal(p, before[n]), n          # nothing moves inside the window
+    a.train_step(ids, mask)
+    b.train_step(ids, mask)
+    assert a.optimizer.count == 1 and b.optimizer.count == 1
+    pa, pb = _params(a), _params(b)
+    for n in pa:
+        assert torch.allclose(pa[n], pb[n], atol=2e-6), n
