@@ -46,6 +46,9 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=512)
     ap.add_argument("--batch-per-gpu", type=int, default=0, help="sequences per GPU per step")
     ap.add_argument("--parallelism", default="pool", choices=["pool", "dp"])
+    ap.add_argument("--optimizer", default="auto", choices=["auto", "partitioned", "replicated"],
+                    help="partitioned: reduce-scatter + AdamW on the owned slice + all-gather over "
+                         "peer memory with sharded moments; auto = partitioned for --parallelism dp")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--profile", metavar="FILE",
                     help="after the timed runs, profile one more step with torch.profiler and "
@@ -155,6 +158,10 @@ def main():
     t.batch_size = bpg * world
     t.pool_shards, t.seq_shard = pool_shards, True
     t.log_interval = 0
+    opt_mode = args.optimizer
+    if opt_mode == "auto":
+        opt_mode = "partitioned" if (args.parallelism == "dp" and world > 1) else "replicated"
+    t.zero_pool_state = opt_mode == "partitioned" and world > 1
     cfg.data.synthetic = True
     cfg.data.synthetic_sequences = t.batch_size * 4
     # loss weights of the named reference configs
@@ -247,7 +254,8 @@ def main():
                        "global_batch": t.batch_size, "seq_len": args.seq_len,
                        "parallelism": (f"pool{pool_shards}+seqshard" if pool_shards > 1 else f"dp{world}"),
                        "l2": "inputs and weights per step exceed the 126 MB L2 (no flush needed)",
-                       "layer_recompute": False},
+                       "layer_recompute": False,
+                       "optimizer": type(trainer.optimizer).__name__},
             "clocks": clocks, "gpu_launches": launches, "final_loss": loss_val,
         }
         if e2e:

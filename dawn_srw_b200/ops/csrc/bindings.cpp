@@ -243,6 +243,45 @@ void peer_barrier(const Tensor& pads_dev, int64_t rank, int64_t world, int64_t e
   TORCH_CHECK(rc == 0, "dsb_peer_barrier failed with code ", rc);
 }
 
+void small_allreduce(const Tensor& stage_dev, const Tensor& pads_dev, int64_t rank, int64_t world,
+                     int64_t epoch, int64_t slot_base, const Tensor& in, Tensor& out, int64_t cap,
+                     Tensor& status, int64_t wait_cycles) {
+  TORCH_CHECK(in.is_cuda() && in.scalar_type() == torch::kFloat32 && in.is_contiguous() &&
+              out.scalar_type() == torch::kFloat32 && out.is_contiguous() &&
+              out.numel() == in.numel());
+  const c10::cuda::CUDAGuard guard(in.device());
+  int rc = dsb_small_allreduce(reinterpret_cast<float* const*>(stage_dev.data_ptr<int64_t>()),
+                               reinterpret_cast<unsigned int* const*>(pads_dev.data_ptr<int64_t>()),
+                               rank, world, static_cast<unsigned int>(epoch), slot_base,
+                               in.data_ptr<float>(), out.data_ptr<float>(), in.numel(), cap,
+                               status.data_ptr<int>(), wait_cycles, cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_small_allreduce failed with code ", rc);
+}
+
+void zero_reduce(const Tensor& grads_dev, int64_t world, int64_t lo, int64_t n, double scale,
+                 Tensor& g_own, Tensor& sq) {
+  TORCH_CHECK(g_own.is_cuda() && g_own.scalar_type() == torch::kFloat32 && g_own.is_contiguous() &&
+              g_own.numel() >= n && sq.scalar_type() == torch::kFloat32);
+  const c10::cuda::CUDAGuard guard(g_own.device());
+  int rc = dsb_zero_reduce(reinterpret_cast<const float* const*>(grads_dev.data_ptr<int64_t>()),
+                           world, lo, n, scale, g_own.data_ptr<float>(), sq.data_ptr<float>(),
+                           cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_zero_reduce failed with code ", rc);
+}
+
+void zero_adam_scatter(const Tensor& params_dev, int64_t world, int64_t rank, int64_t lo, int64_t n,
+                       const Tensor& g, Tensor& m, Tensor& v, const Tensor& clip_scale, double lr,
+                       double b1, double b2, double eps, double wd, double bc1, double bc2) {
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == torch::kFloat32 && m.numel() >= n &&
+              v.numel() >= n && g.numel() >= n && m.is_contiguous() && v.is_contiguous());
+  const c10::cuda::CUDAGuard guard(g.device());
+  int rc = dsb_zero_adam_scatter(reinterpret_cast<float* const*>(params_dev.data_ptr<int64_t>()),
+                                 world, rank, lo, n, g.data_ptr<float>(), m.data_ptr<float>(),
+                                 v.data_ptr<float>(), clip_scale.data_ptr<float>(), lr, b1, b2, eps,
+                                 wd, bc1, bc2, cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_zero_adam_scatter failed with code ", rc);
+}
+
 std::vector<Tensor> layernorm_fwd(const Tensor& x, const Tensor& w, const Tensor& b, double eps) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kFloat32 && x.is_contiguous());
   const c10::cuda::CUDAGuard guard(x.device());
@@ -337,4 +376,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
   m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);
   m.def("peer_barrier", &peer_barrier);
+  m.def("small_allreduce", &small_allreduce);
+  m.def("zero_reduce", &zero_reduce);
+  m.def("zero_adam_scatter", &zero_adam_scatter);
 }

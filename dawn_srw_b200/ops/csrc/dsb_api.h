@@ -102,6 +102,29 @@ int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, const void* B,
 int dsb_peer_barrier(unsigned int* const* pads_dev, int rank, int world, unsigned int epoch,
                      int slot_base, int* status, long long wait_cycles, cudaStream_t stream);
 
+// One-shot sum all-reduce of n <= cap fp32 values over symmetric memory.
+// `stage_dev`: DEVICE array of `world` pointers to the ranks' staging buffers
+// (2 * cap floats each); pads / epoch / slot_base as for dsb_peer_barrier (use
+// a slot range of its own: ceil(n / 4096) * world slots, at most 512).  All
+// ranks get bit-identical sums.
+int dsb_small_allreduce(float* const* stage_dev, unsigned int* const* pads_dev, int rank, int world,
+                        unsigned int epoch, int slot_base, const float* in, float* out, int n,
+                        int cap, int* status, long long wait_cycles, cudaStream_t stream);
+
+// Partitioned optimizer step over peer memory.  `grads_dev` / `params_dev` are
+// DEVICE arrays of `world` pointers to flat fp32 buffers of identical layout;
+// this rank owns elements [lo, lo + n) (both multiples of 4).
+//   dsb_zero_reduce:       g_own[i] = scale * sum_r grads[r][lo+i];  sq[0] += |g_own|^2
+//   dsb_zero_adam_scatter: AdamW on the owned slice (m, v are slice-sized and
+//                          local), new parameters stored to every rank.
+// The caller orders them against the peers with dsb_peer_barrier.
+int dsb_zero_reduce(const float* const* grads_dev, int world, long long lo, long long n, float scale,
+                    float* g_own, float* sq, cudaStream_t stream);
+int dsb_zero_adam_scatter(float* const* params_dev, int world, int rank, long long lo, long long n,
+                          const float* g, float* m, float* v, const float* clip_scale, float lr,
+                          float b1, float b2, float eps, float wd, float bc1, float bc2,
+                          cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -353,6 +353,7 @@ def fused_adamw(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps,
         cs = clip_scale.detach().float().reshape(1).contiguous()
         e.adamw_multi([p.data for p in params], [g.float().contiguous() for g in grads], exp_avg,
                       exp_avg_sq, cs, lr, b1, b2, eps, wd, bc1, bc2)
+        mark_updated(params)
         return
     g = torch._foreach_mul(grads, clip_scale)
     torch._foreach_mul_(exp_avg, b1)
@@ -367,6 +368,19 @@ def fused_adamw(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps,
     if wd != 0.0:
         torch._foreach_add_(upd, params, alpha=wd)
     torch._foreach_add_(params, upd, alpha=-lr)
+
+
+def count_launches(n: int) -> None:
+    """Account for kernels launched outside this module (communication kernels)."""
+    global _LAUNCHES
+    _LAUNCHES += int(n)
+
+
+def mark_updated(params) -> None:
+    """Bump the autograd version of tensors a kernel rewrote through raw
+    pointers, so caches keyed on ``_version`` (the bf16 compute copies of the
+    master weights) see the change."""
+    torch._C._increment_version([p for p in params])
 
 
 def grad_sq_norm(grads) -> torch.Tensor:

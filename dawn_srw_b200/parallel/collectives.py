@@ -37,6 +37,26 @@ def group_rank(group) -> int:
     return dist.get_rank(group)
 
 
+# Optional kernel path for small fp32 sums: (callable, max elements) per group,
+# installed by the owner of a symmetric-memory workspace for that group.
+_SMALL_ALLREDUCE = {}
+
+
+def register_small_allreduce(group, fn, max_elems: int) -> None:
+    _SMALL_ALLREDUCE[id(group)] = (fn, int(max_elems))
+
+
+def _all_reduce_sum_(y: torch.Tensor, group) -> None:
+    """In-place sum over ``group``.  Shapes and dtypes agree on all ranks, so
+    all ranks pick the same path."""
+    hit = _SMALL_ALLREDUCE.get(id(group))
+    if (hit is not None and y.is_cuda and y.dtype == torch.float32 and y.is_contiguous()
+            and 0 < y.numel() <= hit[1]):
+        hit[0](y)
+    else:
+        dist.all_reduce(y, group=group)
+
+
 class _CopyToShards(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
@@ -67,13 +87,13 @@ class _SumOverShards(torch.autograd.Function):
     def forward(ctx, x, group):
         ctx.group = group
         y = x.contiguous().clone()
-        dist.all_reduce(y, group=group)
+        _all_reduce_sum_(y, group)
         return y
 
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous().clone()
-        dist.all_reduce(g, group=ctx.group)
+        _all_reduce_sum_(g, ctx.group)
         return g, None
 
 
@@ -153,7 +173,10 @@ def all_reduce_nograd(x: torch.Tensor, group, op: str = "sum") -> torch.Tensor:
     if group_size(group) == 1:
         return x
     y = x.detach().contiguous().clone()
-    red = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op]
+    if op == "sum":
+        _all_reduce_sum_(y, group)
+        return y
+    red = {"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op]
     dist.all_reduce(y, op=red, group=group)
     return y
 
@@ -172,11 +195,11 @@ class _PMean(torch.autograd.Function):
         ctx.group = group
         n = dist.get_world_size(group)
         y = x.contiguous().clone()
-        dist.all_reduce(y, group=group)
+        _all_reduce_sum_(y, group)
         return y / n
 
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous().clone()
-        dist.all_reduce(g, group=ctx.group)
+        _all_reduce_sum_(g, ctx.group)
         return g / dist.get_world_size(ctx.group), None

@@ -63,6 +63,13 @@ class FusedShardComm:
         self.epoch = 0
         self.parity = 0
         self.rows = slice(self.rank * t_local, (self.rank + 1) * t_local)
+        # small fp32 sums over this group (per-token statistics, denominators, loss terms)
+        # go through one peer-memory kernel instead of a library all-reduce
+        from . import collectives as C
+        self.ws.enable_small_allreduce()
+        C.register_small_allreduce(group, self.ws.all_reduce_small, self.ws.AR_CAP)
+        if group is not self.group:
+            C.register_small_allreduce(self.group, self.ws.all_reduce_small, self.ws.AR_CAP)
 
     def next_buffers(self):
         self.parity ^= 1

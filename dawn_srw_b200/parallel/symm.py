@@ -49,6 +49,7 @@ class SymmWorkspace:
         dist.barrier(group=self.group)
         self.pads_dev = torch.tensor(pad.ptrs, dtype=torch.int64, device=self.device)
         self._epoch: Dict[int, int] = {}
+        self._ar_stage, self._ar_stage_dev, self._ar_epoch = None, None, 0
 
     def alloc(self, name: str, shape, dtype) -> SymmBuffer:
         """Collective: every rank of the group must call it with the same arguments."""
@@ -62,6 +63,29 @@ class SymmWorkspace:
         buf = SymmBuffer(t, [int(p) for p in hdl.buffer_ptrs], hdl)
         self.buffers[name] = buf
         return buf
+
+    AR_SLOT_BASE = 512          # pad slots [512, 1024) belong to all_reduce_small
+    AR_CAP = 65536              # largest vector (fp32 elements) it takes
+
+    def all_reduce_small(self, x: torch.Tensor) -> torch.Tensor:
+        """In-place sum over the group of a contiguous fp32 tensor of at most
+        ``AR_CAP`` elements, by one kernel over peer memory (no library call)."""
+        from ..ops import cuda_backend as CB
+        if self._ar_stage is None:
+            raise RuntimeError("enable_small_allreduce() was not called (it is collective)")
+        self._ar_epoch += 1
+        CB.ext().small_allreduce(self._ar_stage_dev, self.pads_dev, self.rank, self.world,
+                                 self._ar_epoch, self.AR_SLOT_BASE, x, x, self.AR_CAP,
+                                 CB.status_word(self.device), 0)
+        CB.count_launches(1)
+        return x
+
+    def enable_small_allreduce(self) -> None:
+        """Collective: allocate the staging buffers of ``all_reduce_small``."""
+        if self._ar_stage is None:
+            self._ar_stage = self.alloc("__ar_stage__", (2 * self.AR_CAP,), torch.float32)
+            self._ar_stage_dev = torch.tensor(self._ar_stage.ptrs, dtype=torch.int64,
+                                              device=self.device)
 
     def barrier(self, channel: int = 0, wait_cycles: int = 0) -> None:
         """Enqueue a bounded cross-GPU barrier on the current stream.  Channels

@@ -75,10 +75,19 @@ class Trainer:
         self.total_steps = total_steps
         warm = int(total_steps * t.warmup_ratio)
         self.schedule = lambda s: warmup_cosine(s, t.lr, warm, total_steps)
-        self.optimizer = DawnAdamW(
-            self.model.named_parameters(), lr=t.lr, weight_decay=t.weight_decay,
-            pool_weight_decay=t.pool_weight_decay, schedule=self.schedule, accumulation_steps=k,
-            grad_sync=GradSync(self.topo) if self.topo.world > 1 else None)
+        if t.zero_pool_state and self.topo.world > 1:
+            # replicated parameters: reduce-scatter + AdamW on the owned slice + all-gather,
+            # moments sharded over the replicas
+            from ..parallel.zero import PartitionedAdamW
+            self.optimizer = PartitionedAdamW(
+                self.model.named_parameters(), self.topo, lr=t.lr, weight_decay=t.weight_decay,
+                pool_weight_decay=t.pool_weight_decay, schedule=self.schedule,
+                accumulation_steps=k)
+        else:
+            self.optimizer = DawnAdamW(
+                self.model.named_parameters(), lr=t.lr, weight_decay=t.weight_decay,
+                pool_weight_decay=t.pool_weight_decay, schedule=self.schedule, accumulation_steps=k,
+                grad_sync=GradSync(self.topo) if self.topo.world > 1 else None)
         self.global_step = 0          # micro-steps taken
         self.epoch = 0
         self.step_in_epoch = 0
@@ -190,6 +199,8 @@ class Trainer:
             return None
         t = self.topo
         writes = t.is_main or (t.pool_shards > 1 and t.dp_index == 0)
+        if hasattr(self.optimizer, "gather_state"):
+            self.optimizer.gather_state()       # collective: sharded moments -> per-parameter form
         path = None
         if writes:
             path = ckpt.save_checkpoint(

@@ -87,17 +87,33 @@ def test_sequence_sharding_matches_single_rank():
             assert torch.allclose(got, full[f"neuron_pool.know_{kind}"][lo:hi], atol=2e-5), (kind, k)
 
 
-def _dp_trainer_worker(rank, world, pool_shards, seq_shard):
+def _dp_trainer_worker(rank, world, pool_shards, seq_shard, zero=False, accum=1, ckpt_dir=None):
     from dawn_srw_b200.parallel.topology import init_topology
     from dawn_srw_b200.train.trainer import Trainer
     topo = init_topology(pool_shards=pool_shards, seq_shard=seq_shard, backend="gloo")
-    cfg = tiny_config(version="spatial-r1-v4.0.1", max_steps=3, diversity_weight=0.0)
-    tr = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10)
-    for i in range(3):
+    cfg = tiny_config(version="spatial-r1-v4.0.1", max_steps=3, diversity_weight=0.0,
+                      zero_pool_state=zero, gradient_accumulation_steps=accum)
+    tr = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10, run_dir=ckpt_dir)
+    for i in range(3 * accum):
         ids, mask = tr.train_loader.batch(i)
         m = tr.train_step(ids, mask)
-    sd = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
-    return {"sd": sd, "gn": float(m["grad_norm"])}
+    out = {"gn": float(m["grad_norm"]), "opt": type(tr.optimizer).__name__}
+    if ckpt_dir is not None:
+        # save, perturb, resume: parameters and sharded moments come back
+        import os
+        os.makedirs(ckpt_dir, exist_ok=True)
+        tr.save("checkpoint_step3.pt")
+        torch.distributed.barrier()
+        tr2 = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10, run_dir=ckpt_dir)
+        tr2.resume(os.path.join(ckpt_dir, "checkpoint_step3.pt"))
+        for t_ in (tr, tr2):
+            ids, mask = t_.train_loader.batch(7)
+            t_.train_step(ids, mask)
+        out["resume_diff"] = max(float((a - b).abs().max()) for (_, a), (_, b) in zip(
+            tr.model.named_parameters(), tr2.model.named_parameters()))
+        out["state_bytes"] = tr.optimizer.state_bytes() if zero else 0
+    out["sd"] = {n: p.detach().clone() for n, p in tr.model.named_parameters()}
+    return out
 
 
 def _dp_grad_worker(rank, world):
@@ -140,6 +156,30 @@ def test_pool_and_sequence_sharded_training_runs_and_agrees_across_ranks():
     for n in ("router.proj_know.weight", "token_emb.weight", "layers.1.norm2.weight"):
         assert torch.allclose(outs[0]["sd"][n], outs[1]["sd"][n], atol=1e-6), n
     assert abs(outs[0]["gn"] - outs[1]["gn"]) < 1e-5
+
+
+@pytest.mark.parametrize("layout", [(2, 1, False), (2, 2, True), (4, 2, True)])
+def test_partitioned_optimizer_matches_replicated_adamw(layout):
+    """Reduce-scatter + AdamW on the owned slice + all-gather gives the same
+    parameters as all-reduce + full AdamW, for pure data parallelism, for
+    sharded pools (pool slices private to a rank) and for dp 2 x pool shards 2
+    (pool slices replicated over the data-parallel pair only)."""
+    world, shards, seq = layout
+    a = run_ranks(_dp_trainer_worker, world, shards, seq, False, 2)
+    b = run_ranks(_dp_trainer_worker, world, shards, seq, True, 2)
+    assert a[0]["opt"] == "DawnAdamW" and b[0]["opt"] == "PartitionedAdamW"
+    for r in range(world):
+        assert abs(a[r]["gn"] - b[r]["gn"]) < 1e-5
+        for n in a[r]["sd"]:
+            assert torch.allclose(a[r]["sd"][n], b[r]["sd"][n], atol=2e-6), (r, n)
+
+
+def test_partitioned_optimizer_checkpoint_roundtrip(tmp_path):
+    outs = run_ranks(_dp_trainer_worker, 2, 1, False, True, 1, str(tmp_path / "run"))
+    assert outs[0]["resume_diff"] == 0.0 and outs[1]["resume_diff"] == 0.0
+    n_params = sum(v.numel() for v in outs[0]["sd"].values())
+    # two moments, fp32, half of the parameters each (plus padding)
+    assert outs[0]["state_bytes"] <= 2 * 4 * (n_params // 2 + 64)
 
 
 def _consensus_worker(rank, world):

@@ -196,6 +196,13 @@ def test_fused_adamw_and_grad_norm(cb):
     assert abs(float(oa.last_grad_norm) - float(ob.last_grad_norm)) < 1e-3
     for p, q in zip(pa, pb):
         assert torch.allclose(p, q, atol=2e-6)
+    # the backend's cached bf16 compute copy follows a weight the kernel rewrote
+    be = cb.CudaBackend()
+    w0 = be._w(pa[0]).clone()
+    pa[0].grad = torch.ones_like(pa[0])
+    oa.step()
+    assert not torch.equal(be._w(pa[0]), w0)
+    assert torch.equal(be._w(pa[0]), pa[0].detach().to(torch.bfloat16))
 
 
 def test_tiny_model_matches_reference_backend_and_trains(cb):

@@ -164,3 +164,85 @@ def test_peer_barrier_times_out_when_a_peer_never_arrives():
     assert int(st.item()) == 0                                  # cleared; the GPU is still usable
     x = torch.ones(4, device=dev)
     assert float((x + 1).sum()) == 8.0
+
+
+def _small_allreduce(rank, world):
+    import torch.distributed as dist
+    from dawn_srw_b200.ops import cuda_backend as CB
+    from dawn_srw_b200.parallel.symm import SymmWorkspace
+    dev = torch.device("cuda", rank)
+    ws = SymmWorkspace(None, dev)
+    ws.enable_small_allreduce()
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    errs = []
+    for n in (1, 7, 256, 4096, 4097, 30000, 65536, 3, 9000):   # repeated calls reuse the two halves
+        x = torch.randn(n, device=dev, generator=g)
+        ref = x.clone()
+        dist.all_reduce(ref)
+        ws.all_reduce_small(x)
+        errs.append(float((x - ref).abs().max()))
+        # every rank holds bit-identical sums
+        both = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(both, x)
+        assert all(torch.equal(both[0], b) for b in both)
+    torch.cuda.synchronize()
+    CB.check_status()
+    return max(errs)
+
+
+def test_small_allreduce_kernel_matches_nccl():
+    _need(2)
+    errs = _spawn(_small_allreduce, 2)
+    assert max(errs) < 1e-5, errs
+
+
+def _zero_peer_vs_library(rank, world):
+    """PartitionedAdamW with the peer-memory kernels against the same class on
+    NCCL collectives and against replicated AdamW + all-reduce."""
+    from dawn_srw_b200.ops import cuda_backend as CB
+    from dawn_srw_b200.parallel.grad_sync import GradSync
+    from dawn_srw_b200.parallel.topology import init_topology
+    from dawn_srw_b200.parallel.zero import PartitionedAdamW
+    from dawn_srw_b200.train.optimizer import DawnAdamW
+    dev = torch.device("cuda", rank)
+    topo = init_topology(pool_shards=1, seq_shard=False)
+    shapes = {"router.proj_know.weight": (130, 70), "router.proj_know.bias": (70,),
+              "neuron_pool.know_read": (1001, 33), "layers.0.norm1.weight": (70,),
+              "token_emb.weight": (513, 70)}
+    g0 = torch.Generator(device=dev).manual_seed(1)
+    init = {n: torch.randn(*s, device=dev, generator=g0) for n, s in shapes.items()}
+    sets = []
+    for _ in range(3):
+        sets.append([(n, torch.nn.Parameter(v.clone())) for n, v in init.items()])
+    opts = [PartitionedAdamW(sets[0], topo, lr=1e-2, accumulation_steps=2, peer_kernels=True),
+            PartitionedAdamW(sets[1], topo, lr=1e-2, accumulation_steps=2, peer_kernels=False),
+            DawnAdamW(sets[2], lr=1e-2, accumulation_steps=2, grad_sync=GradSync(topo), fused=True)]
+    gr = torch.Generator(device=dev).manual_seed(100 + rank)           # rank-specific gradients
+    for step in range(6):
+        grads = {n: torch.randn(*s, device=dev, generator=gr) * 3 for n, s in shapes.items()}
+        for named, opt in zip(sets, opts):
+            for n, p in named:
+                if p.grad is None:
+                    p.grad = grads[n].clone()
+                else:
+                    p.grad.add_(grads[n])
+            opt.step()
+            opt.zero_grad()
+    torch.cuda.synchronize()
+    CB.check_status()
+    out = {"gn": [float(o.last_grad_norm) for o in opts], "count": [o.count for o in opts]}
+    out["peer_vs_lib"] = max(float((a - b).abs().max()) for (_, a), (_, b) in zip(sets[0], sets[1]))
+    out["peer_vs_replicated"] = max(float((a - b).abs().max()) for (_, a), (_, b) in zip(sets[0], sets[2]))
+    out["params"] = torch.cat([p.detach().reshape(-1) for _, p in sets[0]]).cpu().numpy()
+    return out
+
+
+def test_partitioned_adamw_peer_kernels():
+    _need(2)
+    outs = _spawn(_zero_peer_vs_library, 2)
+    for o in outs:
+        assert o["count"] == [3, 3, 3]
+        assert abs(o["gn"][0] - o["gn"][1]) < 1e-3 and abs(o["gn"][0] - o["gn"][2]) < 1e-3
+        assert o["peer_vs_lib"] < 2e-6 and o["peer_vs_replicated"] < 2e-6, o
+    import numpy as np
+    assert np.array_equal(outs[0]["params"], outs[1]["params"])       # replicas stay identical
