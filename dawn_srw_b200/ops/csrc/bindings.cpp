@@ -332,6 +332,46 @@ void ce_bwd(const Tensor& logits, const Tensor& labels, const Tensor& lse, const
                          dl.data_ptr(), dl.stride(0), cur_stream()) == 0);
 }
 
+std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, int64_t H,
+                                  double p_drop, int64_t seed, Tensor& status) {
+  TORCH_CHECK(q.is_cuda() && q.dim() == 3 && q.scalar_type() == torch::kBFloat16 &&
+              q.is_contiguous() && k.is_contiguous() && v.is_contiguous() &&
+              k.scalar_type() == torch::kBFloat16 && v.scalar_type() == torch::kBFloat16 &&
+              k.sizes() == q.sizes() && v.sizes() == q.sizes());
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int B = q.size(0), S = q.size(1), D = q.size(2);
+  TORCH_CHECK(H > 0 && D % H == 0, "d_model must be a multiple of the head count");
+  auto out = torch::empty_like(q);
+  auto lse = torch::empty({B, H, S}, q.options().dtype(torch::kFloat32));
+  int rc = dsb_attention_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                             lse.data_ptr<float>(), B, H, S, D / H, p_drop,
+                             static_cast<unsigned long long>(seed), status.data_ptr<int>(),
+                             cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_attention_fwd failed with code ", rc);
+  return {out, lse};
+}
+
+std::vector<Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor& v,
+                                  const Tensor& out, const Tensor& d_out, const Tensor& lse,
+                                  int64_t H, double p_drop, int64_t seed, Tensor& status) {
+  TORCH_CHECK(d_out.is_cuda() && d_out.scalar_type() == torch::kBFloat16 && d_out.is_contiguous() &&
+              d_out.sizes() == q.sizes() && out.is_contiguous() && q.is_contiguous() &&
+              k.is_contiguous() && v.is_contiguous() && lse.is_contiguous());
+  const c10::cuda::CUDAGuard guard(q.device());
+  const int B = q.size(0), S = q.size(1), D = q.size(2);
+  auto dq = torch::zeros({B, S, D}, q.options().dtype(torch::kFloat32));
+  auto dk = torch::empty_like(q);
+  auto dv = torch::empty_like(q);
+  auto delta = torch::empty_like(lse);
+  int rc = dsb_attention_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                             d_out.data_ptr(), lse.data_ptr<float>(), delta.data_ptr<float>(),
+                             dq.data_ptr<float>(), dk.data_ptr(), dv.data_ptr(), B, H, S, D / H,
+                             p_drop, static_cast<unsigned long long>(seed), status.data_ptr<int>(),
+                             cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_attention_bwd failed with code ", rc);
+  return {dq, dk, dv};
+}
+
 void adamw_multi(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> exp_avg,
                  std::vector<Tensor> exp_avg_sq, const Tensor& clip_scale, double lr, double b1,
                  double b2, double eps, double wd, double bc1, double bc2) {
@@ -372,6 +412,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("adamw_multi", &adamw_multi);
+  m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd);
   m.def("grad_sq_norm", &grad_sq_norm);
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
   m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);

@@ -28,6 +28,21 @@ int dsb_adamw(float* p, const float* g, float* m, float* v, long long n, const f
 // out[0] += sum(g^2)
 int dsb_sqnorm_accumulate(const float* g, long long n, float* out, cudaStream_t stream);
 
+// Causal self-attention (tcgen05 kernels).  q, k, v, out, d_out: bf16 [B, S, H*dh]
+// (head h in columns [h*dh, (h+1)*dh)); dh a multiple of 16, at most 128.
+// lse, delta: fp32 [B, H, S] (delta is scratch filled by the backward call).
+// Dropout on the attention weights is a hash of (seed, batch*head, query, key):
+// pass the forward call's p_drop and seed to the backward call.
+int dsb_attention_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                      int H, int S, int dh, float p_drop, unsigned long long seed, int* status,
+                      cudaStream_t stream);
+// dq: fp32 [B, S, H*dh], ZEROED by the caller (query tiles are reduce-added into
+// it); dk, dv: bf16 [B, S, H*dh].
+int dsb_attention_bwd(const void* q, const void* k, const void* v, const void* out,
+                      const void* d_out, const float* lse, float* delta, float* dq, void* dk,
+                      void* dv, int B, int H, int S, int dh, float p_drop,
+                      unsigned long long seed, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -343,6 +343,37 @@ class _LMHeadCEFn(torch.autograd.Function):
 
 
 # ---------------------------------------------------------------------------
+class _AttentionFn(torch.autograd.Function):
+    """Causal attention on token-major [B, S, H*dh] tensors (tcgen05 kernels,
+    ops/csrc/attention_kernels.cu).  Dropout acts on the softmax weights and is
+    regenerated in backward from ``seed``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, n_heads, p_drop, seed):
+        qb, kb, vb = (t.detach().to(torch.bfloat16).contiguous() for t in (q, k, v))
+        out, lse = ext().attention_fwd(qb, kb, vb, n_heads, float(p_drop), int(seed),
+                                       status_word(q.device))
+        count_launches(1)
+        ctx.save_for_backward(qb, kb, vb, out, lse)
+        ctx.meta = (n_heads, float(p_drop), int(seed), q.dtype, k.dtype, v.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        qb, kb, vb, out, lse = ctx.saved_tensors
+        n_heads, p_drop, seed, dq_t, dk_t, dv_t = ctx.meta
+        dq, dk, dv = ext().attention_bwd(qb, kb, vb, out, d_out.to(torch.bfloat16).contiguous(),
+                                         lse, n_heads, p_drop, seed, status_word(qb.device))
+        count_launches(2)
+        return dq.to(dq_t), dk.to(dk_t), dv.to(dv_t), None, None, None
+
+
+def causal_attention(q, k, v, n_heads: int, dropout_p: float = 0.0, seed: int = 0):
+    """q, k, v [B, S, H*dh] -> bf16 [B, S, H*dh]."""
+    return _AttentionFn.apply(q, k, v, n_heads, dropout_p, seed)
+
+
+# ---------------------------------------------------------------------------
 def fused_adamw(params, grads, exp_avg, exp_avg_sq, clip_scale, lr, b1, b2, eps, wd, bc1, bc2):
     """Multi-tensor AdamW step with the clip factor applied on the fly
     (``clip_scale`` is a device scalar so no host sync is needed)."""
@@ -426,9 +457,16 @@ class CudaBackend:
         return R.dropout(x, p, training)
 
     def attention(self, q, k, v, dropout_p, training):
-        o = F.scaled_dot_product_attention(q.bfloat16(), k.bfloat16(), v.bfloat16(),
-                                           dropout_p=dropout_p if training else 0.0, is_causal=True)
-        return o.float()
+        """q, k, v [B, H, S, dh] (head-major views of token-major projections)."""
+        B, H, S, dh = q.shape
+        if dh % 16 != 0 or dh > 128:
+            raise ValueError(f"head dimension {dh} is not supported by the attention kernels "
+                             "(multiple of 16, at most 128)")
+        tok = lambda t: t.transpose(1, 2).reshape(B, S, H * dh)
+        p = float(dropout_p) if training else 0.0
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if p > 0.0 else 0
+        o = causal_attention(tok(q), tok(k), tok(v), H, p, seed)
+        return o.view(B, S, H, dh).transpose(1, 2).float()
 
     def lm_head_ce(self, x, tok_emb, labels):
         B, S, D = x.shape

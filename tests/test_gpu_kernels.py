@@ -178,6 +178,67 @@ def test_lm_head_cross_entropy(cb):
     assert _rel(x.grad, x2.grad) < 1e-2 and _rel(emb.grad, emb2.grad) < 1e-2
 
 
+def _attn_ref(q, k, v, H, keep=None, p_drop=0.0):
+    """fp32 dense causal attention on [B, S, H*dh]; ``keep`` is a [B,H,S,S] 0/1 mask."""
+    B, S, D = q.shape
+    dh = D // H
+    hd = lambda t: t.float().view(B, S, H, dh).transpose(1, 2)
+    s = hd(q) @ hd(k).transpose(-1, -2) / dh ** 0.5
+    s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device=q.device).tril(), float("-inf"))
+    w = torch.softmax(s, -1)
+    if keep is not None:
+        w = w * keep / (1.0 - p_drop)
+    return (w @ hd(v)).transpose(1, 2).reshape(B, S, D)
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 512, 80), (3, 2, 200, 64), (1, 3, 64, 32),
+                                   (2, 2, 384, 128), (1, 1, 7, 16), (1, 2, 130, 96)])
+def test_attention_kernels_against_fp32_reference(cb, shape):
+    B, H, S, dh = shape
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(3)
+    mk = lambda: (torch.randn(B, S, H * dh, device=dev, generator=g)).bfloat16().float().requires_grad_(True)
+    q, k, v = mk(), mk(), mk()
+    w = torch.randn(B, S, H * dh, device=dev, generator=g)
+    out = cb.causal_attention(q, k, v, H)
+    (out.float() * w).sum().backward()
+    got = [out.float(), q.grad.clone(), k.grad.clone(), v.grad.clone()]
+    q.grad = k.grad = v.grad = None
+    ref = _attn_ref(q, k, v, H)
+    (ref * w).sum().backward()
+    want = [ref, q.grad, k.grad, v.grad]
+    cb.check_status()
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        assert _rel(a, b) < 1.5e-2, (name, _rel(a, b))
+
+
+def test_attention_dropout_mask_is_shared_by_forward_and_backward(cb):
+    """Recover the kernel's keep-mask with V = identity (S <= dh), then check
+    forward and backward on random tensors against the reference with that mask."""
+    B, H, S, dh, p_drop, seed = 2, 2, 128, 128, 0.25, 1234
+    dev = torch.device("cuda")
+    z = torch.zeros(B, S, H * dh, device=dev)
+    eye = torch.eye(S, dh, device=dev).repeat(1, H).unsqueeze(0).repeat(B, 1, 1)
+    o = cb.causal_attention(z, z, eye, H, p_drop, seed).float()
+    keep = (o.view(B, S, H, dh).transpose(1, 2) > 0).float()          # [B,H,S,S]
+    tri = torch.ones(S, S, device=dev).tril()
+    frac = float((keep * tri).sum() / (tri.sum() * B * H))
+    assert abs(frac - (1 - p_drop)) < 0.02, frac
+    g = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda: torch.randn(B, S, H * dh, device=dev, generator=g).bfloat16().float().requires_grad_(True)
+    q, k, v = mk(), mk(), mk()
+    w = torch.randn(B, S, H * dh, device=dev, generator=g)
+    out = cb.causal_attention(q, k, v, H, p_drop, seed)
+    (out.float() * w).sum().backward()
+    got = [out.float(), q.grad.clone(), k.grad.clone(), v.grad.clone()]
+    q.grad = k.grad = v.grad = None
+    ref = _attn_ref(q, k, v, H, keep, p_drop)
+    (ref * w).sum().backward()
+    cb.check_status()
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, [ref, q.grad, k.grad, v.grad]):
+        assert _rel(a, b) < 1.5e-2, (name, _rel(a, b))
+
+
 def test_fused_adamw_and_grad_norm(cb):
     from dawn_srw_b200.train.optimizer import DawnAdamW
     dev = torch.device("cuda")
