@@ -199,14 +199,12 @@ class DAWN(nn.Module):
         tau_all = be.linear(xf, rt.tau_attn.weight, rt.tau_attn.bias).float()    # [T,3]
         h_qk = h_all[:, : 2 * r].reshape(T, 2, r)
         h_v = h_all[:, 2 * r:].reshape(T, 1, r)
-        res_qk = be.srw(xf, h_qk, tau_all[:, 0:2], pools["qk"], self.gate,
-                        pctx=self.pctx("qk"), want_diag=want_diag)
-        res_v = be.srw(xf, h_v, tau_all[:, 2:3], pools["v"], self.gate,
-                       pctx=self.pctx("v"), want_diag=want_diag)
         qk_scale, v_scale = self.pool_scale("qk"), self.pool_scale("v")
-        Q = res_qk.out[:, 0] * qk_scale
-        K = res_qk.out[:, 1] * qk_scale
-        V = res_v.out[:, 0] * v_scale
+        res_qk = be.srw(xf, h_qk, tau_all[:, 0:2], pools["qk"], self.gate,
+                        pctx=self.pctx("qk"), want_diag=want_diag, out_scale=qk_scale)
+        res_v = be.srw(xf, h_v, tau_all[:, 2:3], pools["v"], self.gate,
+                       pctx=self.pctx("v"), want_diag=want_diag, out_scale=v_scale)
+        Q, K, V = res_qk.route(0), res_qk.route(1), res_v.route(0)
         dh = D // H
         to_heads = lambda t: t.reshape(B, S, H, dh).transpose(1, 2)
         o = be.attention(to_heads(Q), to_heads(K), to_heads(V), self.dropout_rate, training)
@@ -221,7 +219,7 @@ class DAWN(nn.Module):
             aux, tau_reg = lb, tau_relu
         if want_diag:
             with torch.no_grad():
-                self._attn_diag(m, res_qk, res_v, Q, K, V, o, out, tau_all, dh)
+                self._attn_diag(m, res_qk, res_v, Q, K, V, o, out, tau_all, dh, qk_scale, v_scale)
         zero = tau_relu.new_zeros(())
         return out_d, (aux, res_qk.dead_penalty + res_v.dead_penalty,
                        tau_all.reshape(B, S, 3), tau_reg if tau_reg is not None else zero)
@@ -234,10 +232,11 @@ class DAWN(nn.Module):
         h = be.linear(xf, rt.proj_know.weight, rt.proj_know.bias)
         h = be.dropout(h, self.router_dropout, training)
         tau = be.linear(xf, rt.tau_know.weight, rt.tau_know.bias).float()         # [T,1]
+        k_scale = self.pool_scale("know")
         res = be.srw(xf, h.reshape(T, 1, self.d_route), tau, pools["know"], self.gate,
-                     pctx=self.pctx("know"), want_diag=want_diag)
-        raw = res.out[:, 0]
-        out = raw * self.pool_scale("know")
+                     pctx=self.pctx("know"), want_diag=want_diag, out_scale=k_scale)
+        out = res.route(0)
+        raw = (out.detach() / k_scale) if want_diag else None     # pre-scale output, diagnostics only
         out_d = be.dropout(out, self.dropout_rate, training).reshape(B, S, D)
         tau_relu = torch.relu(tau).mean()
         if self.gate.tau_reg_in_aux:
@@ -256,7 +255,7 @@ class DAWN(nn.Module):
     def _rownorm_mean(t):
         return torch.linalg.vector_norm(t.float(), dim=-1).mean()
 
-    def _attn_diag(self, m, rq, rv, Q, K, V, o, out, tau_all, dh):
+    def _attn_diag(self, m, rq, rv, Q, K, V, o, out, tau_all, dh, qk_scale, v_scale):
         dq, dv = rq.diag, rv.diag
         if not dq:
             return
@@ -283,8 +282,8 @@ class DAWN(nn.Module):
         m["attn_tau_mean"].append(tau_all.mean())
         m["attn_tau_std"].append(tau_all.std(dim=0, unbiased=False))
         m["attn_tau_kernel_norm"].append(torch.sqrt(self.router.tau_attn.weight.float().square().sum() + 1e-12))
-        m["attn_qk_raw_norm"].append(self._rownorm_mean(rq.out))
-        m["attn_v_raw_norm"].append(self._rownorm_mean(rv.out))
+        m["attn_qk_raw_norm"].append(self._rownorm_mean(rq.stacked()) / qk_scale)
+        m["attn_v_raw_norm"].append(self._rownorm_mean(rv.stacked()) / v_scale)
         qn, kn = self._rownorm_mean(Q.reshape(-1, dh)), self._rownorm_mean(K.reshape(-1, dh))
         m["debug_q_norm"].append(qn)
         m["debug_k_norm"].append(kn)

@@ -62,7 +62,7 @@ def _layer_qkv(model, be, normed, pools, masks=None, return_gates=False):
     rv = _srw(model, be, normed, h_all[:, 2 * r:].reshape(T, 1, r), tau_all[:, 2:3], pools, "v",
               return_gates=return_gates, unit_mask=m.get("v"))
     qs, vs = model.pool_scale("qk"), model.pool_scale("v")
-    return rq.out[:, 0] * qs, rq.out[:, 1] * qs, rv.out[:, 0] * vs, rq, rv
+    return rq.route(0) * qs, rq.route(1) * qs, rv.route(0) * vs, rq, rv
 
 
 def _know(model, be, normed, pools, masks=None, return_gates=False):
@@ -72,7 +72,7 @@ def _know(model, be, normed, pools, masks=None, return_gates=False):
     tau = be.linear(normed, rt.tau_know.weight, rt.tau_know.bias).float()
     res = _srw(model, be, normed, h.reshape(T, 1, model.d_route), tau, pools, "know",
                return_gates=return_gates, unit_mask=(masks or {}).get("know"))
-    return res.out[:, 0] * model.pool_scale("know"), res
+    return res.route(0) * model.pool_scale("know"), res
 
 
 @torch.no_grad()

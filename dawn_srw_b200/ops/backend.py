@@ -87,8 +87,16 @@ class ReferenceBackend:
 
     def srw(self, x, h, tau_off, pool: PreparedPool, spec: GateSpec, *,
             pctx: Optional[ParallelCtx] = None, want_diag: bool = True,
-            return_gates: bool = False, unit_mask=None) -> SRWResult:
+            return_gates: bool = False, unit_mask=None, out_scale=None) -> SRWResult:
+        """``out_scale`` (float or 0-dim tensor): the pool's output scale; when
+        given, ``SRWResult.out`` / ``route(i)`` are already multiplied by it."""
         pctx = pctx or ParallelCtx()
+        res = self._srw(x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask)
+        if out_scale is not None:
+            res.out = res.out * out_scale
+        return res
+
+    def _srw(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask):
         return srw_pool_ref(
             x, h, tau_off, pool.emb, pool.read, pool.write, spec,
             compute_dtype=self.compute_dtype, chunk_size=self.chunk_size,

@@ -372,6 +372,61 @@ std::vector<Tensor> attention_bwd(const Tensor& q, const Tensor& k, const Tensor
   return {dq, dk, dv};
 }
 
+Tensor embed_fwd(const Tensor& ids, const Tensor& tok, const Tensor& pos) {
+  TORCH_CHECK(ids.is_cuda() && ids.dim() == 2 && ids.scalar_type() == torch::kInt64 &&
+              ids.is_contiguous() && tok.scalar_type() == torch::kFloat32 && tok.is_contiguous() &&
+              pos.scalar_type() == torch::kFloat32 && pos.is_contiguous());
+  const c10::cuda::CUDAGuard guard(ids.device());
+  const int B = ids.size(0), S = ids.size(1), D = tok.size(1);
+  TORCH_CHECK(pos.size(0) >= S && pos.size(1) == D);
+  auto out = torch::empty({B, S, D}, tok.options());
+  TORCH_CHECK(dsb_embed_fwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                            tok.data_ptr<float>(), pos.data_ptr<float>(), out.data_ptr<float>(),
+                            B * S, S, D, tok.size(0), cur_stream()) == 0);
+  return out;
+}
+
+std::vector<Tensor> embed_bwd(const Tensor& ids, const Tensor& dy, int64_t V, int64_t P) {
+  TORCH_CHECK(dy.is_cuda() && dy.dim() == 3 && dy.scalar_type() == torch::kFloat32 &&
+              dy.is_contiguous() && ids.is_contiguous());
+  const c10::cuda::CUDAGuard guard(dy.device());
+  const int B = dy.size(0), S = dy.size(1), D = dy.size(2);
+  auto dtok = torch::zeros({V, D}, dy.options());
+  auto dpos = torch::zeros({P, D}, dy.options());
+  TORCH_CHECK(dsb_embed_bwd(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()),
+                            dy.data_ptr<float>(), dtok.data_ptr<float>(), dpos.data_ptr<float>(),
+                            B, S, D, V, cur_stream()) == 0);
+  return {dtok, dpos};
+}
+
+std::vector<Tensor> offdiag_abs(const Tensor& sim) {
+  TORCH_CHECK(sim.is_cuda() && sim.dim() == 2 && sim.scalar_type() == torch::kFloat32 &&
+              sim.stride(1) == 1 && sim.size(0) == sim.size(1));
+  const c10::cuda::CUDAGuard guard(sim.device());
+  const int m = sim.size(0);
+  const int64_t ld_s = (m + 7) / 8 * 8;
+  auto sgn = torch::empty({m, ld_s}, sim.options().dtype(torch::kBFloat16));
+  auto total = torch::zeros({}, sim.options());
+  TORCH_CHECK(dsb_offdiag_abs(sim.data_ptr<float>(), sim.stride(0), m, sgn.data_ptr(), ld_s,
+                              total.data_ptr<float>(), cur_stream()) == 0);
+  return {total, sgn.slice(1, 0, m)};
+}
+
+std::vector<Tensor> route_bwd_prologue(const Tensor& dy, const Tensor& y, const Tensor& row_scale) {
+  TORCH_CHECK(dy.is_cuda() && dy.dim() == 2 && dy.scalar_type() == torch::kFloat32 &&
+              dy.is_contiguous() && y.scalar_type() == torch::kFloat32 && y.is_contiguous() &&
+              y.sizes() == dy.sizes() && row_scale.scalar_type() == torch::kFloat32 &&
+              row_scale.is_contiguous() && row_scale.numel() == dy.size(0));
+  const c10::cuda::CUDAGuard guard(dy.device());
+  const int T = dy.size(0), D = dy.size(1);
+  auto dyb = torch::empty({T, D}, dy.options().dtype(torch::kBFloat16));
+  auto rowdot = torch::empty({T}, dy.options());
+  TORCH_CHECK(dsb_route_bwd_prologue(dy.data_ptr<float>(), y.data_ptr<float>(), row_scale.data_ptr<float>(),
+                                     dyb.data_ptr(), rowdot.data_ptr<float>(), T, D,
+                                     cur_stream()) == 0);
+  return {dyb, rowdot};
+}
+
 void adamw_multi(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> exp_avg,
                  std::vector<Tensor> exp_avg_sq, const Tensor& clip_scale, double lr, double b1,
                  double b2, double eps, double wd, double bc1, double bc2) {
@@ -412,6 +467,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("adamw_multi", &adamw_multi);
+  m.def("embed_fwd", &embed_fwd);
+  m.def("embed_bwd", &embed_bwd);
+  m.def("offdiag_abs", &offdiag_abs);
+  m.def("route_bwd_prologue", &route_bwd_prologue);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
   m.def("grad_sq_norm", &grad_sq_norm);

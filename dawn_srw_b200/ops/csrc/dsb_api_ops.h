@@ -28,6 +28,19 @@ int dsb_adamw(float* p, const float* g, float* m, float* v, long long n, const f
 // out[0] += sum(g^2)
 int dsb_sqnorm_accumulate(const float* g, long long n, float* out, cudaStream_t stream);
 
+// out[t, :] = tok[ids[t], :] + pos[t % S, :]  (fp32, D % 4 == 0; ids clamped to [0, V)).
+int dsb_embed_fwd(const long long* ids, const float* tok, const float* pos, float* out, int T, int S,
+                  int D, int V, cudaStream_t stream);
+// dtok[ids[t], :] += dy[t, :] (dtok zeroed by the caller); dpos[s, :] = sum_b dy[b*S+s, :].
+int dsb_embed_bwd(const long long* ids, const float* dy, float* dtok, float* dpos, int B, int S,
+                  int D, int V, cudaStream_t stream);
+// total[0] += sum_{i != j} |sim_ij|; sgn (bf16 [m, ld_s]) = sign(sim) off the diagonal, 0 on it.
+int dsb_offdiag_abs(const float* sim, long long ld, int m, void* sgn_bf16, long long ld_s,
+                    float* total, cudaStream_t stream);
+// dy_bf = bf16(dy * row_scale[t]); rowdot[t] = <dy[t], y[t]>   (dy, y fp32 [T, D], D % 4 == 0)
+int dsb_route_bwd_prologue(const float* dy, const float* y, const float* row_scale,
+                           void* dy_bf16, float* rowdot, int T, int D, cudaStream_t stream);
+
 // Causal self-attention (tcgen05 kernels).  q, k, v, out, d_out: bf16 [B, S, H*dh]
 // (head h in columns [h*dh, (h+1)*dh)); dh a multiple of 16, at most 128.
 // lse, delta: fp32 [B, H, S] (delta is scratch filled by the backward call).

@@ -193,6 +193,114 @@ __global__ void sqnorm_kernel(const float* __restrict__ g, long long n, float* _
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Token + position embedding.  out[t, :] = tok[ids[t], :] + pos[t % S, :]
+// (models/dawn_spatial_v41_exp.py:1504-1507).  One warp per token, float4 lanes.
+__global__ void embed_fwd_kernel(const long long* __restrict__ ids, const float* __restrict__ tok,
+                                 const float* __restrict__ pos, float* __restrict__ out, int T,
+                                 int S, int D, int V) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  long long id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const float4* a = reinterpret_cast<const float4*>(tok + static_cast<size_t>(id) * D);
+  const float4* b = reinterpret_cast<const float4*>(pos + static_cast<size_t>(t % S) * D);
+  float4* o = reinterpret_cast<float4*>(out + static_cast<size_t>(t) * D);
+  for (int i = lane; i < (D >> 2); i += 32) {
+    const float4 x = a[i], y = b[i];
+    o[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  }
+}
+
+// dtok[ids[t], :] += dy[t, :] (atomic: a token may repeat), one warp per token.
+__global__ void embed_bwd_tok_kernel(const long long* __restrict__ ids, const float* __restrict__ dy,
+                                     float* __restrict__ dtok, int T, int D, int V) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  long long id = ids[t];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const float* g = dy + static_cast<size_t>(t) * D;
+  float* d = dtok + static_cast<size_t>(id) * D;
+  for (int i = lane; i < D; i += 32) atomicAdd(d + i, g[i]);
+}
+
+// dpos[s, :] = sum_b dy[b*S + s, :]; one thread per (s, column), fixed order.
+__global__ void embed_bwd_pos_kernel(const float* __restrict__ dy, float* __restrict__ dpos, int B,
+                                     int S, int D) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(S) * D) return;
+  float acc = 0.f;
+  for (int b = 0; b < B; ++b) acc += dy[static_cast<size_t>(b) * S * D + idx];
+  dpos[idx] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// Off-diagonal |cos| statistics of a similarity matrix sim [m, m] (fp32, row
+// stride ld): total[0] += sum_{i != j} |sim_ij|, and sgn[i, j] = sign(sim_ij)
+// (0 on the diagonal) as bf16 for the backward GEMM.
+__global__ void offdiag_abs_kernel(const float* __restrict__ sim, long long ld, int m,
+                                   __nv_bfloat16* __restrict__ sgn, long long ld_s,
+                                   float* __restrict__ total) {
+  float acc = 0.f;
+  const long long n = static_cast<long long>(m) * m;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long k = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; k < n;
+       k += stride) {
+    const int i = static_cast<int>(k / m), j = static_cast<int>(k % m);
+    const float v = sim[i * ld + j];
+    float sg = 0.f;
+    if (i != j) {
+      acc += fabsf(v);
+      sg = v > 0.f ? 1.f : (v < 0.f ? -1.f : 0.f);
+    }
+    sgn[i * ld_s + j] = __float2bfloat16(sg);
+  }
+  acc = warp_sum(acc);
+  __shared__ float sh[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sh[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int k = 0; k < (blockDim.x >> 5); ++k) t += sh[k];
+    atomicAdd(total, t);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Backward prologue of a scaled, sum-normalised SRW route y = s * raw / den:
+//   dy_bf[t, :] = bf16(dy[t, :] * row_scale[t])        (row_scale = s / max(den, 1))
+//   rowdot[t]   = sum_d dy[t, d] * y[t, d]             (feeds d_den and d_s)
+// One warp per row; dy and y fp32.
+__global__ void route_bwd_prologue_kernel(const float* __restrict__ dy, const float* __restrict__ y,
+                                          const float* __restrict__ row_scale,
+                                          __nv_bfloat16* __restrict__ dy_bf,
+                                          float* __restrict__ rowdot, int T, int D) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float rs = row_scale[t];
+  const float4* g = reinterpret_cast<const float4*>(dy + static_cast<size_t>(t) * D);
+  const float4* yy = reinterpret_cast<const float4*>(y + static_cast<size_t>(t) * D);
+  uint2* o = reinterpret_cast<uint2*>(dy_bf + static_cast<size_t>(t) * D);
+  float acc = 0.f;
+  for (int i = lane; i < (D >> 2); i += 32) {
+    const float4 a = g[i], b = yy[i];
+    acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * rs, a.y * rs);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(a.z * rs, a.w * rs);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&lo);
+    w.y = *reinterpret_cast<uint32_t*>(&hi);
+    o[i] = w;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) rowdot[t] = acc;
+}
+
 inline int grid_for(long long n, int block, int cap) {
   long long g = (n + block - 1) / block;
   return static_cast<int>(g < cap ? (g < 1 ? 1 : g) : cap);
@@ -251,5 +359,42 @@ extern "C" int dsb_sqnorm_accumulate(const float* g, long long n, float* out,
                                      cudaStream_t stream) {
   if (n <= 0) return 0;
   sqnorm_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(g, n, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_embed_fwd(const long long* ids, const float* tok, const float* pos, float* out,
+                             int T, int S, int D, int V, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D & 3) return 2;
+  embed_fwd_kernel<<<(T + 7) / 8, 256, 0, stream>>>(ids, tok, pos, out, T, S, D, V);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_embed_bwd(const long long* ids, const float* dy, float* dtok, float* dpos, int B,
+                             int S, int D, int V, cudaStream_t stream) {
+  const int T = B * S;
+  if (T <= 0) return 0;
+  embed_bwd_tok_kernel<<<(T + 7) / 8, 256, 0, stream>>>(ids, dy, dtok, T, D, V);
+  const long long n = static_cast<long long>(S) * D;
+  embed_bwd_pos_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(dy, dpos, B, S, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_offdiag_abs(const float* sim, long long ld, int m, void* sgn_bf16,
+                               long long ld_s, float* total, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  const long long n = static_cast<long long>(m) * m;
+  offdiag_abs_kernel<<<grid_for(n, 256, 148 * 8), 256, 0, stream>>>(
+      sim, ld, m, reinterpret_cast<__nv_bfloat16*>(sgn_bf16), ld_s, total);
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+extern "C" int dsb_route_bwd_prologue(const float* dy, const float* y, const float* row_scale,
+                                      void* dy_bf16, float* rowdot, int T, int D,
+                                      cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D & 3) return 2;
+  route_bwd_prologue_kernel<<<(T + 7) / 8, 256, 0, stream>>>(
+      dy, y, row_scale, reinterpret_cast<__nv_bfloat16*>(dy_bf16), rowdot, T, D);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }

@@ -294,6 +294,70 @@ class _SRWRouteFn(torch.autograd.Function):
                 None, None, None)
 
 
+class _SRWRouteScaledFn(torch.autograd.Function):
+    """One SRW route with the sum-normalisation and the pool scale folded into
+    the write GEMM's epilogue: ``y = scale * (p . write) / max(den, 1)`` leaves
+    the engine as the final fp32 output (no [T, D] pass for the divide or the
+    scale).  Backward starts with one row kernel that produces the bf16
+    ``dy * scale / max(den, 1)`` operand and ``<dy, y>`` per row, from which the
+    denominator and scale gradients follow:
+        d_den = -<dy, y> / den  (den > 1),   d_scale = sum_t <dy, y> / scale.
+    Only for unsharded pools (the denominator is complete on this rank)."""
+
+    @staticmethod
+    def forward(ctx, x_bf, h_bf, tau, inv_sd, anchor, holder, spec, U, alive, unit_mask, scale):
+        e = ext()
+        dev = x_bf.device
+        T, D = x_bf.shape
+        Up = _round_up(U, 8)
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)           # scratch
+        den = torch.zeros(T, dtype=torch.float32, device=dev)
+        count_launches(2)
+        e.srw_fwd_gate(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, tau, inv_sd, den, None,
+                       alive, unit_mask, _gate_list(spec), status_word(dev))
+        rs = (scale.detach().float() / den.clamp(min=1.0)).contiguous()
+        y = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32, row_scale=rs)
+        ctx.save_for_backward(x_bf, h_bf, tau, inv_sd, y, den, rs, scale)
+        ctx.holder, ctx.spec, ctx.U = holder, spec, U
+        return y, den
+
+    @staticmethod
+    def backward(ctx, d_y, d_den_ext):
+        x_bf, h_bf, tau, inv_sd, y, den, rs, scale = ctx.saved_tensors
+        hd, spec, U = ctx.holder, ctx.spec, ctx.U
+        e = ext()
+        dev = x_bf.device
+        T, D = x_bf.shape
+        Up = _round_up(U, 8)
+        dy, rowdot = e.route_bwd_prologue(d_y.contiguous().float(), y, rs)
+        d_den = torch.where(den > 1.0, -rowdot / den.clamp(min=1.0), torch.zeros_like(rowdot))
+        if d_den_ext is not None:
+            d_den = d_den + d_den_ext.float()
+        d_scale = (rowdot.sum() / scale.detach().float()).reshape(scale.shape).to(scale.dtype) \
+            if ctx.needs_input_grad[10] else None
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+        dxr = torch.empty_like(p)
+        ds = torch.empty_like(p)
+        dtau = torch.zeros(T, dtype=torch.float32, device=dev)
+        dsz = torch.zeros(T, dtype=torch.float32, device=dev)
+        emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
+        count_launches(2)
+        e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den.contiguous(),
+                       dtau, dsz, _gate_list(spec), status_word(dev))
+        pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
+        gemm(pv, True, dy, True, out=hd.g_write[:U], accumulate=True)       # p^T dy
+        gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
+        gemm(dsv, True, h_bf, True, out=hd.g_emb[:U], accumulate=True)      # ds^T h
+        dx = gemm(dxrv, False, read, True, out_dtype=torch.bfloat16)        # dxr . read
+        dh32 = gemm(dsv, False, emb, True, out_dtype=torch.float32)         # ds . emb
+        d_isd = None
+        if spec.kind == GATE_GELU_Z:
+            dsz = inv_sd * ((h_bf.float() * dh32).sum(-1) + tau * dtau)
+            d_isd = dsz / (inv_sd * inv_sd)
+        return (dx, dh32.to(torch.bfloat16), dtau, d_isd, torch.zeros(1, device=dev), None, None,
+                None, None, None, d_scale)
+
+
 # ---------------------------------------------------------------------------
 class _LMHeadCEFn(torch.autograd.Function):
     """Tied-embedding cross entropy without keeping [T, V] logits: logits are
@@ -340,6 +404,64 @@ class _LMHeadCEFn(torch.autograd.Function):
             gemm(dl, False, emb_bf, True, out=dx[a:b])                         # dl . E
             gemm(dl, True, xb[a:b], True, out=demb, accumulate=True)           # dl^T x
         return dx, demb, None, None
+
+
+# ---------------------------------------------------------------------------
+class _EmbedFn(torch.autograd.Function):
+    """Token + position embedding gather; backward scatters with atomics into the
+    token table and sums the batch for the position table."""
+
+    @staticmethod
+    def forward(ctx, ids, tok, pos):
+        ids = ids.long().contiguous()
+        ctx.save_for_backward(ids)
+        ctx.sizes = (tok.shape[0], pos.shape[0])
+        count_launches(1)
+        return ext().embed_fwd(ids, tok.detach().contiguous(), pos.detach().contiguous())
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        count_launches(2)
+        dtok, dpos = ext().embed_bwd(ids, dy.float().contiguous(), ctx.sizes[0], ctx.sizes[1])
+        return None, dtok, dpos
+
+
+class _OffDiagAbsCosFn(torch.autograd.Function):
+    """sum_{i != j} |<n_i, n_j>| for unit rows ``n`` [m, d]: similarity matrix on
+    the tcgen05 engine (bf16 operands), |.| reduction and sign matrix in one
+    pass, gradient 2 * sign(sim) . n as a second engine GEMM."""
+
+    @staticmethod
+    def forward(ctx, n):
+        nb = _bf16_2d(n.detach())
+        sim = gemm(nb, False, nb, False, out_dtype=torch.float32)
+        total, sgn = ext().offdiag_abs(sim)
+        count_launches(1)
+        ctx.save_for_backward(nb, sgn)
+        ctx.n_dtype = n.dtype
+        return total
+
+    @staticmethod
+    def backward(ctx, g):
+        nb, sgn = ctx.saved_tensors
+        dn = gemm(sgn, False, nb, True, out_dtype=torch.float32)          # sign(sim) . n
+        return (dn * (2.0 * g)).to(ctx.n_dtype)
+
+
+def pool_diversity_cuda(tensors, max_sample: int = 4096):
+    """Mean |cos| between distinct rows per pool tensor, averaged over tensors
+    (same sampling rule as ops/reference.pool_diversity)."""
+    total = 0.0
+    for w in tensors:
+        n_rows = w.shape[0]
+        if n_rows > max_sample:
+            w = w[:: n_rows // max_sample][:max_sample]
+        wf = w.float()
+        n = wf / (torch.linalg.vector_norm(wf, dim=-1, keepdim=True) + 1e-8)
+        m = n.shape[0]
+        total = total + _OffDiagAbsCosFn.apply(n) / float(m * m - m)
+    return total / len(tensors)
 
 
 # ---------------------------------------------------------------------------
@@ -446,12 +568,20 @@ class CudaBackend:
 
     def linear(self, x, w, b=None):
         n = w.shape[0]
-        if n % 8 != 0:       # tiny heads (tau): keep them in fp32 on the library path
-            return F.linear(x.float(), w, b)
+        if n % 8 != 0:
+            # tiny heads (the tau projections): pad the output dimension to the engine's
+            # 8-column granularity; the padding rows are zero and sliced away again
+            pad = _round_up(n, 8) - n
+            wp = F.pad(w, (0, 0, 0, pad))
+            bp = F.pad(b, (0, pad)) if b is not None else None
+            y = _LinearFn.apply(x, wp, bp, wp.detach().to(torch.bfloat16), torch.float32)
+            return y[:, :n]
         return _LinearFn.apply(x, w, b, self._w(w), torch.float32)
 
     def embed(self, ids, tok, pos):
-        return R.embed(ids, tok, pos)
+        if tok.shape[1] % 4 != 0 or tok.dtype != torch.float32:
+            return R.embed(ids, tok, pos)
+        return _EmbedFn.apply(ids, tok, pos)
 
     def dropout(self, x, p, training):
         return R.dropout(x, p, training)
@@ -486,7 +616,7 @@ class CudaBackend:
         return lg.reshape(*shp[:-1], -1)
 
     def diversity(self, tensors):
-        return R.pool_diversity(tensors)
+        return pool_diversity_cuda(tensors)
 
     # ---- SRW pool op ---------------------------------------------------
     def prepare_pool(self, emb, read, write, spec: GateSpec, pctx: Optional[ParallelCtx] = None):
@@ -501,8 +631,73 @@ class CudaBackend:
 
     def srw(self, x, h, tau_off, pool: CudaPool, spec: GateSpec, *,
             pctx: Optional[ParallelCtx] = None, want_diag: bool = True,
-            return_gates: bool = False, unit_mask=None) -> SRWResult:
+            return_gates: bool = False, unit_mask=None, out_scale=None) -> SRWResult:
+        """``out_scale`` (float or 0-dim tensor): the pool's output scale; when
+        given, the returned route outputs are already multiplied by it."""
         pctx = pctx or ParallelCtx()
+        nsh0 = C.group_size(pctx.shard_group)
+        if return_gates or nsh0 > 1:
+            res = self._srw_unscaled(x, h, tau_off, pool, spec, pctx, want_diag, return_gates,
+                                     unit_mask)
+            if out_scale is not None:
+                res.out = res.out * out_scale
+            return res
+        return self._srw_local(x, h, tau_off, pool, spec, pctx, want_diag, unit_mask, out_scale)
+
+    def _srw_local(self, x, h, tau_off, pool, spec, pctx, want_diag, unit_mask, out_scale):
+        """Unsharded pools: statistics, then per route the gate kernel and the
+        write GEMM with normalisation and scale in its epilogue."""
+        ex = pool.extra
+        U, anchor = ex["U"], ex["anchor"]
+        U_tot = pctx.n_total if pctx.n_total is not None else U
+        T, Rr, r = h.shape
+        x_bf = _bf16_2d(x)
+        h_bf3 = h.to(torch.bfloat16)
+        hf = h_bf3.float()
+        mu = hf @ (ex["esum"] / U_tot)                                     # [T,R]
+        m2 = ((hf @ ex["gram"]) * hf).sum(-1) / U_tot
+        sd = torch.sqrt((m2 - mu * mu).clamp_min(0.0)) + 1e-8
+        tau = mu + tau_off * sd
+        inv_sd = 1.0 / sd
+        hbar = hf.mean(dim=(0, 1))
+        m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
+        ns_sum = C.mean_over_group(m_u.sum(), pctx.dp_group)
+        ns_sq = C.mean_over_group((m_u * m_u).sum(), pctx.dp_group)
+        mean_score = ns_sum / U_tot
+        var_score = ns_sq / U_tot - mean_score ** 2
+        lb = var_score / (mean_score ** 2 + var_score + 1e-2)
+        alive = torch.zeros(U, dtype=torch.uint8, device=x.device) if spec.has_dead_penalty else None
+        um = None if unit_mask is None else unit_mask[:U].float().contiguous()
+        if out_scale is None:
+            scale = torch.ones((), device=x.device)
+        elif isinstance(out_scale, torch.Tensor):
+            scale = out_scale
+        else:
+            scale = torch.full((), float(out_scale), device=x.device)
+        outs, dens = [], []
+        for ri in range(Rr):
+            y, den = _SRWRouteScaledFn.apply(x_bf, _bf16_2d(h_bf3[:, ri]), tau[:, ri].contiguous(),
+                                             inv_sd[:, ri].contiguous(), anchor, pool, spec, U,
+                                             alive, um, scale)
+            outs.append(y)
+            dens.append(den)
+        den = torch.stack(dens, dim=1).clamp(min=1.0)
+        dead_pen = x.new_zeros(())
+        if spec.has_dead_penalty:
+            al = C.all_reduce_nograd(alive.float(), pctx.dp_group, "max")
+            dead = (al < 0.5).float()
+            ms = C.mean_over_group(m_u, pctx.dp_group)
+            dead_pen = (torch.relu(-ms) * dead).sum()
+        diag = {}
+        if want_diag:
+            with torch.no_grad():
+                diag = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec,
+                                         ParallelCtx(None, pctx.dp_group, pctx.n_total, pctx.n_valid,
+                                                     False), True, False, unit_mask).diag
+        out = outs[0].unsqueeze(1) if Rr == 1 else None
+        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den, outs=outs)
+
+    def _srw_unscaled(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask):
         if return_gates:
             return self._srw_library(x, h, tau_off, pool, spec, pctx, True, True, unit_mask)
         ex = pool.extra

@@ -48,6 +48,14 @@ class SRWResult:
     diag: Dict[str, torch.Tensor] = field(default_factory=dict)
     gates: Optional[torch.Tensor] = None    # [T, R, U_local] raw gate (analysis)
     den: Optional[torch.Tensor] = None      # [T, R] denominator
+    outs: Optional[list] = None             # per-route [T, D] tensors when `out` was not stacked
+
+    def route(self, i: int) -> torch.Tensor:
+        """Output of route ``i`` ([T, D]) whichever way the backend stored it."""
+        return self.outs[i] if self.outs is not None else self.out[:, i]
+
+    def stacked(self) -> torch.Tensor:
+        return self.out if self.out is not None else torch.stack(self.outs, dim=1)
 
 
 def normalize_rows(w: torch.Tensor) -> torch.Tensor:

@@ -53,7 +53,7 @@ def run_case(N, d, U, r, version, iters, only_fwd=False):
         pool = be.prepare_pool(emb, read, write, spec, ParallelCtx())
         res = be.srw(x, h, off, pool, spec, pctx=ParallelCtx(), want_diag=False)
         if backward:
-            (res.out * w).sum().backward()
+            (res.stacked() * w).sum().backward()
         return res
     times = {}
     for name, bwd in (("fwd", False), ("fwd_bwd", True)):
