@@ -1,0 +1,285 @@
+#!/usr/bin/env python
+"""Analysis suite for a trained DAWN-SRW checkpoint.
+
+    python -m dawn_srw_b200.tools.analyze --checkpoint run/best_model.pt [--config cfg.yaml]
+        [--bin-val val.bin | --synthetic] [--only info,health,...] [--skip weights]
+        [--batch-size 8] [--n-batches 4] [--output out_dir]
+
+Analyses (``--only`` / ``--skip`` keys), each a function returning a JSON-able
+dict; the selection mirrors the SRW part of the reference's analysis CLI
+(scripts/analysis/standalone/spatial_analysis.py:6933-7287):
+
+  info         parameter counts, configuration, forward FLOPs per token
+  val          validation loss / perplexity / accuracy
+  health       pool norm statistics, dead rows, scales, tau biases
+  weights      pairwise |cos| summary and effective rank per pool tensor
+  generate     sampled continuations (temperature / top-k, KV cache)
+  routing      per layer and route: active units per token, gate entropy, top-1 mass
+  gate_dist    quantiles of the raw gate values per route
+  utilization  fraction of units ever selected, per pool and per layer
+  sel_gini     Gini coefficient of per-unit selection frequency
+  layer_role   attention vs knowledge output norm per layer
+  intervene    loss change when the most-used knowledge units are suppressed
+  pool_geom    spectrum of the pool embeddings (variance explained by top directions)
+
+All analyses run on one device through the model's public inference API
+(models/inference.py).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+from typing import Callable, Dict, List
+
+import torch
+
+from ..data.loaders import BinDataLoader, BinDataset, SyntheticDataset
+from ..models import inference as I
+from .common import load_model, tokenizer_or_none
+
+ROUTES = ("Q", "K", "V", "Know")
+POOL_OF = {"Q": "qk", "K": "qk", "V": "v", "Know": "know"}
+
+
+class Context:
+    def __init__(self, model, cfg, info, args):
+        self.model, self.cfg, self.info, self.args = model, cfg, info, args
+        self.device = next(model.parameters()).device
+        self._batches = None
+        self._gates = None
+
+    def batches(self) -> List[torch.Tensor]:
+        if self._batches is None:
+            a, S = self.args, self.cfg.model.max_seq_len
+            if a.synthetic or not a.bin_val:
+                ds = SyntheticDataset(a.batch_size * a.n_batches, S, self.cfg.model.vocab_size, seed=1)
+            else:
+                ds = BinDataset(a.bin_val, S, self.cfg.data.max_val_tokens)
+            loader = BinDataLoader(ds, a.batch_size, pin=False)
+            self._batches = [loader.batch(i)[0].to(self.device).long()
+                             for i in range(min(a.n_batches, len(loader)))]
+        return self._batches
+
+    def gates(self) -> Dict[str, torch.Tensor]:
+        """analysis_forward(mode='full') of the first batch (cached)."""
+        if self._gates is None:
+            self._gates = I.analysis_forward(self.model, self.batches()[0], mode="full")
+        return self._gates
+
+
+# ---------------------------------------------------------------------------
+def analyze_info(c: Context) -> Dict:
+    m = c.model
+    n_params = sum(p.numel() for p in m.parameters())
+    pool = sum(p.numel() for n, p in m.named_parameters() if "neuron_pool" in n)
+    out = {"parameters": n_params, "pool_parameters": pool, "config": m.get_config(),
+           "checkpoint": c.info}
+    if hasattr(m, "n_know"):
+        out["flops_per_token"] = I.estimate_flops_per_token(m)
+    return out
+
+
+def analyze_val(c: Context) -> Dict:
+    loss, ppl, acc, n = I.vectorized_eval(c.model, iter(c.batches()))
+    return {"val_loss": loss, "ppl": ppl, "accuracy_pct": acc, "valid_tokens": n}
+
+
+def analyze_health(c: Context) -> Dict:
+    return I.neuron_health(c.model)
+
+
+def analyze_weights(c: Context) -> Dict:
+    return I.weight_analysis(c.model, max_rows=c.args.max_rows)
+
+
+def analyze_generate(c: Context) -> Dict:
+    a = c.args
+    tok = tokenizer_or_none()
+    prompts = a.prompt or ["the"]
+    outs = []
+    for ptxt in prompts:
+        if tok is not None:
+            ids = torch.tensor([tok.encode(ptxt, add_special_tokens=False)], device=c.device)
+        else:
+            ids = c.batches()[0][:1, :8]
+        gen, stats = I.generate(c.model, ids, max_new_tokens=a.max_new_tokens,
+                                temperature=a.temperature, top_k=a.top_k)
+        rec = {"prompt": ptxt, "token_ids": gen[0].tolist(),
+               "tokens_per_sec": stats["tokens_per_sec"]}
+        if tok is not None:
+            rec["text"] = tok.decode(gen[0].tolist())
+        outs.append(rec)
+    return {"samples": outs, "tokenizer": "bert-base-uncased" if tok is not None else None}
+
+
+def analyze_routing(c: Context) -> Dict:
+    g = c.gates()
+    out = {}
+    for r in ROUTES:
+        raw, nrm = g[f"gate_{r}_raw"], g[f"gate_{r}"]                # [L,B,S,N]
+        active = (raw > 0).float().sum(-1)                           # units per token
+        ent = -(nrm * torch.log(nrm.clamp(min=1e-12))).sum(-1)
+        out[r] = {"active_per_token_mean": active.mean(dim=(1, 2)).tolist(),
+                  "active_per_token_std": active.std(dim=(1, 2), unbiased=False).tolist(),
+                  "gate_entropy": ent.mean(dim=(1, 2)).tolist(),
+                  "top1_mass": nrm.max(-1).values.mean(dim=(1, 2)).tolist(),
+                  "n_units": int(raw.shape[-1])}
+    return out
+
+
+def analyze_gate_dist(c: Context) -> Dict:
+    g = c.gates()
+    qs = torch.tensor([0.5, 0.9, 0.99, 0.999], device=c.device)
+    out = {}
+    for r in ROUTES:
+        raw = g[f"gate_{r}_raw"].float()
+        pos = raw[raw > 0]
+        rec = {"zero_frac": float((raw <= 0).float().mean()), "max": float(raw.max())}
+        if pos.numel():
+            sample = pos[torch.randint(0, pos.numel(), (min(pos.numel(), 1_000_000),), device=pos.device)]
+            for q, v in zip(qs.tolist(), torch.quantile(sample, qs).tolist()):
+                rec[f"p{q * 100:g}"] = v
+            rec["mean_active"] = float(pos.mean())
+        out[r] = rec
+    return out
+
+
+def _selection_counts(c: Context) -> Dict[str, torch.Tensor]:
+    """Per route: [L, N] number of tokens that selected each unit."""
+    g = c.gates()
+    return {r: (g[f"gate_{r}_raw"] > 0).float().sum(dim=(1, 2)) for r in ROUTES}
+
+
+def analyze_utilization(c: Context) -> Dict:
+    cnt = _selection_counts(c)
+    out = {}
+    for r in ROUTES:
+        k = cnt[r]
+        out[r] = {"used_frac_per_layer": (k > 0).float().mean(-1).tolist(),
+                  "used_frac_any_layer": float((k.sum(0) > 0).float().mean()),
+                  "never_used": int((k.sum(0) == 0).sum())}
+    return out
+
+
+def _gini(x: torch.Tensor) -> float:
+    x = torch.sort(x.flatten().double()).values
+    n = x.numel()
+    if n == 0 or float(x.sum()) == 0.0:
+        return 0.0
+    idx = torch.arange(1, n + 1, dtype=torch.double, device=x.device)
+    return float(((2 * idx - n - 1) * x).sum() / (n * x.sum()))
+
+
+def analyze_sel_gini(c: Context) -> Dict:
+    cnt = _selection_counts(c)
+    return {r: {"gini_all_layers": _gini(cnt[r].sum(0)),
+                "gini_per_layer": [_gini(row) for row in cnt[r]]} for r in ROUTES}
+
+
+def analyze_layer_role(c: Context) -> Dict:
+    g = c.gates()
+    a, k = g["attn_out_norm"], g["know_out_norm"]
+    return {"attn_out_norm": a.tolist(), "know_out_norm": k.tolist(),
+            "know_share": (k / (a + k).clamp(min=1e-12)).tolist()}
+
+
+def _mean_loss(logits: torch.Tensor, ids: torch.Tensor) -> float:
+    lp = torch.log_softmax(logits[:, :-1].float(), -1)
+    return float(-lp.gather(-1, ids[:, 1:].unsqueeze(-1)).mean())
+
+
+def analyze_intervene(c: Context) -> Dict:
+    m, ids = c.model, c.batches()[0]
+    cnt = _selection_counts(c)["Know"].sum(0)
+    base = _mean_loss(c.gates()["logits"], ids)
+    out = {"baseline_loss": base, "suppressed": []}
+    for k in c.args.suppress_top:
+        k = min(int(k), cnt.numel())
+        mask = torch.zeros(m.neuron_pool.know_emb.shape[0], dtype=torch.bool, device=c.device)
+        mask[torch.topk(cnt, k).indices] = True
+        logits = I.build_suppressed_forward(m, {"know": mask})(ids)
+        rnd = torch.zeros_like(mask)
+        rnd[torch.randperm(cnt.numel(), device=c.device)[:k]] = True
+        logits_r = I.build_suppressed_forward(m, {"know": rnd})(ids)
+        out["suppressed"].append({"k": k, "loss_top_used": _mean_loss(logits, ids),
+                                  "loss_random": _mean_loss(logits_r, ids)})
+    return out
+
+
+def analyze_pool_geom(c: Context) -> Dict:
+    out = {}
+    p = c.model.neuron_pool
+    for name in ("qk", "v", "know"):
+        e = getattr(p, f"{name}_emb")[: p.n_valid(name)].float()
+        e = e - e.mean(0, keepdim=True)
+        sv = torch.linalg.svdvals(e.cpu())
+        var = sv.square() / sv.square().sum()
+        out[name] = {"top8_variance": var[:8].tolist(),
+                     "dims_for_90pct": int((var.cumsum(0) < 0.9).sum()) + 1,
+                     "participation_ratio": float(1.0 / var.square().sum())}
+    return out
+
+
+ANALYSES: Dict[str, Callable[[Context], Dict]] = {
+    "info": analyze_info, "val": analyze_val, "health": analyze_health, "weights": analyze_weights,
+    "generate": analyze_generate, "routing": analyze_routing, "gate_dist": analyze_gate_dist,
+    "utilization": analyze_utilization, "sel_gini": analyze_sel_gini,
+    "layer_role": analyze_layer_role, "intervene": analyze_intervene, "pool_geom": analyze_pool_geom,
+}
+SPATIAL_ONLY = {"health", "weights", "routing", "gate_dist", "utilization", "sel_gini", "layer_role",
+                "intervene", "pool_geom"}
+
+
+def run(model, cfg, info, args) -> Dict:
+    keys = [k for k in (args.only.split(",") if args.only else ANALYSES) if k]
+    skip = set(args.skip.split(",")) if args.skip else set()
+    unknown = [k for k in keys if k not in ANALYSES]
+    if unknown:
+        raise SystemExit(f"unknown analysis key(s) {unknown}; choose from {sorted(ANALYSES)}")
+    ctx = Context(model, cfg, info, args)
+    results = {}
+    for k in keys:
+        if k in skip or (k in SPATIAL_ONLY and not cfg.model.is_spatial):
+            continue
+        with torch.no_grad():
+            results[k] = ANALYSES[k](ctx)
+    return results
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
+    ap.add_argument("--checkpoint")
+    ap.add_argument("--config")
+    ap.add_argument("--bin-val")
+    ap.add_argument("--synthetic", action="store_true")
+    ap.add_argument("--only", default="")
+    ap.add_argument("--skip", default="")
+    ap.add_argument("--batch-size", type=int, default=8)
+    ap.add_argument("--n-batches", type=int, default=4)
+    ap.add_argument("--max-rows", type=int, default=2048)
+    ap.add_argument("--prompt", action="append")
+    ap.add_argument("--max-new-tokens", type=int, default=32)
+    ap.add_argument("--temperature", type=float, default=0.8)
+    ap.add_argument("--top-k", type=int, default=50)
+    ap.add_argument("--suppress-top", type=int, nargs="*", default=[16, 128])
+    ap.add_argument("--output")
+    ap.add_argument("--library", action="store_true")
+    ap.add_argument("--device")
+    args = ap.parse_args(argv)
+    model, cfg, info = load_model(args.checkpoint, args.config, device=args.device,
+                                  library=args.library)
+    results = run(model, cfg, info, args)
+    text = json.dumps(results, indent=2, default=lambda o: o if not isinstance(o, float) or math.isfinite(o) else None)
+    if args.output:
+        os.makedirs(args.output, exist_ok=True)
+        with open(os.path.join(args.output, "analysis.json"), "w") as f:
+            f.write(text)
+    print(text)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,63 @@
+"""Command-line tools on CPU: pretokenize -> train -> analyze / eval / generate."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import tiny_config
+
+
+def test_pretokenize_packs_rows_and_resumes(tmp_path):
+    from dawn_srw_b200.data.loaders import ShardedBinDataset
+    from dawn_srw_b200.tools import pretokenize as P
+    txt = tmp_path / "docs.txt"
+    txt.write_text("\n".join(f"document number {i} " + "x" * (i % 17) for i in range(200)))
+    out = str(tmp_path / "tok" / "train")
+    assert P.main(["--input", str(txt), "--output", out, "--seq-len", "16", "--shard-tokens", "640",
+                   "--tokenizer", "bytes"]) == 0
+    meta = json.load(open(out + "_meta.json"))
+    assert meta["complete"] and meta["seq_len"] == 16 and len(meta["shards"]) > 1
+    ds = ShardedBinDataset(out + "_meta.json", 16)
+    rows = ds.rows(0, len(ds))
+    stream = rows.reshape(-1)
+    want = []
+    for i in range(200):
+        want += list((f"document number {i} " + "x" * (i % 17)).strip().encode()) + [256]
+    assert np.array_equal(stream, np.asarray(want[: len(stream)], dtype=np.uint16))   # packed, no padding
+    # resume: drop the last shard and its meta entry, run again, same shard count
+    last = meta["shards"][-1]
+    os.remove(os.path.join(os.path.dirname(out), last["path"]))
+    assert P.main(["--input", str(txt), "--output", out, "--seq-len", "16", "--shard-tokens", "640",
+                   "--tokenizer", "bytes", "--resume"]) == 0
+    meta2 = json.load(open(out + "_meta.json"))
+    assert meta2["complete"] and len(meta2["shards"]) >= len(meta["shards"]) - 1
+
+
+def test_analysis_cli_runs_every_key(tmp_path):
+    from dawn_srw_b200.tools import analyze as A
+    from dawn_srw_b200.train.trainer import Trainer
+    cfg = tiny_config(version="spatial-r1-v4.0.1", max_steps=2)
+    tr = Trainer(cfg, run_dir=str(tmp_path / "run"), total_steps=2)
+    os.makedirs(tr.run_dir, exist_ok=True)
+    ids, mask = tr.train_loader.batch(0)
+    tr.train_step(ids, mask)
+    path = tr.save("checkpoint_step1.pt")
+    out_dir = str(tmp_path / "ana")
+    assert A.main(["--checkpoint", path, "--synthetic", "--batch-size", "2", "--n-batches", "2",
+                   "--suppress-top", "4", "--max-new-tokens", "4", "--output", out_dir,
+                   "--device", "cpu"]) == 0
+    res = json.load(open(os.path.join(out_dir, "analysis.json")))
+    assert set(res) == set(A.ANALYSES)
+    assert res["info"]["parameters"] > 0 and res["val"]["val_loss"] > 0
+    L = cfg.model.n_layers
+    assert len(res["routing"]["Know"]["gate_entropy"]) == L
+    assert 0.0 <= res["utilization"]["Know"]["used_frac_any_layer"] <= 1.0
+    assert 0.0 <= res["sel_gini"]["Q"]["gini_all_layers"] <= 1.0
+    assert len(res["intervene"]["suppressed"]) == 1
+    assert len(res["generate"]["samples"][0]["token_ids"]) >= 4
+    # key selection
+    assert A.main(["--checkpoint", path, "--synthetic", "--only", "info,health", "--device", "cpu"]) == 0
+    with pytest.raises(SystemExit):
+        A.main(["--checkpoint", path, "--only", "nope", "--device", "cpu"])
