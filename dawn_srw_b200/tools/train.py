@@ -53,6 +53,8 @@ def main(argv=None):
     ap.add_argument("--synthetic", action="store_true", help="uniform-random tokens instead of files")
     ap.add_argument("--library", action="store_true", help="library baseline backend (torch matmuls)")
     ap.add_argument("--debug", action="store_true")
+    ap.add_argument("--no-startup-check", action="store_true",
+                    help="skip the start-up memory check and per-block timing table")
     args = ap.parse_args(argv)
 
     cfg = load_config(args.config)
@@ -90,6 +92,9 @@ def main(argv=None):
     if resume_path:
         trainer.resume(resume_path)
         trainer.logger.message(f"Resumed from {resume_path} at step {trainer.global_step}")
+    if not args.no_startup_check:
+        from ..train.startup import startup_report
+        startup_report(trainer, print_fn=trainer.logger.message)
     out = trainer.fit()
     if topo.is_main:
         print(json.dumps({"final": out, "run_dir": run_dir}))

@@ -123,3 +123,17 @@ def test_gradient_accumulation_in_the_trainer():
     pa, pb = _params(a), _params(b)
     for n in pa:
         assert torch.allclose(pa[n], pb[n], atol=2e-6), n
+
+
+def test_startup_report_leaves_training_state_untouched():
+    from dawn_srw_b200.train.startup import startup_report
+    tr = Trainer(tiny_config(version="spatial-r1-v4.0.1"), total_steps=50)
+    before = _params(tr)
+    lines = []
+    rep = startup_report(tr, n_runs=1, print_fn=lines.append)
+    assert rep["fwd_bwd_ms"] > 0 and rep["eta_hours"] > 0
+    assert set(rep["ops_forward_ms"]) >= {"layer_norm", "srw_know", "self_attention"}
+    assert any("forward+backward" in l for l in lines)
+    for n, p in _params(tr).items():
+        assert torch.equal(p, before[n]), n
+    assert tr.optimizer.count == 0 and all(p.grad is None for p in tr.model.parameters())
