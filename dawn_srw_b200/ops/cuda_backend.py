@@ -637,9 +637,9 @@ class CudaBackend:
         pctx = pctx or ParallelCtx()
         nsh0 = C.group_size(pctx.shard_group)
         if return_gates or nsh0 > 1:
-            res = self._srw_unscaled(x, h, tau_off, pool, spec, pctx, want_diag, return_gates,
-                                     unit_mask)
-            if out_scale is not None:
+            res, scaled = self._srw_unscaled(x, h, tau_off, pool, spec, pctx, want_diag,
+                                             return_gates, unit_mask, out_scale)
+            if out_scale is not None and not scaled:
                 res.out = res.out * out_scale
             return res
         return self._srw_local(x, h, tau_off, pool, spec, pctx, want_diag, unit_mask, out_scale)
@@ -697,9 +697,11 @@ class CudaBackend:
         out = outs[0].unsqueeze(1) if Rr == 1 else None
         return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den, outs=outs)
 
-    def _srw_unscaled(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask):
+    def _srw_unscaled(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask,
+                      out_scale=None):
+        """Sharded pools (and gate dumps).  Returns (result, scale_applied)."""
         if return_gates:
-            return self._srw_library(x, h, tau_off, pool, spec, pctx, True, True, unit_mask)
+            return self._srw_library(x, h, tau_off, pool, spec, pctx, True, True, unit_mask), False
         ex = pool.extra
         U, anchor = ex["U"], ex["anchor"]
         nsh = C.group_size(pctx.shard_group)
@@ -708,7 +710,8 @@ class CudaBackend:
         if seq and self.fused_comm and unit_mask is None and not spec.has_dead_penalty \
                 and x.shape[0] % 256 == 0 and x.shape[1] % 64 == 0 and h.shape[-1] % 64 == 0 \
                 and nsh <= 8:
-            return self._srw_fused_sharded(x, h, tau_off, pool, spec, pctx, want_diag)
+            return self._srw_fused_sharded(x, h, tau_off, pool, spec, pctx, want_diag,
+                                           out_scale), True
         if seq:
             x = C.gather_tokens(x, pctx.shard_group)
             h = C.gather_tokens(h, pctx.shard_group)
@@ -767,9 +770,9 @@ class CudaBackend:
                                         ParallelCtx(pctx.shard_group, pctx.dp_group, pctx.n_total,
                                                     pctx.n_valid, False), True, False, unit_mask)
                 diag = lib.diag
-        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den)
+        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den), False
 
-    def _srw_fused_sharded(self, x, h, tau_off, pool, spec, pctx, want_diag):
+    def _srw_fused_sharded(self, x, h, tau_off, pool, spec, pctx, want_diag, out_scale=None):
         """Sequence- and pool-sharded route through the kernels with fused
         collectives (parallel/fused_srw.py).  x/h/tau_off hold this rank's tokens."""
         from ..parallel.fused_srw import FusedShardComm, _SRWRouteGatherFn
@@ -799,15 +802,21 @@ class CudaBackend:
         mean_score = ns_sum / U_tot
         var_score = ns_sq / U_tot - mean_score ** 2
         lb = var_score / (mean_score ** 2 + var_score + 1e-2)
+        if out_scale is None:
+            scale = torch.ones((), device=x.device)
+        elif isinstance(out_scale, torch.Tensor):
+            scale = out_scale
+        else:
+            scale = torch.full((), float(out_scale), device=x.device)
         outs, dens = [], []
         for ri in range(Rr):
             tau_f = C.gather_tokens(tau[:, ri].contiguous(), grp)
             isd_f = C.gather_tokens(inv_sd[:, ri].contiguous(), grp)
             o, d = _SRWRouteGatherFn.apply(x_bf, _bf16_2d(h_bf3[:, ri]), tau_f, isd_f, anchor, pool,
-                                           spec, U, comm)
+                                           spec, U, comm, scale)
             outs.append(o)
             dens.append(d[comm.rows])
-        out = torch.stack(outs, dim=1)                                    # [Tl,R,D], normalised
+        out = outs[0].unsqueeze(1) if Rr == 1 else None       # [Tl,R,D], normalised and scaled
         den = torch.stack(dens, dim=1).clamp(min=1.0)
         dead_pen = x.new_zeros(())     # gates with a dead-unit penalty take the NCCL path
         diag = {}
@@ -816,7 +825,7 @@ class CudaBackend:
                 lib = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec, pctx,
                                         True, False, None)
                 diag = lib.diag
-        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den)
+        return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den, outs=outs)
 
     def _srw_library(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask):
         """The same op through torch matmuls (diagnostics / gate dumps only)."""

@@ -86,7 +86,7 @@ class FusedShardComm:
 
 class _SRWRouteGatherFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x_bf, h_bf, tau_full, inv_sd_full, anchor, holder, spec, U, comm):
+    def forward(ctx, x_bf, h_bf, tau_full, inv_sd_full, anchor, holder, spec, U, comm, scale):
         from ..ops import cuda_backend as CB
         e, dev = CB.ext(), x_bf.device
         st = CB.status_word(dev)
@@ -106,13 +106,13 @@ class _SRWRouteGatherFn(torch.autograd.Function):
                               inv_sd_full, den, gl, st, [xf.ptrs, hf.ptrs], c.rank, Tl, c.ready,
                               c.next_epoch())
         dist.all_reduce(den, group=c.group)              # [T] fp32
-        inv_den = 1.0 / den.clamp(min=1.0)
+        inv_den = (scale.detach().float() / den.clamp(min=1.0)).contiguous()   # pool scale folded in
         tgt = c.out_rs[c.next_rs("out")]
         e.gemm_scatter(p[:, :U], False, holder.write[:U], True, tgt.ptrs, Tl, D, 1.0, inv_den, st)
         c.ws.barrier()                                   # every rank's contributions have landed
         out = tgt.local.clone()
         tgt.local.zero_()                                # ready for its next use, two ops from now
-        ctx.save_for_backward(x_bf, h_bf, tau_full, inv_sd_full, den, out)
+        ctx.save_for_backward(x_bf, h_bf, tau_full, inv_sd_full, den, out, scale)
         ctx.holder, ctx.spec, ctx.U, ctx.comm = holder, spec, U, c
         ctx.mark_non_differentiable(den)
         return out, den
@@ -120,21 +120,26 @@ class _SRWRouteGatherFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_out, _d_den):
         from ..ops import cuda_backend as CB
-        x_bf, h_bf, tau_full, inv_sd_full, den, out = ctx.saved_tensors
+        x_bf, h_bf, tau_full, inv_sd_full, den, out, scale = ctx.saved_tensors
         hd, spec, U, c = ctx.holder, ctx.spec, ctx.U, ctx.comm
         e, dev = CB.ext(), x_bf.device
         st = CB.status_word(dev)
         T, Tl, D, r = c.t_total, c.t_local, x_bf.shape[1], h_bf.shape[1]
         Up = CB._round_up(U, 8)
         den_l = den[c.rows]
-        inv_den_l = 1.0 / den_l.clamp(min=1.0)
-        d_out = d_out.float()
+        rs_l = (scale.detach().float() / den_l.clamp(min=1.0)).contiguous()
         b = c.next_buffers()
         xf, hf, dyf = c.xfull[b], c.hfull[b], c.dyfull[b]
         xf.local[c.rows].copy_(x_bf)
         hf.local[c.rows].copy_(h_bf)
-        dyf.local[c.rows].copy_(d_out * inv_den_l[:, None])
-        dden_l = -(d_out * out).sum(-1) * inv_den_l * (den_l > 1.0)
+        # one pass over (d_out, out): bf16 dy * scale / den, and <d_out, out> per token, which
+        # gives the denominator and scale gradients (out = scale * raw / den)
+        dyb, rowdot = e.route_bwd_prologue(d_out.float().contiguous(), out, rs_l)
+        CB.count_launches(1)
+        dyf.local[c.rows].copy_(dyb)
+        dden_l = torch.where(den_l > 1.0, -rowdot / den_l.clamp(min=1.0), torch.zeros_like(rowdot))
+        d_scale = (rowdot.sum() / scale.detach().float()).reshape(scale.shape).to(scale.dtype) \
+            if ctx.needs_input_grad[9] else None
         dden = torch.empty(T, dtype=torch.float32, device=dev)
         dist.all_gather_into_tensor(dden, dden_l.contiguous(), group=c.group)
         c.ws.barrier()
@@ -172,4 +177,4 @@ class _SRWRouteGatherFn(torch.autograd.Function):
             d_isd = torch.zeros(T, dtype=torch.float32, device=dev)
             d_isd[c.rows] = dsz_l / (isd_l * isd_l)
         return (dx, dh32.to(torch.bfloat16), dtau, d_isd, torch.zeros(1, device=dev), None, None,
-                None, None)
+                None, None, d_scale)

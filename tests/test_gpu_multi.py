@@ -124,14 +124,16 @@ def _fused_vs_nccl(rank, world, version):
         be = CB.CudaBackend(fused_comm=fused)
         ps = [t.clone().requires_grad_(True) for t in
               (local_pool(emb_f), local_pool(read_f), local_pool(write_f), x_f[rows], h_f[rows], off_f[rows])]
+        sc = torch.tensor(1.7, device=dev, requires_grad=True)          # learnable pool scale
         pool = be.prepare_pool(ps[0], ps[1], ps[2], spec, pctx)
-        out = be.srw(ps[3], ps[4], ps[5], pool, spec, pctx=pctx, want_diag=False)
-        ((out.out * w_f[rows]).sum() + 3.0 * out.lb).backward()
+        out = be.srw(ps[3], ps[4], ps[5], pool, spec, pctx=pctx, want_diag=False, out_scale=sc)
+        ((out.stacked() * w_f[rows]).sum() + 3.0 * out.lb).backward()
         torch.cuda.synchronize()
-        res[name] = [out.out.detach(), out.lb.detach(), out.den.detach()] + [p.grad.clone() for p in ps]
+        res[name] = [out.stacked().detach(), out.lb.detach(), out.den.detach()] + \
+            [p.grad.clone() for p in ps] + [sc.grad.clone()]
     CB.check_status()
     rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
-    names = ["out", "lb", "den", "demb", "dread", "dwrite", "dx", "dh", "doff"]
+    names = ["out", "lb", "den", "demb", "dread", "dwrite", "dx", "dh", "doff", "dscale"]
     return {n: rel(a, b) for n, a, b in zip(names, res["fused"], res["nccl"])}
 
 
@@ -142,7 +144,8 @@ def test_fused_all_gather_and_reduce_scatter_match_nccl_path(version):
     for o in outs:
         for k, v in o.items():
             # same kernels and math; differences: fp32 (fused) vs bf16 (NCCL) partial sums
-            assert v < 2e-2, (k, v, o)
+            # (dscale is one scalar summed with heavy cancellation)
+            assert v < (6e-2 if k == "dscale" else 2e-2), (k, v, o)
 
 
 def test_peer_barrier_times_out_when_a_peer_never_arrives():
