@@ -809,9 +809,11 @@ class CudaBackend:
         else:
             scale = torch.full((), float(out_scale), device=x.device)
         outs, dens = [], []
+        # one all-gather for the thresholds and 1/sigma of every route of this call
+        stats_f = C.gather_tokens(torch.stack([tau, inv_sd], dim=0).permute(1, 0, 2).contiguous(), grp)
         for ri in range(Rr):
-            tau_f = C.gather_tokens(tau[:, ri].contiguous(), grp)
-            isd_f = C.gather_tokens(inv_sd[:, ri].contiguous(), grp)
+            tau_f = stats_f[:, 0, ri].contiguous()
+            isd_f = stats_f[:, 1, ri].contiguous()
             o, d = _SRWRouteGatherFn.apply(x_bf, _bf16_2d(h_bf3[:, ri]), tau_f, isd_f, anchor, pool,
                                            spec, U, comm, scale)
             outs.append(o)

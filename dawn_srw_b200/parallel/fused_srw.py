@@ -32,6 +32,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops.gates import GATE_GELU_Z
+from . import collectives as C
 from .symm import SymmWorkspace
 
 
@@ -105,7 +106,7 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         e.srw_fwd_gate_gather(hf.local, holder.emb[:U], xf.local, holder.read[:U], p, tau_full,
                               inv_sd_full, den, gl, st, [xf.ptrs, hf.ptrs], c.rank, Tl, c.ready,
                               c.next_epoch())
-        dist.all_reduce(den, group=c.group)              # [T] fp32
+        C._all_reduce_sum_(den, c.group)                 # [T] fp32: peer-memory kernel when it fits
         inv_den = (scale.detach().float() / den.clamp(min=1.0)).contiguous()   # pool scale folded in
         tgt = c.out_rs[c.next_rs("out")]
         e.gemm_scatter(p[:, :U], False, holder.write[:U], True, tgt.ptrs, Tl, D, 1.0, inv_den, st)

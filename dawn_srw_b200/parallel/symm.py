@@ -65,7 +65,7 @@ class SymmWorkspace:
         return buf
 
     AR_SLOT_BASE = 512          # pad slots [512, 1024) belong to all_reduce_small
-    AR_CAP = 65536              # largest vector (fp32 elements) it takes
+    AR_CAP = 131072             # largest vector (fp32 elements) it takes: 32 CTAs x 8 ranks of slots
 
     def all_reduce_small(self, x: torch.Tensor) -> torch.Tensor:
         """In-place sum over the group of a contiguous fp32 tensor of at most

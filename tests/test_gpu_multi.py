@@ -178,7 +178,7 @@ def _small_allreduce(rank, world):
     ws.enable_small_allreduce()
     g = torch.Generator(device=dev).manual_seed(5 + rank)
     errs = []
-    for n in (1, 7, 256, 4096, 4097, 30000, 65536, 3, 9000):   # repeated calls reuse the two halves
+    for n in (1, 7, 256, 4096, 4097, 30000, 65536, 131072, 100001, 3, 9000):   # repeated calls reuse the two halves
         x = torch.randn(n, device=dev, generator=g)
         ref = x.clone()
         dist.all_reduce(ref)
