@@ -112,6 +112,7 @@ def test_srw_op_forward_backward_against_fp32_oracle(cb, version, dims):
     from dawn_srw_b200.ops.gates import gate_spec_for
     T, R, U, r, D = dims
     dev = torch.device("cuda")
+    torch.manual_seed(11)
     spec = gate_spec_for(version)
     rb, kb = ReferenceBackend(torch.float32), cb.CudaBackend()
     q = lambda t: t.bfloat16().float()
@@ -139,6 +140,12 @@ def test_srw_op_forward_backward_against_fp32_oracle(cb, version, dims):
     # check the same math tightly
     sharp = 0.08
     for n, a, b in zip(names, res["cuda"], res["ref"]):
+        if n == "dscale":
+            # one scalar, sum_t <d_out, out> / scale, with heavy cancellation between tokens:
+            # compare against the size of the summed terms instead of the sum
+            terms = float((res["ref"][0].abs() * w.abs()).sum() / 1.7)
+            assert abs(float(a) - float(b)) < 2e-3 * terms, (n, float(a), float(b), terms)
+            continue
         assert _rel(a, b) < tol.get(n, sharp), (n, _rel(a, b))
     cb.check_status()
 
