@@ -216,8 +216,9 @@ void srw_bwd_gate_gather(const Tensor& h_full, const Tensor& emb, const Tensor& 
 // Fused GEMM -> reduce-scatter.  `out_ptrs`: data pointers of every rank's
 // [rows_per_rank, N] fp32 buffer (index = rank), as integers.
 void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
-                  std::vector<int64_t> out_ptrs, int64_t rows_per_rank, int64_t ldc, double alpha,
-                  c10::optional<Tensor> row_scale, Tensor& status) {
+                  std::vector<int64_t> out_ptrs, int64_t my_rank, int64_t rows_per_rank,
+                  int64_t ldc, bool out_bf16, double alpha, c10::optional<Tensor> row_scale,
+                  Tensor& status) {
   check_bf16_2d(A, "A");
   check_bf16_2d(B, "B");
   const c10::cuda::CUDAGuard guard(A.device());
@@ -227,10 +228,23 @@ void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
   std::vector<void*> outs;
   for (auto p : out_ptrs) outs.push_back(reinterpret_cast<void*>(p));
   int rc = dsb_gemm_bf16_scatter(A.data_ptr(), a_mn, A.stride(0), B.data_ptr(), b_mn, B.stride(0),
-                                 M, N, K, outs.data(), static_cast<int>(outs.size()),
-                                 rows_per_rank, ldc, alpha, opt_f32(row_scale),
+                                 M, N, K, outs.data(), static_cast<int>(outs.size()), my_rank,
+                                 rows_per_rank, ldc, out_bf16 ? 1 : 0, alpha, opt_f32(row_scale),
                                  status.data_ptr<int>(), cur_stream());
   TORCH_CHECK(rc == 0, "dsb_gemm_bf16_scatter failed with code ", rc);
+}
+
+// [n_slabs * rows, cols] (bf16 / fp32, contiguous) -> [rows, cols] sum over slabs
+Tensor sum_slabs(const Tensor& in, int64_t n_slabs, bool out_bf16) {
+  TORCH_CHECK(in.is_cuda() && in.dim() == 2 && in.is_contiguous() && in.size(0) % n_slabs == 0 &&
+              (in.scalar_type() == torch::kBFloat16 || in.scalar_type() == torch::kFloat32));
+  const c10::cuda::CUDAGuard guard(in.device());
+  const int64_t rows = in.size(0) / n_slabs, cols = in.size(1);
+  auto out = torch::empty({rows, cols}, in.options().dtype(out_bf16 ? torch::kBFloat16 : torch::kFloat32));
+  int rc = dsb_sum_slabs(in.data_ptr(), in.scalar_type() == torch::kBFloat16 ? 1 : 0, n_slabs,
+                         rows * cols, out.data_ptr(), out_bf16 ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_sum_slabs failed with code ", rc);
+  return out;
 }
 
 void peer_barrier(const Tensor& pads_dev, int64_t rank, int64_t world, int64_t epoch,
@@ -462,6 +476,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_bwd_gate", &srw_bwd_gate);
   m.def("srw_forward", &srw_forward);
   m.def("gemm_scatter", &gemm_scatter);
+  m.def("sum_slabs", &sum_slabs);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("ce_fwd", &ce_fwd);

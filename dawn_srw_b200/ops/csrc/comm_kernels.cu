@@ -170,6 +170,50 @@ __global__ void zero_adam_scatter_kernel(float* const* params, int world, int ra
   }
 }
 
+// out[i] = sum over slabs of in[w * n + i]: the local half of the fused
+// reduce-scatter (the slabs were stored by the ranks' GEMM epilogues).
+template <bool kInBf16, bool kOutBf16>
+__global__ void sum_slabs_kernel(const void* __restrict__ in, int n_slabs, long long n,
+                                 void* __restrict__ out) {
+  const long long n8 = n >> 3;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += stride) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int w = 0; w < n_slabs; ++w) {
+      if (kInBf16) {
+        const uint4 v = reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(in) + static_cast<size_t>(w) * n)[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(h[k]);
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(
+            static_cast<const float*>(in) + static_cast<size_t>(w) * n) + 2 * i;
+        const float4 a = src[0], b = src[1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+    }
+    if (kOutBf16) {
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(out)[i] = o;
+    } else {
+      float4* dst = reinterpret_cast<float4*>(out) + 2 * i;
+      dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+}
+
 }  // namespace dsb
 
 extern "C" int dsb_peer_barrier(unsigned int* const* pads_dev, int rank, int world,
@@ -223,5 +267,18 @@ extern "C" int dsb_zero_adam_scatter(float* const* params_dev, int world, int ra
   if ((n & 3) || (lo & 3)) return 603;
   dsb::zero_adam_scatter_kernel<<<zero_grid(n >> 2), 256, 0, stream>>>(
       params_dev, world, rank, lo, n, g, m, v, clip_scale, lr, b1, b2, eps, wd, bc1, bc2);
+  return cudaGetLastError() == cudaSuccess ? 0 : 601;
+}
+
+extern "C" int dsb_sum_slabs(const void* in, int in_is_bf16, int n_slabs, long long n, void* out,
+                             int out_is_bf16, cudaStream_t stream) {
+  if (n <= 0 || n_slabs <= 0) return 0;
+  if ((n & 7) || (reinterpret_cast<uintptr_t>(in) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return 603;
+  const int grid = zero_grid(n >> 3);
+  if (in_is_bf16 && out_is_bf16) dsb::sum_slabs_kernel<true, true><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
+  else if (in_is_bf16) dsb::sum_slabs_kernel<true, false><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
+  else if (out_is_bf16) dsb::sum_slabs_kernel<false, true><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
+  else dsb::sum_slabs_kernel<false, false><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
   return cudaGetLastError() == cudaSuccess ? 0 : 601;
 }

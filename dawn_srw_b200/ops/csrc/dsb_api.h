@@ -88,12 +88,19 @@ int dsb_srw_forward(const void* h, long long ldh, const void* emb, long long lde
                     long long ldo, float* den_sum, unsigned char* alive, const float* unit_mask,
                     const DsbGate* gate /*host*/, int* status, cudaStream_t stream);
 
-// GEMM with the reduce-scatter fused into its epilogue (see gemm_kernels.cu).
-// `outs` is a HOST array of n_ranks device pointers (peer pointers included).
+// GEMM whose output row blocks are stored to their owner ranks (first half of
+// a fused reduce-scatter, see gemm_kernels.cu).  `outs` is a HOST array of
+// n_ranks device pointers to the ranks' receive buffers [n_ranks *
+// rows_per_rank, ldc] (bf16 or fp32; peer pointers included); this rank fills
+// slot `my_rank` of each.  After a barrier the owner sums its slots:
 int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, const void* B, int b_mn,
                           long long ldb, int M, int N, int K, void* const* outs, int n_ranks,
-                          int rows_per_rank, long long ldc, float alpha, const float* row_scale,
-                          int* status, cudaStream_t stream);
+                          int my_rank, int rows_per_rank, long long ldc, int out_is_bf16,
+                          float alpha, const float* row_scale, int* status, cudaStream_t stream);
+// out[i] = sum_w in[w * n + i], w < n_slabs; in bf16 or fp32, out bf16 or fp32
+// (accumulated in fp32); n a multiple of 8, pointers 16-byte aligned.
+int dsb_sum_slabs(const void* in, int in_is_bf16, int n_slabs, long long n, void* out,
+                  int out_is_bf16, cudaStream_t stream);
 
 // Bounded cross-GPU barrier over symmetric signal pads.  `pads_dev` is a DEVICE
 // array of `world` pointers to the ranks' pads (uint32); slots

@@ -134,10 +134,15 @@ struct PlainEpi {
     int out_bf16;            // 1: bf16 output, 0: fp32
     int accumulate;          // 1: out += result (fp32 output only; TMA reduce-add)
     int dbg;                 // profiling toggle: 1 = skip the stores
-    // Fused reduce-scatter: when > 0, global row R of the result belongs to rank
-    // R / scatter_rows and is reduce-added (fp32) into that rank's buffer
-    // (tensor map index = owner rank; peer memory for the other ranks).
+    // Fused reduce-scatter, first half: when > 0, global row R of the result
+    // belongs to rank R / scatter_rows and is stored into slot `scatter_rank` of
+    // that rank's receive buffer [n_ranks * scatter_rows, N] (tensor map index =
+    // owner rank; peer memory for the other ranks).  Plain TMA stores: every
+    // (owner, slot) row is written by exactly one rank, the owner sums its
+    // slots afterwards (dsb_sum_slabs).  Stores cross NVLink at write bandwidth,
+    // which remote reduce-adds (atomics) do not.
     int scatter_rows;
+    int scatter_rank;
   };
   template <int BN, class Ctl>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
@@ -171,7 +176,13 @@ struct PlainEpi {
           }
           stage_bf16_32(st, buf, 4 * half, v);
         }
-        st.flush(&maps[0], buf, col0, r0, false, !(p.dbg & 1));
+        if (p.scatter_rows > 0) {
+          const int owner = r0 / p.scatter_rows;
+          st.flush(&maps[owner], buf, col0,
+                   p.scatter_rank * p.scatter_rows + (r0 - owner * p.scatter_rows), false, true);
+        } else {
+          st.flush(&maps[0], buf, col0, r0, false, !(p.dbg & 1));
+        }
       }
     } else {
 #pragma unroll 1
@@ -198,7 +209,8 @@ struct PlainEpi {
                  __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
         if (p.scatter_rows > 0) {
           const int owner = r0 / p.scatter_rows;
-          st.flush(&maps[owner], buf, col0, r0 - owner * p.scatter_rows, true, true);
+          st.flush(&maps[owner], buf, col0,
+                   p.scatter_rank * p.scatter_rows + (r0 - owner * p.scatter_rows), false, true);
         } else {
           st.flush(&maps[0], buf, col0, r0, p.accumulate != 0, !(p.dbg & 1));
         }
@@ -292,6 +304,107 @@ struct FwdGateEpi {
     ctl.release(0);
     ctl.release(1);
     st.flush(&maps[0], buf, col0, r0, false, true);
+    if (row_ok) {
+      atomicAdd(p.den_sum + row, den_acc);
+      if (p.gate_sum != nullptr) atomicAdd(p.gate_sum + row, g_acc);
+    }
+  }
+};
+
+// Wide variant: 256-column tiles on CTA pairs.  S and XR take 256 TMEM columns
+// each (all 512), one buffer per accumulator, so the overlap comes from the
+// order of work instead of double buffering: phase 1 turns S into gate values
+// (held in registers as bf16, 128 columns per thread) while the five-times-
+// longer XR MMAs of the same tile still run, and frees S for the next tile;
+// phase 2 multiplies by XR and stores.  The tensor core only idles while phase
+// 2 of tile t and the S MMAs of tile t+1 are both finished.  256-wide tiles
+// halve the shared-memory bytes per FLOP of the 128-wide variant, whose
+// tensor-pipe utilisation is capped by shared-memory bandwidth.
+// Warp w: rows 32(w%4).., columns 128(w/4).. of the CTA's 128 x 256 tile.
+template <int KIND>
+struct FwdGateEpiWide {
+  static constexpr int kNumAcc = 2;
+  static constexpr int kNumOut = 1;
+  static constexpr int kOutBufs = 2;
+  static constexpr int kEpiWarps = 8;
+  __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
+  using Params = FwdGateParams;
+
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
+    static_assert(BN == 256, "two 64-column slabs per warp");
+    const int r0 = m0 + (warp & 3) * 32;
+    const int c = (warp >> 2) * 128;
+    const int col0 = n0 + c;
+    if (r0 >= M || col0 >= N) { ctl.skip(); return; }  // warp-uniform
+    const int row = r0 + lane;
+    const bool row_ok = row < M;
+    const float tau = row_ok ? p.tau[row] : 0.f;
+    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
+    float den_acc = 0.f, g_acc = 0.f;
+    const bool general = (col0 + 128 > N) || p.unit_mask != nullptr || p.alive != nullptr;
+    // ---- phase 1: scores -> gate values (bf16 pairs in registers)
+    uint32_t gp[64];
+    const uint32_t acc_s = ctl.wait(0) + c;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float s[32];
+      tmem_ld32(acc_s + 32 * q, s);
+      tmem_ld_wait();
+      const int cbase = col0 + 32 * q;
+      unsigned alive_bits = 0u;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float g, dt;
+        gate_fwd<KIND>(p.gc, s[j], tau, isg, g, dt);
+        if (general) {
+          if (cbase + j >= N) { g = 0.f; dt = 0.f; }
+          if (p.unit_mask != nullptr && cbase + j < N) {
+            const float um = p.unit_mask[cbase + j];
+            g *= um;
+            dt *= um;
+          }
+          if (row_ok && g >= p.gc.dead_thr) alive_bits |= 1u << j;
+        }
+        den_acc += dt;
+        g_acc += g;
+        s[j] = g;
+      }
+      if (general && p.alive != nullptr) {
+        const unsigned any = __reduce_or_sync(0xffffffffu, alive_bits);
+        if (((any >> lane) & 1u) && cbase + lane < N) p.alive[cbase + lane] = 1;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) gp[16 * q + j] = pack_bf16x2(s[2 * j], s[2 * j + 1]);
+    }
+    ctl.release(0);   // the next tile's score MMAs may start
+    // ---- phase 2: p = g * xr, two 64-column slabs
+    const uint32_t acc_xr = ctl.wait(1) + c;
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      if (col0 + 64 * sl < N) {        // warp-uniform
+        st.wait_free<1>();
+        const uint32_t buf = st.buf(sl);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float xr[32];
+          tmem_ld32(acc_xr + 64 * sl + 32 * half, xr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const __nv_bfloat162 g2 =
+                *reinterpret_cast<const __nv_bfloat162*>(&gp[32 * sl + 16 * half + j]);
+            const float2 gf = __bfloat1622float2(g2);
+            xr[2 * j] *= gf.x;
+            xr[2 * j + 1] *= gf.y;
+          }
+          stage_bf16_32(st, buf, 4 * half, xr);
+        }
+        if (sl == 1 || col0 + 64 >= N) ctl.release(1);   // last TMEM read of this tile
+        st.flush(&maps[0], buf, col0 + 64 * sl, r0, false, true);
+      }
+    }
     if (row_ok) {
       atomicAdd(p.den_sum + row, den_acc);
       if (p.gate_sum != nullptr) atomicAdd(p.gate_sum + row, g_acc);
@@ -448,6 +561,7 @@ struct OperandDesc {
 };
 
 static bool use_cta_pairs();
+static bool use_wide_gate();
 static int fill_operand(CUtensorMap* map, const OperandDesc& o, long long rows, long long K,
                         int box_rows) {
   if (o.mn_major) return make_tmap_bf16(map, o.ptr, rows, K, o.ld, 64, 64);
@@ -491,6 +605,16 @@ static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, gp) == cudaSuccess ? 0 : 11;
+}
+
+// Environment switch DSB_WIDE_GATE=0 keeps the forward gate kernel on 128-wide tiles (profiling).
+static bool use_wide_gate() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DSB_WIDE_GATE");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 // Environment switch DSB_CTA_PAIRS=0 falls back to single-CTA tiles (profiling).
@@ -612,7 +736,9 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
   constexpr int BN = 128;
   GemmParams<FwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
-  const int brows = use_cta_pairs() ? BN / 2 : BN;
+  // 256-wide tiles (CTA pairs only) once the pool is wide enough to fill the machine with them
+  const bool wide = use_cta_pairs() && use_wide_gate() && U >= 2048;
+  const int brows = wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
   rc |= fill_operand(&gp.tma_a[1], {x, 0, ldx}, T, D, kBlockM);
@@ -632,9 +758,19 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
     if (!use_cta_pairs()) return 702;
     rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
     if (rc) return rc;
+    if (wide) {
+      if (gate->kind == 0) return launch_engine_gather<256, FwdGateEpiWide<0>>(gp, stream);
+      if (gate->kind == 1) return launch_engine_gather<256, FwdGateEpiWide<1>>(gp, stream);
+      return launch_engine_gather<256, FwdGateEpiWide<2>>(gp, stream);
+    }
     if (gate->kind == 0) return launch_engine_gather<BN, FwdGateEpi<0>>(gp, stream);
     if (gate->kind == 1) return launch_engine_gather<BN, FwdGateEpi<1>>(gp, stream);
     return launch_engine_gather<BN, FwdGateEpi<2>>(gp, stream);
+  }
+  if (wide) {
+    if (gate->kind == 0) return launch_engine_impl<256, FwdGateEpiWide<0>, 2>(gp, stream);
+    if (gate->kind == 1) return launch_engine_impl<256, FwdGateEpiWide<1>, 2>(gp, stream);
+    return launch_engine_impl<256, FwdGateEpiWide<2>, 2>(gp, stream);
   }
   if (gate->kind == 0) return launch_engine<BN, FwdGateEpi<0>>(gp, stream);
   if (gate->kind == 1) return launch_engine<BN, FwdGateEpi<1>>(gp, stream);
@@ -721,20 +857,22 @@ extern "C" int dsb_srw_forward(const void* h, long long ldh, const void* emb, lo
                        nullptr, nullptr, 256, status, stream);
 }
 
-// GEMM with a fused reduce-scatter over `n_ranks` GPUs: this rank's product
-// A.B^T [M, N] (M = n_ranks * rows_per_rank) is row-scaled and reduce-added
-// (fp32, TMA reduce over NVLink) straight from the epilogue into the owner
-// rank's buffer outs[j] ([rows_per_rank, N] fp32, ldc elements between rows).
-// The buffers must have been zeroed on every rank before any rank launches,
-// and read only after every rank's kernel has finished (see parallel/symm.py).
+// GEMM whose output rows are scattered to their owner ranks (first half of a
+// fused reduce-scatter): C = alpha * row_scale * A.B^T over M = n_ranks *
+// rows_per_rank rows; row block j goes to rank j.  `outs[j]` is rank j's
+// receive buffer [n_ranks * rows_per_rank, ldc] (bf16 or fp32, peer memory for
+// j != my_rank); this rank writes slot `my_rank` of each.  The owner reads its
+// buffer only after every rank's kernel has finished (a barrier) and sums the
+// n_ranks slots with dsb_sum_slabs.
 extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, const void* B,
                                      int b_mn, long long ldb, int M, int N, int K,
-                                     void* const* outs, int n_ranks, int rows_per_rank,
-                                     long long ldc, float alpha, const float* row_scale,
-                                     int* status, cudaStream_t stream) {
+                                     void* const* outs, int n_ranks, int my_rank,
+                                     int rows_per_rank, long long ldc, int out_is_bf16,
+                                     float alpha, const float* row_scale, int* status,
+                                     cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (n_ranks < 1 || n_ranks > kMaxOut || rows_per_rank % 32 != 0 ||
-      static_cast<long long>(n_ranks) * rows_per_rank != M)
+  if (n_ranks < 1 || n_ranks > kMaxOut || rows_per_rank % 32 != 0 || my_rank < 0 ||
+      my_rank >= n_ranks || static_cast<long long>(n_ranks) * rows_per_rank != M)
     return 500;
   GemmParams<PlainEpi::Params> gp;
   memset(&gp, 0, sizeof(gp));
@@ -744,7 +882,8 @@ extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, con
   rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, use_cta_pairs() ? BN / 2 : BN);
   if (rc) return 200 + rc;
   for (int j = 0; j < n_ranks; ++j) {
-    rc = make_out_tmap(&gp.tma_out[j], outs[j], rows_per_rank, N, ldc, 4);
+    rc = make_out_tmap(&gp.tma_out[j], outs[j], static_cast<uint64_t>(n_ranks) * rows_per_rank, N,
+                       ldc, out_is_bf16 ? 2 : 4);
     if (rc) return 300 + rc;
   }
   gp.seg[0] = {(K + kBlockK - 1) / kBlockK, 0, a_mn, b_mn};
@@ -752,6 +891,6 @@ extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, con
   gp.M = M;
   gp.N = N;
   gp.status = status;
-  gp.epi = {alpha, row_scale, nullptr, 0, 1, 0, rows_per_rank};
+  gp.epi = {alpha, row_scale, nullptr, out_is_bf16 ? 1 : 0, 0, 0, rows_per_rank, my_rank};
   return launch_engine<BN, PlainEpi>(gp, stream);
 }

@@ -13,8 +13,10 @@ Layout (8 GPUs = one shard group): rank k stores ``U/8`` units of every pool and
        ``sum_U den_term`` per token;
     3. the per-token denominators are summed over ranks (``[T]`` fp32, NCCL);
     4. write GEMM with the reduce-scatter fused into its epilogue: each 32-row
-       slab of ``(p . write) / den`` is TMA-reduce-added (fp32) into the owner
-       rank's ``[T/8, D]`` buffer, locally or over NVLink.
+       slab of ``scale * (p . write) / den`` is TMA-stored (bf16) into this
+       rank's slot of the owner rank's receive buffer, locally or over NVLink;
+       after a barrier the owner sums its slots in fp32.  (Plain stores cross
+       NVLink at write bandwidth; remote fp32 reduce-adds measured 3-4x slower.)
   backward mirrors it: ``dy`` rows are gathered by the backward gate kernel
   together with ``x`` and ``h``; ``dx`` and ``dh`` leave through the same fused
   reduce-scatter epilogue; pool gradients stay on the rank that owns the units.
@@ -51,14 +53,14 @@ class FusedShardComm:
         self.xfull = [self.ws.alloc(f"xfull{i}", (T, d_model), bf) for i in range(2)]
         self.hfull = [self.ws.alloc(f"hfull{i}", (T, d_route), bf) for i in range(2)]
         self.dyfull = [self.ws.alloc(f"dyfull{i}", (T, d_model), bf) for i in range(2)]
-        # reduce-scatter targets, two of each: a buffer is cleared right after it has been
-        # consumed and next used two ops later, with at least two barriers in between, so
-        # no peer can add into it before it is zero (no "everyone has zeroed" barrier)
-        self.out_rs = [self.ws.alloc(f"out_rs{i}", (t_local, d_model), f32) for i in range(2)]
-        self.dx_rs = [self.ws.alloc(f"dx_rs{i}", (t_local, d_model), f32) for i in range(2)]
-        self.dh_rs = [self.ws.alloc(f"dh_rs{i}", (t_local, d_route), f32) for i in range(2)]
-        for b_ in self.out_rs + self.dx_rs + self.dh_rs:
-            b_.local.zero_()
+        # reduce-scatter receive buffers: every rank stores its partial rows for this rank's
+        # tokens into its own slot ([world, t_local, cols], bf16); the owner sums the slots.
+        # Two of each: a buffer is next written two ops after it was read, with a barrier in
+        # between that the reader only passes after its read, so no peer can overwrite early.
+        W = self.world
+        self.out_rs = [self.ws.alloc(f"out_rs{i}", (W * t_local, d_model), bf) for i in range(2)]
+        self.dx_rs = [self.ws.alloc(f"dx_rs{i}", (W * t_local, d_model), bf) for i in range(2)]
+        self.dh_rs = [self.ws.alloc(f"dh_rs{i}", (W * t_local, d_route), bf) for i in range(2)]
         self._rs_parity = {"out": 0, "dx": 0}
         self.ready = torch.zeros(T // 128, dtype=torch.int32, device=device)
         self.epoch = 0
@@ -109,10 +111,11 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         C._all_reduce_sum_(den, c.group)                 # [T] fp32: peer-memory kernel when it fits
         inv_den = (scale.detach().float() / den.clamp(min=1.0)).contiguous()   # pool scale folded in
         tgt = c.out_rs[c.next_rs("out")]
-        e.gemm_scatter(p[:, :U], False, holder.write[:U], True, tgt.ptrs, Tl, D, 1.0, inv_den, st)
-        c.ws.barrier()                                   # every rank's contributions have landed
-        out = tgt.local.clone()
-        tgt.local.zero_()                                # ready for its next use, two ops from now
+        e.gemm_scatter(p[:, :U], False, holder.write[:U], True, tgt.ptrs, c.rank, Tl, D, True, 1.0,
+                       inv_den, st)
+        c.ws.barrier()                                   # every rank's partial rows have landed
+        out = e.sum_slabs(tgt.local, c.world, False)     # fp32 [Tl, D]
+        CB.count_launches(1)
         ctx.save_for_backward(x_bf, h_bf, tau_full, inv_sd_full, den, out, scale)
         ctx.holder, ctx.spec, ctx.U, ctx.comm = holder, spec, U, c
         ctx.mark_non_differentiable(den)
@@ -160,13 +163,12 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         bi = c.next_rs("dx")
         dxt, dht = c.dx_rs[bi], c.dh_rs[bi]
         CB._LAUNCHES += 2
-        e.gemm_scatter(dxrv, False, read, True, dxt.ptrs, Tl, D, 1.0, None, st)       # dxr . read
-        e.gemm_scatter(dsv, False, emb, True, dht.ptrs, Tl, r, 1.0, None, st)         # ds . emb
+        e.gemm_scatter(dxrv, False, read, True, dxt.ptrs, c.rank, Tl, D, True, 1.0, None, st)   # dxr . read
+        e.gemm_scatter(dsv, False, emb, True, dht.ptrs, c.rank, Tl, r, True, 1.0, None, st)     # ds . emb
         c.ws.barrier()
-        dx = dxt.local.to(torch.bfloat16)
-        dh32 = dht.local.clone()
-        dxt.local.zero_()
-        dht.local.zero_()
+        dx = e.sum_slabs(dxt.local, c.world, True)       # bf16 [Tl, D]
+        dh32 = e.sum_slabs(dht.local, c.world, False)    # fp32 [Tl, r]
+        CB.count_launches(2)
         d_isd = None
         if spec.kind == GATE_GELU_Z:
             # sum_u ds_u z_u = (1/sigma)(<h, ds.emb> + tau * dtau), evaluated by the owner of

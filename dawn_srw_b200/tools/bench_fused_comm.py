@@ -14,8 +14,9 @@ operands larger than the L2:
    its gather warps pull the peers' rows (fused) vs NCCL all-gather followed by
    the same kernel without gathering.
 2. write GEMM -> reduce-scatter: p [T,U/N] . write [U/N,D] with each output
-   slab TMA-reduce-added into the owner's buffer (fused, fp32) vs the plain
-   GEMM followed by NCCL reduce-scatter (bf16, what the library path sends).
+   slab TMA-stored (bf16) into this rank's slot of the owner's receive buffer,
+   barrier, slots summed in fp32 by the owner (fused) vs the plain GEMM
+   followed by NCCL reduce-scatter (bf16, what the library path sends).
 3. partitioned optimizer: gradient slices summed from the peers + AdamW +
    parameters stored to the peers (two kernels, two barriers) vs NCCL
    all-reduce + full AdamW on every rank.
@@ -144,14 +145,15 @@ def main(argv=None):
         # ---- 2. write GEMM -> reduce-scatter ------------------------------
         flops = 2.0 * T * U * D
         if world > 1:
-            tgt = ws.alloc("rs_tgt", (Tl, D), torch.float32)
+            tgt = ws.alloc("rs_tgt", (world * Tl, D), bf)
             full32 = torch.empty(T, D, device=dev)
             fullbf = torch.empty(T, D, dtype=bf, device=dev)
             outbf = torch.empty(Tl, D, dtype=bf, device=dev)
 
             def fused_rs():
-                e.gemm_scatter(p, False, write, True, tgt.ptrs, Tl, D, 1.0, None, st)
+                e.gemm_scatter(p, False, write, True, tgt.ptrs, rank, Tl, D, True, 1.0, None, st)
                 ws.barrier()
+                e.sum_slabs(tgt.local, world, False)
 
             def nccl_rs():
                 CB.gemm(p, False, write, True, out=fullbf)
@@ -161,7 +163,7 @@ def main(argv=None):
             full32 = torch.empty(T, D, device=dev)
             t_f = t_n = timed(lambda: CB.gemm(p, False, write, True, out=full32), args.iters, world, dev)
         t_local = timed(lambda: CB.gemm(p, False, write, True, out=full32), args.iters, world, dev)
-        link_b = (world - 1) * Tl * D * 4.0
+        link_b = (world - 1) * Tl * D * 2.0              # bf16 slabs to the other owners
         roof = max(flops / (peak * 1e9), link_b / (NVLINK_GBS * 1e6))
         recs.append({"path": "write GEMM -> reduce-scatter", "units_per_rank": U, "fused_ms": t_f,
                      "nccl_ms": t_n, "kernel_without_comm_ms": t_local, "roofline_ms": roof,

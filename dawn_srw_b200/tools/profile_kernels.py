@@ -11,6 +11,12 @@ shape holds < 2 GB on the device and its operands exceed the 126 MB L2, so an
 
     ncu --set full --clock-control none -k regex:gemm_engine_kernel -s 4 -c 4 \
         -o prof python -m dawn_srw_b200.tools.profile_kernels
+
+``--attention`` launches the causal attention forward and backward kernels
+instead (batch 8 x 16 heads x 512 tokens x head dimension 80 by default):
+
+    ncu --set full --clock-control none -k regex:attn_ -s 2 -c 2 -o prof_attn \
+        python -m dawn_srw_b200.tools.profile_kernels --attention
 """
 from __future__ import annotations
 
@@ -18,6 +24,32 @@ import argparse
 import sys
 
 import torch
+
+
+def attention(args):
+    import time
+    from ..ops import cuda_backend as CB
+    dev = torch.device("cuda")
+    B, H, S, dh = args.batch, args.heads, args.seq, args.head_dim
+    g = torch.Generator(device=dev).manual_seed(0)
+    q, k, v = (torch.randn(B, S, H * dh, device=dev, generator=g).bfloat16().requires_grad_(True)
+               for _ in range(3))
+    w = torch.randn(B, S, H * dh, device=dev, generator=g).bfloat16()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for it in range(args.iters):
+        ev[0].record()
+        out = CB.causal_attention(q, k, v, H, 0.1, 1234)
+        ev[1].record()
+        out.backward(w)
+        ev[2].record()
+        q.grad = k.grad = v.grad = None
+    torch.cuda.synchronize()
+    CB.check_status()
+    fl = 4.0 * B * H * S * S * dh / 2            # causal: half of the S x S tiles
+    f_ms, b_ms = ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])
+    print(f"ok: attention B={B} H={H} S={S} dh={dh}: forward {f_ms:.3f} ms ({fl / f_ms / 1e9:.0f} TFLOP/s), "
+          f"backward {b_ms:.3f} ms ({2.5 * fl / b_ms / 1e9:.0f} TFLOP/s)")
+    return 0
 
 
 def main(argv=None):
@@ -28,7 +60,14 @@ def main(argv=None):
     ap.add_argument("--d-route", type=int, default=256)
     ap.add_argument("--kind", type=int, default=1)
     ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--attention", action="store_true")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=512)
+    ap.add_argument("--head-dim", type=int, default=80)
     args = ap.parse_args(argv)
+    if args.attention:
+        return attention(args)
     from ..ops import cuda_backend as CB
     from ..ops.gates import GateSpec
     dev = torch.device("cuda")

@@ -64,28 +64,31 @@ def _barrier_and_scatter(rank, world):
         ws.barrier()
     torch.cuda.synchronize()
     CB.check_status()
-    # fused GEMM -> reduce-scatter against NCCL reduce_scatter of the same products
+    # fused GEMM -> reduce-scatter against NCCL reduce_scatter of the same products,
+    # with fp32 and with bf16 receive slots (N = 520: ragged last column tile)
     rows, N, K = 256, 520, 384
     M = rows * world
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     A = torch.randn(M, K, device=dev, generator=g).bfloat16()
     B = torch.randn(N, K, device=dev, generator=g).bfloat16()
     rs = torch.rand(M, device=dev, generator=g) + 0.5
-    out = ws.alloc("rs_out", (rows, N), torch.float32)
-    res = []
-    for it in range(2):                       # twice: buffers are reused across calls
-        out.local.zero_()
-        ws.barrier()                          # every rank has zeroed its buffer
-        CB.ext().gemm_scatter(A, False, B, False, out.ptrs, rows, N, 1.0, rs, CB.status_word(dev))
-        ws.barrier()                          # every rank's adds have landed
-        torch.cuda.synchronize()
-        res.append(out.local.clone())
-    CB.check_status()
     full = (A.float() @ B.float().t()) * rs[:, None]
     ref = torch.empty(rows, N, device=dev)
     dist.reduce_scatter_tensor(ref, full.contiguous())
-    err = max(((r - ref).norm() / ref.norm()).item() for r in res)
-    return err
+    errs = []
+    for name, dt, tol_scale in (("f32", torch.float32, 1.0), ("bf16", torch.bfloat16, 400.0)):
+        buf = ws.alloc("rs_" + name, (world * rows, N), dt)
+        buf.local.fill_(float("nan"))             # every element must be overwritten
+        for it in range(2):                       # twice: buffers are reused across calls
+            ws.barrier()
+            CB.ext().gemm_scatter(A, False, B, False, buf.ptrs, rank, rows, N, dt == torch.bfloat16,
+                                  1.0, rs, CB.status_word(dev))
+            ws.barrier()                          # every rank's stores have landed
+            got = CB.ext().sum_slabs(buf.local, world, False)
+            torch.cuda.synchronize()
+            errs.append(((got - ref).norm() / ref.norm()).item() / tol_scale)
+    CB.check_status()
+    return max(errs)
 
 
 def test_peer_barrier_and_fused_gemm_reduce_scatter():
