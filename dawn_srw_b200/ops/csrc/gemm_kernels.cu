@@ -737,7 +737,7 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
   GemmParams<FwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
   // 256-wide tiles (CTA pairs only) once the pool is wide enough to fill the machine with them
-  const bool wide = use_cta_pairs() && use_wide_gate() && U >= 2048;
+  const bool wide = use_cta_pairs() && use_wide_gate() && U >= 512;
   const int brows = wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);

@@ -60,7 +60,7 @@ def test_gemm_epilogue_options(cb):
 
 @pytest.mark.parametrize("kind", [0, 1, 2])
 @pytest.mark.parametrize("dims", [(256, 384, 128, 384), (300, 1580, 128, 384), (130, 197, 64, 256),
-                                  (300, 2504, 128, 384), (520, 4099, 64, 256)])   # the last two: 256-wide tiles
+                                  (300, 2504, 128, 384), (520, 4099, 64, 256), (260, 777, 64, 256)])   # U >= 512: 256-wide tiles
 def test_gate_kernels(cb, kind, dims):
     from dawn_srw_b200.ops.gates import GateSpec, gate_backward, gate_forward
     T, U, r, D = dims
