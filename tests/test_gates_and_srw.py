@@ -142,3 +142,27 @@ def test_gram_statistics_and_their_gradient(normalize):
     assert torch.allclose(mu, s.mean(-1), atol=1e-5) and torch.allclose(m2, (s * s).mean(-1), atol=1e-5)
     for a, b in zip(got, (emb2.grad, read2.grad, write2.grad, h2.grad)):
         assert torch.allclose(a, b, atol=2e-5), float((a - b).abs().max())
+
+
+def test_out_scale_and_route_accessors():
+    """``out_scale`` multiplies the route outputs inside the backend call and
+    ``route(i)`` / ``stacked()`` agree whichever way a backend stores them."""
+    from dawn_srw_b200.ops.backend import ParallelCtx, ReferenceBackend
+    from dawn_srw_b200.ops.gates import gate_spec_for
+    from dawn_srw_b200.ops.srw_ref import SRWResult
+    torch.manual_seed(0)
+    spec = gate_spec_for("spatial-r1-v4.0.1")
+    be = ReferenceBackend(torch.float32)
+    T, R, U, r, D = 12, 2, 40, 8, 16
+    emb, read, write = torch.randn(U, r), torch.randn(U, D), torch.randn(U, D)
+    x, h, off = torch.randn(T, D), torch.randn(T, R, r), torch.zeros(T, R)
+    pool = be.prepare_pool(emb, read, write, spec, ParallelCtx())
+    a = be.srw(x, h, off, pool, spec, want_diag=False)
+    sc = torch.tensor(2.5, requires_grad=True)
+    b = be.srw(x, h, off, pool, spec, want_diag=False, out_scale=sc)
+    assert torch.allclose(b.out, a.out * 2.5)
+    assert torch.equal(b.route(1), b.out[:, 1]) and torch.equal(b.stacked(), b.out)
+    b.out.sum().backward()
+    assert torch.allclose(sc.grad, a.out.sum())
+    listed = SRWResult(out=None, lb=a.lb, dead_penalty=a.dead_penalty, outs=[a.out[:, 0], a.out[:, 1]])
+    assert torch.equal(listed.route(0), a.out[:, 0]) and torch.equal(listed.stacked(), a.out)
