@@ -892,5 +892,10 @@ extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, con
   gp.N = N;
   gp.status = status;
   gp.epi = {alpha, row_scale, nullptr, out_is_bf16 ? 1 : 0, 0, 0, rows_per_rank, my_rank};
+  // Every rank starts with the rows of a different owner (rank+1, rank+2, ..., itself last), so
+  // at any moment the ranks store to distinct peers instead of all converging on one GPU.
+  const int tile_m = (use_cta_pairs() ? 2 : 1) * kBlockM;
+  if (rows_per_rank % tile_m == 0)
+    gp.m_rot = ((my_rank + 1) % n_ranks) * (rows_per_rank / tile_m);
   return launch_engine<BN, PlainEpi>(gp, stream);
 }
