@@ -52,7 +52,9 @@ int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, long long ld
                      cudaStream_t stream);
 
 // SRW backward gate kernel: recomputes S and XR, adds DP = dy.write^T, writes
-// p, dxr = DP*g and ds (all bf16 [T, ld_out]) and accumulates dtau_sum / dsz_sum.
+// p, dxr = DP*g and ds (all bf16 [T, ld_out]) and accumulates dtau_sum[T] -= sum_U ds.
+// dsz_sum is accepted for ABI stability and left untouched: the caller derives
+// sum_U ds*z from ds.emb and dtau (see ops/cuda_backend.py).
 int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, long long lde, const void* x,
                      long long ldx, const void* read, long long ldr, const void* dy,
                      long long lddy, const void* write, long long ldw, int T, int U, int r, int D,
