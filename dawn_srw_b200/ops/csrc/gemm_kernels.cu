@@ -16,6 +16,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <cuda_fp16.h>
+
 #include "common/gemm_engine.cuh"
 #include "common/host_utils.cuh"
 #include "dsb_api.h"
@@ -553,6 +555,168 @@ struct BwdGateEpi {
   }
 };
 
+// ------------------------------------------- wide backward gate kernel pair
+// With three accumulators (S, XR, DP) the backward gate kernel cannot use
+// 256-column tiles (768 TMEM columns).  The wide variant is two launches of two
+// accumulators each, both with the two-phase epilogue of FwdGateEpiWide:
+//   A: S, XR -> p = g * xr and c1 = A1 * xr                     (bf16 [T, U] each)
+//   B: S, DP -> dxr = dp * g,  ds = dp * c1 + A2 * dden,  dtau  (reads c1 back)
+// S (K = d_route) is computed twice, +9 % MMA work, in exchange for tiles that
+// run ~1.5x faster.  Between the phases a thread keeps the shifted score of
+// its 128 columns as fp16 pairs (64 registers) and re-evaluates the gate
+// coefficients from it in phase 2.  c1 lives in the ds output buffer: B reads
+// a slab's c1 values before it stores ds over them.
+template <int KIND>
+__device__ __forceinline__ float gate_shifted(const GateConsts& gc, float s, float tau, float isg) {
+  if constexpr (KIND == 0) return s - tau;
+  else if constexpr (KIND == 1) return (s - tau) * isg;
+  else return s - tau - gc.thr;
+}
+// (g, A1, A2) from the shifted score; ds = A1 * (dp * xr) + A2 * dden.
+template <int KIND>
+__device__ __forceinline__ float gate_coeffs_shifted(const GateConsts& gc, float zt, float isg,
+                                                     float& a1, float& a2) {
+  float g;
+  if constexpr (KIND == 0) {
+    g = fminf(fmaxf(zt, 0.f), gc.clip_max);
+    a1 = (zt > 0.f && zt < gc.clip_max) ? 1.f : 0.f;
+    a2 = a1;
+  } else if constexpr (KIND == 1) {
+    const float z = fmaxf(zt, 0.f);
+    float phi, pdf;
+    phi_pdf(z, phi, pdf);
+    g = z * phi;
+    a1 = zt > 0.f ? fmaf(z, pdf, phi) * isg : 0.f;
+    a2 = a1;
+  } else {
+    const float act = rcp_approx(1.f + __expf(-gc.sharp * zt));
+    const float amr = zt - gc.cut;
+    const float inten = gc.eps + fminf(fmaxf(amr, 0.f), gc.max_int);
+    g = act * inten;
+    a2 = (amr > 0.f && amr < gc.max_int) ? 1.f : 0.f;
+    a1 = inten * gc.sharp * act * (1.f - act) + act * a2;
+  }
+  return g;
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_half2(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
+struct BwdWideParams {
+  const float* tau;        // [T]
+  const float* inv_sigma;  // [T]
+  const float* dden;       // [T]   (kernel B)
+  float* dtau_sum;         // [T] += -sum_U ds   (kernel B)
+  const __nv_bfloat16* c1; // [T, ldc1] written by kernel A, read by kernel B
+  long long ldc1;
+  GateConsts gc;
+};
+
+// kStage: 0 = kernel A (accumulators S, XR), 1 = kernel B (accumulators S, DP).
+template <int KIND, int kStage>
+struct BwdGateEpiWide {
+  static constexpr int kNumAcc = 2;
+  static constexpr int kNumOut = 2;
+  static constexpr int kOutBufs = 2;
+  static constexpr int kEpiWarps = 8;
+  __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
+  using Params = BwdWideParams;
+
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
+    static_assert(BN == 256, "two 64-column slabs per warp");
+    const int r0 = m0 + (warp & 3) * 32;
+    const int c = (warp >> 2) * 128;
+    const int col0 = n0 + c;
+    if (r0 >= M || col0 >= N) { ctl.skip(); return; }  // warp-uniform
+    const int row = r0 + lane;
+    const bool row_ok = row < M;
+    const float tau = row_ok ? p.tau[row] : 0.f;
+    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
+    // ---- phase 1: shifted scores, fp16 pairs in registers
+    uint32_t zp[64];
+    const uint32_t acc_s = ctl.wait(0) + c;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float s[32];
+      tmem_ld32(acc_s + 32 * q, s);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        zp[16 * q + j] = pack_half2(gate_shifted<KIND>(p.gc, s[2 * j], tau, isg),
+                                    gate_shifted<KIND>(p.gc, s[2 * j + 1], tau, isg));
+    }
+    ctl.release(0);   // the next tile's score MMAs may start
+    // ---- phase 2
+    const float dden = (kStage == 1 && row_ok) ? p.dden[row] : 0.f;
+    float dtau_acc = 0.f;
+    const uint32_t acc_v = ctl.wait(1) + c;       // XR (A) or DP (B)
+    const __nv_bfloat16* c1row = kStage == 1 ? p.c1 + static_cast<size_t>(row) * p.ldc1 : nullptr;
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      if (col0 + 64 * sl < N) {                   // warp-uniform
+        st.wait_free<0>();
+        const uint32_t b0 = st.buf(0), b1 = st.buf(1);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float v[32], w[32];
+          tmem_ld32(acc_v + 64 * sl + 32 * half, v);
+          const int cb = col0 + 64 * sl + 32 * half;
+          if (kStage == 1) {
+            // this row's c1 values of the 32 columns: 4 x 16 bytes (the buffer's row pitch
+            // is a multiple of 8 columns, so a chunk that starts inside it is in bounds)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              uint4 u = make_uint4(0u, 0u, 0u, 0u);
+              if (row_ok && cb + 8 * k < p.ldc1)
+                u = *reinterpret_cast<const uint4*>(c1row + cb + 8 * k);
+              const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h2[e]);
+                w[8 * k + 2 * e] = f.x;
+                w[8 * k + 2 * e + 1] = f.y;
+              }
+            }
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float2 zt = unpack_half2(zp[32 * sl + 16 * half + j]);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int jj = 2 * j + e;
+              float a1, a2;
+              const float g = gate_coeffs_shifted<KIND>(p.gc, e == 0 ? zt.x : zt.y, isg, a1, a2);
+              if (kStage == 0) {
+                w[jj] = a1 * v[jj];     // c1
+                v[jj] = g * v[jj];      // p
+              } else {
+                float d = fmaf(v[jj], w[jj], a2 * dden);
+                if (cb + jj >= N) d = 0.f;
+                dtau_acc -= d;
+                w[jj] = d;              // ds
+                v[jj] = v[jj] * g;      // dxr
+              }
+            }
+          }
+          stage_bf16_32(st, b0, 4 * half, v);
+          stage_bf16_32(st, b1, 4 * half, w);
+        }
+        if (sl == 1 || col0 + 64 >= N) ctl.release(1);   // last TMEM read of this tile
+        st.flush(&maps[0], b0, col0 + 64 * sl, r0, false, true);
+        st.flush(&maps[1], b1, col0 + 64 * sl, r0, false, true);
+      }
+    }
+    if (kStage == 1 && row_ok) atomicAdd(p.dtau_sum + row, dtau_acc);
+  }
+};
+
 // ----------------------------------------------------------- host launchers
 struct OperandDesc {
   const void* ptr;
@@ -663,6 +827,92 @@ static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int*
     g->dst[t] = g->src[t][d->my_rank];
   }
   *m_rot = d->my_rank * d->rows_per_rank / (2 * kBlockM);
+  return 0;
+}
+
+static GateConsts gate_consts_of(const DsbGate* g) {
+  return {g->kind, g->sharpness, g->act_threshold, g->act_cutoff, g->epsilon, g->max_intensity,
+          g->clip_max, g->dead_threshold};
+}
+
+// Environment switch DSB_WIDE_BWD=0 keeps the backward gate kernel on 128-wide tiles.
+static bool use_wide_bwd() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DSB_WIDE_BWD");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <int kStage>
+static int launch_bwd_wide(GemmParams<BwdWideParams>& gp, int kind, bool fused, cudaStream_t stream) {
+  if (fused) {
+    if (kind == 0) return launch_engine_gather<256, BwdGateEpiWide<0, kStage>>(gp, stream);
+    if (kind == 1) return launch_engine_gather<256, BwdGateEpiWide<1, kStage>>(gp, stream);
+    return launch_engine_gather<256, BwdGateEpiWide<2, kStage>>(gp, stream);
+  }
+  if (kind == 0) return launch_engine_impl<256, BwdGateEpiWide<0, kStage>, 2>(gp, stream);
+  if (kind == 1) return launch_engine_impl<256, BwdGateEpiWide<1, kStage>, 2>(gp, stream);
+  return launch_engine_impl<256, BwdGateEpiWide<2, kStage>, 2>(gp, stream);
+}
+
+// The backward gate step as two 256-wide launches (see BwdGateEpiWide).  With a
+// gather, launch A pulls the peers' x and h rows (tensors 0 and 1 of the
+// descriptor, epoch e) and launch B the dy rows (tensor 2, epoch e + 1): the
+// caller must not reuse e + 1.
+static int bwd_gate_wide(const void* h, long long ldh, const void* emb, long long lde, const void* x,
+                         long long ldx, const void* read, long long ldr, const void* dy,
+                         long long lddy, const void* write, long long ldw, int T, int U, int r,
+                         int D, void* p_out, void* dxr_out, void* ds_out, long long ld_out,
+                         const float* tau, const float* inv_sigma, const float* dden,
+                         float* dtau_sum, const DsbGate* gate, const DsbGather* gather, int* status,
+                         cudaStream_t stream) {
+  const bool fused = gather != nullptr && gather->n_ranks > 1;
+  if (fused && gather->n_tensors != 3) return 703;
+  const int brows = 128;
+  for (int stage = 0; stage < 2; ++stage) {
+    GemmParams<BwdWideParams> gp;
+    memset(&gp, 0, sizeof(gp));
+    int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
+    rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
+    if (stage == 0) {
+      rc |= fill_operand(&gp.tma_a[1], {x, 0, ldx}, T, D, kBlockM);
+      rc |= fill_operand(&gp.tma_b[1], {read, 0, ldr}, U, D, brows);
+    } else {
+      rc |= fill_operand(&gp.tma_a[1], {dy, 0, lddy}, T, D, kBlockM);
+      rc |= fill_operand(&gp.tma_b[1], {write, 0, ldw}, U, D, brows);
+    }
+    if (rc) return 100 + rc;
+    gp.seg[0] = {(r + kBlockK - 1) / kBlockK, 0, 0, 0};
+    gp.seg[1] = {(D + kBlockK - 1) / kBlockK, 1, 0, 0};
+    gp.n_seg = 2;
+    gp.M = T;
+    gp.N = U;
+    gp.status = status;
+    rc = make_out_tmap(&gp.tma_out[0], stage == 0 ? p_out : dxr_out, T, U, ld_out, 2);
+    rc |= make_out_tmap(&gp.tma_out[1], ds_out, T, U, ld_out, 2);
+    if (rc) return 300 + rc;
+    gp.epi = {tau, inv_sigma, dden, dtau_sum, reinterpret_cast<const __nv_bfloat16*>(ds_out), ld_out,
+              gate_consts_of(gate)};
+    if (fused) {
+      DsbGather sub = *gather;
+      if (stage == 0) {
+        sub.n_tensors = 2;                       // x, h
+      } else {
+        sub.n_tensors = 1;                       // dy
+        sub.bufs[0] = gather->bufs[2];
+        sub.ld[0] = gather->ld[2];
+        sub.cols[0] = gather->cols[2];
+        sub.epoch = gather->epoch + 1;
+      }
+      rc = fill_gather(&gp.gather, &sub, T, &gp.m_rot);
+      if (rc) return rc;
+    }
+    rc = stage == 0 ? launch_bwd_wide<0>(gp, gate->kind, fused, stream)
+                    : launch_bwd_wide<1>(gp, gate->kind, fused, stream);
+    if (rc) return rc;
+  }
   return 0;
 }
 
@@ -800,6 +1050,10 @@ extern "C" int dsb_srw_bwd_gate_gather(const void* h, long long ldh, const void*
                                        float* dsz_sum, const DsbGate* gate,
                                        const DsbGather* gather, int* status, cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
+  if (use_cta_pairs() && use_wide_bwd() && U >= 512)
+    return bwd_gate_wide(h, ldh, emb, lde, x, ldx, read, ldr, dy, lddy, write, ldw, T, U, r, D, p_out,
+                         dxr_out, ds_out, ld_out, tau, inv_sigma, dden, dtau_sum, gate, gather,
+                         status, stream);
   constexpr int BN = 128;
   GemmParams<BwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));

@@ -152,10 +152,12 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         dtau = torch.zeros(T, dtype=torch.float32, device=dev)
         dsz = torch.zeros(T, dtype=torch.float32, device=dev)
         emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
-        CB._LAUNCHES += 1
+        CB._LAUNCHES += 2
+        ep = c.next_epoch()      # the wide kernel pair uses ep (x, h rows) and ep + 1 (dy rows)
+        c.next_epoch()
         e.srw_bwd_gate_gather(hf.local, emb, xf.local, read, dyf.local, write, p, dxr, ds, tau_full,
                               inv_sd_full, dden, dtau, dsz, CB._gate_list(spec), st,
-                              [xf.ptrs, hf.ptrs, dyf.ptrs], c.rank, Tl, c.ready, c.next_epoch())
+                              [xf.ptrs, hf.ptrs, dyf.ptrs], c.rank, Tl, c.ready, ep)
         pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
         CB.gemm(pv, True, dyf.local, True, out=hd.g_write[:U], accumulate=True)      # p^T dy
         CB.gemm(dxrv, True, xf.local, True, out=hd.g_read[:U], accumulate=True)      # dxr^T x

@@ -97,7 +97,7 @@ def test_peer_barrier_and_fused_gemm_reduce_scatter():
     assert max(errs) < 1e-5, errs
 
 
-def _fused_vs_nccl(rank, world, version):
+def _fused_vs_nccl(rank, world, version, U_total):
     """One sequence+pool-sharded SRW op: in-kernel collectives vs NCCL collectives."""
     from dawn_srw_b200.ops import cuda_backend as CB
     from dawn_srw_b200.ops.backend import ParallelCtx
@@ -106,7 +106,7 @@ def _fused_vs_nccl(rank, world, version):
     import torch.distributed as dist
     dev = torch.device("cuda", rank)
     spec = gate_spec_for(version)
-    Tl, R, U, r, D = 512, 2, 300, 64, 128
+    Tl, R, U, r, D = 512, 2, U_total, 64, 128
     g = torch.Generator(device=dev).manual_seed(7)             # same full tensors on every rank
     rn = lambda *s: torch.randn(*s, device=dev, generator=g)
     nz = torch.nn.functional.normalize
@@ -140,10 +140,11 @@ def _fused_vs_nccl(rank, world, version):
     return {n: rel(a, b) for n, a, b in zip(names, res["fused"], res["nccl"])}
 
 
-@pytest.mark.parametrize("version", ["spatial-r1-v4.0.1", "spatial-r1-v3.9.4"])
-def test_fused_all_gather_and_reduce_scatter_match_nccl_path(version):
+@pytest.mark.parametrize("version,units", [("spatial-r1-v4.0.1", 300), ("spatial-r1-v3.9.4", 300),
+                                           ("spatial-r1-v4.0.1", 1301)])    # 1301: 256-wide kernels
+def test_fused_all_gather_and_reduce_scatter_match_nccl_path(version, units):
     _need(2)
-    outs = _spawn(_fused_vs_nccl, 2, version)
+    outs = _spawn(_fused_vs_nccl, 2, version, units)
     for o in outs:
         for k, v in o.items():
             # same kernels and math; differences: fp32 (fused) vs bf16 (NCCL) partial sums
