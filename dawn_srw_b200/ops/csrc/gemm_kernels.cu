@@ -598,6 +598,20 @@ __device__ __forceinline__ float gate_coeffs_shifted(const GateConsts& gc, float
   }
   return g;
 }
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   const __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -621,7 +635,7 @@ template <int KIND, int kStage>
 struct BwdGateEpiWide {
   static constexpr int kNumAcc = 2;
   static constexpr int kNumOut = 2;
-  static constexpr int kOutBufs = 2;
+  static constexpr int kOutBufs = kStage == 1 ? 3 : 2;   // B: dxr, and one c1/ds buffer per slab
   static constexpr int kEpiWarps = 8;
   __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
   using Params = BwdWideParams;
@@ -655,26 +669,46 @@ struct BwdGateEpiWide {
     // ---- phase 2
     const float dden = (kStage == 1 && row_ok) ? p.dden[row] : 0.f;
     float dtau_acc = 0.f;
+    if (kStage == 1) {
+      // Fetch this warp's two 32 x 64 c1 slabs while the DP MMAs still run: asynchronous
+      // 16-byte copies straight into shared memory (8 lanes per row, coalesced), in the
+      // swizzled layout of the staging buffers.  Slab sl lands in buffer 1 + sl, the buffer
+      // that later stages ds of the same slab, so a thread reads its c1 chunk before it
+      // overwrites it.
+      st.wait_free<0>();                          // the previous tile's stores have read them
+      const int ch = lane & 7;
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) {
+        const int colS = col0 + 64 * sl + ch * 8;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + (lane >> 3);
+          const bool ok = r0 + rr < M && colS < p.ldc1;
+          const __nv_bfloat16* src = ok ? p.c1 + static_cast<size_t>(r0 + rr) * p.ldc1 + colS : p.c1;
+          cp_async_16(st.buf(1 + sl) + rr * 128 + ((ch ^ (rr & 7)) << 4), src, ok ? 16 : 0);
+        }
+      }
+    }
     const uint32_t acc_v = ctl.wait(1) + c;       // XR (A) or DP (B)
-    const __nv_bfloat16* c1row = kStage == 1 ? p.c1 + static_cast<size_t>(row) * p.ldc1 : nullptr;
 #pragma unroll
     for (int sl = 0; sl < 2; ++sl) {
       if (col0 + 64 * sl < N) {                   // warp-uniform
-        st.wait_free<0>();
-        const uint32_t b0 = st.buf(0), b1 = st.buf(1);
+        if (kStage == 0 || sl == 1) st.wait_free<0>();
+        const uint32_t b0 = st.buf(0), b1 = st.buf(kStage == 1 ? 1 + sl : 1);
+        if (kStage == 1 && sl == 0) {
+          cp_async_wait_all();          // both c1 slabs of this tile are in shared memory
+          __syncwarp();
+        }
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           float v[32], w[32];
           tmem_ld32(acc_v + 64 * sl + 32 * half, v);
           const int cb = col0 + 64 * sl + 32 * half;
           if (kStage == 1) {
-            // this row's c1 values of the 32 columns: 4 x 16 bytes (the buffer's row pitch
-            // is a multiple of 8 columns, so a chunk that starts inside it is in bounds)
+            // this row's c1 values of the 32 columns, from the slab the warp just staged
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              uint4 u = make_uint4(0u, 0u, 0u, 0u);
-              if (row_ok && cb + 8 * k < p.ldc1)
-                u = *reinterpret_cast<const uint4*>(c1row + cb + 8 * k);
+              const uint4 u = ld_shared_v4(b1 + lane * 128 + (((4 * half + k) ^ (lane & 7)) << 4));
               const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
