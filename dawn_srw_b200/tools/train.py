@@ -52,12 +52,15 @@ def main(argv=None):
     ap.add_argument("--max-steps", type=int)
     ap.add_argument("--synthetic", action="store_true", help="uniform-random tokens instead of files")
     ap.add_argument("--library", action="store_true", help="library baseline backend (torch matmuls)")
+    ap.add_argument("--checkpoint-dir", help="override the config's checkpoint_dir")
     ap.add_argument("--debug", action="store_true")
     ap.add_argument("--no-startup-check", action="store_true",
                     help="skip the start-up memory check and per-block timing table")
     args = ap.parse_args(argv)
 
     cfg = load_config(args.config)
+    if args.checkpoint_dir:
+        cfg.checkpoint_dir = args.checkpoint_dir
     t = cfg.training
     topo = init_topology(pool_shards=t.pool_shards, dp=t.dp, seq_shard=t.seq_shard)
     if args.synthetic:

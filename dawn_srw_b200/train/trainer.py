@@ -301,6 +301,8 @@ class Trainer:
                         rec_m.update(total_loss=w[0] / w[3], ce_loss=w[1] / w[3], accuracy=w[2] / w[3])
                     for key in ("total_loss", "ce_loss", "aux_loss", "div_loss", "grad_norm"):
                         val = rec_m.get(key)
+                        if isinstance(val, torch.Tensor):
+                            val = val.detach()
                         val = float(val) if val is not None else 0.0
                         if not math.isfinite(val):
                             raise NonFiniteLoss(f"non-finite {key}={val} in the log window at step {self.global_step}")
@@ -319,6 +321,9 @@ class Trainer:
                     self.save(f"checkpoint_step{self.global_step}.pt")
                 last = m
                 if t.max_steps and self.global_step >= t.max_steps:
+                    # a run cut short by max_steps still leaves a checkpoint to resume from
+                    if not (t.checkpoint_interval and self.global_step % t.checkpoint_interval == 0):
+                        self.save(f"checkpoint_step{self.global_step}.pt")
                     done = True
                     break
             if done:

@@ -61,3 +61,58 @@ def test_analysis_cli_runs_every_key(tmp_path):
     assert A.main(["--checkpoint", path, "--synthetic", "--only", "info,health", "--device", "cpu"]) == 0
     with pytest.raises(SystemExit):
         A.main(["--checkpoint", path, "--only", "nope", "--device", "cpu"])
+
+
+def test_train_eval_generate_clis_and_resume(tmp_path, capsys):
+    """configs/smoke_tiny_synthetic.yaml through the train CLI (start-up report,
+    checkpoints, resume from the newest run), then eval and generate on the result."""
+    import glob
+    from dawn_srw_b200.tools import eval as E, generate as G, train as T
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(root, "configs", "smoke_tiny_synthetic.yaml")
+    ck = str(tmp_path / "ck")
+    assert T.main(["--config", cfg, "--from-scratch", "--max-steps", "6", "--checkpoint-dir", ck]) == 0
+    out = capsys.readouterr().out
+    assert "[startup] forward+backward" in out and '"final"' in out
+    runs = glob.glob(os.path.join(ck, "run_*"))
+    assert len(runs) == 1
+    ckpts = sorted(glob.glob(os.path.join(runs[0], "*.pt")))
+    assert ckpts, os.listdir(runs[0])
+    # a second invocation without --from-scratch resumes the same run folder
+    assert T.main(["--config", cfg, "--max-steps", "8", "--checkpoint-dir", ck, "--no-startup-check"]) == 0
+    out = capsys.readouterr().out
+    assert "Resumed from" in out and len(glob.glob(os.path.join(ck, "run_*"))) == 1
+    newest = max(glob.glob(os.path.join(runs[0], "*.pt")), key=os.path.getmtime)
+    assert E.main(["--checkpoint", newest, "--synthetic", "--batch-size", "4", "--max-batches", "2"]) == 0
+    rec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rec["val_loss"] > 0 and rec["valid_tokens"] > 0
+    assert G.main(["--checkpoint", newest, "--ids", "5,6,7", "--max-new-tokens", "5"]) == 0
+    assert capsys.readouterr().out.strip()
+
+
+def test_every_shipped_config_loads_without_unknown_keys():
+    import glob
+    import warnings
+    from dawn_srw_b200.config import load_config
+    from dawn_srw_b200.models.registry import MODEL_REGISTRY
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "configs", "*.yaml")))
+    assert len(files) >= 15
+    for f in files:
+        with warnings.catch_warnings():
+            warnings.simplefilter("error")
+            cfg = load_config(f)
+        assert cfg.model.model_version in MODEL_REGISTRY, f
+        t = cfg.training
+        assert t.pool_shards >= 1 and (t.dp == 0 or t.dp * t.pool_shards in (1, 8)), f
+
+
+def test_bench_reference_arm_reports_unavailable():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    rec = json.loads(r.stdout.strip().splitlines()[-1])
+    assert rec["impl"] == "reference" and "unavailable" in rec
