@@ -21,6 +21,10 @@ dict; the selection mirrors the SRW part of the reference's analysis CLI
   layer_role   attention vs knowledge output norm per layer
   intervene    loss change when the most-used knowledge units are suppressed
   pool_geom    spectrum of the pool embeddings (variance explained by top directions)
+  rw_align     cos(read_u, write_u) per unit and its correlation with selection frequency
+  tau_dist     threshold offsets produced by the tau heads on the sample (per route: mean,
+               spread, quantiles, fraction below zero)
+  drift        movement of the pool tensors against a second checkpoint (--compare-checkpoint)
 
 All analyses run on one device through the model's public inference API
 (models/inference.py).
@@ -223,14 +227,76 @@ def analyze_pool_geom(c: Context) -> Dict:
     return out
 
 
+def analyze_rw_align(c: Context) -> Dict:
+    p = c.model.neuron_pool
+    cnt = _selection_counts(c)
+    freq = {"qk": (cnt["Q"] + cnt["K"]).sum(0), "v": cnt["V"].sum(0), "know": cnt["Know"].sum(0)}
+    out = {}
+    for name in ("qk", "v", "know"):
+        n = p.n_valid(name)
+        rd = getattr(p, f"{name}_read")[:n].float()
+        wr = getattr(p, f"{name}_write")[:n].float()
+        cos = torch.nn.functional.cosine_similarity(rd, wr, dim=-1)
+        f = freq[name][:n].float()
+        rec = {"cos_mean": float(cos.mean()), "cos_std": float(cos.std(unbiased=False)),
+               "cos_min": float(cos.min()), "cos_max": float(cos.max()),
+               "frac_negative": float((cos < 0).float().mean())}
+        if float(f.std(unbiased=False)) > 0 and float(cos.std(unbiased=False)) > 0:
+            rec["corr_with_selection_freq"] = float(torch.corrcoef(torch.stack([cos, f]))[0, 1])
+        out[name] = rec
+    return out
+
+
+def analyze_tau_dist(c: Context) -> Dict:
+    m, ids = c.model, c.batches()[0]
+    be = I._be(m, c.device)
+    B, S = ids.shape
+    x = be.embed(ids, m.token_emb.weight, m.pos_emb.weight).float()
+    blk = m.layers[0]
+    n1 = be.layer_norm(x, blk.norm1.weight, blk.norm1.bias).reshape(B * S, m.d_model)
+    rt = m.router
+    taus = {"attn": be.linear(n1, rt.tau_attn.weight, rt.tau_attn.bias).float(),
+            "know": be.linear(n1, rt.tau_know.weight, rt.tau_know.bias).float()}
+    names = {"attn": ("Q", "K", "V"), "know": ("Know",)}
+    qs = torch.tensor([0.01, 0.5, 0.99], device=c.device)
+    out = {"layer": 0}
+    for key, t in taus.items():
+        for i, nm in enumerate(names[key]):
+            col = t[:, i]
+            q = torch.quantile(col, qs).tolist()
+            out[nm] = {"mean": float(col.mean()), "std": float(col.std(unbiased=False)),
+                       "p01": q[0], "p50": q[1], "p99": q[2],
+                       "neg_frac": float((col < 0).float().mean())}
+    return out
+
+
+def analyze_drift(c: Context) -> Dict:
+    other = c.args.compare_checkpoint
+    if not other:
+        return {"skipped": "pass --compare-checkpoint to measure drift against another checkpoint"}
+    ref, _, info = load_model(other, c.args.config, device=str(c.device))
+    out = {"against": info}
+    p, q = c.model.neuron_pool, ref.neuron_pool
+    for name in ("qk", "v", "know"):
+        n = p.n_valid(name)
+        for kind in ("emb", "read", "write"):
+            a = getattr(p, f"{name}_{kind}")[:n].float()
+            b = getattr(q, f"{name}_{kind}")[:n].float()
+            cos = torch.nn.functional.cosine_similarity(a, b, dim=-1)
+            out[f"{name}_{kind}"] = {"rel_l2": float((a - b).norm() / b.norm().clamp(min=1e-12)),
+                                     "row_cos_mean": float(cos.mean()), "row_cos_min": float(cos.min())}
+    return out
+
+
 ANALYSES: Dict[str, Callable[[Context], Dict]] = {
     "info": analyze_info, "val": analyze_val, "health": analyze_health, "weights": analyze_weights,
     "generate": analyze_generate, "routing": analyze_routing, "gate_dist": analyze_gate_dist,
     "utilization": analyze_utilization, "sel_gini": analyze_sel_gini,
     "layer_role": analyze_layer_role, "intervene": analyze_intervene, "pool_geom": analyze_pool_geom,
+    "rw_align": analyze_rw_align, "tau_dist": analyze_tau_dist, "drift": analyze_drift,
 }
 SPATIAL_ONLY = {"health", "weights", "routing", "gate_dist", "utilization", "sel_gini", "layer_role",
-                "intervene", "pool_geom"}
+                "intervene", "pool_geom", "rw_align", "tau_dist", "drift"}
 
 
 def run(model, cfg, info, args) -> Dict:
@@ -265,6 +331,7 @@ def main(argv=None):
     ap.add_argument("--temperature", type=float, default=0.8)
     ap.add_argument("--top-k", type=int, default=50)
     ap.add_argument("--suppress-top", type=int, nargs="*", default=[16, 128])
+    ap.add_argument("--compare-checkpoint")
     ap.add_argument("--output")
     ap.add_argument("--library", action="store_true")
     ap.add_argument("--device")

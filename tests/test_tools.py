@@ -47,7 +47,7 @@ def test_analysis_cli_runs_every_key(tmp_path):
     out_dir = str(tmp_path / "ana")
     assert A.main(["--checkpoint", path, "--synthetic", "--batch-size", "2", "--n-batches", "2",
                    "--suppress-top", "4", "--max-new-tokens", "4", "--output", out_dir,
-                   "--device", "cpu"]) == 0
+                   "--compare-checkpoint", path, "--device", "cpu"]) == 0
     res = json.load(open(os.path.join(out_dir, "analysis.json")))
     assert set(res) == set(A.ANALYSES)
     assert res["info"]["parameters"] > 0 and res["val"]["val_loss"] > 0
@@ -56,6 +56,9 @@ def test_analysis_cli_runs_every_key(tmp_path):
     assert 0.0 <= res["utilization"]["Know"]["used_frac_any_layer"] <= 1.0
     assert 0.0 <= res["sel_gini"]["Q"]["gini_all_layers"] <= 1.0
     assert len(res["intervene"]["suppressed"]) == 1
+    assert -1.0 <= res["rw_align"]["know"]["cos_mean"] <= 1.0
+    assert res["tau_dist"]["Know"]["std"] >= 0.0
+    assert res["drift"]["know_emb"]["rel_l2"] == 0.0          # compared with itself
     assert len(res["generate"]["samples"][0]["token_ids"]) >= 4
     # key selection
     assert A.main(["--checkpoint", path, "--synthetic", "--only", "info,health", "--device", "cpu"]) == 0
