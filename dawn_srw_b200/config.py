@@ -92,6 +92,7 @@ class TrainingConfig:
     dp: int = 0
     seq_shard: bool = True
     zero_pool_state: bool = False
+    overlap_grad_reduce: bool = True     # replicated-parameter gradients are all-reduced during backward
     n_chunks_know: int = 0
     n_chunks_qk: int = 0
     n_chunks_v: int = 0

@@ -19,6 +19,16 @@ Small tensors are packed into one flat bucket per reduction; pool tensors are
 reduced in place.  The squared global norm counts each parameter once: pool
 slices are summed over the shard group, replicated parameters are taken from
 the local copy.
+
+Overlap with backward (``attach``): the gradients of replicated parameters are
+final at different times during backward (per-layer tensors early, the shared
+router and the embeddings at the very end).  A post-accumulate hook appends
+each finished gradient to the current bucket and launches an asynchronous
+all-reduce as soon as the bucket holds ``bucket_bytes``; ``reduce`` then only
+flushes the last bucket, waits and copies back.  The hook order is a property
+of the graph, so all ranks build identical buckets.  Pool gradients complete
+only when the whole backward is done (every layer adds into them) and are
+reduced afterwards as before.
 """
 from __future__ import annotations
 
@@ -33,6 +43,72 @@ from ..train.optimizer import wd_group_of
 class GradSync:
     def __init__(self, topo):
         self.topo = topo
+        self._overlap = False
+        self._bucket_bytes = 0
+        self._open: List[torch.nn.Parameter] = []     # finished gradients not yet launched
+        self._open_bytes = 0
+        self._inflight = []                            # (flat, work, params)
+        self._hooks = []
+
+    # ---- overlap with backward ---------------------------------------------
+    def attach(self, named_params, bucket_bytes: int = 32 << 20) -> None:
+        """Start reducing replicated-parameter gradients while backward still runs.
+        Only valid when every backward is followed by ``reduce`` on the ``.grad``
+        tensors themselves (no gradient accumulation over micro-steps)."""
+        if self.topo.world == 1 or self._overlap:
+            return
+        self._overlap, self._bucket_bytes = True, int(bucket_bytes)
+        for n, p in named_params:
+            if p.requires_grad and not self._is_pool(n):
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad_ready))
+
+    def detach(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks, self._overlap = [], False
+        self.discard()
+
+    def discard(self) -> None:
+        """Forget the gradients of a backward whose result is not used (every
+        rank must call it at the same point)."""
+        for _flat, work, _ps in self._inflight:
+            work.wait()
+        self._inflight, self._open, self._open_bytes = [], [], 0
+
+    def _on_grad_ready(self, p: torch.nn.Parameter) -> None:
+        self._open.append(p)
+        self._open_bytes += p.grad.numel() * 4
+        if self._open_bytes >= self._bucket_bytes:
+            self._launch()
+
+    def _launch(self) -> None:
+        if not self._open:
+            return
+        ps = self._open
+        flat = torch.cat([p.grad.reshape(-1).float() for p in ps])
+        work = dist.all_reduce(flat, group=self.topo.world_group, async_op=True)
+        self._inflight.append((flat, work, ps))
+        self._open, self._open_bytes = [], 0
+
+    def _finish_overlapped(self, named, grads) -> set:
+        """Wait for the buckets launched during backward; returns the ids of the
+        gradient tensors they covered."""
+        self._launch()
+        by_param = {id(p): g for (_, p), g in zip(named, grads)}
+        done = set()
+        for flat, work, ps in self._inflight:
+            work.wait()
+            flat /= self.topo.world
+            off = 0
+            for p in ps:
+                g = by_param.get(id(p))
+                n = p.numel()
+                if g is not None:
+                    g.copy_(flat[off: off + n].view_as(g))
+                    done.add(id(g))
+                off += n
+        self._inflight = []
+        return done
 
     def _is_pool(self, name: str) -> bool:
         return wd_group_of(name) == "pool"
@@ -41,7 +117,8 @@ class GradSync:
         t = self.topo
         if t.world == 1:
             return grads
-        small = [g for (n, _), g in zip(named, grads) if not self._is_pool(n)]
+        done = self._finish_overlapped(named, grads) if self._overlap else set()
+        small = [g for (n, _), g in zip(named, grads) if not self._is_pool(n) and id(g) not in done]
         if small:
             flat = torch.cat([g.reshape(-1).float() for g in small])
             dist.all_reduce(flat, group=t.world_group)

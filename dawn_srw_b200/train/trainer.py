@@ -84,10 +84,13 @@ class Trainer:
                 pool_weight_decay=t.pool_weight_decay, schedule=self.schedule,
                 accumulation_steps=k)
         else:
+            sync = GradSync(self.topo) if self.topo.world > 1 else None
+            if sync is not None and k == 1 and t.overlap_grad_reduce:
+                sync.attach(self.model.named_parameters())     # reduce while backward still runs
             self.optimizer = DawnAdamW(
                 self.model.named_parameters(), lr=t.lr, weight_decay=t.weight_decay,
                 pool_weight_decay=t.pool_weight_decay, schedule=self.schedule, accumulation_steps=k,
-                grad_sync=GradSync(self.topo) if self.topo.world > 1 else None)
+                grad_sync=sync)
         self.global_step = 0          # micro-steps taken
         self.epoch = 0
         self.step_in_epoch = 0

@@ -87,12 +87,14 @@ def test_sequence_sharding_matches_single_rank():
             assert torch.allclose(got, full[f"neuron_pool.know_{kind}"][lo:hi], atol=2e-5), (kind, k)
 
 
-def _dp_trainer_worker(rank, world, pool_shards, seq_shard, zero=False, accum=1, ckpt_dir=None):
+def _dp_trainer_worker(rank, world, pool_shards, seq_shard, zero=False, accum=1, ckpt_dir=None,
+                       overlap=True):
     from dawn_srw_b200.parallel.topology import init_topology
     from dawn_srw_b200.train.trainer import Trainer
     topo = init_topology(pool_shards=pool_shards, seq_shard=seq_shard, backend="gloo")
     cfg = tiny_config(version="spatial-r1-v4.0.1", max_steps=3, diversity_weight=0.0,
-                      zero_pool_state=zero, gradient_accumulation_steps=accum)
+                      zero_pool_state=zero, gradient_accumulation_steps=accum,
+                      overlap_grad_reduce=overlap)
     tr = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10, run_dir=ckpt_dir)
     for i in range(3 * accum):
         ids, mask = tr.train_loader.batch(i)
@@ -128,7 +130,10 @@ def _dp_grad_worker(rank, world):
     r = tr.model(ids.long(), labels=ids.long(), want_diag=False)
     r["loss"].backward()
     named = list(tr.model.named_parameters())
-    grads = GradSync(topo).reduce(named, [p.grad for _, p in named])
+    sync = tr.optimizer.grad_sync          # hooks launched bucketed all-reduces during backward
+    assert sync._overlap and (sync._inflight or sync._open)
+    grads = sync.reduce(named, [p.grad for _, p in named])
+    assert not sync._inflight and not sync._open
     return {n: g for (n, _), g in zip(named, grads)}
 
 
@@ -180,6 +185,17 @@ def test_partitioned_optimizer_checkpoint_roundtrip(tmp_path):
     n_params = sum(v.numel() for v in outs[0]["sd"].values())
     # two moments, fp32, half of the parameters each (plus padding)
     assert outs[0]["state_bytes"] <= 2 * 4 * (n_params // 2 + 64)
+
+
+@pytest.mark.parametrize("layout", [(2, 1, False), (2, 2, True)])
+def test_overlapped_gradient_reduction_changes_nothing(layout):
+    world, shards, seq = layout
+    a = run_ranks(_dp_trainer_worker, world, shards, seq, False, 1, None, True)
+    b = run_ranks(_dp_trainer_worker, world, shards, seq, False, 1, None, False)
+    for r in range(world):
+        assert a[r]["gn"] == b[r]["gn"]
+        for n in a[r]["sd"]:
+            assert torch.equal(a[r]["sd"][n], b[r]["sd"][n]), (r, n)
 
 
 def _consensus_worker(rank, world):
