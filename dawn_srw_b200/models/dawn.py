@@ -35,6 +35,7 @@ import torch
 import torch.nn as nn
 import torch.utils.checkpoint as ckpt
 
+from ..utils.tracing import trace
 from ..ops.backend import ParallelCtx, ReferenceBackend, default_backend
 from ..ops.gates import GateSpec, gate_spec_for
 from ..parallel.topology import PoolShard
@@ -194,22 +195,27 @@ class DAWN(nn.Module):
         T = B * S
         rt = self.router
         xf = x.reshape(T, D)
-        h_all = be.linear(xf, rt.proj_attn.weight, rt.proj_attn.bias)
-        h_all = be.dropout(h_all, self.router_dropout, training)
-        tau_all = be.linear(xf, rt.tau_attn.weight, rt.tau_attn.bias).float()    # [T,3]
+        with trace("attn/router"):
+            h_all = be.linear(xf, rt.proj_attn.weight, rt.proj_attn.bias)
+            h_all = be.dropout(h_all, self.router_dropout, training)
+            tau_all = be.linear(xf, rt.tau_attn.weight, rt.tau_attn.bias).float()    # [T,3]
         h_qk = h_all[:, : 2 * r].reshape(T, 2, r)
         h_v = h_all[:, 2 * r:].reshape(T, 1, r)
         qk_scale, v_scale = self.pool_scale("qk"), self.pool_scale("v")
-        res_qk = be.srw(xf, h_qk, tau_all[:, 0:2], pools["qk"], self.gate,
-                        pctx=self.pctx("qk"), want_diag=want_diag, out_scale=qk_scale)
-        res_v = be.srw(xf, h_v, tau_all[:, 2:3], pools["v"], self.gate,
-                       pctx=self.pctx("v"), want_diag=want_diag, out_scale=v_scale)
+        with trace("attn/srw_qk"):
+            res_qk = be.srw(xf, h_qk, tau_all[:, 0:2], pools["qk"], self.gate,
+                            pctx=self.pctx("qk"), want_diag=want_diag, out_scale=qk_scale)
+        with trace("attn/srw_v"):
+            res_v = be.srw(xf, h_v, tau_all[:, 2:3], pools["v"], self.gate,
+                           pctx=self.pctx("v"), want_diag=want_diag, out_scale=v_scale)
         Q, K, V = res_qk.route(0), res_qk.route(1), res_v.route(0)
         dh = D // H
         to_heads = lambda t: t.reshape(B, S, H, dh).transpose(1, 2)
-        o = be.attention(to_heads(Q), to_heads(K), to_heads(V), self.dropout_rate, training)
-        o = o.transpose(1, 2).reshape(T, D)
-        out = be.linear(o, blk.attn.expand_O.weight, None)
+        with trace("attn/self_attention"):
+            o = be.attention(to_heads(Q), to_heads(K), to_heads(V), self.dropout_rate, training)
+            o = o.transpose(1, 2).reshape(T, D)
+        with trace("attn/expand_O"):
+            out = be.linear(o, blk.attn.expand_O.weight, None)
         out_d = be.dropout(out, self.dropout_rate, training).reshape(B, S, D)
         tau_relu = torch.relu(tau_all).mean()
         lb = (res_qk.lb + res_v.lb) / 3.0
@@ -229,12 +235,14 @@ class DAWN(nn.Module):
         T = B * S
         rt = self.router
         xf = x.reshape(T, D)
-        h = be.linear(xf, rt.proj_know.weight, rt.proj_know.bias)
-        h = be.dropout(h, self.router_dropout, training)
-        tau = be.linear(xf, rt.tau_know.weight, rt.tau_know.bias).float()         # [T,1]
+        with trace("know/router"):
+            h = be.linear(xf, rt.proj_know.weight, rt.proj_know.bias)
+            h = be.dropout(h, self.router_dropout, training)
+            tau = be.linear(xf, rt.tau_know.weight, rt.tau_know.bias).float()         # [T,1]
         k_scale = self.pool_scale("know")
-        res = be.srw(xf, h.reshape(T, 1, self.d_route), tau, pools["know"], self.gate,
-                     pctx=self.pctx("know"), want_diag=want_diag, out_scale=k_scale)
+        with trace("know/srw"):
+            res = be.srw(xf, h.reshape(T, 1, self.d_route), tau, pools["know"], self.gate,
+                         pctx=self.pctx("know"), want_diag=want_diag, out_scale=k_scale)
         out = res.route(0)
         raw = (out.detach() / k_scale) if want_diag else None     # pre-scale output, diagnostics only
         out_d = be.dropout(out, self.dropout_rate, training).reshape(B, S, D)
@@ -347,9 +355,11 @@ class DAWN(nn.Module):
             raise ValueError(f"Sequence length {S} exceeds max_seq_len")
         training = self.training if deterministic is None else (not deterministic)
         be = self._backend(input_ids.device)
-        x = be.embed(input_ids, self.token_emb.weight, self.pos_emb.weight)
-        x = be.dropout(x, self.dropout_rate, training)
-        pools = self.prepare_pools(be)
+        with trace("embed"):
+            x = be.embed(input_ids, self.token_emb.weight, self.pos_emb.weight)
+            x = be.dropout(x, self.dropout_rate, training)
+        with trace("prepare_pools"):
+            pools = self.prepare_pools(be)
         from collections import defaultdict
         m: Dict[str, list] = defaultdict(list)
         names = ("attn_aux", "attn_dead_penalty", "attn_tau_offset", "attn_tau_reg",
@@ -407,7 +417,8 @@ class DAWN(nn.Module):
                     [torch.linalg.matrix_norm(b.attn.expand_O.weight.float()) for b in self.layers]).mean()
         x = be.layer_norm(x, self.norm.weight, self.norm.bias)
         if labels is not None:
-            loss, per_tok, correct, nvalid, vmask = be.lm_head_ce(x, self.token_emb.weight, labels)
+            with trace("lm_head_ce"):
+                loss, per_tok, correct, nvalid, vmask = be.lm_head_ce(x, self.token_emb.weight, labels)
             res.update(loss=loss, correct=correct, valid_count=nvalid, per_token_ce=per_tok,
                        valid_mask=vmask)
         else:

@@ -54,6 +54,10 @@ def main(argv=None):
     ap.add_argument("--library", action="store_true", help="library baseline backend (torch matmuls)")
     ap.add_argument("--checkpoint-dir", help="override the config's checkpoint_dir")
     ap.add_argument("--debug", action="store_true")
+    ap.add_argument("--trace-steps", type=int, default=0,
+                    help="after training, run this many extra steps with device-timed ranges "
+                         "(forward blocks, backward, optimizer) and print the table; DAWN_NVTX=1 "
+                         "additionally emits NVTX ranges for external profilers")
     ap.add_argument("--no-startup-check", action="store_true",
                     help="skip the start-up memory check and per-block timing table")
     args = ap.parse_args(argv)
@@ -99,6 +103,14 @@ def main(argv=None):
         from ..train.startup import startup_report
         startup_report(trainer, print_fn=trainer.logger.message)
     out = trainer.fit()
+    if args.trace_steps > 0:
+        from ..utils import tracing
+        tracing.enable(timers=True)
+        for i in range(args.trace_steps):
+            trainer.train_step(*trainer.train_loader.batch(i % max(len(trainer.train_loader), 1)))
+        rep = tracing.report()
+        tracing.enable(timers=False)
+        trainer.logger.message("[trace] %d steps\n%s" % (args.trace_steps, tracing.format_report(rep)))
     if topo.is_main:
         print(json.dumps({"final": out, "run_dir": run_dir}))
     if topo.world > 1:

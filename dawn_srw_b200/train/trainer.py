@@ -35,6 +35,7 @@ from ..parallel.topology import Topology
 from . import checkpoint as ckpt
 from . import logging as L
 from .losses import total_loss
+from ..utils.tracing import trace
 from .optimizer import DawnAdamW, warmup_cosine
 
 
@@ -125,14 +126,17 @@ class Trainer:
         self.model.train()
         ids, mask = self._to_device(ids, mask)
         labels = torch.where(mask == 1, ids, torch.full_like(ids, -100))
-        result = self.model(ids, labels=labels, attention_mask=mask, want_diag=want_diag)
+        with trace("forward"):
+            result = self.model(ids, labels=labels, attention_mask=mask, want_diag=want_diag)
         opt_step = self.optimizer.count
         total, parts = total_loss(result, self.model, t, opt_step, is_baseline=self.is_baseline,
                                   dp_group=self.topo.world_group if self.topo.world > 1 else None,
                                   backend=self.backend, want_stats=want_diag)
-        total.backward()
-        self.optimizer.step()         # consumes this micro-step's gradients (it keeps its own sum)
-        self.optimizer.zero_grad()
+        with trace("backward"):
+            total.backward()
+        with trace("optimizer"):
+            self.optimizer.step()     # consumes this micro-step's gradients (it keeps its own sum)
+            self.optimizer.zero_grad()
         self.backend.finish_step()
         self.global_step += 1
         metrics: Dict[str, Any] = {"total_loss": total.detach()}

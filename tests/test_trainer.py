@@ -137,3 +137,22 @@ def test_startup_report_leaves_training_state_untouched():
     for n, p in _params(tr).items():
         assert torch.equal(p, before[n]), n
     assert tr.optimizer.count == 0 and all(p.grad is None for p in tr.model.parameters())
+
+
+def test_trace_ranges_cover_a_training_step():
+    from dawn_srw_b200.utils import tracing
+    tr = Trainer(tiny_config(version="spatial-r1-v4.0.1"), total_steps=50)
+    ids, mask = tr.train_loader.batch(0)
+    tracing.enable(timers=True)
+    try:
+        tr.train_step(ids, mask)
+        rep = tracing.report()
+    finally:
+        tracing.enable(timers=False)
+    L = tr.cfg.model.n_layers
+    assert rep["forward"][0] == 1 and rep["backward"][0] == 1 and rep["optimizer"][0] == 1
+    assert rep["attn/srw_qk"][0] == L and rep["know/srw"][0] == L and rep["lm_head_ce"][0] == 1
+    assert rep["forward"][1] >= rep["know/srw"][1] > 0
+    assert "know/srw" in tracing.format_report(rep)
+    tr.train_step(ids, mask)
+    assert tracing.report() == {}                 # off again: nothing is recorded
