@@ -105,6 +105,9 @@ class ReferenceBackend:
             return_gates=return_gates, use_checkpoint=self.use_checkpoint,
             seq_sharded=pctx.seq_sharded)
 
+    def finish_run(self):
+        pass
+
     def finish_step(self):
         pass
 

@@ -39,45 +39,63 @@ __global__ void ln_fwd_kernel(const float* __restrict__ x, const float* __restri
   if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
 }
 
-// dx fp32 [T, D]; dw/db fp32 [D] accumulated with atomics (must be zeroed).
-__global__ void ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
-                              const float* __restrict__ w, const float* __restrict__ mean,
-                              const float* __restrict__ rstd, float* __restrict__ dx,
-                              float* __restrict__ dw, float* __restrict__ db, int T, int D,
-                              int rows_per_block) {
-  extern __shared__ float sh[];  // [2 * D] partial dw, db of this block
-  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) sh[i] = 0.f;
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  const int row0 = blockIdx.x * rows_per_block;
-  for (int rr = warp; rr < rows_per_block; rr += nwarp) {
-    const int row = row0 + rr;
-    if (row >= T) break;
-    const float mu = mean[row], rs = rstd[row];
-    const float* xr = x + static_cast<size_t>(row) * D;
-    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * D;
-    float s1 = 0.f, s2 = 0.f;
-    for (int i = lane; i < D; i += 32) {
-      const float g = __bfloat162float(dyr[i]) * w[i];
-      const float xh = (xr[i] - mu) * rs;
-      s1 += g;
-      s2 += g * xh;
-    }
-    s1 = warp_sum(s1) / D;
-    s2 = warp_sum(s2) / D;
-    float* dxr = dx + static_cast<size_t>(row) * D;
-    for (int i = lane; i < D; i += 32) {
-      const float d = __bfloat162float(dyr[i]);
-      const float xh = (xr[i] - mu) * rs;
-      dxr[i] = rs * (d * w[i] - s1 - xh * s2);
-      atomicAdd(&sh[i], d * xh);
-      atomicAdd(&sh[D + i], d);
+// LayerNorm backward in two kernels.  (1) dx: one warp per row, two passes over
+// the row (row sums, then dx).  (2) dw, db: a block covers 32 columns x 256
+// rows (a warp reads 32 consecutive columns of one row, so loads are
+// coalesced), reduces over its rows in shared memory and adds one partial per
+// column to dw / db.
+__global__ void ln_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                                 const float* __restrict__ w, const float* __restrict__ mean,
+                                 const float* __restrict__ rstd, float* __restrict__ dx, int T,
+                                 int D) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const float mu = mean[row], rs = rstd[row];
+  const float* xr = x + static_cast<size_t>(row) * D;
+  const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * D;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float g = __bfloat162float(dyr[i]) * w[i];
+    s1 += g;
+    s2 += g * (xr[i] - mu) * rs;
+  }
+  s1 = warp_sum(s1) / D;
+  s2 = warp_sum(s2) / D;
+  float* dxr = dx + static_cast<size_t>(row) * D;
+  for (int i = lane; i < D; i += 32) {
+    const float xh = (xr[i] - mu) * rs;
+    dxr[i] = rs * (__bfloat162float(dyr[i]) * w[i] - s1 - xh * s2);
+  }
+}
+
+constexpr int kLnRowsPerBlock = 256;
+__global__ void ln_bwd_dwdb_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                                   const float* __restrict__ mean, const float* __restrict__ rstd,
+                                   float* __restrict__ dw, float* __restrict__ db, int T, int D) {
+  __shared__ float sw[8][33], sb[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;      // 32 columns x 8 row lanes
+  const int col = blockIdx.x * 32 + cx;
+  const int row_lo = blockIdx.y * kLnRowsPerBlock;
+  const int row_hi = min(T, row_lo + kLnRowsPerBlock);
+  float aw = 0.f, ab = 0.f;
+  if (col < D) {
+    for (int row = row_lo + ry; row < row_hi; row += 8) {
+      const float d = __bfloat162float(dy[static_cast<size_t>(row) * D + col]);
+      const float xh = (x[static_cast<size_t>(row) * D + col] - mean[row]) * rstd[row];
+      aw += d * xh;
+      ab += d;
     }
   }
+  sw[ry][cx] = aw;
+  sb[ry][cx] = ab;
   __syncthreads();
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
-    atomicAdd(&dw[i], sh[i]);
-    atomicAdd(&db[i], sh[D + i]);
+  if (ry == 0 && col < D) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { tw += sw[k][cx]; tb += sb[k][cx]; }
+    atomicAdd(dw + col, tw);
+    atomicAdd(db + col, tb);
   }
 }
 
@@ -322,11 +340,10 @@ extern "C" int dsb_layernorm_bwd(const void* dy_bf16, const float* x, const floa
                                  const float* mean, const float* rstd, float* dx, float* dw,
                                  float* db, int T, int D, cudaStream_t stream) {
   if (T <= 0) return 0;
-  const int rows_per_block = 64;
-  const int blocks = (T + rows_per_block - 1) / rows_per_block;
-  ln_bwd_kernel<<<blocks, 256, 2 * D * sizeof(float), stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(dy_bf16), x, w, mean, rstd, dx, dw, db, T, D,
-      rows_per_block);
+  const __nv_bfloat16* dy = reinterpret_cast<const __nv_bfloat16*>(dy_bf16);
+  ln_bwd_dx_kernel<<<(T + 7) / 8, 256, 0, stream>>>(dy, x, w, mean, rstd, dx, T, D);
+  const dim3 grid((D + 31) / 32, (T + kLnRowsPerBlock - 1) / kLnRowsPerBlock);
+  ln_bwd_dwdb_kernel<<<grid, 256, 0, stream>>>(dy, x, mean, rstd, dw, db, T, D);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

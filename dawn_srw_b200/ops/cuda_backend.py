@@ -71,11 +71,42 @@ def check_status(device=None) -> None:
     """Raise if any kernel since the last check reported a device-side failure
     (a bounded wait that ran out).  Synchronises the device."""
     for key, st in list(_STATUS.items()):
+        _PENDING.pop(key, None)
         code = int(st.item())
         if code != 0:
             st.zero_()
             raise RuntimeError(f"dawn_srw_b200 kernel reported status {code} on cuda:{key} "
                                "(1 = barrier wait timed out, 3 = peer wait timed out)")
+
+
+_PENDING = {}
+
+
+def check_status_deferred() -> None:
+    """Per-step variant of ``check_status`` that does not stall the launching
+    thread: it raises on the status word as it stood at the *previous* call
+    (copied to pinned host memory asynchronously then) and queues the next
+    copy.  A device-side failure is therefore reported one step late, while
+    the CPU keeps running ahead of the GPU across step boundaries."""
+    for key, st in list(_STATUS.items()):
+        prev = _PENDING.get(key)
+        if prev is not None:
+            ev, host = prev
+            ev.synchronize()
+            code = int(host[0])
+            if code != 0:
+                st.zero_()
+                _PENDING.pop(key, None)
+                raise RuntimeError(f"dawn_srw_b200 kernel reported status {code} on cuda:{key} "
+                                   "(1 = barrier wait timed out, 3 = peer wait timed out)")
+            host_buf = host
+        else:
+            host_buf = torch.zeros(1, dtype=torch.int32).pin_memory()
+        with torch.cuda.device(st.device):
+            host_buf.copy_(st, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        _PENDING[key] = (ev, host_buf)
 
 
 def _gate_list(spec: GateSpec) -> List[float]:
@@ -839,4 +870,8 @@ class CudaBackend:
                             seq_sharded=pctx.seq_sharded)
 
     def finish_step(self):
+        check_status_deferred()
+
+    def finish_run(self):
+        """Synchronise and raise on any device-side failure not yet reported."""
         check_status()

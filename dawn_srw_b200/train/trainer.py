@@ -351,6 +351,7 @@ class Trainer:
             self.step_in_epoch = 0
         if self.preempt_requested:
             self.save(f"emergency_step{self.global_step}.pt")
+        self.backend.finish_run()
         return {k: (float(v) if isinstance(v, torch.Tensor) and v.numel() == 1 else v)
                 for k, v in last.items() if k in ("total_loss", "ce_loss", "accuracy", "grad_norm", "lr")}
 
