@@ -74,6 +74,36 @@ def exploration_loss(result: Dict[str, Any], *, asymmetry: float, lower: float, 
     return ex_a + ex_k, stats
 
 
+def global_strided_sample(w_local: torch.Tensor, n_total: int, shard, group,
+                          max_sample: int = 4096) -> torch.Tensor:
+    """The rows ``w[::stride][:max_sample]`` of the *global* pool tensor, on
+    every rank of ``group``, when each rank stores a contiguous slice of the
+    unit axis (``shard.slice_of``).  Every rank picks the sampled rows that fall
+    into its slice, the picks are all-gathered (autograd: reduce-scatter of the
+    cotangents) and put back into global order.  Which rows each rank holds
+    follows from the slice arithmetic, so no sizes are exchanged.  Pools of at
+    most ``max_sample`` rows are gathered whole (reference sampling rule:
+    scripts/train_jax.py:440-485)."""
+    world = C.group_size(group)
+    stride = max(1, n_total // max_sample) if n_total > max_sample else 1
+    PoolShard = type(shard)
+    picks = []
+    for k in range(world):
+        lo, hi, _ = PoolShard(k, world, shard.align).slice_of(n_total)
+        first = lo + ((-lo) % stride)
+        picks.append(list(range(first, hi, stride)))
+    cmax = max(1, max(len(pk) for pk in picks))
+    mine = picks[shard.index]
+    lo = shard.slice_of(n_total)[0]
+    buf = w_local.new_zeros((cmax,) + tuple(w_local.shape[1:]))
+    if mine:
+        idx = torch.tensor([g - lo for g in mine], device=w_local.device)
+        buf = torch.cat([w_local.index_select(0, idx), buf[len(mine):]], dim=0)
+    gathered = C.gather_tokens(buf, group)                       # [world * cmax, ...]
+    keep = [k * cmax + i for k in range(world) for i in range(len(picks[k]))][:max_sample]
+    return gathered.index_select(0, torch.tensor(keep, device=w_local.device))
+
+
 def total_loss(result: Dict[str, Any], model, tcfg, step: int, *, is_baseline: bool,
                dp_group=None, backend=None, want_stats: bool = True):
     """Returns (total, parts) where parts holds the unweighted components."""
@@ -89,9 +119,17 @@ def total_loss(result: Dict[str, Any], model, tcfg, step: int, *, is_baseline: b
     dead = result.get("dead_penalty", z)
     pool = model.neuron_pool
     tensors = []
-    for name in ("qk", "v", "know"):
-        n = pool.n_valid(name)
-        tensors += [getattr(pool, f"{name}_{k}")[:n] for k in ("emb", "read", "write")]
+    shard_group = getattr(model, "shard_group", None)
+    sharded = C.group_size(shard_group) > 1
+    if tcfg.diversity_weight != 0.0:
+        for name in ("qk", "v", "know"):
+            n = pool.n_valid(name)
+            for k in ("emb", "read", "write"):
+                w = getattr(pool, f"{name}_{k}")[:n]
+                if sharded:
+                    # the statistic is defined on a sample of the whole pool, not of a shard
+                    w = global_strided_sample(w, pool.sizes[name], pool.shard, shard_group)
+                tensors.append(w)
     if tcfg.diversity_weight != 0.0:
         div = backend.diversity(tensors) if backend is not None else pool_diversity(tensors)
     else:

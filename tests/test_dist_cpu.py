@@ -219,3 +219,38 @@ def test_preemption_consensus_and_step_check():
     outs = run_ranks(_consensus_worker, 2)
     assert all(a for a, _ in outs)          # every rank leaves the loop together
     assert all(m for _, m in outs)          # a split resume is detected on every rank
+
+
+def _diversity_worker(rank, world):
+    from dawn_srw_b200.ops.reference import pool_diversity
+    from dawn_srw_b200.parallel.topology import PoolShard, init_topology
+    from dawn_srw_b200.train.losses import global_strided_sample
+    topo = init_topology(pool_shards=world, backend="gloo")
+    out = {}
+    for n_total, max_sample in ((50, 16), (21, 64)):           # strided sample / whole small pool
+        full = torch.randn(n_total, 6, generator=torch.Generator().manual_seed(3))
+        sh = PoolShard(rank, world)
+        lo, hi, _ = sh.slice_of(n_total)
+        local = full[lo:hi].clone().requires_grad_(True)
+        sample = global_strided_sample(local, n_total, sh, topo.shard_group, max_sample)
+        div = pool_diversity([sample], max_sample=max_sample)
+        div.backward()
+        out[n_total] = {"div": float(div), "grad": local.grad / world, "lo": lo, "hi": hi,
+                        "rows": sample.detach().clone()}
+    return out
+
+
+def test_diversity_sample_of_a_sharded_pool_matches_the_global_sample():
+    from dawn_srw_b200.ops.reference import pool_diversity
+    outs = run_ranks(_diversity_worker, 2)
+    for n_total, max_sample in ((50, 16), (21, 64)):
+        full = torch.randn(n_total, 6, generator=torch.Generator().manual_seed(3)).requires_grad_(True)
+        stride = max(1, n_total // max_sample) if n_total > max_sample else 1
+        want_rows = full[::stride][:max_sample]
+        ref = pool_diversity([full], max_sample=max_sample)
+        ref.backward()
+        for o in outs:
+            r = o[n_total]
+            assert torch.equal(r["rows"], want_rows.detach())
+            assert abs(r["div"] - float(ref)) < 1e-6
+            assert torch.allclose(r["grad"], full.grad[r["lo"]:r["hi"]], atol=1e-6)
