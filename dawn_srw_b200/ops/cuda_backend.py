@@ -270,6 +270,41 @@ class _PoolMatVecFn(torch.autograd.Function):
         return hd.emb[:U].float().t() @ dm, torch.zeros_like(dm[:1]), None, None
 
 
+def _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den, hd, spec, U):
+    """Backward of one local SRW route given the bf16 output cotangent ``dy``
+    (already scaled by whatever multiplied ``p . write``) and the cotangent of
+    the per-token denominator: the gate step (recomputes S and XR, adds
+    DP = dy . write^T, emits p, dxr, ds, dtau) and five engine GEMMs.  Pool
+    gradients are accumulated into the holder's fp32 buffers.
+    Returns (dx bf16, dh bf16, dtau, d_inv_sigma or None)."""
+    e = ext()
+    dev = x_bf.device
+    T = x_bf.shape[0]
+    Up = _round_up(U, 8)
+    p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+    dxr = torch.empty_like(p)
+    ds = torch.empty_like(p)
+    dtau = torch.zeros(T, dtype=torch.float32, device=dev)
+    dsz = torch.zeros(T, dtype=torch.float32, device=dev)
+    emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
+    count_launches(2)
+    e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den, dtau, dsz,
+                   _gate_list(spec), status_word(dev))
+    pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
+    gemm(pv, True, dy, True, out=hd.g_write[:U], accumulate=True)       # p^T dy
+    gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
+    gemm(dsv, True, h_bf, True, out=hd.g_emb[:U], accumulate=True)      # ds^T h
+    dx = gemm(dxrv, False, read, True, out_dtype=torch.bfloat16)        # dxr . read
+    dh32 = gemm(dsv, False, emb, True, out_dtype=torch.float32)         # ds . emb
+    d_isd = None
+    if spec.kind == GATE_GELU_Z:
+        # sum_u ds_u z_u = (1/sigma) (<h, ds.emb> + tau * dtau): the sigma path needs no
+        # reduction of its own in the kernel
+        dsz = inv_sd * ((h_bf.float() * dh32).sum(-1) + tau * dtau)
+        d_isd = dsz / (inv_sd * inv_sd)
+    return dx, dh32.to(torch.bfloat16), dtau, d_isd
+
+
 class _SRWRouteFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_bf, h_bf, tau, inv_sd, anchor, holder, spec, U, alive, unit_mask):
@@ -291,38 +326,11 @@ class _SRWRouteFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, d_raw, d_den):
         x_bf, h_bf, tau, inv_sd = ctx.saved_tensors
-        hd, spec, U = ctx.holder, ctx.spec, ctx.U
-        e = ext()
         dev = x_bf.device
-        st = status_word(dev)
-        T, D = x_bf.shape
-        Up = _round_up(U, 8)
-        dy = _bf16_2d(d_raw)
-        d_den = d_den.contiguous().float() if d_den is not None else torch.zeros(T, device=dev)
-        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
-        dxr = torch.empty_like(p)
-        ds = torch.empty_like(p)
-        dtau = torch.zeros(T, dtype=torch.float32, device=dev)
-        dsz = torch.zeros(T, dtype=torch.float32, device=dev)
-        emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
-        global _LAUNCHES
-        _LAUNCHES += 1
-        e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den, dtau, dsz,
-                       _gate_list(spec), st)
-        pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
-        gemm(pv, True, dy, True, out=hd.g_write[:U], accumulate=True)       # p^T dy
-        gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
-        gemm(dsv, True, h_bf, True, out=hd.g_emb[:U], accumulate=True)      # ds^T h
-        dx = gemm(dxrv, False, read, True, out_dtype=torch.bfloat16)        # dxr . read
-        dh32 = gemm(dsv, False, emb, True, out_dtype=torch.float32)         # ds . emb
-        d_isd = None
-        if spec.kind == GATE_GELU_Z:
-            # sum_u ds_u z_u = (1/sigma) (<h, ds.emb> + tau * dtau): the sigma path needs no
-            # reduction of its own in the kernel
-            dsz = inv_sd * ((h_bf.float() * dh32).sum(-1) + tau * dtau)
-            d_isd = dsz / (inv_sd * inv_sd)
-        return (dx, dh32.to(torch.bfloat16), dtau, d_isd, torch.zeros(1, device=dev), None, None,
-                None, None, None)
+        d_den = d_den.contiguous().float() if d_den is not None else torch.zeros(x_bf.shape[0], device=dev)
+        dx, dh, dtau, d_isd = _route_backward_core(x_bf, h_bf, tau, inv_sd, _bf16_2d(d_raw), d_den,
+                                                   ctx.holder, ctx.spec, ctx.U)
+        return (dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None, None)
 
 
 class _SRWRouteScaledFn(torch.autograd.Function):
@@ -356,37 +364,18 @@ class _SRWRouteScaledFn(torch.autograd.Function):
     def backward(ctx, d_y, d_den_ext):
         x_bf, h_bf, tau, inv_sd, y, den, rs, scale = ctx.saved_tensors
         hd, spec, U = ctx.holder, ctx.spec, ctx.U
-        e = ext()
         dev = x_bf.device
-        T, D = x_bf.shape
-        Up = _round_up(U, 8)
-        dy, rowdot = e.route_bwd_prologue(d_y.contiguous().float(), y, rs)
+        dy, rowdot = ext().route_bwd_prologue(d_y.contiguous().float(), y, rs)
+        count_launches(1)
         d_den = torch.where(den > 1.0, -rowdot / den.clamp(min=1.0), torch.zeros_like(rowdot))
         if d_den_ext is not None:
             d_den = d_den + d_den_ext.float()
         d_scale = (rowdot.sum() / scale.detach().float()).reshape(scale.shape).to(scale.dtype) \
             if ctx.needs_input_grad[10] else None
-        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
-        dxr = torch.empty_like(p)
-        ds = torch.empty_like(p)
-        dtau = torch.zeros(T, dtype=torch.float32, device=dev)
-        dsz = torch.zeros(T, dtype=torch.float32, device=dev)
-        emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
-        count_launches(2)
-        e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den.contiguous(),
-                       dtau, dsz, _gate_list(spec), status_word(dev))
-        pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
-        gemm(pv, True, dy, True, out=hd.g_write[:U], accumulate=True)       # p^T dy
-        gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
-        gemm(dsv, True, h_bf, True, out=hd.g_emb[:U], accumulate=True)      # ds^T h
-        dx = gemm(dxrv, False, read, True, out_dtype=torch.bfloat16)        # dxr . read
-        dh32 = gemm(dsv, False, emb, True, out_dtype=torch.float32)         # ds . emb
-        d_isd = None
-        if spec.kind == GATE_GELU_Z:
-            dsz = inv_sd * ((h_bf.float() * dh32).sum(-1) + tau * dtau)
-            d_isd = dsz / (inv_sd * inv_sd)
-        return (dx, dh32.to(torch.bfloat16), dtau, d_isd, torch.zeros(1, device=dev), None, None,
-                None, None, None, d_scale)
+        dx, dh, dtau, d_isd = _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den.contiguous(), hd,
+                                                   spec, U)
+        return (dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None, None,
+                d_scale)
 
 
 # ---------------------------------------------------------------------------
