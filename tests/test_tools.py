@@ -119,3 +119,36 @@ def test_bench_reference_arm_reports_unavailable():
     assert r.returncode == 0
     rec = json.loads(r.stdout.strip().splitlines()[-1])
     assert rec["impl"] == "reference" and "unavailable" in rec
+
+
+def test_pretokenized_files_feed_the_trainer(tmp_path, capsys):
+    """text -> pretokenize (byte tokenizer, sharded) -> YAML with bin_train / bin_val ->
+    train CLI: the vocabulary size comes from the shard metadata and validation runs."""
+    import yaml
+    from dawn_srw_b200.tools import pretokenize as P, train as T
+    rng = np.random.default_rng(0)
+    words = ["alpha", "beta", "gamma", "delta", "epsilon", "zeta"]
+    txt = tmp_path / "corpus.txt"
+    txt.write_text("\n".join(" ".join(rng.choice(words, size=12)) for _ in range(400)))
+    train_prefix, val_prefix = str(tmp_path / "data" / "train"), str(tmp_path / "data" / "val")
+    for prefix in (train_prefix, val_prefix):
+        assert P.main(["--input", str(txt), "--output", prefix, "--seq-len", "32",
+                       "--shard-tokens", "8192", "--tokenizer", "bytes"]) == 0
+    capsys.readouterr()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = yaml.safe_load(open(os.path.join(root, "configs", "smoke_tiny_synthetic.yaml")))
+    cfg["data"].update(synthetic=False, bin_train=train_prefix, bin_val=val_prefix,
+                       max_train_tokens=32 * 8 * 12)
+    cfg["training"].update(val_interval=4, checkpoint_interval=0, log_interval=2)
+    cfg_path = tmp_path / "cfg.yaml"
+    cfg_path.write_text(yaml.safe_dump(cfg))
+    assert T.main(["--config", str(cfg_path), "--from-scratch", "--max-steps", "8",
+                   "--checkpoint-dir", str(tmp_path / "ck"), "--no-startup-check"]) == 0
+    out = capsys.readouterr().out
+    assert "[val @ 4]" in out and "[val @ 8]" in out
+    import glob
+    run = glob.glob(str(tmp_path / "ck" / "run_*"))[0]
+    saved = json.load(open(os.path.join(run, "config.json")))
+    assert saved["model"]["vocab_size"] == 257                  # byte tokenizer + separator
+    recs = [json.loads(l) for l in open(glob.glob(os.path.join(run, "metrics_*.jsonl"))[0])]
+    assert any(r.get("type") == "val" for r in recs) and any(r.get("type") == "train" for r in recs)
