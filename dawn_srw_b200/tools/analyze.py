@@ -25,6 +25,13 @@ dict; the selection mirrors the SRW part of the reference's analysis CLI
   tau_dist     threshold offsets produced by the tau heads on the sample (per route: mean,
                spread, quantiles, fraction below zero)
   drift        movement of the pool tensors against a second checkpoint (--compare-checkpoint)
+  cross_ref    Q vs K specialisation of the shared QK pool (share of units used by one route only,
+               Jaccard overlap of the per-token selections)
+  layer_sim    cosine similarity of the per-unit selection profile between layers
+  sel_trans    how much of a token's selected set survives from one layer to the next
+  gate_ci      bootstrap confidence interval of the active fraction per route
+  read_cov / write_cov   participation ratio of the selection-weighted read / write vectors
+  samples      for the most-used knowledge units: the token ids that open them most strongly
 
 All analyses run on one device through the model's public inference API
 (models/inference.py).
@@ -288,15 +295,116 @@ def analyze_drift(c: Context) -> Dict:
     return out
 
 
+def analyze_cross_ref(c: Context) -> Dict:
+    g = c.gates()
+    q, k = g["gate_Q_raw"] > 0, g["gate_K_raw"] > 0                     # [L,B,S,N]
+    fq, fk = q.float().sum(dim=(0, 1, 2)), k.float().sum(dim=(0, 1, 2))
+    used = (fq + fk) > 0
+    share_q = fq / (fq + fk).clamp(min=1.0)
+    special = ((share_q > 0.9) | (share_q < 0.1)) & used
+    inter = (q & k).float().sum(-1)
+    union = (q | k).float().sum(-1).clamp(min=1.0)
+    return {"units_used": int(used.sum()), "specialised_frac": float(special.float().sum() / used.float().sum().clamp(min=1.0)),
+            "q_only_frac": float(((share_q > 0.9) & used).float().sum() / used.float().sum().clamp(min=1.0)),
+            "token_jaccard_mean": float((inter / union).mean())}
+
+
+def analyze_layer_sim(c: Context) -> Dict:
+    cnt = _selection_counts(c)
+    out = {}
+    for r in ROUTES:
+        prof = torch.nn.functional.normalize(cnt[r].float(), dim=-1)      # [L,N]
+        sim = prof @ prof.t()
+        L = sim.shape[0]
+        off = sim[~torch.eye(L, dtype=torch.bool, device=sim.device)]
+        out[r] = {"adjacent": [float(sim[i, i + 1]) for i in range(L - 1)],
+                  "mean_off_diagonal": float(off.mean()) if off.numel() else 1.0}
+    return out
+
+
+def analyze_sel_trans(c: Context) -> Dict:
+    g = c.gates()
+    out = {}
+    for r in ROUTES:
+        sel = g[f"gate_{r}_raw"] > 0                                        # [L,B,S,N]
+        keep = []
+        for l in range(sel.shape[0] - 1):
+            a, b = sel[l], sel[l + 1]
+            keep.append(float(((a & b).float().sum(-1) / a.float().sum(-1).clamp(min=1.0)).mean()))
+        out[r] = {"survival_to_next_layer": keep}
+    return out
+
+
+def analyze_gate_ci(c: Context) -> Dict:
+    g = c.gates()
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    out = {}
+    for r in ROUTES:
+        frac = (g[f"gate_{r}_raw"] > 0).float().mean(-1).flatten().cpu()      # per (layer, token)
+        n = frac.numel()
+        boots = torch.stack([frac[torch.randint(0, n, (n,), generator=gen)].mean() for _ in range(200)])
+        lo, hi = torch.quantile(boots, torch.tensor([0.025, 0.975])).tolist()
+        out[r] = {"active_frac": float(frac.mean()), "ci95": [lo, hi], "tokens": n}
+    return out
+
+
+def _coverage(c: Context, kind: str) -> Dict:
+    p = c.model.neuron_pool
+    cnt = _selection_counts(c)
+    freq = {"qk": (cnt["Q"] + cnt["K"]).sum(0), "v": cnt["V"].sum(0), "know": cnt["Know"].sum(0)}
+    out = {}
+    for name in ("qk", "v", "know"):
+        n = p.n_valid(name)
+        w = getattr(p, f"{name}_{kind}")[:n].float()
+        f = freq[name][:n].float()
+        f = f / f.sum().clamp(min=1e-12)
+        cov = (w * f[:, None]).t() @ w                                       # [D,D], selection-weighted
+        ev = torch.linalg.eigvalsh(cov.cpu().double()).clamp(min=0)
+        out[name] = {"participation_ratio": float(ev.sum() ** 2 / ev.square().sum().clamp(min=1e-30)),
+                     "dims": int(w.shape[1])}
+    return out
+
+
+def analyze_read_cov(c: Context) -> Dict:
+    return _coverage(c, "read")
+
+
+def analyze_write_cov(c: Context) -> Dict:
+    return _coverage(c, "write")
+
+
+def analyze_samples(c: Context) -> Dict:
+    g, ids = c.gates(), c.batches()[0]
+    raw = g["gate_Know_raw"]                                                 # [L,B,S,N]
+    cnt = (raw > 0).float().sum(dim=(0, 1, 2))
+    top_units = torch.topk(cnt, min(5, cnt.numel())).indices.tolist()
+    tok = tokenizer_or_none()
+    out = []
+    for u in top_units:
+        strength = raw[..., u].max(0).values                                  # [B,S] strongest layer
+        k = min(8, strength.numel())
+        flat = torch.topk(strength.flatten(), k).indices
+        tids = ids.flatten()[flat].tolist()
+        rec = {"unit": u, "selected_by_tokens": int(cnt[u]), "top_token_ids": tids}
+        if tok is not None:
+            rec["top_tokens"] = tok.convert_ids_to_tokens(tids)
+        out.append(rec)
+    return {"know_units": out}
+
+
 ANALYSES: Dict[str, Callable[[Context], Dict]] = {
     "info": analyze_info, "val": analyze_val, "health": analyze_health, "weights": analyze_weights,
     "generate": analyze_generate, "routing": analyze_routing, "gate_dist": analyze_gate_dist,
     "utilization": analyze_utilization, "sel_gini": analyze_sel_gini,
     "layer_role": analyze_layer_role, "intervene": analyze_intervene, "pool_geom": analyze_pool_geom,
     "rw_align": analyze_rw_align, "tau_dist": analyze_tau_dist, "drift": analyze_drift,
+    "cross_ref": analyze_cross_ref, "layer_sim": analyze_layer_sim, "sel_trans": analyze_sel_trans,
+    "gate_ci": analyze_gate_ci, "read_cov": analyze_read_cov, "write_cov": analyze_write_cov,
+    "samples": analyze_samples,
 }
 SPATIAL_ONLY = {"health", "weights", "routing", "gate_dist", "utilization", "sel_gini", "layer_role",
-                "intervene", "pool_geom", "rw_align", "tau_dist", "drift"}
+                "intervene", "pool_geom", "rw_align", "tau_dist", "drift", "cross_ref", "layer_sim",
+                "sel_trans", "gate_ci", "read_cov", "write_cov", "samples"}
 
 
 def run(model, cfg, info, args) -> Dict:

@@ -59,6 +59,13 @@ def test_analysis_cli_runs_every_key(tmp_path):
     assert -1.0 <= res["rw_align"]["know"]["cos_mean"] <= 1.0
     assert res["tau_dist"]["Know"]["std"] >= 0.0
     assert res["drift"]["know_emb"]["rel_l2"] == 0.0          # compared with itself
+    assert 0.0 <= res["cross_ref"]["token_jaccard_mean"] <= 1.0
+    assert len(res["layer_sim"]["Know"]["adjacent"]) == L - 1
+    assert len(res["sel_trans"]["Q"]["survival_to_next_layer"]) == L - 1
+    lo, hi = res["gate_ci"]["V"]["ci95"]
+    assert lo <= res["gate_ci"]["V"]["active_frac"] <= hi or abs(hi - lo) < 1e-6
+    assert 1.0 <= res["write_cov"]["know"]["participation_ratio"] <= res["write_cov"]["know"]["dims"] + 1e-6
+    assert res["samples"]["know_units"] and len(res["samples"]["know_units"][0]["top_token_ids"]) > 0
     assert len(res["generate"]["samples"][0]["token_ids"]) >= 4
     # key selection
     assert A.main(["--checkpoint", path, "--synthetic", "--only", "info,health", "--device", "cpu"]) == 0
