@@ -83,6 +83,11 @@ class VanillaTransformer(nn.Module):
     def set_parallel(self, **kw):
         pass
 
+    def _backend(self, device):
+        if self.backend is None:
+            self.backend = default_backend(device)
+        return self.backend
+
     def _layer(self, be, x, lyr, training):
         B, S, D = x.shape
         H = self.n_heads

@@ -75,11 +75,69 @@ def _know(model, be, normed, pools, masks=None, return_gates=False):
     return res.route(0) * model.pool_scale("know"), res
 
 
+def _is_dense(model) -> bool:
+    return getattr(model, "version", "") == "baseline"
+
+
+def _dense_layer_cached(model, be, x, lyr, li, cache_k, cache_v, pos0: int, decode: bool):
+    """One layer of the dense baseline on x [B,S,D] whose first position is
+    ``pos0``; K / V of the new positions are written into the caches
+    (reference: vanilla_cached_forward, models/baseline_transformer_jax.py)."""
+    import torch.nn.functional as F
+    B, S, D = x.shape
+    H = model.n_heads
+    dh = D // H
+    a = lyr.attn
+    n = be.layer_norm(x, lyr.norm1.weight, lyr.norm1.bias).reshape(B * S, D)
+    heads = lambda t: t.float().reshape(B, S, H, dh).transpose(1, 2)
+    q = heads(be.linear(n, a.q_proj.weight, a.q_proj.bias))
+    k = heads(be.linear(n, a.k_proj.weight, a.k_proj.bias))
+    v = heads(be.linear(n, a.v_proj.weight, a.v_proj.bias))
+    cache_k[li, :, :, pos0: pos0 + S] = k
+    cache_v[li, :, :, pos0: pos0 + S] = v
+    if decode:
+        o = R.cached_attention(q, cache_k[li], cache_v[li], pos0 + 1)
+    else:
+        o = be.attention(q, k, v, 0.0, False)
+    o = o.transpose(1, 2).reshape(B * S, D)
+    x = x + be.linear(o, a.o_proj.weight, None).reshape(B, S, D)
+    n = be.layer_norm(x, lyr.norm2.weight, lyr.norm2.bias).reshape(B * S, D)
+    hdn = F.gelu(be.linear(n, lyr.ffn.w_up.weight, lyr.ffn.w_up.bias), approximate="tanh")
+    return x + be.linear(hdn, lyr.ffn.w_down.weight, lyr.ffn.w_down.bias).reshape(B, S, D)
+
+
+def _dense_prefill(model, input_ids):
+    B, S = input_ids.shape
+    dev = input_ids.device
+    be = _be(model, dev)
+    L, H, D = model.n_layers, model.n_heads, model.d_model
+    cache_k = torch.zeros(L, B, H, model.max_seq_len, D // H, device=dev)
+    cache_v = torch.zeros_like(cache_k)
+    x = be.embed(input_ids, model.token_emb.weight, model.pos_emb.weight).float()
+    for li, lyr in enumerate(model.layers):
+        x = _dense_layer_cached(model, be, x, lyr, li, cache_k, cache_v, 0, False)
+    x = be.layer_norm(x, model.norm.weight, model.norm.bias)
+    return be.logits(x, model.token_emb.weight), cache_k, cache_v, S
+
+
+def _dense_decode(model, token, cache_k, cache_v, length):
+    B = token.shape[0]
+    be = _be(model, token.device)
+    D = model.d_model
+    x = (model.token_emb.weight[token] + model.pos_emb.weight[length]).float().reshape(B, 1, D)
+    for li, lyr in enumerate(model.layers):
+        x = _dense_layer_cached(model, be, x, lyr, li, cache_k, cache_v, length, True)
+    x = be.layer_norm(x, model.norm.weight, model.norm.bias)
+    return be.logits(x, model.token_emb.weight)[:, 0], cache_k, cache_v, length + 1
+
+
 @torch.no_grad()
 def prefill(model, input_ids: torch.Tensor):
     B, S = input_ids.shape
     if S > model.max_seq_len:
         raise ValueError(f"Sequence length {S} exceeds max_seq_len")
+    if _is_dense(model):
+        return _dense_prefill(model, input_ids)
     dev = input_ids.device
     be = _be(model, dev)
     pools = _pools(model, be)
@@ -110,6 +168,8 @@ def decode_step(model, token: torch.Tensor, cache_k, cache_v, length: int):
     B = token.shape[0]
     if length >= model.max_seq_len:
         raise ValueError("KV cache is full")
+    if _is_dense(model):
+        return _dense_decode(model, token, cache_k, cache_v, length)
     dev = token.device
     be = _be(model, dev)
     pools = _pools(model, be)

@@ -104,3 +104,21 @@ def test_health_and_weight_analysis_and_flops():
     # 0.79 GF/token when the scores are counted twice (two sweeps); one sweep here
     scores = 2 * 128 * (2 * 1580 + 2600 + 25200)
     assert abs((f["total"] + 12 * scores) / 1e9 - 0.79) < 0.01
+
+
+def test_dense_baseline_kv_cache_matches_full_forward():
+    from dawn_srw_b200.models.baseline import VanillaTransformer
+    m = VanillaTransformer(vocab_size=200, d_model=32, d_ff=64, n_layers=2, n_heads=4, max_seq_len=24,
+                           dropout_rate=0.0, seed=2)
+    m.eval()
+    ids = torch.randint(1, 200, (2, 10))
+    logits, ck, cv, n = I.prefill(m, ids[:, :6])
+    with torch.no_grad():
+        assert torch.allclose(logits, m(ids[:, :6])["logits"], atol=1e-4)
+    for t in range(6, 10):
+        lg, ck, cv, n = I.decode_step(m, ids[:, t], ck, cv, n)
+        with torch.no_grad():
+            ref = m(ids[:, : t + 1])["logits"][:, -1]
+        assert torch.allclose(lg, ref, atol=2e-4), t
+    out, stats = I.generate(m, ids[:, :4], max_new_tokens=5, temperature=0.0)
+    assert out.shape == (2, 9) and stats["new_tokens"] == 5
