@@ -175,7 +175,9 @@ def config_from_dict(raw: Dict[str, Any]) -> Config:
 
 
 def load_config(path: str) -> Config:
-    with open(path, "r") as f:
+    """YAML from a local path or an fsspec URL."""
+    from .utils.fileio import open_file
+    with open_file(path, "r") as f:
         return config_from_dict(yaml.safe_load(f))
 
 

@@ -26,6 +26,8 @@ from typing import Iterator, List, Optional, Tuple
 import numpy as np
 import torch
 
+from ..utils.fileio import fetch_to_local, is_remote
+
 
 class BinDataset:
     def __init__(self, path: str, seq_len: int, max_tokens: Optional[int] = None):
@@ -145,9 +147,13 @@ def load_data(data_cfg, seq_len: int, global_batch: int, vocab_size: int, *, bat
     def open_ds(path, max_tokens):
         if path is None:
             return None
-        if path.startswith("gs://"):
-            raise ValueError("remote (gs://) data is not reachable from this runtime; copy the "
-                             ".bin files locally and point bin_train / bin_val at them")
+        if is_remote(path):
+            # token files are memory-mapped: fetch a remote one into the local cache first
+            cache = getattr(data_cfg, "local_cache_dir", None)
+            if not cache:
+                raise ValueError(f"{path}: set data.local_cache_dir so the remote token file can be "
+                                 "copied next to the trainer (token files are memory-mapped)")
+            path = fetch_to_local(path, cache)
         if os.path.isdir(path) or path.endswith("_meta.json") or os.path.exists(path + "_meta.json"):
             meta = path if not os.path.exists(path + "_meta.json") else path + "_meta.json"
             return ShardedBinDataset(meta, seq_len, max_tokens)

@@ -130,3 +130,38 @@ def test_shard_consolidation(tmp_path):
     blob = torch.load(out, weights_only=False)
     for k, v in full.state_dict().items():
         assert torch.equal(blob["params"][k], v), k
+
+
+def test_fileio_local_and_url_paths(tmp_path):
+    """The five file operations on local paths and on an fsspec URL (the
+    in-process ``memory://`` filesystem stands in for a bucket)."""
+    import numpy as np
+    from dawn_srw_b200.config import load_config
+    from dawn_srw_b200.data.loaders import load_data
+    from dawn_srw_b200.utils import fileio as F
+    p = str(tmp_path / "a" / "b.txt")
+    with F.open_file(p, "w") as f:
+        f.write("x")
+    assert F.file_exists(p) and F.list_files(str(tmp_path / "a" / "*.txt")) == [p]
+    F.delete_file(p)
+    assert not F.file_exists(p)
+    url = "memory://bucket/cfg.yaml"
+    with F.open_file(url, "w") as f:
+        f.write("seed: 7\nmodel:\n  d_model: 96\n")
+    assert F.is_remote(url) and F.file_exists(url)
+    cfg = load_config(url)
+    assert cfg.seed == 7 and cfg.model.d_model == 96
+    assert any(q.endswith("cfg.yaml") for q in F.list_files("memory://bucket/*.yaml"))
+    # a remote token file is copied into the local cache and memory-mapped from there
+    toks = (np.arange(16 * 8) % 100).astype(np.uint16)
+    with F.open_file("memory://bucket/train.bin", "wb") as f:
+        f.write(toks.tobytes())
+    cfg.data.bin_train, cfg.data.bin_val = "memory://bucket/train.bin", None
+    cfg.data.local_cache_dir = str(tmp_path / "cache")
+    tl, vl, _ = load_data(cfg.data, 8, 4, 100)
+    ids, mask = tl.batch(0)
+    assert ids.shape == (4, 8) and int(ids[0, 1]) == 1 and vl is None
+    F.delete_file(url)
+    import pytest
+    with pytest.raises(RuntimeError):
+        F.file_exists("nosuchscheme://x/y")
