@@ -159,3 +159,15 @@ def test_pretokenized_files_feed_the_trainer(tmp_path, capsys):
     assert saved["model"]["vocab_size"] == 257                  # byte tokenizer + separator
     recs = [json.loads(l) for l in open(glob.glob(os.path.join(run, "metrics_*.jsonl"))[0])]
     assert any(r.get("type") == "val" for r in recs) and any(r.get("type") == "train" for r in recs)
+
+
+def test_inference_speed_harness(capsys):
+    from dawn_srw_b200.tools import bench_inference as B
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(root, "configs", "smoke_tiny_synthetic.yaml")
+    assert B.main(["--config", cfg, "--batch-sizes", "1,3", "--seq-len", "16", "--warmup", "1",
+                   "--iters", "3", "--new-tokens", "4", "--device", "cpu"]) == 0
+    recs = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert [r["batch"] for r in recs] == [1, 3]
+    assert all(r["forward_tokens_per_sec"] > 0 and r["decode_new_tokens"] == 4 for r in recs)
+    assert recs[0]["forward_ms_p50"] <= recs[0]["forward_ms_p95"] + 1e-9
