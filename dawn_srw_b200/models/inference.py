@@ -41,8 +41,19 @@ def _be(model, device):
 
 
 def _pools(model, be):
+    """Prepared pools (compute copies, Gram statistics) for inference.  They
+    depend only on the pool parameters, so they are kept until a parameter
+    changes (its autograd version or storage moves) instead of being rebuilt
+    for every decoded token."""
+    ps = model.neuron_pool
+    key = tuple((p.data_ptr(), p._version, p.device) for p in ps.parameters()) + (id(be),)
+    hit = getattr(model, "_inference_pools", None)
+    if hit is not None and hit[0] == key:
+        return hit[1]
     with torch.no_grad():
-        return model.prepare_pools(be)
+        pools = model.prepare_pools(be)
+    model._inference_pools = (key, pools)
+    return pools
 
 
 def _srw(model, be, x, h, tau, pools, name, *, return_gates=False, unit_mask=None):

@@ -122,3 +122,19 @@ def test_dense_baseline_kv_cache_matches_full_forward():
         assert torch.allclose(lg, ref, atol=2e-4), t
     out, stats = I.generate(m, ids[:, :4], max_new_tokens=5, temperature=0.0)
     assert out.shape == (2, 9) and stats["new_tokens"] == 5
+
+
+def test_prepared_pools_are_cached_until_a_parameter_changes():
+    m = _model("spatial-r1-v4.0.1")
+    ids = torch.randint(1, 200, (1, 8))
+    a, *_ = I.prefill(m, ids)
+    pools1 = m._inference_pools[1]
+    b, *_ = I.prefill(m, ids)
+    assert m._inference_pools[1] is pools1 and torch.equal(a, b)       # reused
+    with torch.no_grad():
+        m.neuron_pool.know_write.mul_(1.5)                             # in-place update bumps the version
+    c, *_ = I.prefill(m, ids)
+    assert m._inference_pools[1] is not pools1 and not torch.allclose(a, c)
+    with torch.no_grad():
+        ref = m(ids, want_diag=False)["logits"]
+    assert torch.allclose(c, ref, atol=1e-4)
