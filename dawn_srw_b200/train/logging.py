@@ -89,6 +89,51 @@ class RunLogger:
                 f.write(json.dumps(rec) + "\n")
 
 
+class Heartbeat:
+    """Per-rank liveness file for an external supervisor: every rank rewrites
+    ``heartbeat_rank{r}.json`` (step, wall time, pid) at most every
+    ``min_interval`` seconds.  A rank stuck in a collective or a crashed
+    process stops refreshing its file; ``stale_ranks`` lists the ranks whose
+    file is older than a limit (tools/watchdog.py wraps it).  The reference has
+    no heartbeat (its only liveness signal is the SIGTERM flag exchange)."""
+
+    def __init__(self, run_dir: Optional[str], rank: int, world: int, min_interval: float = 10.0):
+        self.path = None if run_dir is None else os.path.join(run_dir, f"heartbeat_rank{rank}.json")
+        self.rank, self.world, self.min_interval = rank, world, float(min_interval)
+        self._last = 0.0
+
+    def beat(self, step: int, force: bool = False) -> None:
+        now = time.time()
+        if self.path is None or (not force and now - self._last < self.min_interval):
+            return
+        self._last = now
+        os.makedirs(os.path.dirname(self.path), exist_ok=True)
+        tmp = self.path + ".tmp"
+        with open(tmp, "w") as f:
+            json.dump({"rank": self.rank, "world": self.world, "step": int(step), "time": now,
+                       "pid": os.getpid()}, f)
+        os.replace(tmp, self.path)
+
+
+def stale_ranks(run_dir: str, max_age_s: float, now: Optional[float] = None) -> Dict[str, Any]:
+    """{'world', 'missing': [...], 'stale': {rank: age_s}, 'steps': {rank: step}} from the
+    heartbeat files of ``run_dir``."""
+    now = time.time() if now is None else now
+    beats = {}
+    for fn in os.listdir(run_dir):
+        if fn.startswith("heartbeat_rank") and fn.endswith(".json"):
+            try:
+                with open(os.path.join(run_dir, fn)) as f:
+                    b = json.load(f)
+                beats[int(b["rank"])] = b
+            except (ValueError, KeyError, OSError):
+                continue
+    world = max([b.get("world", 1) for b in beats.values()], default=0)
+    return {"world": world, "missing": [r for r in range(world) if r not in beats],
+            "stale": {r: now - b["time"] for r, b in beats.items() if now - b["time"] > max_age_s},
+            "steps": {r: b["step"] for r, b in beats.items()}}
+
+
 def build_train_record(step, epoch, metrics: Dict[str, Any], *, steps_per_sec, elapsed,
                        analysis: bool = False) -> Dict[str, Any]:
     rec = {"type": "train_analysis" if analysis else "train", "step": step, "epoch": epoch,

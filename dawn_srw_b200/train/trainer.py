@@ -98,6 +98,7 @@ class Trainer:
         self.best_val_loss = float("inf")
         self.run_dir = run_dir
         self.logger = L.RunLogger(run_dir, enabled=self.topo.is_main)
+        self.heartbeat = L.Heartbeat(run_dir, self.topo.rank, self.topo.world)
         self._emb_snap = None
         self.preempt_requested = False
         self._t0 = time.time()
@@ -291,6 +292,7 @@ class Trainer:
                 is_log = L.is_log_step(nxt, t.log_interval)
                 is_an = L.is_analysis_step(nxt, t.log_interval, t.log_analysis_multiplier)
                 m = self.train_step(ids, mask, want_diag=is_log or is_an)
+                self.heartbeat.beat(self.global_step)
                 self.step_in_epoch = local_step + 1
                 tl = float(m["total_loss"])                      # the per-step device->host read
                 if not math.isfinite(tl):

@@ -156,3 +156,23 @@ def test_trace_ranges_cover_a_training_step():
     assert "know/srw" in tracing.format_report(rep)
     tr.train_step(ids, mask)
     assert tracing.report() == {}                 # off again: nothing is recorded
+
+
+def test_heartbeat_files_and_watchdog(tmp_path, capsys):
+    import time
+    from dawn_srw_b200.tools import watchdog as W
+    from dawn_srw_b200.train.logging import Heartbeat, stale_ranks
+    run = str(tmp_path / "run")
+    tr = Trainer(tiny_config(max_steps=2), run_dir=run, total_steps=2)
+    tr.fit()
+    rep = stale_ranks(run, max_age_s=60)
+    assert rep["world"] == 1 and not rep["stale"] and not rep["missing"] and rep["steps"][0] >= 1
+    assert W.main([run, "--max-age", "60"]) == 0
+    capsys.readouterr()
+    # a second rank that stopped refreshing long ago, and a third that never wrote one
+    hb = Heartbeat(run, rank=1, world=3)
+    hb.beat(5, force=True)
+    old = stale_ranks(run, max_age_s=60, now=time.time() + 3600)
+    assert set(old["stale"]) == {0, 1} and old["missing"] == [2] and old["world"] == 3
+    assert W.main([run, "--max-age", "60"]) == 3          # rank 2 is missing
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["missing"] == [2]
