@@ -32,6 +32,13 @@ dict; the selection mirrors the SRW part of the reference's analysis CLI
   gate_ci      bootstrap confidence interval of the active fraction per route
   read_cov / write_cov   participation ratio of the selection-weighted read / write vectors
   samples      for the most-used knowledge units: the token ids that open them most strongly
+  resid_dyn    residual-stream dynamics: norm per layer, rotation between consecutive layers and
+               from the embedding to the last layer, top-1 agreement of each layer's read-out
+  z_dist       distribution of the standardised score z = (s - mean) / std of the first layer's
+               knowledge route (quantiles, fraction above the threshold)
+  addit        additivity of suppressions: loss change of two unit sets together vs separately
+  cross_suppress  effect of suppressing the most-used units of one pool on the loss and on the
+               activity of the other pools
 
 All analyses run on one device through the model's public inference API
 (models/inference.py).
@@ -392,6 +399,99 @@ def analyze_samples(c: Context) -> Dict:
     return {"know_units": out}
 
 
+def analyze_resid_dyn(c: Context) -> Dict:
+    m, ids = c.model, c.batches()[0]
+    be = I._be(m, c.device)
+    pools = I._pools(m, be)
+    B, S = ids.shape
+    D, H = m.d_model, m.n_heads
+    heads = lambda t: t.reshape(B, S, H, D // H).transpose(1, 2)
+    x = be.embed(ids, m.token_emb.weight, m.pos_emb.weight).float()
+    states = [x]
+    for blk in m.layers:
+        n = be.layer_norm(x, blk.norm1.weight, blk.norm1.bias).reshape(B * S, D)
+        q, k, v, _, _ = I._layer_qkv(m, be, n, pools)
+        o = be.attention(heads(q), heads(k), heads(v), 0.0, False).transpose(1, 2).reshape(B * S, D)
+        x = x + be.linear(o, blk.attn.expand_O.weight, None).float().reshape(B, S, D)
+        n = be.layer_norm(x, blk.norm2.weight, blk.norm2.bias).reshape(B * S, D)
+        ko, _ = I._know(m, be, n, pools)
+        x = x + ko.float().reshape(B, S, D)
+        states.append(x)
+    cos = torch.nn.functional.cosine_similarity
+    deg = lambda a, b: float(torch.rad2deg(torch.acos(cos(a, b, dim=-1).clamp(-1, 1))).mean())
+    final_top1 = be.logits(be.layer_norm(states[-1], m.norm.weight, m.norm.bias), m.token_emb.weight).argmax(-1)
+    agree = []
+    for st in states[1:]:
+        top1 = be.logits(be.layer_norm(st, m.norm.weight, m.norm.bias), m.token_emb.weight).argmax(-1)
+        agree.append(float((top1 == final_top1).float().mean()))
+    return {"norm_per_layer": [float(torch.linalg.vector_norm(s_, dim=-1).mean()) for s_ in states],
+            "rotation_deg_per_layer": [deg(states[i], states[i + 1]) for i in range(len(states) - 1)],
+            "rotation_deg_total": deg(states[0], states[-1]),
+            "cumulative_rotation_deg": sum(deg(states[i], states[i + 1]) for i in range(len(states) - 1)),
+            "top1_agreement_with_final": agree}
+
+
+def analyze_z_dist(c: Context) -> Dict:
+    m, ids = c.model, c.batches()[0]
+    be = I._be(m, c.device)
+    B, S = ids.shape
+    x = be.embed(ids, m.token_emb.weight, m.pos_emb.weight).float()
+    blk = m.layers[0]
+    # knowledge route of the first layer, scores against the (optionally normalised) embeddings
+    n1 = be.layer_norm(x, blk.norm1.weight, blk.norm1.bias).reshape(B * S, m.d_model)
+    h = be.linear(n1, m.router.proj_know.weight, m.router.proj_know.bias).float()
+    p = m.neuron_pool
+    emb = p.know_emb[: p.n_valid("know")].float()
+    if m.gate.normalize_pool:
+        emb = emb / (torch.linalg.vector_norm(emb, dim=-1, keepdim=True) + 1e-8)
+    s = h @ emb.t()
+    z = (s - s.mean(-1, keepdim=True)) / (s.std(-1, unbiased=False, keepdim=True) + 1e-8)
+    off = be.linear(n1, m.router.tau_know.weight, m.router.tau_know.bias).float()      # [T,1]
+    flat = z.flatten()
+    sample = flat[torch.randint(0, flat.numel(), (min(flat.numel(), 1_000_000),), device=flat.device)]
+    qs = torch.tensor([0.01, 0.25, 0.5, 0.75, 0.99, 0.999], device=c.device)
+    qv = torch.quantile(sample, qs).tolist()
+    return {"quantiles": dict(zip(["p1", "p25", "p50", "p75", "p99", "p99.9"], qv)),
+            "skew": float((z ** 3).mean()), "excess_kurtosis": float((z ** 4).mean() - 3.0),
+            "frac_above_threshold": float((z > off).float().mean()),
+            "threshold_offset_mean": float(off.mean())}
+
+
+def _loss_with(c: Context, masks: Dict[str, torch.Tensor]) -> float:
+    ids = c.batches()[0]
+    return _mean_loss(I.build_suppressed_forward(c.model, masks)(ids), ids)
+
+
+def _top_mask(c: Context, pool: str, counts: torch.Tensor, k: int, skip: int = 0) -> torch.Tensor:
+    n_rows = getattr(c.model.neuron_pool, f"{pool}_emb").shape[0]
+    mask = torch.zeros(n_rows, dtype=torch.bool, device=c.device)
+    idx = torch.topk(counts, min(k + skip, counts.numel())).indices[skip:]
+    mask[idx] = True
+    return mask
+
+
+def analyze_addit(c: Context) -> Dict:
+    cnt = _selection_counts(c)["Know"].sum(0)
+    k = max(1, min(int(c.args.suppress_top[0]) if c.args.suppress_top else 16, cnt.numel() // 2))
+    a, b = _top_mask(c, "know", cnt, k), _top_mask(c, "know", cnt, k, skip=k)
+    base = _mean_loss(c.gates()["logits"], c.batches()[0])
+    la, lb, lab = _loss_with(c, {"know": a}), _loss_with(c, {"know": b}), _loss_with(c, {"know": a | b})
+    return {"k": k, "baseline": base, "delta_a": la - base, "delta_b": lb - base, "delta_ab": lab - base,
+            "interaction": (lab - base) - (la - base) - (lb - base)}
+
+
+def analyze_cross_suppress(c: Context) -> Dict:
+    cnt = _selection_counts(c)
+    freq = {"qk": (cnt["Q"] + cnt["K"]).sum(0), "v": cnt["V"].sum(0), "know": cnt["Know"].sum(0)}
+    base = _mean_loss(c.gates()["logits"], c.batches()[0])
+    k = int(c.args.suppress_top[0]) if c.args.suppress_top else 16
+    out = {"baseline": base, "k": k}
+    for pool in ("qk", "v", "know"):
+        kk = max(1, min(k, freq[pool].numel() // 2))
+        out[pool] = {"loss_delta": _loss_with(c, {pool: _top_mask(c, pool, freq[pool], kk)}) - base}
+    return out
+
+
 ANALYSES: Dict[str, Callable[[Context], Dict]] = {
     "info": analyze_info, "val": analyze_val, "health": analyze_health, "weights": analyze_weights,
     "generate": analyze_generate, "routing": analyze_routing, "gate_dist": analyze_gate_dist,
@@ -400,11 +500,13 @@ ANALYSES: Dict[str, Callable[[Context], Dict]] = {
     "rw_align": analyze_rw_align, "tau_dist": analyze_tau_dist, "drift": analyze_drift,
     "cross_ref": analyze_cross_ref, "layer_sim": analyze_layer_sim, "sel_trans": analyze_sel_trans,
     "gate_ci": analyze_gate_ci, "read_cov": analyze_read_cov, "write_cov": analyze_write_cov,
-    "samples": analyze_samples,
+    "samples": analyze_samples, "resid_dyn": analyze_resid_dyn, "z_dist": analyze_z_dist,
+    "addit": analyze_addit, "cross_suppress": analyze_cross_suppress,
 }
 SPATIAL_ONLY = {"health", "weights", "routing", "gate_dist", "utilization", "sel_gini", "layer_role",
                 "intervene", "pool_geom", "rw_align", "tau_dist", "drift", "cross_ref", "layer_sim",
-                "sel_trans", "gate_ci", "read_cov", "write_cov", "samples"}
+                "sel_trans", "gate_ci", "read_cov", "write_cov", "samples", "resid_dyn", "z_dist",
+                "addit", "cross_suppress"}
 
 
 def run(model, cfg, info, args) -> Dict:

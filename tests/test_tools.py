@@ -66,6 +66,12 @@ def test_analysis_cli_runs_every_key(tmp_path):
     assert lo <= res["gate_ci"]["V"]["active_frac"] <= hi or abs(hi - lo) < 1e-6
     assert 1.0 <= res["write_cov"]["know"]["participation_ratio"] <= res["write_cov"]["know"]["dims"] + 1e-6
     assert res["samples"]["know_units"] and len(res["samples"]["know_units"][0]["top_token_ids"]) > 0
+    assert len(res["resid_dyn"]["norm_per_layer"]) == L + 1
+    assert res["resid_dyn"]["top1_agreement_with_final"][-1] == 1.0
+    assert res["z_dist"]["quantiles"]["p1"] < res["z_dist"]["quantiles"]["p99"]
+    ad = res["addit"]
+    assert abs(ad["interaction"] - (ad["delta_ab"] - ad["delta_a"] - ad["delta_b"])) < 1e-9
+    assert set(res["cross_suppress"]) >= {"qk", "v", "know", "baseline"}
     assert len(res["generate"]["samples"][0]["token_ids"]) >= 4
     # key selection
     assert A.main(["--checkpoint", path, "--synthetic", "--only", "info,health", "--device", "cpu"]) == 0
