@@ -109,7 +109,7 @@ class SyntheticDataset:
 
 class BinDataLoader:
     def __init__(self, dataset, global_batch: int, batch_index: int = 0, batch_replicas: int = 1,
-                 pin: bool = True):
+                 pin: bool = True, prefetch: int = 2):
         if global_batch % batch_replicas != 0:
             raise ValueError(f"global batch {global_batch} is not divisible by "
                              f"{batch_replicas} batch shards")
@@ -119,6 +119,7 @@ class BinDataLoader:
         self.steps = len(dataset) // global_batch
         self.start_step = 0
         self.pin = pin and torch.cuda.is_available()
+        self.prefetch = max(0, int(prefetch))     # batches prepared ahead by a background thread
 
     def __len__(self):
         return self.steps
@@ -136,9 +137,48 @@ class BinDataLoader:
         return ids, mask
 
     def __iter__(self) -> Iterator[Tuple[torch.Tensor, torch.Tensor]]:
+        """Batches ``start_step .. steps-1`` in order.  With ``prefetch > 0`` a
+        background thread reads, converts and pins up to that many batches ahead
+        of the consumer (file reads and pinning overlap the training step); the
+        sequence of batches is the same as without it."""
         first, self.start_step = self.start_step, 0
-        for step in range(first, self.steps):
-            yield self.batch(step)
+        if self.prefetch == 0 or self.steps - first <= 1:
+            for step in range(first, self.steps):
+                yield self.batch(step)
+            return
+        import queue
+        import threading
+        q: "queue.Queue" = queue.Queue(maxsize=self.prefetch)
+        stop = threading.Event()
+
+        def produce():
+            try:
+                for step in range(first, self.steps):
+                    if stop.is_set():
+                        return
+                    item = self.batch(step)
+                    while not stop.is_set():
+                        try:
+                            q.put(item, timeout=0.1)
+                            break
+                        except queue.Full:
+                            continue
+                q.put(None)
+            except BaseException as e:            # surfaces in the consumer, never lost in the thread
+                q.put(e)
+
+        th = threading.Thread(target=produce, daemon=True, name="dawn-data-prefetch")
+        th.start()
+        try:
+            while True:
+                item = q.get()
+                if item is None:
+                    return
+                if isinstance(item, BaseException):
+                    raise item
+                yield item
+        finally:
+            stop.set()
 
 
 def load_data(data_cfg, seq_len: int, global_batch: int, vocab_size: int, *, batch_index=0,

@@ -165,3 +165,27 @@ def test_fileio_local_and_url_paths(tmp_path):
     import pytest
     with pytest.raises(RuntimeError):
         F.file_exists("nosuchscheme://x/y")
+
+
+def test_prefetching_loader_yields_the_same_batches_and_propagates_errors(tmp_path):
+    import numpy as np
+    import pytest
+    from dawn_srw_b200.data.loaders import BinDataLoader, BinDataset, SyntheticDataset
+    ds = SyntheticDataset(64, 8, 100, seed=3)
+    plain = [b[0].clone() for b in BinDataLoader(ds, 8, prefetch=0)]
+    ahead = [b[0].clone() for b in BinDataLoader(ds, 8, prefetch=3)]
+    assert len(plain) == len(ahead) == 8 and all(torch.equal(a, b) for a, b in zip(plain, ahead))
+    ld = BinDataLoader(ds, 8, prefetch=2)
+    ld.reset(5)                                                   # resume position
+    assert [int(b[0][0, 0]) for b in ld] == [int(p[0, 0]) for p in plain[5:]]
+    it = iter(BinDataLoader(ds, 8, prefetch=2))                   # abandoning an iterator stops its thread
+    next(it)
+    it.close()
+
+    class Broken(SyntheticDataset):
+        def rows(self, lo, hi):
+            if lo >= 16:
+                raise OSError("disk went away")
+            return super().rows(lo, hi)
+    with pytest.raises(OSError):
+        list(BinDataLoader(Broken(64, 8, 100), 8, prefetch=2))
