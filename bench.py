@@ -78,6 +78,30 @@ def reference_arm(args):
     return 0
 
 
+def parse_clock_csv(text: str):
+    """Summary of `nvidia-smi --query-gpu=... --format=csv,noheader,nounits -lms` output
+    (fields of ClockSampler.FIELDS): median SM clock under load, maximum SM clock and
+    the throttle reasons that were active in any sample.  None if no line parses."""
+    sm, smax, reasons = [], [], set()
+    for line in text.splitlines():
+        f = [x.strip() for x in line.split(",")]
+        if len(f) < 9:
+            continue
+        try:
+            sm.append(float(f[1]))
+            smax.append(float(f[2]))
+        except ValueError:
+            continue
+        for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                              "sw_power_cap"), f[5:9]):
+            if val.lower().startswith("active"):
+                reasons.add(name)
+    if not sm:
+        return None
+    return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+            "samples": len(sm)}
+
+
 class ClockSampler:
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -106,27 +130,12 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, smax, reasons = [], [], set()
         try:
-            for line in open(self.path):
-                f = [x.strip() for x in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    sm.append(float(f[1])); smax.append(float(f[2]))
-                except ValueError:
-                    continue
-                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                      "sw_power_cap"), f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
+            text = open(self.path).read()
             os.remove(self.path)
         except Exception:
-            pass
-        if sm:
-            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                   "samples": len(sm)}
-        return out
+            return out
+        return parse_clock_csv(text) or out
 
 
 def main():

@@ -177,3 +177,24 @@ def test_inference_speed_harness(capsys):
     assert [r["batch"] for r in recs] == [1, 3]
     assert all(r["forward_tokens_per_sec"] > 0 and r["decode_new_tokens"] == 4 for r in recs)
     assert recs[0]["forward_ms_p50"] <= recs[0]["forward_ms_p95"] + 1e-9
+
+
+def test_bench_clock_csv_parsing():
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    text = "\n".join([
+        "0, 1965, 1965, 410.2, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active",
+        "0, 1710, 1965, 995.0, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+        "0, 1650, 1965, 998.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active",
+        "garbage line",
+        "0, [N/A], 1965, 1.0, x, Not Active, Not Active, Not Active, Not Active",
+    ])
+    rec = bench.parse_clock_csv(text)
+    assert rec == {"sm_mhz": 1710.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 3}
+    hot = bench.parse_clock_csv("0, 900, 1965, 300, x, Active, Active, Not Active, Not Active")
+    assert hot["reasons"] == ["hw_slowdown", "hw_thermal_slowdown"]
+    assert bench.parse_clock_csv("") is None
+    assert bench.ClockSampler(0).stop()["sm_mhz"] is None         # never started: neutral record
