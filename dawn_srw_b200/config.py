@@ -174,6 +174,42 @@ def config_from_dict(raw: Dict[str, Any]) -> Config:
     return cfg
 
 
+def validate_config(cfg: Config, world: int = 1, pool_shards: int = 1, on_gpu: bool = False) -> None:
+    """Reject configurations that cannot run, with the reason, before any
+    memory is allocated (the reference fails late inside XLA for most of these)."""
+    m, t = cfg.model, cfg.training
+    errs = []
+    if m.d_model % m.n_heads != 0:
+        errs.append(f"model.d_model ({m.d_model}) is not a multiple of model.n_heads ({m.n_heads})")
+    elif on_gpu and ((m.d_model // m.n_heads) % 16 != 0 or m.d_model // m.n_heads > 128):
+        errs.append(f"head dimension {m.d_model // m.n_heads} is outside what the attention kernels "
+                    "take (a multiple of 16, at most 128)")
+    if on_gpu and m.d_model % 8 != 0:
+        errs.append(f"model.d_model ({m.d_model}) must be a multiple of 8 (16-byte rows for TMA)")
+    if m.is_spatial:
+        if on_gpu and m.d_route % 8 != 0:
+            errs.append(f"model.d_route ({m.d_route}) must be a multiple of 8 (16-byte rows for TMA)")
+        for name in ("n_qk", "n_v", "n_know"):
+            if getattr(m, name) < max(1, pool_shards):
+                errs.append(f"model.{name} ({getattr(m, name)}) is smaller than the number of pool shards")
+    if world % max(1, pool_shards) != 0:
+        errs.append(f"world size {world} is not a multiple of training.pool_shards ({pool_shards})")
+    else:
+        dp = world // max(1, pool_shards)
+        batch_shards = world if (pool_shards == 1 or t.seq_shard) else dp
+        if t.batch_size % max(1, batch_shards) != 0:
+            errs.append(f"training.batch_size ({t.batch_size}) is not divisible by the {batch_shards} "
+                        "ranks that each take a slice of the batch")
+    if not (0.0 <= m.dropout < 1.0 and 0.0 <= m.router_dropout < 1.0):
+        errs.append("dropout rates must be in [0, 1)")
+    if t.gradient_accumulation_steps < 1:
+        errs.append("training.gradient_accumulation_steps must be at least 1")
+    if m.max_seq_len < 2:
+        errs.append("model.max_seq_len must be at least 2 (next-token loss)")
+    if errs:
+        raise ValueError("invalid configuration:\n  - " + "\n  - ".join(errs))
+
+
 def load_config(path: str) -> Config:
     """YAML from a local path or an fsspec URL."""
     from .utils.fileio import open_file

@@ -26,7 +26,7 @@ from typing import Any, Dict, Optional
 import torch
 import torch.distributed as dist
 
-from ..config import Config, save_run_config
+from ..config import Config, validate_config, save_run_config
 from ..data.loaders import load_data
 from ..models.registry import build_model_from_config, count_parameters
 from ..ops.backend import default_backend
@@ -53,6 +53,8 @@ class Trainer:
             device = torch.device("cuda", self.topo.local_rank) if torch.cuda.is_available() \
                 else torch.device("cpu")
         self.device = torch.device(device)
+        validate_config(cfg, world=self.topo.world, pool_shards=self.topo.pool_shards,
+                        on_gpu=self.device.type == "cuda" and backend is None)
         self.backend = backend or default_backend(self.device)
         t, m = cfg.training, cfg.model
         self.is_baseline = not m.is_spatial

@@ -84,3 +84,27 @@ def test_registry_versions():
     cfg.model.model_version = "spatial-r1-v9"
     with pytest.raises(ValueError):
         build_model_from_config(cfg)
+
+
+def test_validate_config_reports_every_problem_at_once():
+    import pytest
+    from dawn_srw_b200.config import preset, validate_config
+    cfg = preset("40M")
+    validate_config(cfg, world=8, pool_shards=1, on_gpu=True)               # the shipped shape is fine
+    cfg.model.d_model, cfg.model.n_heads = 100, 3
+    cfg.training.batch_size = 30
+    cfg.model.dropout = 1.5
+    with pytest.raises(ValueError) as e:
+        validate_config(cfg, world=8, pool_shards=2, on_gpu=True)
+    msg = str(e.value)
+    assert "n_heads" in msg and "batch_size" in msg and "dropout" in msg and "multiple of 8" in msg
+    cfg = preset("40M", d_model=384, n_heads=16)                             # head dimension 24
+    validate_config(cfg, on_gpu=False)
+    with pytest.raises(ValueError, match="head dimension 24"):
+        validate_config(cfg, on_gpu=True)
+    cfg = preset("40M")
+    cfg.training.batch_size, cfg.training.seq_shard = 12, False
+    validate_config(cfg, world=8, pool_shards=4)                             # 2 replicas share 12 sequences
+    cfg.training.seq_shard = True
+    with pytest.raises(ValueError, match="batch_size"):
+        validate_config(cfg, world=8, pool_shards=4)                         # 8 ranks each take a slice
