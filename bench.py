@@ -245,6 +245,7 @@ def main():
                 for k, t_ms, n in rows[:40]:
                     f.write(f"{t_ms:10.2f} ms {n:6d}x  {k[:120]}\n")
 
+    trainer.backend.finish_run()          # raise now if any kernel reported a device-side failure
     vals = torch.tensor([ms, e2e[0] if e2e else 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
