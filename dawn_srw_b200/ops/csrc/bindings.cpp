@@ -213,6 +213,90 @@ void srw_bwd_gate_gather(const Tensor& h_full, const Tensor& emb, const Tensor& 
   TORCH_CHECK(rc == 0, "dsb_srw_bwd_gate_gather failed with code ", rc);
 }
 
+// Forward gate kernel with optional extras: xr_out keeps the read scalars for
+// the backward pass; a non-empty ptr_lists (order x, h) fuses the all-gather of
+// the token operands (h / x are then this rank's full buffers).
+void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const Tensor& read,
+                     Tensor& p_out, c10::optional<Tensor> xr_out, const Tensor& tau,
+                     const Tensor& inv_sigma, Tensor& den_sum, c10::optional<Tensor> alive,
+                     c10::optional<Tensor> unit_mask, std::vector<double> gate, Tensor& status,
+                     std::vector<std::vector<int64_t>> ptr_lists, int64_t my_rank,
+                     int64_t rows_per_rank, c10::optional<Tensor> ready, int64_t epoch) {
+  check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(x, "x");
+  check_bf16_2d(read, "read"); check_bf16_2d(p_out, "p_out");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = x.size(0), D = x.size(1), U = emb.size(0), r = emb.size(1);
+  TORCH_CHECK(h.size(0) == T && h.size(1) == r && read.size(0) == U && read.size(1) == D);
+  TORCH_CHECK(p_out.size(0) == T && p_out.size(1) >= U);
+  void* xr_p = nullptr;
+  long long ldxr = 0;
+  if (xr_out.has_value() && xr_out->defined()) {
+    check_bf16_2d(*xr_out, "xr_out");
+    TORCH_CHECK(xr_out->size(0) == T && xr_out->size(1) >= U);
+    xr_p = xr_out->data_ptr();
+    ldxr = xr_out->stride(0);
+  }
+  unsigned char* alive_p = nullptr;
+  if (alive.has_value() && alive->defined()) {
+    TORCH_CHECK(alive->scalar_type() == torch::kUInt8 && alive->numel() >= U);
+    alive_p = alive->data_ptr<unsigned char>();
+  }
+  DsbGate g = to_gate(gate);
+  GatherHolder gh;
+  const DsbGather* gp = nullptr;
+  if (!ptr_lists.empty()) {
+    TORCH_CHECK(ptr_lists.size() == 2 && ready.has_value());
+    fill_gather(gh, ptr_lists, {x.stride(0), h.stride(0)}, {D, r}, my_rank, rows_per_rank, *ready,
+                epoch);
+    gp = &gh.g;
+  }
+  int rc = dsb_srw_fwd_gate_xr(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0),
+                               x.data_ptr(), x.stride(0), read.data_ptr(), read.stride(0), T, U, r,
+                               D, p_out.data_ptr(), p_out.stride(0), xr_p, ldxr,
+                               tau.data_ptr<float>(), inv_sigma.data_ptr<float>(),
+                               den_sum.data_ptr<float>(), nullptr, alive_p, opt_f32(unit_mask), &g,
+                               gp, status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_fwd_gate_xr failed with code ", rc);
+}
+
+// Backward gate step from saved read scalars.  Gathered tensors (optional), in
+// this order: h_full, dy_full[, x_full]; x_full is not an operand of this
+// kernel, it is only brought in for the GEMMs that follow.
+void srw_bwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& dy, const Tensor& write,
+                     const Tensor& xr, Tensor& p_out, Tensor& dxr_out, Tensor& ds_out,
+                     const Tensor& tau, const Tensor& inv_sigma, const Tensor& dden,
+                     Tensor& dtau_sum, std::vector<double> gate, Tensor& status,
+                     std::vector<std::vector<int64_t>> ptr_lists, std::vector<int64_t> lds,
+                     std::vector<int64_t> cols, int64_t my_rank, int64_t rows_per_rank,
+                     c10::optional<Tensor> ready, int64_t epoch) {
+  check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(dy, "dy");
+  check_bf16_2d(write, "write"); check_bf16_2d(xr, "xr");
+  check_bf16_2d(p_out, "p_out"); check_bf16_2d(dxr_out, "dxr_out"); check_bf16_2d(ds_out, "ds_out");
+  const c10::cuda::CUDAGuard guard(h.device());
+  const int T = h.size(0), D = dy.size(1), U = emb.size(0), r = emb.size(1);
+  TORCH_CHECK(dy.size(0) == T && write.size(0) == U && write.size(1) == D && h.size(1) == r);
+  TORCH_CHECK(xr.size(0) == T && xr.size(1) >= U && p_out.size(0) == T && p_out.size(1) >= U);
+  TORCH_CHECK(p_out.stride(0) == dxr_out.stride(0) && p_out.stride(0) == ds_out.stride(0));
+  DsbGate g = to_gate(gate);
+  GatherHolder gh;
+  const DsbGather* gp = nullptr;
+  if (!ptr_lists.empty()) {
+    TORCH_CHECK(ptr_lists.size() == lds.size() && lds.size() == cols.size() && ready.has_value());
+    fill_gather(gh, ptr_lists, lds, cols, my_rank, rows_per_rank, *ready, epoch);
+    gp = &gh.g;
+  }
+  int rc = dsb_srw_bwd_gate_xr(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0),
+                               dy.data_ptr(), dy.stride(0), write.data_ptr(), write.stride(0),
+                               xr.data_ptr(), xr.stride(0), T, U, r, D, p_out.data_ptr(),
+                               dxr_out.data_ptr(), ds_out.data_ptr(), p_out.stride(0),
+                               tau.data_ptr<float>(), inv_sigma.data_ptr<float>(),
+                               dden.data_ptr<float>(), dtau_sum.data_ptr<float>(), &g, gp,
+                               status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_bwd_gate_xr failed with code ", rc);
+}
+
+bool srw_wide_tiles(int64_t U) { return dsb_srw_wide_tiles(static_cast<int>(U)) != 0; }
+
 // Fused GEMM -> reduce-scatter.  `out_ptrs`: data pointers of every rank's
 // [rows_per_rank, N] fp32 buffer (index = rank), as integers.
 void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
@@ -475,6 +559,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_fwd_gate", &srw_fwd_gate);
   m.def("srw_bwd_gate", &srw_bwd_gate);
   m.def("srw_forward", &srw_forward);
+  m.def("srw_fwd_gate_xr", &srw_fwd_gate_xr);
+  m.def("srw_bwd_gate_xr", &srw_bwd_gate_xr);
+  m.def("srw_wide_tiles", &srw_wide_tiles);
   m.def("gemm_scatter", &gemm_scatter);
   m.def("sum_slabs", &sum_slabs);
   m.def("layernorm_fwd", &layernorm_fwd);

@@ -79,7 +79,6 @@ struct alignas(64) GemmParams {
   int M, N;
   int m_tiles, n_tiles;
   int n_fastest;  // tile raster: 1 = consecutive tiles walk N first
-  int dbg;        // profiling only: 1 = no loads, MMAs run on whatever is in shared memory
   int m_rot;      // tile rows are visited starting from this m-tile (own rows first)
   int k_splits;   // > 1: the K range of segment 0 is cut into this many tiles that all
                   // reduce-add into the same output (accumulating fp32 epilogues only)
@@ -279,7 +278,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
 
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------ producer
-    if (lane == 0 && !(p.dbg & 1)) {
+    if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -357,7 +356,6 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       int it = 0;
       bool ok = true;
       const uint32_t smem_base = smem_u32(smem);
-      const bool no_loads = (p.dbg & 1) != 0;
       const int n_seg = p.n_seg;
       auto issue_seg = [&](auto a_mn_c, auto b_mn_c, const int k_tiles, const uint32_t d_tmem,
                            uint32_t accum) {
@@ -368,11 +366,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         const uint64_t b_base = umma_desc(smem_base + Smem::kABytes, kBmn ? 8192u : 16u, 1024);
 #pragma unroll 1
         for (int kt = 0; kt < k_tiles; ++kt) {
-          if (!no_loads) {
-            if (!mbar_try_wait(&full_bar[stage], phase) &&
-                !mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; return; }
-            tc_fence_after();
-          }
+          if (!mbar_try_wait(&full_bar[stage], phase) &&
+              !mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; return; }
+          tc_fence_after();
           const uint64_t so = static_cast<uint64_t>(static_cast<uint32_t>(stage) *
                                                     (Smem::kStageBytes >> 4));
           const uint64_t ad = a_base + so, bd = b_base + so;
@@ -382,11 +378,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
             else mma_bf16_ss(d_tmem, ad + kk * kAInc, bd + kk * kBInc, idesc, accum);
             accum = 1u;
           }
-          if (!no_loads) {
-            // frees the smem stage (in both CTAs) when the MMAs retire
-            if (kCtas == 2) mma_commit_pair(&empty_bar[stage]);
-            else mma_commit(&empty_bar[stage]);
-          }
+          // frees the smem stage (in both CTAs) when the MMAs retire
+          if (kCtas == 2) mma_commit_pair(&empty_bar[stage]);
+          else mma_commit(&empty_bar[stage]);
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       };

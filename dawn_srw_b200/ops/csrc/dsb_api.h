@@ -79,6 +79,34 @@ int dsb_srw_bwd_gate_gather(const void* h, long long ldh, const void* emb, long 
                             const DsbGate* gate, const DsbGather* gather /*host*/, int* status,
                             cudaStream_t stream);
 
+// 1 when a pool of U units runs on the 256-column gate kernels (CTA pairs, U >= 512);
+// only those can keep / consume the read scalars below.
+int dsb_srw_wide_tiles(int U);
+
+// Forward gate kernel that can also keep the read scalars: xr_out (nullable)
+// receives bf16 xr = x.read^T [T, ldxr] next to p.  Needs dsb_srw_wide_tiles(U).
+// gather may be null.
+int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
+                        const void* x, long long ldx, const void* read, long long ldr, int T,
+                        int U, int r, int D, void* p_out, long long ldp, void* xr_out,
+                        long long ldxr, const float* tau, const float* inv_sigma, float* den_sum,
+                        float* gate_sum, unsigned char* alive, const float* unit_mask,
+                        const DsbGate* gate, const DsbGather* gather /*host*/, int* status,
+                        cudaStream_t stream);
+
+// Backward gate step from the read scalars the forward pass kept: one launch
+// computing S = h.emb^T and DP = dy.write^T, writing p = g*xr, dxr = DP*g and ds
+// (bf16 [T, ld_out]) and accumulating dtau_sum[T] -= sum_U ds.  No x / read
+// operands: xr is read back instead of recomputed.  With a gather, every tensor
+// it lists is pulled under its one epoch.
+int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
+                        const void* dy, long long lddy, const void* write, long long ldw,
+                        const void* xr, long long ldxr, int T, int U, int r, int D, void* p_out,
+                        void* dxr_out, void* ds_out, long long ld_out, const float* tau,
+                        const float* inv_sigma, const float* dden, float* dtau_sum,
+                        const DsbGate* gate, const DsbGather* gather /*host*/, int* status,
+                        cudaStream_t stream);
+
 // One route of the SRW forward op (gate kernel + write GEMM).  `p_scratch` is
 // caller-provided scratch: bf16 [T, ldp] with ldp >= U and ldp % 8 == 0; its
 // contents on return are unspecified.  den_sum[T] is cleared and filled here;

@@ -36,19 +36,27 @@ __device__ __forceinline__ float rcp_approx(float x) {
   return y;  // rcp(+inf) = 0, no slow path
 }
 
-// Phi(z) = 0.5 (1 + erf(z / sqrt 2)) for z > 0 and the N(0,1) density, sharing
-// one exponential.  erf uses the 5-term rational form 1 - poly(t) e^{-x^2},
-// t = 1 / (1 + 0.3275911 x) (absolute error 1.5e-7), which is branch-free.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 1 - Phi(z) for z >= 0, Phi the standard normal CDF, as 2^P(z) with P a
+// degree-5 polynomial fitted to log2(0.5 erfc(z / sqrt 2)): absolute error
+// below 5e-7 for all z >= 0 (P decreases without bound, so large z give 0).
+// One exponential and five FMAs; no reciprocal, no branch.
+__device__ __forceinline__ float phi_tail(float z) {
+  float p = fmaf(z, -0.0005216513f, 0.0073997346f);
+  p = fmaf(p, z, -0.052554633f);
+  p = fmaf(p, z, -0.45927137f);
+  p = fmaf(p, z, -1.1510814f);
+  p = fmaf(p, z, -1.0000014f);
+  return ex2_approx(p);
+}
+// Phi(z) and the N(0,1) density for z >= 0.
 __device__ __forceinline__ void phi_pdf(float z, float& phi, float& pdf) {
-  const float e = __expf(-0.5f * z * z);
-  const float t = rcp_approx(fmaf(0.3275911f * 0.70710678f, z, 1.f));
-  float poly = fmaf(t, 1.061405429f, -1.453152027f);
-  poly = fmaf(t, poly, 1.421413741f);
-  poly = fmaf(t, poly, -0.284496736f);
-  poly = fmaf(t, poly, 0.254829592f);
-  poly *= t;
-  phi = fmaf(-0.5f * poly, e, 1.f);
-  pdf = 0.39894228f * e;
+  phi = 1.f - phi_tail(z);
+  pdf = 0.39894228f * ex2_approx(-0.72134752f * z * z);
 }
 
 template <int KIND>
@@ -59,9 +67,7 @@ __device__ __forceinline__ void gate_fwd(const GateConsts& gc, float s, float ta
     dterm = g;
   } else if constexpr (KIND == 1) {
     const float z = fmaxf((s - tau) * isg, 0.f);
-    float phi, pdf;
-    phi_pdf(z, phi, pdf);
-    g = z * phi;  // z == 0 gives exactly 0
+    g = fmaf(-z, phi_tail(z), z);  // z * Phi(z); z == 0 gives exactly 0
     dterm = g;
   } else {
     const float m = s - tau - gc.thr;
@@ -135,7 +141,6 @@ struct PlainEpi {
     const float* bias;       // optional [N]
     int out_bf16;            // 1: bf16 output, 0: fp32
     int accumulate;          // 1: out += result (fp32 output only; TMA reduce-add)
-    int dbg;                 // profiling toggle: 1 = skip the stores
     // Fused reduce-scatter, first half: when > 0, global row R of the result
     // belongs to rank R / scatter_rows and is stored into slot `scatter_rank` of
     // that rank's receive buffer [n_ranks * scatter_rows, N] (tensor map index =
@@ -183,7 +188,7 @@ struct PlainEpi {
           st.flush(&maps[owner], buf, col0,
                    p.scatter_rank * p.scatter_rows + (r0 - owner * p.scatter_rows), false, true);
         } else {
-          st.flush(&maps[0], buf, col0, r0, false, !(p.dbg & 1));
+          st.flush(&maps[0], buf, col0, r0, false, true);
         }
       }
     } else {
@@ -214,7 +219,7 @@ struct PlainEpi {
           st.flush(&maps[owner], buf, col0,
                    p.scatter_rank * p.scatter_rows + (r0 - owner * p.scatter_rows), false, true);
         } else {
-          st.flush(&maps[0], buf, col0, r0, p.accumulate != 0, !(p.dbg & 1));
+          st.flush(&maps[0], buf, col0, r0, p.accumulate != 0, true);
         }
       }
     }
@@ -313,24 +318,155 @@ struct FwdGateEpi {
   }
 };
 
+// ------------------------------------------------ shifted-score gate helpers
+// The wide epilogues work on the shifted score zt = a * s + b with per-row
+// constants (a, b), so the per-element cost of the shift is one FMA:
+//   v3.9.4: zt = s - tau;  v4.0.1: zt = (s - tau) / sigma;  v4.1: zt = s - tau - threshold.
+struct RowGate {
+  float a, b;
+};
+template <int KIND>
+__device__ __forceinline__ RowGate row_gate(const GateConsts& gc, float tau, float isg) {
+  if constexpr (KIND == 0) return {1.f, -tau};
+  else if constexpr (KIND == 1) return {isg, -tau * isg};
+  else return {1.f, -tau - gc.thr};
+}
+// Forward gate value and denominator term from the shifted score.
+template <int KIND>
+__device__ __forceinline__ void gate_fwd_shifted(const GateConsts& gc, float zt, float& g,
+                                                 float& dterm) {
+  if constexpr (KIND == 0) {
+    g = fminf(fmaxf(zt, 0.f), gc.clip_max);
+    dterm = g;
+  } else if constexpr (KIND == 1) {
+    const float z = fmaxf(zt, 0.f);
+    g = fmaf(-z, phi_tail(z), z);
+    dterm = g;
+  } else {
+    const float act = rcp_approx(1.f + __expf(-gc.sharp * zt));
+    const float inten = gc.eps + fminf(fmaxf(zt - gc.cut, 0.f), gc.max_int);
+    g = act * inten;
+    dterm = inten;
+  }
+}
+template <int KIND>
+__device__ __forceinline__ float gate_shifted(const GateConsts& gc, float s, float tau, float isg) {
+  if constexpr (KIND == 0) return s - tau;
+  else if constexpr (KIND == 1) return (s - tau) * isg;
+  else return s - tau - gc.thr;
+}
+// (g, A1, A2) from the shifted score; ds = A1 * (dp * xr) + A2 * dden.
+template <int KIND>
+__device__ __forceinline__ float gate_coeffs_shifted(const GateConsts& gc, float zt, float isg,
+                                                     float& a1, float& a2) {
+  float g;
+  if constexpr (KIND == 0) {
+    g = fminf(fmaxf(zt, 0.f), gc.clip_max);
+    a1 = (zt > 0.f && zt < gc.clip_max) ? 1.f : 0.f;
+    a2 = a1;
+  } else if constexpr (KIND == 1) {
+    const float z = fmaxf(zt, 0.f);
+    float phi, pdf;
+    phi_pdf(z, phi, pdf);
+    g = z * phi;
+    a1 = zt > 0.f ? fmaf(z, pdf, phi) * isg : 0.f;
+    a2 = a1;
+  } else {
+    const float act = rcp_approx(1.f + __expf(-gc.sharp * zt));
+    const float amr = zt - gc.cut;
+    const float inten = gc.eps + fminf(fmaxf(amr, 0.f), gc.max_int);
+    g = act * inten;
+    a2 = (amr > 0.f && amr < gc.max_int) ? 1.f : 0.f;
+    a1 = inten * gc.sharp * act * (1.f - act) + act * a2;
+  }
+  return g;
+}
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_half2(uint32_t w) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+
 // Wide variant: 256-column tiles on CTA pairs.  S and XR take 256 TMEM columns
 // each (all 512), one buffer per accumulator, so the overlap comes from the
 // order of work instead of double buffering: phase 1 turns S into gate values
 // (held in registers as bf16, 128 columns per thread) while the five-times-
 // longer XR MMAs of the same tile still run, and frees S for the next tile;
 // phase 2 multiplies by XR and stores.  The tensor core only idles while phase
-// 2 of tile t and the S MMAs of tile t+1 are both finished.  256-wide tiles
+// 2 of tile t outlasts the S MMAs of tile t+1, so phase 2 is kept short and the
+// gate arithmetic (one exponential, ~10 FP32 instructions per element for the
+// z * Phi(z) gate) sits in phase 1.  TMEM loads are software-pipelined: the
+// load of chunk q+1 is in flight while chunk q is processed.  256-wide tiles
 // halve the shared-memory bytes per FLOP of the 128-wide variant, whose
 // tensor-pipe utilisation is capped by shared-memory bandwidth.
 // Warp w: rows 32(w%4).., columns 128(w/4).. of the CTA's 128 x 256 tile.
-template <int KIND>
+// kSaveXr: the read scalars xr = x . read^T are written out as bf16 next to p,
+// so that the backward pass need not recompute them (BwdGateEpiXr).
+template <int KIND, bool kSaveXr>
 struct FwdGateEpiWide {
   static constexpr int kNumAcc = 2;
-  static constexpr int kNumOut = 1;
+  static constexpr int kNumOut = kSaveXr ? 2 : 1;
   static constexpr int kOutBufs = 2;
   static constexpr int kEpiWarps = 8;
   __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
   using Params = FwdGateParams;
+
+  template <bool kGeneral>
+  __device__ static __forceinline__ void phase1(const Params& p, uint32_t acc_s, int col0, int N,
+                                                bool row_ok, RowGate rg, uint32_t (&gp)[64],
+                                                float& den_acc, float& g_acc, int lane) {
+    float sb[2][32];
+    tmem_ld32(acc_s, sb[0]);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float* s = sb[q & 1];
+      tmem_ld_wait_dep32(s);
+      if (q < 3) tmem_ld32(acc_s + 32 * (q + 1), sb[(q + 1) & 1]);
+      const int cbase = col0 + 32 * q;
+      unsigned alive_bits = 0u;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float g, dt;
+        gate_fwd_shifted<KIND>(p.gc, fmaf(s[j], rg.a, rg.b), g, dt);
+        if constexpr (kGeneral) {
+          if (cbase + j >= N) { g = 0.f; dt = 0.f; }
+          if (p.unit_mask != nullptr && cbase + j < N) {
+            const float um = p.unit_mask[cbase + j];
+            g *= um;
+            dt *= um;
+          }
+          if (row_ok && g >= p.gc.dead_thr) alive_bits |= 1u << j;
+        }
+        den_acc += dt;
+        if constexpr (KIND == 2) g_acc += g;
+        s[j] = g;
+      }
+      if constexpr (kGeneral) {
+        if (p.alive != nullptr) {
+          const unsigned any = __reduce_or_sync(0xffffffffu, alive_bits);
+          if (((any >> lane) & 1u) && cbase + lane < N) p.alive[cbase + lane] = 1;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) gp[16 * q + j] = pack_bf16x2(s[2 * j], s[2 * j + 1]);
+    }
+  }
 
   template <int BN, class Ctl>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
@@ -344,67 +480,50 @@ struct FwdGateEpiWide {
     const bool row_ok = row < M;
     const float tau = row_ok ? p.tau[row] : 0.f;
     const float isg = row_ok ? p.inv_sigma[row] : 1.f;
+    const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
     float den_acc = 0.f, g_acc = 0.f;
     const bool general = (col0 + 128 > N) || p.unit_mask != nullptr || p.alive != nullptr;
     // ---- phase 1: scores -> gate values (bf16 pairs in registers)
     uint32_t gp[64];
     const uint32_t acc_s = ctl.wait(0) + c;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float s[32];
-      tmem_ld32(acc_s + 32 * q, s);
-      tmem_ld_wait();
-      const int cbase = col0 + 32 * q;
-      unsigned alive_bits = 0u;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float g, dt;
-        gate_fwd<KIND>(p.gc, s[j], tau, isg, g, dt);
-        if (general) {
-          if (cbase + j >= N) { g = 0.f; dt = 0.f; }
-          if (p.unit_mask != nullptr && cbase + j < N) {
-            const float um = p.unit_mask[cbase + j];
-            g *= um;
-            dt *= um;
-          }
-          if (row_ok && g >= p.gc.dead_thr) alive_bits |= 1u << j;
-        }
-        den_acc += dt;
-        g_acc += g;
-        s[j] = g;
-      }
-      if (general && p.alive != nullptr) {
-        const unsigned any = __reduce_or_sync(0xffffffffu, alive_bits);
-        if (((any >> lane) & 1u) && cbase + lane < N) p.alive[cbase + lane] = 1;
-      }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) gp[16 * q + j] = pack_bf16x2(s[2 * j], s[2 * j + 1]);
-    }
+    if (general) phase1<true>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
+    else phase1<false>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
     ctl.release(0);   // the next tile's score MMAs may start
-    // ---- phase 2: p = g * xr, two 64-column slabs
+    if constexpr (KIND != 2) g_acc = den_acc;
+    // ---- phase 2: p = g * xr, two 64-column slabs (and xr itself when it is kept)
     const uint32_t acc_xr = ctl.wait(1) + c;
+    float xb[2][32];
+    tmem_ld32(acc_xr, xb[0]);
 #pragma unroll
-    for (int sl = 0; sl < 2; ++sl) {
-      if (col0 + 64 * sl < N) {        // warp-uniform
-        st.wait_free<1>();
-        const uint32_t buf = st.buf(sl);
+    for (int i = 0; i < 4; ++i) {
+      const int sl = i >> 1, half = i & 1;
+      float* xr = xb[i & 1];
+      tmem_ld_wait_dep32(xr);
+      if (i < 3) tmem_ld32(acc_xr + 32 * (i + 1), xb[(i + 1) & 1]);
+      else ctl.release(1);   // last TMEM read of this tile
+      const bool in_range = col0 + 64 * sl < N;   // warp-uniform
+      uint32_t b_p, b_x;
+      if constexpr (kSaveXr) {
+        b_p = st.buf(0);
+        b_x = st.buf(1);
+        if (half == 0) st.wait_free<0>();         // both buffers have been read by their stores
+      } else {
+        b_p = st.buf(sl);
+        b_x = 0;
+        if (half == 0) st.wait_free<1>();
+      }
+      if constexpr (kSaveXr) stage_bf16_32(st, b_x, 4 * half, xr);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float xr[32];
-          tmem_ld32(acc_xr + 64 * sl + 32 * half, xr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const __nv_bfloat162 g2 =
-                *reinterpret_cast<const __nv_bfloat162*>(&gp[32 * sl + 16 * half + j]);
-            const float2 gf = __bfloat1622float2(g2);
-            xr[2 * j] *= gf.x;
-            xr[2 * j + 1] *= gf.y;
-          }
-          stage_bf16_32(st, buf, 4 * half, xr);
-        }
-        if (sl == 1 || col0 + 64 >= N) ctl.release(1);   // last TMEM read of this tile
-        st.flush(&maps[0], buf, col0 + 64 * sl, r0, false, true);
+      for (int j = 0; j < 16; ++j) {
+        const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gp[16 * i + j]);
+        const float2 gf = __bfloat1622float2(g2);
+        xr[2 * j] *= gf.x;
+        xr[2 * j + 1] *= gf.y;
+      }
+      stage_bf16_32(st, b_p, 4 * half, xr);
+      if (half == 1) {
+        st.flush(&maps[0], b_p, col0 + 64 * sl, r0, false, in_range);
+        if constexpr (kSaveXr) st.flush(&maps[1], b_x, col0 + 64 * sl, r0, false, in_range);
       }
     }
     if (row_ok) {
@@ -566,60 +685,6 @@ struct BwdGateEpi {
 // its 128 columns as fp16 pairs (64 registers) and re-evaluates the gate
 // coefficients from it in phase 2.  c1 lives in the ds output buffer: B reads
 // a slab's c1 values before it stores ds over them.
-template <int KIND>
-__device__ __forceinline__ float gate_shifted(const GateConsts& gc, float s, float tau, float isg) {
-  if constexpr (KIND == 0) return s - tau;
-  else if constexpr (KIND == 1) return (s - tau) * isg;
-  else return s - tau - gc.thr;
-}
-// (g, A1, A2) from the shifted score; ds = A1 * (dp * xr) + A2 * dden.
-template <int KIND>
-__device__ __forceinline__ float gate_coeffs_shifted(const GateConsts& gc, float zt, float isg,
-                                                     float& a1, float& a2) {
-  float g;
-  if constexpr (KIND == 0) {
-    g = fminf(fmaxf(zt, 0.f), gc.clip_max);
-    a1 = (zt > 0.f && zt < gc.clip_max) ? 1.f : 0.f;
-    a2 = a1;
-  } else if constexpr (KIND == 1) {
-    const float z = fmaxf(zt, 0.f);
-    float phi, pdf;
-    phi_pdf(z, phi, pdf);
-    g = z * phi;
-    a1 = zt > 0.f ? fmaf(z, pdf, phi) * isg : 0.f;
-    a2 = a1;
-  } else {
-    const float act = rcp_approx(1.f + __expf(-gc.sharp * zt));
-    const float amr = zt - gc.cut;
-    const float inten = gc.eps + fminf(fmaxf(amr, 0.f), gc.max_int);
-    g = act * inten;
-    a2 = (amr > 0.f && amr < gc.max_int) ? 1.f : 0.f;
-    a1 = inten * gc.sharp * act * (1.f - act) + act * a2;
-  }
-  return g;
-}
-// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros.
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.wait_all;" ::: "memory");
-}
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-__device__ __forceinline__ float2 unpack_half2(uint32_t w) {
-  return __half22float2(*reinterpret_cast<const __half2*>(&w));
-}
-
 struct BwdWideParams {
   const float* tau;        // [T]
   const float* inv_sigma;  // [T]
@@ -751,6 +816,173 @@ struct BwdGateEpiWide {
   }
 };
 
+// ------------------------------------- backward gate kernel on saved read scalars
+// When the forward pass kept xr = x . read^T (bf16 [T, U], FwdGateEpiWide with
+// kSaveXr), the backward gate step is ONE 256-wide launch with two accumulators:
+//   S = h . emb^T (K = d_route)  and  DP = dy . write^T (K = d_model),
+// i.e. neither the XR product nor a second pass over S is recomputed.
+//   phase 1 (while the DP MMAs of the tile run): S -> (g, A1[, A2]) kept as one
+//            bf16 pair per element in registers; p = g * xr is staged and stored;
+//            S is released for the next tile.
+//   phase 2 (short): dxr = DP * g,  ds = A1 * (DP * xr) + A2 * dden,  dtau.
+// The xr rows of the tile are fetched into two staging buffers with 16-byte
+// asynchronous copies before phase 1 and stay there until phase 2 overwrites
+// them, chunk by chunk, with ds (a thread reads its own chunk first).
+struct BwdXrParams {
+  const float* tau;        // [T]
+  const float* inv_sigma;  // [T]
+  const float* dden;       // [T]
+  float* dtau_sum;         // [T] += -sum_U ds
+  const __nv_bfloat16* xr; // [T, ldxr] read scalars saved by the forward pass
+  long long ldxr;
+  GateConsts gc;
+};
+
+template <int KIND>
+struct BwdGateEpiXr {
+  static constexpr int kNumAcc = 2;
+  static constexpr int kNumOut = 3;    // p, dxr, ds
+  static constexpr int kOutBufs = 3;   // 0: p / dxr staging, 1 and 2: xr -> ds of slab 0 and 1
+  static constexpr int kEpiWarps = 8;
+  __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
+  using Params = BwdXrParams;
+
+  // 16 bf16 values of this thread's row: 16-byte chunks k0 and k0 + 1 of a staged slab
+  __device__ static __forceinline__ void load16(uint32_t slab, int lane, int k0, float* out) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const uint4 u = ld_shared_v4(slab + lane * 128 + (((k0 + k) ^ (lane & 7)) << 4));
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        out[8 * k + 2 * e] = f.x;
+        out[8 * k + 2 * e + 1] = f.y;
+      }
+    }
+  }
+
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
+    static_assert(BN == 256, "two 64-column slabs per warp");
+    const int r0 = m0 + (warp & 3) * 32;
+    const int c = (warp >> 2) * 128;
+    const int col0 = n0 + c;
+    if (r0 >= M || col0 >= N) { ctl.skip(); return; }  // warp-uniform
+    const int row = r0 + lane;
+    const bool row_ok = row < M;
+    const float tau = row_ok ? p.tau[row] : 0.f;
+    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
+    const float dden = row_ok ? p.dden[row] : 0.f;
+    const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
+    const bool tail = col0 + 128 > N;
+    const uint32_t b_io = st.buf(0);
+
+    // ---- fetch the tile's xr rows (32 x 64 bf16 per slab; 8 lanes per row, coalesced)
+    st.wait_free<0>();                          // the previous tile's stores have read all buffers
+    {
+      const int ch = lane & 7;
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) {
+        const int colS = col0 + 64 * sl + ch * 8;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int rr = it * 4 + (lane >> 3);
+          const bool ok = r0 + rr < M && colS < p.ldxr;
+          const __nv_bfloat16* src = ok ? p.xr + static_cast<size_t>(r0 + rr) * p.ldxr + colS : p.xr;
+          cp_async_16(st.buf(1 + sl) + rr * 128 + ((ch ^ (rr & 7)) << 4), src, ok ? 16 : 0);
+        }
+      }
+    }
+
+    // ---- phase 1: S -> (g, A1) pairs; p = g * xr.  For the two-stage gate A2
+    // (0 or 1) rides in the sign of g, which is never negative itself.
+    uint32_t ga[128];
+    {
+      const uint32_t acc_s = ctl.wait(0) + c;
+      float sb[2][16];
+      tmem_ld16(acc_s, sb[0]);
+      cp_async_wait_all();                      // issued a whole MMA segment ago
+      __syncwarp();
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float* s = sb[q & 1];
+        tmem_ld_wait_dep16(s);
+        if (q < 7) tmem_ld16(acc_s + 16 * (q + 1), sb[(q + 1) & 1]);
+        else ctl.release(0);                    // the next tile's score MMAs may start
+        const int sl = q >> 2, k0 = 2 * (q & 3);
+        float xr[16];
+        load16(st.buf(1 + sl), lane, k0, xr);
+        if ((q & 3) == 0 && sl == 1) st.wait_free<0>();   // p of slab 0 has left the staging buffer
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float a1, a2;
+          float g = gate_coeffs_shifted<KIND>(p.gc, fmaf(s[j], rg.a, rg.b), isg, a1, a2);
+          xr[j] *= g;                           // p
+          if constexpr (KIND == 2) {
+            if (a2 != 0.f) g = -g;
+          }
+          ga[16 * q + j] = pack_bf16x2(g, a1);
+        }
+        stage_bf16_16(st, b_io, k0, xr);
+        if ((q & 3) == 3) st.flush(&maps[0], b_io, col0 + 64 * sl, r0, false, col0 + 64 * sl < N);
+      }
+    }
+
+    // ---- phase 2: DP
+    float dtau_acc = 0.f;
+    {
+      const uint32_t acc_dp = ctl.wait(1) + c;
+      float db[2][16];
+      tmem_ld16(acc_dp, db[0]);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float* dp = db[q & 1];
+        tmem_ld_wait_dep16(dp);
+        if (q < 7) tmem_ld16(acc_dp + 16 * (q + 1), db[(q + 1) & 1]);
+        else ctl.release(1);                    // last TMEM read of this tile
+        const int sl = q >> 2, k0 = 2 * (q & 3);
+        const uint32_t b_x = st.buf(1 + sl);
+        float xr[16];
+        load16(b_x, lane, k0, xr);
+        if ((q & 3) == 0) {
+          // the staging buffer's previous store (p of slab 1, then dxr of slab 0) has been read;
+          // for slab 1 the ds store of slab 0 may still be pending
+          if (sl == 0) st.wait_free<0>();
+          else st.wait_free<1>();
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const uint32_t w = ga[16 * q + j];
+          float g = __uint_as_float(w << 16);
+          const float a1 = __uint_as_float(w & 0xffff0000u);
+          float d;
+          if constexpr (KIND == 2) {
+            const float a2 = g < 0.f ? 1.f : 0.f;
+            g = fabsf(g);
+            d = fmaf(a1, dp[j] * xr[j], a2 * dden);
+          } else {
+            d = a1 * fmaf(dp[j], xr[j], dden);
+          }
+          if (tail && col0 + 16 * q + j >= N) d = 0.f;
+          dtau_acc -= d;
+          xr[j] = d;                            // ds
+          dp[j] *= g;                           // dxr
+        }
+        stage_bf16_16(st, b_io, k0, dp);
+        stage_bf16_16(st, b_x, k0, xr);
+        if ((q & 3) == 3) {
+          const bool in_range = col0 + 64 * sl < N;
+          st.flush(&maps[1], b_io, col0 + 64 * sl, r0, false, in_range);
+          st.flush(&maps[2], b_x, col0 + 64 * sl, r0, false, in_range);
+        }
+      }
+    }
+    if (row_ok) atomicAdd(p.dtau_sum + row, dtau_acc);
+  }
+};
+
 // ----------------------------------------------------------- host launchers
 struct OperandDesc {
   const void* ptr;
@@ -781,11 +1013,6 @@ static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t
   gp.m_tiles = (gp.M + kBlockM * kCtas - 1) / (kBlockM * kCtas);
   gp.n_tiles = (gp.N + BN - 1) / BN;
   gp.n_fastest = gp.n_tiles <= gp.m_tiles ? 1 : 0;
-  {
-    static int dbg = -1;
-    if (dbg < 0) { const char* e = getenv("DSB_DBG"); dbg = e ? atoi(e) : 0; }
-    gp.dbg = dbg;
-  }
   const long long total = static_cast<long long>(gp.m_tiles) * gp.n_tiles;
   if (total <= 0) return 0;
   const int units = sm_count() / kCtas;
@@ -973,7 +1200,7 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   gp.status = status;
   rc = make_out_tmap(&gp.tma_out[0], C, M, N, ldc, c_is_bf16 ? 2 : 4);
   if (rc) return 300 + rc;
-  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, block_n >> 16, 0};
+  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, 0, 0};
   if (accumulate && !c_is_bf16 && bias == nullptr) {
     // few output tiles but a long K (pool gradients of a small unit shard): cut K so
     // that every SM pair has work; the splits meet in the fp32 reduce-add epilogue
@@ -1003,9 +1230,9 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
                                 const float* tau, const float* inv_sigma, float* den_sum,
                                 float* gate_sum, unsigned char* alive, const float* unit_mask,
                                 const DsbGate* gate, int* status, cudaStream_t stream) {
-  return dsb_srw_fwd_gate_gather(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, tau,
-                                 inv_sigma, den_sum, gate_sum, alive, unit_mask, gate, nullptr,
-                                 status, stream);
+  return dsb_srw_fwd_gate_xr(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, nullptr, 0,
+                             tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, gate, nullptr,
+                             status, stream);
 }
 
 extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void* emb,
@@ -1016,12 +1243,44 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
                                        unsigned char* alive, const float* unit_mask,
                                        const DsbGate* gate, const DsbGather* gather, int* status,
                                        cudaStream_t stream) {
+  return dsb_srw_fwd_gate_xr(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, nullptr, 0,
+                             tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, gate, gather,
+                             status, stream);
+}
+
+extern "C" int dsb_srw_wide_tiles(int U) {
+  return (use_cta_pairs() && use_wide_gate() && U >= 512) ? 1 : 0;
+}
+
+namespace dsb {
+template <bool kSaveXr>
+static int launch_fwd_wide(GemmParams<FwdGateParams>& gp, int kind, bool fused, cudaStream_t stream) {
+  if (fused) {
+    if (kind == 0) return launch_engine_gather<256, FwdGateEpiWide<0, kSaveXr>>(gp, stream);
+    if (kind == 1) return launch_engine_gather<256, FwdGateEpiWide<1, kSaveXr>>(gp, stream);
+    return launch_engine_gather<256, FwdGateEpiWide<2, kSaveXr>>(gp, stream);
+  }
+  if (kind == 0) return launch_engine_impl<256, FwdGateEpiWide<0, kSaveXr>, 2>(gp, stream);
+  if (kind == 1) return launch_engine_impl<256, FwdGateEpiWide<1, kSaveXr>, 2>(gp, stream);
+  return launch_engine_impl<256, FwdGateEpiWide<2, kSaveXr>, 2>(gp, stream);
+}
+}  // namespace dsb
+
+extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
+                                   const void* x, long long ldx, const void* read, long long ldr,
+                                   int T, int U, int r, int D, void* p_out, long long ldp,
+                                   void* xr_out, long long ldxr, const float* tau,
+                                   const float* inv_sigma, float* den_sum, float* gate_sum,
+                                   unsigned char* alive, const float* unit_mask,
+                                   const DsbGate* gate, const DsbGather* gather, int* status,
+                                   cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   constexpr int BN = 128;
   GemmParams<FwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
   // 256-wide tiles (CTA pairs only) once the pool is wide enough to fill the machine with them
-  const bool wide = use_cta_pairs() && use_wide_gate() && U >= 512;
+  const bool wide = dsb_srw_wide_tiles(U) != 0;
+  if (xr_out != nullptr && !wide) return 704;   // only the wide kernel writes the read scalars
   const int brows = wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
@@ -1035,6 +1294,7 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
   gp.N = U;
   gp.status = status;
   rc = make_out_tmap(&gp.tma_out[0], p_out, T, U, ldp, 2);
+  if (xr_out != nullptr) rc |= make_out_tmap(&gp.tma_out[1], xr_out, T, U, ldxr, 2);
   if (rc) return 300 + rc;
   gp.epi = {tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, make_gc(gate)};
   const bool fused = gather != nullptr && gather->n_ranks > 1;
@@ -1042,23 +1302,67 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
     if (!use_cta_pairs()) return 702;
     rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
     if (rc) return rc;
-    if (wide) {
-      if (gate->kind == 0) return launch_engine_gather<256, FwdGateEpiWide<0>>(gp, stream);
-      if (gate->kind == 1) return launch_engine_gather<256, FwdGateEpiWide<1>>(gp, stream);
-      return launch_engine_gather<256, FwdGateEpiWide<2>>(gp, stream);
-    }
+  }
+  if (wide) {
+    return xr_out != nullptr ? launch_fwd_wide<true>(gp, gate->kind, fused, stream)
+                             : launch_fwd_wide<false>(gp, gate->kind, fused, stream);
+  }
+  if (fused) {
     if (gate->kind == 0) return launch_engine_gather<BN, FwdGateEpi<0>>(gp, stream);
     if (gate->kind == 1) return launch_engine_gather<BN, FwdGateEpi<1>>(gp, stream);
     return launch_engine_gather<BN, FwdGateEpi<2>>(gp, stream);
   }
-  if (wide) {
-    if (gate->kind == 0) return launch_engine_impl<256, FwdGateEpiWide<0>, 2>(gp, stream);
-    if (gate->kind == 1) return launch_engine_impl<256, FwdGateEpiWide<1>, 2>(gp, stream);
-    return launch_engine_impl<256, FwdGateEpiWide<2>, 2>(gp, stream);
-  }
   if (gate->kind == 0) return launch_engine<BN, FwdGateEpi<0>>(gp, stream);
   if (gate->kind == 1) return launch_engine<BN, FwdGateEpi<1>>(gp, stream);
   return launch_engine<BN, FwdGateEpi<2>>(gp, stream);
+}
+
+// Backward gate step from saved read scalars (see BwdGateEpiXr): one launch,
+// S = h.emb^T and DP = dy.write^T.  With a gather, the kernel pulls the peers'
+// rows of every listed tensor (the caller lists h, dy and, for the GEMMs that
+// follow, x) under one epoch.
+extern "C" int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
+                                   const void* dy, long long lddy, const void* write,
+                                   long long ldw, const void* xr, long long ldxr, int T, int U,
+                                   int r, int D, void* p_out, void* dxr_out, void* ds_out,
+                                   long long ld_out, const float* tau, const float* inv_sigma,
+                                   const float* dden, float* dtau_sum, const DsbGate* gate,
+                                   const DsbGather* gather, int* status, cudaStream_t stream) {
+  if (T <= 0 || U <= 0) return 0;
+  if (!dsb_srw_wide_tiles(U)) return 704;
+  if (xr == nullptr || ldxr < U || (ldxr & 7) != 0 || (reinterpret_cast<uintptr_t>(xr) & 15) != 0)
+    return 705;
+  GemmParams<BwdXrParams> gp;
+  memset(&gp, 0, sizeof(gp));
+  const int brows = 128;
+  int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
+  rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
+  rc |= fill_operand(&gp.tma_a[1], {dy, 0, lddy}, T, D, kBlockM);
+  rc |= fill_operand(&gp.tma_b[1], {write, 0, ldw}, U, D, brows);
+  if (rc) return 100 + rc;
+  gp.seg[0] = {(r + kBlockK - 1) / kBlockK, 0, 0, 0};
+  gp.seg[1] = {(D + kBlockK - 1) / kBlockK, 1, 0, 0};
+  gp.n_seg = 2;
+  gp.M = T;
+  gp.N = U;
+  gp.status = status;
+  rc = make_out_tmap(&gp.tma_out[0], p_out, T, U, ld_out, 2);
+  rc |= make_out_tmap(&gp.tma_out[1], dxr_out, T, U, ld_out, 2);
+  rc |= make_out_tmap(&gp.tma_out[2], ds_out, T, U, ld_out, 2);
+  if (rc) return 300 + rc;
+  gp.epi = {tau, inv_sigma, dden, dtau_sum, reinterpret_cast<const __nv_bfloat16*>(xr), ldxr,
+            make_gc(gate)};
+  const bool fused = gather != nullptr && gather->n_ranks > 1;
+  if (fused) {
+    rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
+    if (rc) return rc;
+    if (gate->kind == 0) return launch_engine_gather<256, BwdGateEpiXr<0>>(gp, stream);
+    if (gate->kind == 1) return launch_engine_gather<256, BwdGateEpiXr<1>>(gp, stream);
+    return launch_engine_gather<256, BwdGateEpiXr<2>>(gp, stream);
+  }
+  if (gate->kind == 0) return launch_engine_impl<256, BwdGateEpiXr<0>, 2>(gp, stream);
+  if (gate->kind == 1) return launch_engine_impl<256, BwdGateEpiXr<1>, 2>(gp, stream);
+  return launch_engine_impl<256, BwdGateEpiXr<2>, 2>(gp, stream);
 }
 
 extern "C" int dsb_srw_bwd_gate(const void* h, long long ldh, const void* emb, long long lde,
@@ -1179,7 +1483,7 @@ extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, con
   gp.M = M;
   gp.N = N;
   gp.status = status;
-  gp.epi = {alpha, row_scale, nullptr, out_is_bf16 ? 1 : 0, 0, 0, rows_per_rank, my_rank};
+  gp.epi = {alpha, row_scale, nullptr, out_is_bf16 ? 1 : 0, 0, rows_per_rank, my_rank};
   // Every rank starts with the rows of a different owner (rank+1, rank+2, ..., itself last), so
   // at any moment the ranks store to distinct peers instead of all converging on one GPU.
   const int tile_m = (use_cta_pairs() ? 2 : 1) * kBlockM;

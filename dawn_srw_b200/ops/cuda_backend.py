@@ -118,6 +118,58 @@ def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m
 
 
+class _XrBudget:
+    """Accounting for the read scalars ``xr = x . read^T`` that forward passes keep
+    for their backward pass (bf16 [T, U] per route and layer).  Keeping them
+    removes the largest recomputed product from the backward gate step; the
+    budget bounds how much device memory that may take.  ``limit`` defaults to
+    half of the device memory (``DSB_XR_BUDGET_GB`` overrides it, 0 disables)."""
+
+    def __init__(self):
+        self.limit = {}
+        self.live = {}
+
+    def _limit(self, dev: torch.device) -> int:
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
+        if key not in self.limit:
+            import os
+            env = os.environ.get("DSB_XR_BUDGET_GB")
+            if env is not None:
+                self.limit[key] = int(float(env) * (1 << 30))
+            else:
+                self.limit[key] = torch.cuda.get_device_properties(key).total_memory // 2
+            self.live[key] = 0
+        return key
+
+    def acquire(self, dev: torch.device, nbytes: int) -> bool:
+        key = self._limit(dev)
+        if self.live[key] + nbytes > self.limit[key]:
+            return False
+        self.live[key] += nbytes
+        return True
+
+    def release(self, key: int, nbytes: int) -> None:
+        self.live[key] = max(0, self.live.get(key, 0) - nbytes)
+
+
+XR_BUDGET = _XrBudget()
+
+
+def _alloc_saved_xr(dev, T: int, Up: int, U: int, wanted: bool):
+    """bf16 [T, Up] buffer for the read scalars of one route if the pool runs on
+    the wide kernels, gradients are being recorded and the budget allows it."""
+    if not wanted or not torch.is_grad_enabled() or not ext().srw_wide_tiles(U):
+        return None
+    nbytes = T * Up * 2
+    if not XR_BUDGET.acquire(dev, nbytes):
+        return None
+    xr = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    import weakref
+    weakref.finalize(xr, XR_BUDGET.release, key, nbytes)
+    return xr
+
+
 def gemm(a, a_mn, b, b_mn, *, out=None, out_dtype=torch.float32, accumulate=False, alpha=1.0,
          row_scale=None, bias=None, block_n: Optional[int] = None):
     """out[M,N] (=|+=) alpha * row_scale * A.B^T + bias on the tcgen05 engine.
@@ -270,26 +322,36 @@ class _PoolMatVecFn(torch.autograd.Function):
         return hd.emb[:U].float().t() @ dm, torch.zeros_like(dm[:1]), None, None
 
 
-def _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den, hd, spec, U):
+def _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den, hd, spec, U, xr=None):
     """Backward of one local SRW route given the bf16 output cotangent ``dy``
     (already scaled by whatever multiplied ``p . write``) and the cotangent of
-    the per-token denominator: the gate step (recomputes S and XR, adds
-    DP = dy . write^T, emits p, dxr, ds, dtau) and five engine GEMMs.  Pool
-    gradients are accumulated into the holder's fp32 buffers.
+    the per-token denominator: the gate step and five engine GEMMs.  With the
+    read scalars ``xr`` kept by the forward pass the gate step is one launch
+    (S and DP = dy . write^T; p overwrites ``xr`` in place); otherwise S and XR
+    are recomputed.  Either way it emits p, dxr, ds and dtau.  Pool gradients
+    are accumulated into the holder's fp32 buffers.
     Returns (dx bf16, dh bf16, dtau, d_inv_sigma or None)."""
     e = ext()
     dev = x_bf.device
     T = x_bf.shape[0]
     Up = _round_up(U, 8)
-    p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
-    dxr = torch.empty_like(p)
-    ds = torch.empty_like(p)
     dtau = torch.zeros(T, dtype=torch.float32, device=dev)
-    dsz = torch.zeros(T, dtype=torch.float32, device=dev)
     emb, read, write = hd.emb[:U], hd.read[:U], hd.write[:U]
-    count_launches(2)
-    e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den, dtau, dsz,
-                   _gate_list(spec), status_word(dev))
+    if xr is not None:
+        p = xr
+        dxr = torch.empty_like(p)
+        ds = torch.empty_like(p)
+        count_launches(1)
+        e.srw_bwd_gate_xr(h_bf, emb, dy, write, xr, p, dxr, ds, tau, inv_sd, d_den, dtau,
+                          _gate_list(spec), status_word(dev), [], [], [], 0, 0, None, 0)
+    else:
+        p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
+        dxr = torch.empty_like(p)
+        ds = torch.empty_like(p)
+        dsz = torch.zeros(T, dtype=torch.float32, device=dev)
+        count_launches(2)
+        e.srw_bwd_gate(h_bf, emb, x_bf, read, dy, write, p, dxr, ds, tau, inv_sd, d_den, dtau, dsz,
+                       _gate_list(spec), status_word(dev))
     pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]
     gemm(pv, True, dy, True, out=hd.g_write[:U], accumulate=True)       # p^T dy
     gemm(dxrv, True, x_bf, True, out=hd.g_read[:U], accumulate=True)    # dxr^T x
@@ -351,13 +413,15 @@ class _SRWRouteScaledFn(torch.autograd.Function):
         Up = _round_up(U, 8)
         p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)           # scratch
         den = torch.zeros(T, dtype=torch.float32, device=dev)
+        xr = _alloc_saved_xr(dev, T, Up, U, getattr(holder, "keep_xr", True) and unit_mask is None)
         count_launches(2)
-        e.srw_fwd_gate(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, tau, inv_sd, den, None,
-                       alive, unit_mask, _gate_list(spec), status_word(dev))
+        e.srw_fwd_gate_xr(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, xr, tau, inv_sd, den,
+                          alive, unit_mask, _gate_list(spec), status_word(dev), [], 0, 0, None, 0)
         rs = (scale.detach().float() / den.clamp(min=1.0)).contiguous()
         y = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32, row_scale=rs)
         ctx.save_for_backward(x_bf, h_bf, tau, inv_sd, y, den, rs, scale)
         ctx.holder, ctx.spec, ctx.U = holder, spec, U
+        ctx.xr = xr
         return y, den
 
     @staticmethod
@@ -372,8 +436,9 @@ class _SRWRouteScaledFn(torch.autograd.Function):
             d_den = d_den + d_den_ext.float()
         d_scale = (rowdot.sum() / scale.detach().float()).reshape(scale.shape).to(scale.dtype) \
             if ctx.needs_input_grad[10] else None
+        xr, ctx.xr = ctx.xr, None
         dx, dh, dtau, d_isd = _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den.contiguous(), hd,
-                                                   spec, U)
+                                                   spec, U, xr)
         return (dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None, None,
                 d_scale)
 
@@ -566,9 +631,12 @@ class CudaBackend:
     name = "sm100a"
     compute_dtype = torch.bfloat16
 
-    def __init__(self, diag_chunk: int = 12500, fused_comm: bool = True):
+    def __init__(self, diag_chunk: int = 12500, fused_comm: bool = True, keep_xr: bool = True):
         ext()
         self.diag_chunk = diag_chunk
+        # keep the read scalars x . read^T of every route for the backward pass while the
+        # budget (XR_BUDGET) lasts; False always recomputes them
+        self.keep_xr = keep_xr
         self._wcache = {}
         self.fused_comm = fused_comm     # in-kernel all-gather / reduce-scatter when sharded
         self._comm = {}
@@ -643,6 +711,7 @@ class CudaBackend:
         pctx = pctx or ParallelCtx()
         U = pctx.n_valid if pctx.n_valid is not None else emb.shape[0]
         pool = CudaPool(None, None, None)
+        pool.keep_xr = self.keep_xr
         anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, pool, spec.normalize_pool, U)
         gram = C.sum_over_shards(gram, pctx.shard_group)
         esum = C.sum_over_shards(esum, pctx.shard_group)

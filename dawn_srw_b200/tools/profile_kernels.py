@@ -5,7 +5,8 @@
         [--d-model 1280] [--d-route 256] [--kind 1] [--iters 2]
 
 Per iteration, in this order: forward gate kernel, write GEMM (p . write),
-backward gate kernel, pool-gradient GEMM (p^T . dy, reduce-add).  The default
+backward gate step, pool-gradient GEMM (p^T . dy, reduce-add); each is timed
+with CUDA events (second half of the iterations) and printed with its TFLOP/s.  The default
 shape holds < 2 GB on the device and its operands exceed the 126 MB L2, so an
 ``ncu --set full`` capture of one iteration finishes in about a minute:
 
@@ -60,6 +61,8 @@ def main(argv=None):
     ap.add_argument("--d-route", type=int, default=256)
     ap.add_argument("--kind", type=int, default=1)
     ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--recompute", action="store_true",
+                    help="backward gate step without kept read scalars (recomputes S and XR)")
     ap.add_argument("--attention", action="store_true")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--heads", type=int, default=16)
@@ -79,22 +82,48 @@ def main(argv=None):
     rn = lambda *s: torch.randn(*s, device=dev, generator=g)
     h, x, dy = rn(T, r).bfloat16(), rn(T, D).bfloat16(), (rn(T, D) * 0.1).bfloat16()
     emb, read, write = (nz(rn(U, d), dim=-1).bfloat16() for d in (r, D, D))
-    p = torch.empty(T, U, dtype=torch.bfloat16, device=dev)
+    Up = (U + 7) // 8 * 8
+    p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
     dxr, ds = torch.empty_like(p), torch.empty_like(p)
+    keep = bool(e.srw_wide_tiles(U)) and not args.recompute
+    xr = torch.empty_like(p) if keep else None
     den, dtau, dsz = (torch.zeros(T, device=dev) for _ in range(3))
     dden = torch.zeros(T, device=dev)
     tau = torch.full((T,), 1.0, device=dev)
     isd = torch.full((T,), 1.0, device=dev)
     raw = torch.empty(T, D, device=dev)
     gw = torch.zeros(U, D, device=dev)
-    for _ in range(args.iters):
-        e.srw_fwd_gate(h, emb, x, read, p, tau, isd, den, None, None, None, gl, st)
-        CB.gemm(p, False, write, True, out=raw)
-        e.srw_bwd_gate(h, emb, x, read, dy, write, p, dxr, ds, tau, isd, dden, dtau, dsz, gl, st)
-        CB.gemm(p, True, dy, True, out=gw, accumulate=True)
-    torch.cuda.synchronize()
+    names = ["fwd_gate", "write_gemm", "bwd_gate", "dwrite_gemm"]
+    flops = [2.0 * T * U * (r + D), 2.0 * T * U * D,
+             2.0 * T * U * (r + D) * (1 if keep else 2), 2.0 * T * U * D]
+    acc = [0.0] * 4
+    for it in range(args.iters):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        ev[0].record()
+        e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau, isd, den, None, None, gl, st, [], 0, 0, None, 0)
+        ev[1].record()
+        CB.gemm(p[:, :U], False, write, True, out=raw)
+        ev[2].record()
+        if keep:
+            # p overwrites the kept read scalars in place, as in training
+            e.srw_bwd_gate_xr(h, emb, dy, write, xr, xr, dxr, ds, tau, isd, dden, dtau, gl, st,
+                              [], [], [], 0, 0, None, 0)
+        else:
+            e.srw_bwd_gate(h, emb, x, read, dy, write, p, dxr, ds, tau, isd, dden, dtau, dsz, gl, st)
+        ev[3].record()
+        CB.gemm(p[:, :U], True, dy, True, out=gw, accumulate=True)
+        ev[4].record()
+        torch.cuda.synchronize()
+        if it >= args.iters // 2:                       # the first half warms up
+            for k in range(4):
+                acc[k] += ev[k].elapsed_time(ev[k + 1])
     CB.check_status()
-    print(f"ok: T={T} U={U} d={D} r={r} kind={args.kind} iters={args.iters}")
+    n = args.iters - args.iters // 2
+    print(f"ok: T={T} U={U} d={D} r={r} kind={args.kind} iters={args.iters} "
+          f"backward gate step: {'one launch on kept read scalars' if keep else 'recomputes S and XR'}")
+    for k in range(4):
+        ms = acc[k] / n
+        print(f"  {names[k]:12s} {ms:8.3f} ms  {flops[k] / ms / 1e9:7.0f} TFLOP/s")
     return 0
 
 

@@ -50,9 +50,22 @@ def _step_of(path: str) -> int:
     return int(m.group(1)) if m else -1
 
 
+def _shard_set_complete(path: str) -> bool:
+    """A sharded checkpoint ``<name>.shard0of<N>.pt`` counts only when all N
+    shard files are present (each is written atomically by its own rank, so a
+    job that died between two ranks' writes leaves an incomplete set)."""
+    m = re.search(r"^(.*)\.shard0of(\d+)(\.[^.]+)$", path)
+    if not m:
+        return True
+    base, n, ext = m.group(1), int(m.group(2)), m.group(3)
+    return all(os.path.exists(f"{base}.shard{k}of{n}{ext}") for k in range(n))
+
+
 def list_checkpoints(run_dir: str) -> List[str]:
-    files = [f for f in glob.glob(os.path.join(run_dir, "*.pt")) if ".shard" not in f
-             or ".shard0of" in f]
+    """Loadable checkpoints of a run folder: single files, and shard 0 of every
+    sharded checkpoint whose shard set is complete."""
+    files = [f for f in glob.glob(os.path.join(run_dir, "*.pt"))
+             if ".shard" not in f or (".shard0of" in f and _shard_set_complete(f))]
     return sorted(files)
 
 
@@ -80,14 +93,24 @@ def find_latest(checkpoint_dir: str) -> Optional[Tuple[str, str]]:
 
 
 def cleanup_old(run_dir: str, keep_last: int = 3) -> List[str]:
-    """Delete all but the newest ``keep_last`` step checkpoints."""
-    steps = [f for f in glob.glob(os.path.join(run_dir, "checkpoint_step*.pt"))]
+    """Delete all but the newest ``keep_last`` *complete* step checkpoints.
+    Steps newer than the newest complete one are left alone (other ranks may
+    still be writing their shard files); older incomplete sets are removed."""
     by_step: Dict[int, List[str]] = {}
-    for f in steps:
+    for f in glob.glob(os.path.join(run_dir, "checkpoint_step*.pt")):
         by_step.setdefault(_step_of(f), []).append(f)
+
+    def complete(files: List[str]) -> bool:
+        heads = [f for f in files if ".shard" not in f or ".shard0of" in f]
+        return bool(heads) and all(_shard_set_complete(f) for f in heads)
+    done = sorted(s for s, fs in by_step.items() if complete(fs))
+    keep = set(done[-keep_last:]) if keep_last > 0 else set()
+    newest_done = done[-1] if done else -1
     removed = []
-    for s in sorted(by_step)[:-keep_last] if keep_last > 0 else sorted(by_step):
-        for f in by_step[s]:
+    for s_, files in sorted(by_step.items()):
+        if s_ in keep or s_ > newest_done:
+            continue
+        for f in files:
             os.remove(f)
             removed.append(f)
     return removed

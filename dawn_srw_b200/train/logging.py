@@ -154,7 +154,7 @@ def build_train_record(step, epoch, metrics: Dict[str, Any], *, steps_per_sec, e
 
 
 def format_regular(rec: Dict[str, Any]) -> str:
-    g = lambda k, d=0.0: rec.get(k, d) if not isinstance(rec.get(k, d), list) else d
+    g = lambda k, d=0.0: d if rec.get(k) is None or isinstance(rec.get(k), list) else rec.get(k)
     lines = [
         f"[step {rec['step']:>7d} | ep {rec['epoch']}] loss {g('total_loss'):.4f} (ce {g('ce_loss'):.4f} "
         f"aux {g('aux_loss'):.4f} div {g('div_loss'):.4f} dead {g('dead_penalty'):.4f} "
@@ -179,7 +179,7 @@ def format_regular(rec: Dict[str, Any]) -> str:
 
 
 def format_analysis(rec: Dict[str, Any]) -> str:
-    g = lambda k, d=0.0: rec.get(k, d) if not isinstance(rec.get(k, d), list) else d
+    g = lambda k, d=0.0: d if rec.get(k) is None or isinstance(rec.get(k), list) else rec.get(k)
     lines = [
         f"  [analysis] skew a/k {g('attn_score_skew'):.3f}/{g('know_score_skew'):.3f}  "
         f"kurt a/k {g('attn_score_kurt'):.3f}/{g('know_score_kurt'):.3f}",

@@ -74,7 +74,10 @@ class Trainer:
         if total_steps is None:
             total_steps = max(1, t.num_epochs * (self.steps_per_epoch // k))
             if t.max_steps:
-                total_steps = min(total_steps, t.max_steps) if self.steps_per_epoch else t.max_steps
+                # max_steps counts micro-steps (like global_step, the log / val / checkpoint
+                # cadences and the reference's loop); the schedule runs on optimizer steps
+                horizon = max(1, t.max_steps // k)
+                total_steps = min(total_steps, horizon) if self.steps_per_epoch else horizon
         self.total_steps = total_steps
         warm = int(total_steps * t.warmup_ratio)
         self.schedule = lambda s: warmup_cosine(s, t.lr, warm, total_steps)
@@ -207,6 +210,10 @@ class Trainer:
     def save(self, name: str) -> Optional[str]:
         if self.run_dir is None:
             return None
+        # a kernel that gave up on a wait must surface before its results are written out
+        # (the per-step check reports one step late)
+        if hasattr(self.backend, "finish_run"):
+            self.backend.finish_run()
         t = self.topo
         writes = t.is_main or (t.pool_shards > 1 and t.dp_index == 0)
         if hasattr(self.optimizer, "gather_state"):
@@ -224,9 +231,21 @@ class Trainer:
         return path
 
     def resume(self, path: str) -> None:
-        blob = ckpt.load_checkpoint(path, self.model, self.optimizer,
-                                    shard_index=self.topo.shard_index,
-                                    shard_count=self.topo.pool_shards)
+        err = None
+        try:
+            blob = ckpt.load_checkpoint(path, self.model, self.optimizer,
+                                        shard_index=self.topo.shard_index,
+                                        shard_count=self.topo.pool_shards)
+        except Exception as e:       # missing / unreadable shard file on this rank
+            err, blob = e, None
+        if self.topo.world > 1:
+            # every rank learns whether all loads succeeded before anyone enters a collective
+            ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.topo.cpu_group)
+            if int(ok) == 0 and err is None:
+                raise RuntimeError(f"another rank could not load its part of {path}")
+        if err is not None:
+            raise err
         self.global_step = int(blob["step"])
         self.epoch = int(blob.get("epoch", 0))
         self.best_val_loss = float(blob.get("best_val_loss", float("inf")))
@@ -296,9 +315,17 @@ class Trainer:
                 m = self.train_step(ids, mask, want_diag=is_log or is_an)
                 self.heartbeat.beat(self.global_step)
                 self.step_in_epoch = local_step + 1
-                tl = float(m["total_loss"])                      # the per-step device->host read
-                if not math.isfinite(tl):
-                    raise NonFiniteLoss(f"non-finite total_loss {tl} at step {self.global_step}")
+                # the per-step device->host read.  The gradient norm is computed from the
+                # globally reduced gradients, so it is identical on every rank and non-finite
+                # on all of them as soon as one rank's loss is: all ranks leave together.
+                gn = m.get("grad_norm")
+                gn = gn.detach().float().reshape(()) if isinstance(gn, torch.Tensor) else \
+                    torch.tensor(float(gn or 0.0), device=self.device)
+                tl, gnv = torch.stack([m["total_loss"].detach().float().reshape(()),
+                                       gn.to(self.device)]).tolist()
+                if not (math.isfinite(tl) and math.isfinite(gnv)):
+                    raise NonFiniteLoss(f"non-finite total_loss {tl} / grad_norm {gnv} at step "
+                                        f"{self.global_step}")
                 v = m["valid_count"].double()
                 win += torch.stack([m["total_loss"].double() * v, m["ce_loss"].double() * v,
                                     m["correct"].double(), v])

@@ -132,6 +132,38 @@ def test_shard_consolidation(tmp_path):
         assert torch.equal(blob["params"][k], v), k
 
 
+def test_incomplete_shard_sets_are_not_resumed_from(tmp_path):
+    """A job that died between two ranks' shard writes leaves shard 0 of the
+    newest step without its siblings: auto-resume must fall back to the last
+    complete step, and retention must not delete that step."""
+    from dawn_srw_b200.parallel.topology import PoolShard
+    run = ck.new_run_dir(str(tmp_path), "spatial-r1-v4.0.1")
+    kw = dict(epoch=0, step_in_epoch=0, steps_per_epoch=10, best_val_loss=1.0, config={}, training_config={})
+    models = [DAWN(vocab_size=50, d_model=16, n_layers=1, n_heads=2, max_seq_len=8, d_route=4, n_qk=8,
+                   n_v=8, n_know=12, pool_shard=PoolShard(i, 2)) for i in range(2)]
+    for s in (10, 20):
+        for i, m in enumerate(models):
+            ck.save_checkpoint(os.path.join(run, f"checkpoint_step{s}.pt"), m, None, step=s,
+                               shard_index=i, shard_count=2, **kw)
+    # step 30: only shard 0 made it to disk
+    ck.save_checkpoint(os.path.join(run, "checkpoint_step30.pt"), models[0], None, step=30,
+                       shard_index=0, shard_count=2, **kw)
+    names = sorted(os.path.basename(f) for f in ck.list_checkpoints(run))
+    assert names == ["checkpoint_step10.shard0of2.pt", "checkpoint_step20.shard0of2.pt"]
+    _, latest = ck.find_latest(str(tmp_path))
+    assert os.path.basename(latest) == "checkpoint_step20.shard0of2.pt"
+    # rank 1 of the fallback step loads fine; the incomplete step would not
+    assert ck.load_checkpoint(latest, models[1], None, shard_index=1, shard_count=2)["step"] == 20
+    with pytest.raises(FileNotFoundError):
+        ck.load_checkpoint(os.path.join(run, "checkpoint_step30.pt"), models[1], None,
+                           shard_index=1, shard_count=2)
+    # retention keeps the newest complete step and does not touch the newer, unfinished one
+    removed = [os.path.basename(f) for f in ck.cleanup_old(run, keep_last=1)]
+    assert sorted(removed) == ["checkpoint_step10.shard0of2.pt", "checkpoint_step10.shard1of2.pt"]
+    assert os.path.exists(os.path.join(run, "checkpoint_step30.shard0of2.pt"))
+    assert os.path.basename(ck.find_latest(str(tmp_path))[1]) == "checkpoint_step20.shard0of2.pt"
+
+
 def test_fileio_local_and_url_paths(tmp_path):
     """The five file operations on local paths and on an fsspec URL (the
     in-process ``memory://`` filesystem stands in for a bucket)."""

@@ -104,6 +104,50 @@ def test_gate_kernels(cb, kind, dims):
     cb.check_status()
 
 
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("dims", [(300, 2504, 128, 384), (520, 4099, 64, 256), (260, 777, 64, 256),
+                                  (1000, 3000, 256, 1280), (700, 2600, 384, 2048)])   # 400M / 1B widths
+def test_gate_kernels_with_kept_read_scalars(cb, kind, dims):
+    """The forward kernel also writes xr = x . read^T; the backward gate step then
+    is one launch on S and DP that reads xr back (and may overwrite it with p)."""
+    from dawn_srw_b200.ops.gates import GateSpec, gate_backward, gate_forward
+    T, U, r, D = dims
+    dev = torch.device("cuda")
+    spec = GateSpec(kind=kind)
+    nz = torch.nn.functional.normalize
+    gen = torch.Generator(device=dev).manual_seed(T + U)
+    rn = lambda *s: torch.randn(*s, device=dev, generator=gen)
+    h, x = rn(T, r).bfloat16(), rn(T, D).bfloat16()
+    emb, read, write = (nz(rn(U, d), dim=-1).bfloat16() for d in (r, D, D))
+    s = h.float() @ emb.float().t()
+    mu, sd = s.mean(-1, keepdim=True), s.std(-1, unbiased=False, keepdim=True) + 1e-8
+    tau = mu + 0.3 * sd
+    g, dt, _ = gate_forward(spec, s, tau, sd)
+    xr_ref = x.float() @ read.float().t()
+    Up = (U + 7) // 8 * 8
+    p = torch.zeros(T, Up, device=dev, dtype=torch.bfloat16)
+    xr = torch.full((T, Up), float("nan"), device=dev, dtype=torch.bfloat16)
+    den = torch.zeros(T, device=dev)
+    e, st, gl = cb.ext(), cb.status_word(dev), cb._gate_list(spec)
+    assert e.srw_wide_tiles(U)
+    tau_c, isd_c = tau.squeeze(-1).contiguous(), (1 / sd).squeeze(-1).contiguous()
+    e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau_c, isd_c, den, None, None, gl, st, [], 0, 0, None, 0)
+    assert _rel(p[:, :U], g * xr_ref) < 6e-3 and _rel(xr[:, :U], xr_ref) < 4e-3
+    assert _rel(den, dt.sum(-1)) < 1e-4
+    dy = (rn(T, D) * 0.1).bfloat16()
+    dden = rn(T) * 0.01
+    dp = dy.float() @ write.float().t()
+    xr_q = xr[:, :U].float()                       # what the backward kernel actually reads
+    ds_ref, dtau_ref, _ = gate_backward(spec, s, tau, sd, dp * xr_q, dden[:, None])
+    dxr, ds = torch.zeros_like(p), torch.zeros_like(p)
+    dtau = torch.zeros(T, device=dev)
+    e.srw_bwd_gate_xr(h, emb, dy, write, xr, xr, dxr, ds, tau_c, isd_c, dden, dtau, gl, st,
+                      [], [], [], 0, 0, None, 0)            # p overwrites xr in place
+    assert _rel(xr[:, :U], g * xr_q) < 6e-3 and _rel(dxr[:, :U], dp * g) < 6e-3
+    assert _rel(ds[:, :U], ds_ref) < 8e-3 and _rel(dtau, dtau_ref.squeeze(-1)) < 4e-3
+    cb.check_status()
+
+
 @pytest.mark.parametrize("version", ["spatial-r1-v3.9.4", "spatial-r1-v4.0.1", "spatial-r1-v4.1"])
 @pytest.mark.parametrize("dims", [(300, 1, 1580, 128, 384), (256, 2, 777, 64, 256)])
 def test_srw_op_forward_backward_against_fp32_oracle(cb, version, dims):

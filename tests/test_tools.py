@@ -198,3 +198,44 @@ def test_bench_clock_csv_parsing():
     assert hot["reasons"] == ["hw_slowdown", "hw_thermal_slowdown"]
     assert bench.parse_clock_csv("") is None
     assert bench.ClockSampler(0).stop()["sm_mhz"] is None         # never started: neutral record
+
+
+def test_launcher_builds_the_command_and_runs_a_detached_job(tmp_path):
+    """tools/launch.py: dry run prints the torch.distributed.run line; a detached
+    one-rank CPU job trains the smoke config, writes its log and PID file, and a
+    second launch from the same place is refused while it is alive."""
+    import subprocess
+    import sys
+    import time
+    from dawn_srw_b200.tools import launch as Lh
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = os.path.join(root, "configs", "smoke_tiny_synthetic.yaml")
+    cmd = Lh.build_command(cfg, 8, 29511, True, ["--max-steps", "3"])
+    assert cmd[1:4] == ["-m", "torch.distributed.run", "--nnodes=1"]
+    assert "--nproc-per-node=8" in cmd and "127.0.0.1" in cmd and cmd[-3:] == ["--from-scratch", "--max-steps", "3"]
+    log = str(tmp_path / "train.log")
+    env = dict(os.environ, PYTHONPATH=root, CUDA_VISIBLE_DEVICES="")
+    base = [sys.executable, "-m", "dawn_srw_b200.tools.launch", "--log", log]
+    from helpers import free_port
+    r = subprocess.run(base + ["--config", cfg, "--gpus", "1", "--detach", "--from-scratch",
+                               "--master-port", str(free_port()), "--", "--max-steps", "3",
+                               "--no-startup-check", "--checkpoint-dir", str(tmp_path / "ck")],
+                       env=env, capture_output=True, text=True, cwd=root)
+    assert r.returncode == 0, r.stderr
+    assert os.path.exists(log + ".pid")
+    st = json.loads(subprocess.run(base + ["--status"], env=env, capture_output=True, text=True,
+                                   cwd=root).stdout)
+    assert st["pid"] > 0
+    deadline = time.time() + 240
+    while time.time() < deadline:
+        st = json.loads(subprocess.run(base + ["--status"], env=env, capture_output=True, text=True,
+                                       cwd=root).stdout)
+        if not st["alive"]:
+            break
+        time.sleep(1.0)
+    assert not st["alive"], open(log).read()[-2000:]
+    text = open(log).read()
+    assert '"final"' in text and "run_dir" in text, text[-2000:]
+    # nothing alive any more: --stop reports that it had nothing to do
+    out = subprocess.run(base + ["--stop"], env=env, capture_output=True, text=True, cwd=root).stdout
+    assert json.loads(out) == {"stopped": False}

@@ -70,6 +70,20 @@ def test_non_finite_loss_stops_training(tmp_path):
         tr.fit()
 
 
+def test_max_steps_counts_micro_steps_and_the_schedule_runs_on_optimizer_steps():
+    """With gradient accumulation k, max_steps micro-steps are max_steps / k
+    optimizer steps: the cosine schedule must end there (at 0.1 * lr), not
+    stretch over k times as many."""
+    cfg = tiny_config(max_steps=8, gradient_accumulation_steps=2, lr=1e-2, warmup_ratio=0.25)
+    tr = Trainer(cfg)
+    assert tr.total_steps == 4
+    tr.fit()
+    assert tr.global_step == 8 and tr.optimizer.count == 4
+    assert tr.schedule(0) == pytest.approx(1e-3)              # warm-up starts at 0.1 * lr
+    assert tr.schedule(tr.total_steps) == pytest.approx(1e-3)  # cosine has reached 0.1 * lr
+    assert tr.schedule(1) == pytest.approx(1e-2)              # one warm-up step of four
+
+
 def test_loss_decreases_on_a_fixed_batch():
     cfg = tiny_config(lr=3e-3, diversity_weight=0.0)
     tr = Trainer(cfg, total_steps=1000)
