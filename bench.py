@@ -254,8 +254,7 @@ def main():
         ms_per_step = ms / args.steps
         value = tokens_per_step / (ms_per_step / 1e3)
         out = {
-            "metric": "train tokens/s/box (device-timed, max over ranks) DAWN-SRW "
-                      f"{args.model} @{world} B200",
+            "metric": f"train tokens/s/box (device-timed, max over ranks) DAWN-SRW {args.model}",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16",

@@ -77,13 +77,21 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     cuda_lib = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "lib64"
     stamp = max(o.stat().st_mtime for o in objs + cxx_objs)
     if force or not SO_PATH.exists() or SO_PATH.stat().st_mtime < stamp:
-        _run(["g++", "-shared", "-o", str(SO_PATH), *map(str, objs + cxx_objs),
+        # the allocation-free entry point (and its 64 MiB device array) belongs to the plain
+        # C library only
+        ext_objs = [o for o in objs if o.stem != "srw_forward_static"]
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = SO_PATH.with_suffix(".so.tmp")
+        _run(["g++", "-shared", "-o", str(tmp), *map(str, ext_objs + cxx_objs),
               f"-L{torch_lib}", f"-L{cuda_lib}", "-lc10", "-lc10_cuda", "-ltorch_cpu",
               "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart",
               f"-Wl,-rpath,{torch_lib}", f"-Wl,-rpath,{cuda_lib}"])
+        os.replace(tmp, SO_PATH)
     if force or not PLAIN_SO_PATH.exists() or PLAIN_SO_PATH.stat().st_mtime < stamp:
-        _run(["g++", "-shared", "-o", str(PLAIN_SO_PATH), *map(str, objs),
+        tmp = PLAIN_SO_PATH.with_suffix(".so.tmp")
+        _run(["g++", "-shared", "-o", str(tmp), *map(str, objs),
               f"-L{cuda_lib}", "-lcudart", f"-Wl,-rpath,{cuda_lib}"])
+        os.replace(tmp, PLAIN_SO_PATH)
     return SO_PATH
 
 

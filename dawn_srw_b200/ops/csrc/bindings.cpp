@@ -525,6 +525,58 @@ std::vector<Tensor> route_bwd_prologue(const Tensor& dy, const Tensor& y, const 
   return {dyb, rowdot};
 }
 
+// tau, isd, mu, sd [N] and the column sums of h [r] from hg = h . G.
+std::vector<Tensor> score_stats_fwd(const Tensor& hg, const Tensor& h, const Tensor& esum,
+                                    const Tensor& off, double inv_u) {
+  check_bf16_2d(h, "h");
+  TORCH_CHECK(hg.is_cuda() && hg.dim() == 2 && hg.scalar_type() == torch::kFloat32 &&
+              hg.is_contiguous() && hg.size(0) == h.size(0) && hg.size(1) == h.size(1));
+  TORCH_CHECK(esum.scalar_type() == torch::kFloat32 && esum.is_contiguous() &&
+              esum.numel() == h.size(1) && off.scalar_type() == torch::kFloat32 &&
+              off.is_contiguous() && off.numel() == h.size(0));
+  const c10::cuda::CUDAGuard guard(h.device());
+  const int N = h.size(0), r = h.size(1);
+  auto o = hg.options();
+  auto tau = torch::empty({N}, o), isd = torch::empty({N}, o), mu = torch::empty({N}, o),
+       sd = torch::empty({N}, o), hsum = torch::zeros({r}, o);
+  int rc = dsb_score_stats_fwd(hg.data_ptr<float>(), h.data_ptr(), h.stride(0),
+                               esum.data_ptr<float>(), off.data_ptr<float>(), inv_u, N, r,
+                               tau.data_ptr<float>(), isd.data_ptr<float>(), mu.data_ptr<float>(),
+                               sd.data_ptr<float>(), hsum.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_score_stats_fwd failed with code ", rc);
+  return {tau, isd, mu, sd, hsum};
+}
+
+// dh fp32 [N, r], w bf16 [N, r] (row stride padded to 8), d_off [N], d_esum [r].
+std::vector<Tensor> score_stats_bwd(c10::optional<Tensor> d_tau, c10::optional<Tensor> d_isd,
+                                    c10::optional<Tensor> d_hsum, c10::optional<Tensor> d_hb,
+                                    const Tensor& off, const Tensor& mu, const Tensor& sd,
+                                    const Tensor& hg, const Tensor& h, const Tensor& esum,
+                                    double inv_u) {
+  check_bf16_2d(h, "h");
+  const c10::cuda::CUDAGuard guard(h.device());
+  const int N = h.size(0), r = h.size(1);
+  const void* dhb = nullptr;
+  if (d_hb.has_value() && d_hb->defined()) {
+    TORCH_CHECK(d_hb->scalar_type() == torch::kBFloat16 && d_hb->is_contiguous() &&
+                d_hb->numel() == static_cast<int64_t>(N) * r);
+    dhb = d_hb->data_ptr();
+  }
+  auto o = hg.options();
+  const int64_t ldw = (r + 7) / 8 * 8;
+  auto dh = torch::empty({N, r}, o);
+  auto w = torch::empty({N, ldw}, o.dtype(torch::kBFloat16));
+  auto d_off = torch::empty({N}, o), d_esum = torch::zeros({r}, o);
+  int rc = dsb_score_stats_bwd(opt_f32(d_tau), opt_f32(d_isd), opt_f32(d_hsum), dhb,
+                               off.data_ptr<float>(), mu.data_ptr<float>(), sd.data_ptr<float>(),
+                               hg.data_ptr<float>(), h.data_ptr(), h.stride(0),
+                               esum.data_ptr<float>(), inv_u, N, r, dh.data_ptr<float>(),
+                               w.data_ptr(), ldw, d_off.data_ptr<float>(),
+                               d_esum.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_score_stats_bwd failed with code ", rc);
+  return {dh, w.slice(1, 0, r), d_off, d_esum};
+}
+
 void adamw_multi(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> exp_avg,
                  std::vector<Tensor> exp_avg_sq, const Tensor& clip_scale, double lr, double b1,
                  double b2, double eps, double wd, double bc1, double bc2) {
@@ -576,6 +628,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
   m.def("grad_sq_norm", &grad_sq_norm);
+  m.def("score_stats_fwd", &score_stats_fwd);
+  m.def("score_stats_bwd", &score_stats_bwd);
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
   m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);
   m.def("peer_barrier", &peer_barrier);

@@ -196,8 +196,17 @@ struct AccCtl {
 // `warp` is the epilogue warp index (0..kEpiWarps-1); its rows are
 // m0 + 32*(warp%4) + lane and, with 8 warps, its columns the (warp/4)-th half.
 
+// Registers per thread: the whole register file divided by the CTA's threads (one
+// CTA per SM), in allocation units of 8.  Stated explicitly because a bound derived
+// from the thread count alone is rounded to a coarser CTA size and leaves a sixth of
+// the file unused for the 10- and 11-warp configurations.
+constexpr int engine_max_regs(int threads) {
+  const int r = (65536 / threads) / 8 * 8;
+  return r > 255 ? 255 : r;
+}
+
 template <int BN, class Epi, int kCtas, bool kGather = false>
-__global__ void __launch_bounds__((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32, 1)
+__global__ void __maxnreg__(engine_max_regs((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32))
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   // kCtas == 2: the CTA pair of a 2-CTA cluster shares a 256-row tile.  Each CTA
   // stages its own 128 rows of A and BN/2 rows of B; the leader CTA (cluster

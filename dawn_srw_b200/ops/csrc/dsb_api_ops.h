@@ -41,6 +41,21 @@ int dsb_offdiag_abs(const float* sim, long long ld, int m, void* sgn_bf16, long 
 int dsb_route_bwd_prologue(const float* dy, const float* y, const float* row_scale,
                            void* dy_bf16, float* rowdot, int T, int D, cudaStream_t stream);
 
+// Per-token score statistics from hg = h . (E^T E) (fp32 [N, r]) and bf16 h [N, ldh]:
+//   mu = <h, esum> * inv_u,  var = <hg, h> * inv_u - mu^2,  sd = sqrt(max(var, 1e-12)) + 1e-8,
+//   tau = mu + off * sd,  isd = 1 / sd;  hsum[r] += column sums of h (hsum may be null).
+int dsb_score_stats_fwd(const float* hg, const void* h_bf16, long long ldh, const float* esum,
+                        const float* off, float inv_u, int N, int r, float* tau, float* isd,
+                        float* mu, float* sd, float* hsum, cudaStream_t stream);
+// Backward of the above.  d_tau, d_isd [N], d_hsum [r], d_hb (bf16 [N, r] cotangent of the
+// bf16 copy of h) may be null.  Writes dh fp32 [N, r] (all terms summed), w = bf16(d_var * h)
+// [N, ldw] (operand of dG = w^T h * inv_u), d_off [N]; accumulates d_esum [r] (zero it first).
+int dsb_score_stats_bwd(const float* d_tau, const float* d_isd, const float* d_hsum,
+                        const void* d_hb_bf16, const float* off, const float* mu, const float* sd,
+                        const float* hg, const void* h_bf16, long long ldh, const float* esum,
+                        float inv_u, int N, int r, float* dh, void* w_bf16, long long ldw,
+                        float* d_off, float* d_esum, cudaStream_t stream);
+
 // Causal self-attention (tcgen05 kernels).  q, k, v, out, d_out: bf16 [B, S, H*dh]
 // (head h in columns [h*dh, (h+1)*dh)); dh a multiple of 16, at most 128.
 // lse, delta: fp32 [B, H, S] (delta is scratch filled by the backward call).

@@ -404,17 +404,21 @@ __device__ __forceinline__ float2 unpack_half2(uint32_t w) {
 }
 
 // Wide variant: 256-column tiles on CTA pairs.  S and XR take 256 TMEM columns
-// each (all 512), one buffer per accumulator, so the overlap comes from the
-// order of work instead of double buffering: phase 1 turns S into gate values
-// (held in registers as bf16, 128 columns per thread) while the five-times-
-// longer XR MMAs of the same tile still run, and frees S for the next tile;
-// phase 2 multiplies by XR and stores.  The tensor core only idles while phase
-// 2 of tile t outlasts the S MMAs of tile t+1, so phase 2 is kept short and the
-// gate arithmetic (one exponential, ~10 FP32 instructions per element for the
-// z * Phi(z) gate) sits in phase 1.  TMEM loads are software-pipelined: the
-// load of chunk q+1 is in flight while chunk q is processed.  256-wide tiles
-// halve the shared-memory bytes per FLOP of the 128-wide variant, whose
-// tensor-pipe utilisation is capped by shared-memory bandwidth.
+// each (all 512), one buffer per accumulator, so nothing may sit between an
+// accumulator becoming complete and its release: the epilogue drains each
+// accumulator into registers in compact form and releases it at once.
+//   phase 1 (while the five-times-longer XR MMAs of the tile still run): S ->
+//            gate values, kept as bf16 pairs (64 registers for the thread's 128
+//            columns); S released.
+//   drain:   XR -> bf16 pairs (64 registers); XR released.  From here on the
+//            tensor core is free to run the next tile.
+//   phase 2: p = g * xr from registers, staged and stored (and xr itself when
+//            it is kept), overlapping the next tile's MMAs.
+// The gate arithmetic is one exponential and ~10 FP32 instructions per element
+// for the z * Phi(z) gate; TMEM loads are software-pipelined (the load of chunk
+// q+1 is in flight while chunk q is processed).  256-wide tiles halve the
+// shared-memory bytes per FLOP of the 128-wide variant, whose tensor-pipe
+// utilisation is capped by shared-memory bandwidth.
 // Warp w: rows 32(w%4).., columns 128(w/4).. of the CTA's 128 x 256 tile.
 // kSaveXr: the read scalars xr = x . read^T are written out as bf16 next to p,
 // so that the backward pass need not recompute them (BwdGateEpiXr).
@@ -490,41 +494,55 @@ struct FwdGateEpiWide {
     else phase1<false>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
     ctl.release(0);   // the next tile's score MMAs may start
     if constexpr (KIND != 2) g_acc = den_acc;
-    // ---- phase 2: p = g * xr, two 64-column slabs (and xr itself when it is kept)
-    const uint32_t acc_xr = ctl.wait(1) + c;
-    float xb[2][32];
-    tmem_ld32(acc_xr, xb[0]);
+    // ---- drain XR into bf16 pairs and release it
+    uint32_t xp[64];
+    {
+      const uint32_t acc_xr = ctl.wait(1) + c;
+      float xb[2][32];
+      tmem_ld32(acc_xr, xb[0]);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int sl = i >> 1, half = i & 1;
-      float* xr = xb[i & 1];
-      tmem_ld_wait_dep32(xr);
-      if (i < 3) tmem_ld32(acc_xr + 32 * (i + 1), xb[(i + 1) & 1]);
-      else ctl.release(1);   // last TMEM read of this tile
+      for (int i = 0; i < 4; ++i) {
+        float* xr = xb[i & 1];
+        tmem_ld_wait_dep32(xr);
+        if (i < 3) tmem_ld32(acc_xr + 32 * (i + 1), xb[(i + 1) & 1]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) xp[16 * i + j] = pack_bf16x2(xr[2 * j], xr[2 * j + 1]);
+      }
+      ctl.release(1);   // the next tile's read MMAs may start
+    }
+    // ---- phase 2: p = g * xr from registers; nothing here holds the tensor core up
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
       const bool in_range = col0 + 64 * sl < N;   // warp-uniform
       uint32_t b_p, b_x;
       if constexpr (kSaveXr) {
         b_p = st.buf(0);
         b_x = st.buf(1);
-        if (half == 0) st.wait_free<0>();         // both buffers have been read by their stores
+        st.wait_free<0>();                        // both buffers have been read by their stores
       } else {
         b_p = st.buf(sl);
         b_x = 0;
-        if (half == 0) st.wait_free<1>();
+        st.wait_free<1>();
       }
-      if constexpr (kSaveXr) stage_bf16_32(st, b_x, 4 * half, xr);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gp[16 * i + j]);
-        const float2 gf = __bfloat1622float2(g2);
-        xr[2 * j] *= gf.x;
-        xr[2 * j + 1] *= gf.y;
+      for (int k = 0; k < 8; ++k) {               // 16-byte chunk k of the slab: 8 columns
+        uint32_t pw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int idx = 32 * sl + 4 * k + e;
+          const float2 gf =
+              __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gp[idx]));
+          const float2 xf =
+              __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xp[idx]));
+          pw[e] = pack_bf16x2(gf.x * xf.x, gf.y * xf.y);
+        }
+        st.put(b_p, k, pw[0], pw[1], pw[2], pw[3]);
+        if constexpr (kSaveXr)
+          st.put(b_x, k, xp[32 * sl + 4 * k], xp[32 * sl + 4 * k + 1], xp[32 * sl + 4 * k + 2],
+                 xp[32 * sl + 4 * k + 3]);
       }
-      stage_bf16_32(st, b_p, 4 * half, xr);
-      if (half == 1) {
-        st.flush(&maps[0], b_p, col0 + 64 * sl, r0, false, in_range);
-        if constexpr (kSaveXr) st.flush(&maps[1], b_x, col0 + 64 * sl, r0, false, in_range);
-      }
+      st.flush(&maps[0], b_p, col0 + 64 * sl, r0, false, in_range);
+      if constexpr (kSaveXr) st.flush(&maps[1], b_x, col0 + 64 * sl, r0, false, in_range);
     }
     if (row_ok) {
       atomicAdd(p.den_sum + row, den_acc);
@@ -820,14 +838,18 @@ struct BwdGateEpiWide {
 // When the forward pass kept xr = x . read^T (bf16 [T, U], FwdGateEpiWide with
 // kSaveXr), the backward gate step is ONE 256-wide launch with two accumulators:
 //   S = h . emb^T (K = d_route)  and  DP = dy . write^T (K = d_model),
-// i.e. neither the XR product nor a second pass over S is recomputed.
-//   phase 1 (while the DP MMAs of the tile run): S -> (g, A1[, A2]) kept as one
-//            bf16 pair per element in registers; p = g * xr is staged and stored;
-//            S is released for the next tile.
-//   phase 2 (short): dxr = DP * g,  ds = A1 * (DP * xr) + A2 * dden,  dtau.
-// The xr rows of the tile are fetched into two staging buffers with 16-byte
-// asynchronous copies before phase 1 and stay there until phase 2 overwrites
-// them, chunk by chunk, with ds (a thread reads its own chunk first).
+// i.e. neither the XR product nor a second pass over S is recomputed.  Both
+// accumulators are single-buffered, so the epilogue drains each into registers
+// the moment it completes and releases it:
+//   S  -> shifted scores as fp16 pairs (64 registers), while the DP MMAs run;
+//   DP -> bf16 pairs (64 registers).
+// Everything after that works from registers and overlaps the next tile's MMAs:
+// gate coefficients (g, A1, A2) from the shifted score, then
+//   p = g * xr,   dxr = DP * g,   ds = A1 * (DP * xr) + A2 * dden,   dtau -= ds.
+// A thread reads the 128 xr values of its row straight from global memory, 16
+// at a time and one step ahead of their use (each lane covers whole 32-byte
+// sectors of its own row).  p may be written over xr in place: a thread's reads
+// of a chunk precede the store of the slab that contains it.
 struct BwdXrParams {
   const float* tau;        // [T]
   const float* inv_sigma;  // [T]
@@ -838,29 +860,21 @@ struct BwdXrParams {
   GateConsts gc;
 };
 
+__device__ __forceinline__ uint4 ld_global_v4_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 template <int KIND>
 struct BwdGateEpiXr {
   static constexpr int kNumAcc = 2;
   static constexpr int kNumOut = 3;    // p, dxr, ds
-  static constexpr int kOutBufs = 3;   // 0: p / dxr staging, 1 and 2: xr -> ds of slab 0 and 1
+  static constexpr int kOutBufs = 3;   // one staged slab per output
   static constexpr int kEpiWarps = 8;
   __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
   using Params = BwdXrParams;
-
-  // 16 bf16 values of this thread's row: 16-byte chunks k0 and k0 + 1 of a staged slab
-  __device__ static __forceinline__ void load16(uint32_t slab, int lane, int k0, float* out) {
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const uint4 u = ld_shared_v4(slab + lane * 128 + (((k0 + k) ^ (lane & 7)) << 4));
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h2[e]);
-        out[8 * k + 2 * e] = f.x;
-        out[8 * k + 2 * e + 1] = f.y;
-      }
-    }
-  }
 
   template <int BN, class Ctl>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
@@ -877,106 +891,100 @@ struct BwdGateEpiXr {
     const float dden = row_ok ? p.dden[row] : 0.f;
     const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
     const bool tail = col0 + 128 > N;
-    const uint32_t b_io = st.buf(0);
+    const __nv_bfloat16* xrow = p.xr + static_cast<size_t>(row_ok ? row : 0) * p.ldxr + col0;
+    // 16 xr values (two 16-byte loads) of chunk q; zeros outside the matrix
+    auto load_xr = [&](int q, uint4& u0, uint4& u1) {
+      const int cc = col0 + 16 * q;
+      u0 = (row_ok && cc < p.ldxr) ? ld_global_v4_stream(xrow + 16 * q) : make_uint4(0, 0, 0, 0);
+      u1 = (row_ok && cc + 8 < p.ldxr) ? ld_global_v4_stream(xrow + 16 * q + 8)
+                                       : make_uint4(0, 0, 0, 0);
+    };
 
-    // ---- fetch the tile's xr rows (32 x 64 bf16 per slab; 8 lanes per row, coalesced)
-    st.wait_free<0>();                          // the previous tile's stores have read all buffers
-    {
-      const int ch = lane & 7;
-#pragma unroll
-      for (int sl = 0; sl < 2; ++sl) {
-        const int colS = col0 + 64 * sl + ch * 8;
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int rr = it * 4 + (lane >> 3);
-          const bool ok = r0 + rr < M && colS < p.ldxr;
-          const __nv_bfloat16* src = ok ? p.xr + static_cast<size_t>(r0 + rr) * p.ldxr + colS : p.xr;
-          cp_async_16(st.buf(1 + sl) + rr * 128 + ((ch ^ (rr & 7)) << 4), src, ok ? 16 : 0);
-        }
-      }
-    }
-
-    // ---- phase 1: S -> (g, A1) pairs; p = g * xr.  For the two-stage gate A2
-    // (0 or 1) rides in the sign of g, which is never negative itself.
-    uint32_t ga[128];
+    // ---- drain S: shifted scores as fp16 pairs
+    uint32_t zp[64];
     {
       const uint32_t acc_s = ctl.wait(0) + c;
       float sb[2][16];
       tmem_ld16(acc_s, sb[0]);
-      cp_async_wait_all();                      // issued a whole MMA segment ago
-      __syncwarp();
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         float* s = sb[q & 1];
         tmem_ld_wait_dep16(s);
         if (q < 7) tmem_ld16(acc_s + 16 * (q + 1), sb[(q + 1) & 1]);
-        else ctl.release(0);                    // the next tile's score MMAs may start
-        const int sl = q >> 2, k0 = 2 * (q & 3);
-        float xr[16];
-        load16(st.buf(1 + sl), lane, k0, xr);
-        if ((q & 3) == 0 && sl == 1) st.wait_free<0>();   // p of slab 0 has left the staging buffer
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float a1, a2;
-          float g = gate_coeffs_shifted<KIND>(p.gc, fmaf(s[j], rg.a, rg.b), isg, a1, a2);
-          xr[j] *= g;                           // p
-          if constexpr (KIND == 2) {
-            if (a2 != 0.f) g = -g;
-          }
-          ga[16 * q + j] = pack_bf16x2(g, a1);
-        }
-        stage_bf16_16(st, b_io, k0, xr);
-        if ((q & 3) == 3) st.flush(&maps[0], b_io, col0 + 64 * sl, r0, false, col0 + 64 * sl < N);
+        for (int j = 0; j < 8; ++j)
+          zp[8 * q + j] = pack_half2(fmaf(s[2 * j], rg.a, rg.b), fmaf(s[2 * j + 1], rg.a, rg.b));
       }
+      ctl.release(0);   // the next tile's score MMAs may start
     }
-
-    // ---- phase 2: DP
-    float dtau_acc = 0.f;
+    uint4 xa, xb;
+    load_xr(0, xa, xb);
+    // ---- drain DP: bf16 pairs
+    uint32_t dpp[64];
     {
       const uint32_t acc_dp = ctl.wait(1) + c;
       float db[2][16];
       tmem_ld16(acc_dp, db[0]);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        float* dp = db[q & 1];
-        tmem_ld_wait_dep16(dp);
+        float* d = db[q & 1];
+        tmem_ld_wait_dep16(d);
         if (q < 7) tmem_ld16(acc_dp + 16 * (q + 1), db[(q + 1) & 1]);
-        else ctl.release(1);                    // last TMEM read of this tile
-        const int sl = q >> 2, k0 = 2 * (q & 3);
-        const uint32_t b_x = st.buf(1 + sl);
-        float xr[16];
-        load16(b_x, lane, k0, xr);
-        if ((q & 3) == 0) {
-          // the staging buffer's previous store (p of slab 1, then dxr of slab 0) has been read;
-          // for slab 1 the ds store of slab 0 may still be pending
-          if (sl == 0) st.wait_free<0>();
-          else st.wait_free<1>();
-        }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const uint32_t w = ga[16 * q + j];
-          float g = __uint_as_float(w << 16);
-          const float a1 = __uint_as_float(w & 0xffff0000u);
-          float d;
-          if constexpr (KIND == 2) {
-            const float a2 = g < 0.f ? 1.f : 0.f;
-            g = fabsf(g);
-            d = fmaf(a1, dp[j] * xr[j], a2 * dden);
-          } else {
-            d = a1 * fmaf(dp[j], xr[j], dden);
-          }
-          if (tail && col0 + 16 * q + j >= N) d = 0.f;
-          dtau_acc -= d;
-          xr[j] = d;                            // ds
-          dp[j] *= g;                           // dxr
+        for (int j = 0; j < 8; ++j) dpp[8 * q + j] = pack_bf16x2(d[2 * j], d[2 * j + 1]);
+      }
+      ctl.release(1);   // the next tile's MMAs may start
+    }
+
+    // ---- outputs, from registers
+    float dtau_acc = 0.f;
+    const uint32_t b_p = st.buf(0), b_dxr = st.buf(1), b_ds = st.buf(2);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int sl = q >> 2, k0 = 2 * (q & 3);
+      if ((q & 3) == 0) st.wait_free<0>();       // the previous slab's stores have read the buffers
+      const uint4 u0 = xa, u1 = xb;
+      if (q < 7) load_xr(q + 1, xa, xb);
+      const uint32_t xw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+      uint32_t pw[8], dxw[8], dsw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 zt = unpack_half2(zp[8 * q + j]);
+        const float2 dp =
+            __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dpp[8 * q + j]));
+        const float2 xr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[j]));
+        float a1x, a2x, a1y, a2y;
+        const float gx = gate_coeffs_shifted<KIND>(p.gc, zt.x, isg, a1x, a2x);
+        const float gy = gate_coeffs_shifted<KIND>(p.gc, zt.y, isg, a1y, a2y);
+        float dsx, dsy;
+        if constexpr (KIND == 2) {
+          dsx = fmaf(a1x, dp.x * xr.x, a2x * dden);
+          dsy = fmaf(a1y, dp.y * xr.y, a2y * dden);
+        } else {
+          dsx = a1x * fmaf(dp.x, xr.x, dden);
+          dsy = a1y * fmaf(dp.y, xr.y, dden);
         }
-        stage_bf16_16(st, b_io, k0, dp);
-        stage_bf16_16(st, b_x, k0, xr);
-        if ((q & 3) == 3) {
-          const bool in_range = col0 + 64 * sl < N;
-          st.flush(&maps[1], b_io, col0 + 64 * sl, r0, false, in_range);
-          st.flush(&maps[2], b_x, col0 + 64 * sl, r0, false, in_range);
+        if (tail) {
+          const int col = col0 + 16 * q + 2 * j;
+          if (col >= N) dsx = 0.f;
+          if (col + 1 >= N) dsy = 0.f;
         }
+        dtau_acc -= dsx + dsy;
+        pw[j] = pack_bf16x2(gx * xr.x, gy * xr.y);
+        dxw[j] = pack_bf16x2(dp.x * gx, dp.y * gy);
+        dsw[j] = pack_bf16x2(dsx, dsy);
+      }
+      st.put(b_p, k0, pw[0], pw[1], pw[2], pw[3]);
+      st.put(b_p, k0 + 1, pw[4], pw[5], pw[6], pw[7]);
+      st.put(b_dxr, k0, dxw[0], dxw[1], dxw[2], dxw[3]);
+      st.put(b_dxr, k0 + 1, dxw[4], dxw[5], dxw[6], dxw[7]);
+      st.put(b_ds, k0, dsw[0], dsw[1], dsw[2], dsw[3]);
+      st.put(b_ds, k0 + 1, dsw[4], dsw[5], dsw[6], dsw[7]);
+      if ((q & 3) == 3) {
+        const bool in_range = col0 + 64 * sl < N;
+        st.flush(&maps[0], b_p, col0 + 64 * sl, r0, false, in_range);
+        st.flush(&maps[1], b_dxr, col0 + 64 * sl, r0, false, in_range);
+        st.flush(&maps[2], b_ds, col0 + 64 * sl, r0, false, in_range);
       }
     }
     if (row_ok) atomicAdd(p.dtau_sum + row, dtau_acc);

@@ -9,32 +9,29 @@ namespace {
 // Part of the library image; resident on every device that loads it.
 static __device__ __align__(256) unsigned char g_srw_scratch[DSB_SRW_STATIC_SCRATCH_BYTES];
 
-constexpr int kMaxDevices = 64;
-// Device address of g_srw_scratch per device ordinal.  In host code the name
-// g_srw_scratch is only a handle for the runtime, never a pointer a kernel may
-// use, so the real address is looked up once per device.
-void* g_scratch_addr[kMaxDevices] = {nullptr};
-
 thread_local char g_last_error[256] = "";
 
+// Device address of g_srw_scratch on the current device.  In host code the
+// name g_srw_scratch is only a handle for the runtime, never a pointer a kernel
+// may use.  The address is asked for on every call (a cheap table look-up in
+// the runtime) instead of being cached per ordinal: a cached pointer would
+// outlive a context that was torn down and re-created on the same ordinal.
+// Concurrent calls from several host threads are fine: nothing is shared here.
 int scratch_for_current_device(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
     snprintf(g_last_error, sizeof(g_last_error), "no usable current CUDA device (ordinal %d)", dev);
     return DSB_STATIC_ERR_SYMBOL;
   }
-  if (g_scratch_addr[dev] == nullptr) {
-    void* ptr = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_srw_scratch);  // `dev` is current
-    if (e != cudaSuccess || ptr == nullptr) {
-      snprintf(g_last_error, sizeof(g_last_error),
-               "cudaGetSymbolAddress for the static SRW scratch failed on device %d: %s", dev,
-               cudaGetErrorString(e));
-      return DSB_STATIC_ERR_SYMBOL;
-    }
-    g_scratch_addr[dev] = ptr;
+  void* ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&ptr, g_srw_scratch);  // `dev` is current
+  if (e != cudaSuccess || ptr == nullptr) {
+    snprintf(g_last_error, sizeof(g_last_error),
+             "cudaGetSymbolAddress for the static SRW scratch failed on device %d: %s", dev,
+             cudaGetErrorString(e));
+    return DSB_STATIC_ERR_SYMBOL;
   }
-  *out = g_scratch_addr[dev];
+  *out = ptr;
   return 0;
 }
 

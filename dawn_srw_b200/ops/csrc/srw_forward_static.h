@@ -17,9 +17,12 @@
 //     T * round_up(U, 8) * 2 bytes; larger problems are refused with
 //     DSB_STATIC_ERR_TOO_LARGE and nothing is launched.  Every GPU whose
 //     context loads this library keeps those 64 MiB until the process exits.
-//   * The first call on each device looks up the buffer's device address
-//     (cudaGetSymbolAddress, with that device current).  Make that first call
-//     outside any stream capture.
+//   * Every call looks up the buffer's device address (cudaGetSymbolAddress,
+//     with the caller's device current); the first such look-up on a device
+//     initialises the library image there, so make the first call on each
+//     device outside any stream capture.
+//   * The buffer is part of libdsb_kernels.so only (the C library); the Python
+//     extension module does not carry a second copy.
 //   * All calls on a device share the one buffer and it keeps whatever the last
 //     call left there.  The kernels rewrite every element they later read, and
 //     den_sum (an output) is cleared by the call itself, so nothing needs

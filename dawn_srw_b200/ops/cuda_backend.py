@@ -7,8 +7,8 @@ the reference gets its backward from autodiff and recomputes per chunk):
       emb_c/read_c/write_c = bf16(optionally row-normalised pool tensors)
       G = emb_c^T emb_c  [r,r],  e_sum = sum_u emb_c[u]      (fp32)
   per call
-      mu    = h . e_sum / U            E[s^2] = h G h^T / U      (no pass over [T,U])
-      sigma = sqrt(E[s^2] - mu^2) + 1e-8 ;  tau = mu + tau_off * sigma
+      mu    = h . e_sum / U            E[s^2] = h G h^T / U      (no pass over [T,U];
+      sigma = sqrt(E[s^2] - mu^2) + 1e-8 ;  tau = mu + tau_off * sigma    ops/score_stats.py)
       kernel A (tcgen05):  S = h.emb^T, XR = x.read^T in TMEM; epilogue
                            p = gate(S) * XR -> bf16 [T,U];  den_sum[T]
       kernel B (tcgen05):  raw_out = p . write     [T,D]
@@ -38,6 +38,7 @@ from . import build as _build
 from . import reference as R
 from .backend import ParallelCtx, PreparedPool
 from .gates import GATE_GELU_Z, GateSpec
+from .score_stats import score_stats
 from .srw_ref import SRWResult, srw_pool_ref
 from ..parallel import collectives as C
 
@@ -157,8 +158,9 @@ XR_BUDGET = _XrBudget()
 
 def _alloc_saved_xr(dev, T: int, Up: int, U: int, wanted: bool):
     """bf16 [T, Up] buffer for the read scalars of one route if the pool runs on
-    the wide kernels, gradients are being recorded and the budget allows it."""
-    if not wanted or not torch.is_grad_enabled() or not ext().srw_wide_tiles(U):
+    the wide kernels and the budget allows it (``wanted``: a backward pass will
+    follow and no unit mask is in play)."""
+    if not wanted or not ext().srw_wide_tiles(U):
         return None
     nbytes = T * Up * 2
     if not XR_BUDGET.acquire(dev, nbytes):
@@ -270,9 +272,16 @@ class _PoolPrepFn(torch.autograd.Function):
         emb_c, n_e = prep(emb)
         read_c, n_r = prep(read)
         write_c, n_w = prep(write)
-        ef = emb_c[:U].float()
-        gram = ef.t() @ ef
-        esum = ef.sum(0)
+        # E^T E on the tensor engine (bf16 inputs are exact, fp32 accumulation; the long K = U
+        # is split over the SM pairs by the accumulating epilogue)
+        r = emb.shape[1]
+        if emb.is_cuda:
+            gram = torch.zeros(r, r, dtype=torch.float32, device=emb.device)
+            gemm(emb_c[:U], True, emb_c[:U], True, out=gram, accumulate=True)
+        else:                                        # CPU: the algebra only (tests)
+            ef = emb_c[:U].float()
+            gram = ef.t() @ ef
+        esum = emb_c[:U].sum(0, dtype=torch.float32)
         holder.emb, holder.read, holder.write = emb_c, read_c, write_c
         if any(ctx.needs_input_grad[:3]):
             holder.g_emb = torch.zeros_like(emb, dtype=torch.float32)
@@ -289,9 +298,16 @@ class _PoolPrepFn(torch.autograd.Function):
         hd = ctx.holder
         U = ctx.U
         g_emb, g_read, g_write = hd.g_emb, hd.g_read, hd.g_write
-        ef = hd.emb[:U].float()
         if d_gram is not None:
-            g_emb[:U] += ef @ (d_gram + d_gram.t())
+            # d emb = E (dG + dG^T): engine GEMMs on a two-term bf16 split of the symmetric
+            # factor, accumulated into the shared gradient buffer
+            from .score_stats import split_bf16
+            sym = (d_gram + d_gram.t()).float().contiguous()
+            if sym.is_cuda:
+                for part in split_bf16(sym):
+                    gemm(hd.emb[:U], False, part, False, out=g_emb[:U], accumulate=True)
+            else:
+                g_emb[:U] += hd.emb[:U].float() @ sym
         if d_esum is not None:
             g_emb[:U] += d_esum.unsqueeze(0)
 
@@ -413,7 +429,8 @@ class _SRWRouteScaledFn(torch.autograd.Function):
         Up = _round_up(U, 8)
         p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)           # scratch
         den = torch.zeros(T, dtype=torch.float32, device=dev)
-        xr = _alloc_saved_xr(dev, T, Up, U, getattr(holder, "keep_xr", True) and unit_mask is None)
+        xr = _alloc_saved_xr(dev, T, Up, U, getattr(holder, "keep_xr", True) and unit_mask is None
+                             and any(ctx.needs_input_grad))
         count_launches(2)
         e.srw_fwd_gate_xr(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, xr, tau, inv_sd, den,
                           alive, unit_mask, _gate_list(spec), status_word(dev), [], 0, 0, None, 0)
@@ -715,7 +732,9 @@ class CudaBackend:
         anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, pool, spec.normalize_pool, U)
         gram = C.sum_over_shards(gram, pctx.shard_group)
         esum = C.sum_over_shards(esum, pctx.shard_group)
-        pool.extra = {"anchor": anchor, "gram": gram, "esum": esum, "U": U}
+        from .score_stats import split_bf16
+        pool.extra = {"anchor": anchor, "gram": gram, "esum": esum, "U": U,
+                      "gram_split": split_bf16(gram.detach())}
         return pool
 
     def srw(self, x, h, tau_off, pool: CudaPool, spec: GateSpec, *,
@@ -741,14 +760,9 @@ class CudaBackend:
         U_tot = pctx.n_total if pctx.n_total is not None else U
         T, Rr, r = h.shape
         x_bf = _bf16_2d(x)
-        h_bf3 = h.to(torch.bfloat16)
-        hf = h_bf3.float()
-        mu = hf @ (ex["esum"] / U_tot)                                     # [T,R]
-        m2 = ((hf @ ex["gram"]) * hf).sum(-1) / U_tot
-        sd = torch.sqrt((m2 - mu * mu).clamp_min(0.0)) + 1e-8
-        tau = mu + tau_off * sd
-        inv_sd = 1.0 / sd
-        hbar = hf.mean(dim=(0, 1))
+        tau, inv_sd, hsum, h_bf3 = score_stats(h, tau_off, ex["gram"], ex["esum"], U_tot,
+                                               ex["gram_split"])
+        hbar = hsum / float(T * Rr)
         m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
         ns_sum = C.mean_over_group(m_u.sum(), pctx.dp_group)
         ns_sq = C.mean_over_group((m_u * m_u).sum(), pctx.dp_group)
@@ -807,15 +821,10 @@ class CudaBackend:
             tau_off = C.gather_tokens(tau_off, pctx.shard_group)
         T, Rr, r = h.shape
         x_bf = _bf16_2d(x)
-        h_bf3 = h.to(torch.bfloat16)
-        hf = h_bf3.float()
-        mu = hf @ (ex["esum"] / U_tot)                                     # [T,R]
-        m2 = ((hf @ ex["gram"]) * hf).sum(-1) / U_tot
-        sd = torch.sqrt((m2 - mu * mu).clamp_min(0.0)) + 1e-8
-        tau = mu + tau_off * sd
-        inv_sd = 1.0 / sd
+        tau, inv_sd, hsum, h_bf3 = score_stats(h, tau_off, ex["gram"], ex["esum"], U_tot,
+                                               ex["gram_split"])
         # per-unit mean score over the local tokens and routes -> LB / dead statistics
-        hbar = hf.mean(dim=(0, 1))
+        hbar = hsum / float(T * Rr)
         m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
         ns_sum = C.sum_over_shards(C.mean_over_group(m_u.sum(), pctx.dp_group), pctx.shard_group)
         ns_sq = C.sum_over_shards(C.mean_over_group((m_u * m_u).sum(), pctx.dp_group),
@@ -876,15 +885,10 @@ class CudaBackend:
         if comm is None:
             comm = self._comm[key] = FusedShardComm(grp, x.device, Tl, x.shape[1], r)
         x_bf = _bf16_2d(x)
-        h_bf3 = h.to(torch.bfloat16)
-        hf = h_bf3.float()
-        mu = hf @ (ex["esum"] / U_tot)
-        m2 = ((hf @ ex["gram"]) * hf).sum(-1) / U_tot
-        sd = torch.sqrt((m2 - mu * mu).clamp_min(0.0)) + 1e-8
-        tau = mu + tau_off * sd                                           # [Tl,R]
-        inv_sd = 1.0 / sd
+        tau, inv_sd, hsum, h_bf3 = score_stats(h, tau_off, ex["gram"], ex["esum"], U_tot,
+                                               ex["gram_split"])                # [Tl,R]
         # per-unit mean score over ALL tokens of the group (they share one batch)
-        hbar = C.sum_over_shards(hf.sum(dim=(0, 1)), grp) / float(Tl * nsh * Rr)
+        hbar = C.sum_over_shards(hsum, grp) / float(Tl * nsh * Rr)
         m_u = _PoolMatVecFn.apply(hbar, anchor, pool, U)
         ns_sum = C.sum_over_shards(C.mean_over_group(m_u.sum(), pctx.dp_group), grp)
         ns_sq = C.sum_over_shards(C.mean_over_group((m_u * m_u).sum(), pctx.dp_group), grp)

@@ -135,18 +135,95 @@ def state_dict_to_flax_params(sd: Dict[str, torch.Tensor]) -> Dict:
     return tree
 
 
+# ---------------------------------------------------------------------------
+# Optimizer state.  The reference's optimizer is an optax chain
+#   clip_by_global_norm, scale_by_adam, add_decayed_weights (base mask),
+#   add_decayed_weights (pool mask), scale_by_learning_rate(schedule)
+# optionally wrapped in optax.MultiSteps (scripts/train_jax.py:2083-2120), and
+# ``flax.serialization`` writes its state as nested dicts: a tuple becomes
+# {"0": .., "1": ..}, a NamedTuple a dict of its fields, an empty state {}:
+#   chain  = {"0": {}, "1": {"count", "mu": <param tree>, "nu": <param tree>},
+#             "2": {"inner_state": {}}, "3": {"inner_state": {}}, "4": {"count"}}
+#   wrapped = {"mini_step", "gradient_step", "inner_opt_state": chain,
+#              "acc_grads": <param tree>, "skip_state": {}}
+# The moments map onto DawnAdamW's exp_avg / exp_avg_sq (same names and
+# transposes as the parameters), ``count`` onto its step counter, ``mini_step``
+# and ``acc_grads`` onto the gradient-accumulation window.
+
+def _scalar(x, default=0) -> int:
+    if x is None:
+        return default
+    return int(np.asarray(x).reshape(-1)[0])
+
+
+def optax_state_to_torch(opt_state: Dict) -> Dict[str, Any]:
+    """Reference ``opt_state`` tree -> ``DawnAdamW.load_state_dict`` input."""
+    wrapped = isinstance(opt_state, dict) and "inner_opt_state" in opt_state
+    chain = opt_state["inner_opt_state"] if wrapped else opt_state
+    adam = None
+    for key in sorted(chain, key=str):
+        node = chain[key]
+        if isinstance(node, dict) and "mu" in node and "nu" in node:
+            adam = node
+            break
+    if adam is None:
+        raise ValueError("no scale_by_adam state (mu / nu) in the optimizer state")
+    out: Dict[str, Any] = {
+        "count": _scalar(adam.get("count")),
+        "micro": _scalar(opt_state.get("mini_step")) if wrapped else 0,
+        "exp_avg": flax_params_to_state_dict(adam["mu"]),
+        "exp_avg_sq": flax_params_to_state_dict(adam["nu"]),
+        "acc": None,
+    }
+    if wrapped and out["micro"] > 0 and opt_state.get("acc_grads"):
+        # optax keeps the running MEAN of the window's gradients; DawnAdamW keeps their sum
+        acc = flax_params_to_state_dict(opt_state["acc_grads"])
+        out["acc"] = {k: v * float(out["micro"]) for k, v in acc.items()}
+    return out
+
+
+def torch_opt_state_to_optax(sd: Dict[str, Any], accumulation_steps: int = 1) -> Dict:
+    """``DawnAdamW.state_dict()`` -> the reference's ``opt_state`` tree."""
+    count = np.asarray(int(sd["count"]), dtype=np.int32)
+    chain = {"0": {},
+             "1": {"count": count, "mu": state_dict_to_flax_params(sd["exp_avg"]),
+                   "nu": state_dict_to_flax_params(sd["exp_avg_sq"])},
+             "2": {"inner_state": {}}, "3": {"inner_state": {}},
+             "4": {"count": count}}
+    if accumulation_steps <= 1:
+        return chain
+    micro = int(sd.get("micro", 0))
+    acc = sd.get("acc")
+    if acc is None or micro == 0:
+        acc_tree = state_dict_to_flax_params({k: torch.zeros_like(v) for k, v in sd["exp_avg"].items()})
+    else:
+        acc_tree = state_dict_to_flax_params({k: v / float(micro) for k, v in acc.items()})
+    return {"mini_step": np.asarray(micro, dtype=np.int32), "gradient_step": count,
+            "inner_opt_state": chain, "acc_grads": acc_tree, "skip_state": {}}
+
+
 def load_flax_checkpoint(path: str) -> Dict[str, Any]:
     """Read a reference ``.flax`` file.  Returns a dict with ``state_dict``
-    (torch names) plus the scalar fields (epoch, step, config, ...)."""
+    (torch names), ``opt_state`` (``DawnAdamW.load_state_dict`` layout, or None
+    when the file carries no optimizer state) plus the scalar fields (epoch,
+    step, config, ...)."""
     with open(path, "rb") as f:
         raw = msgpack_restore(f.read())
     params = raw.get("params", raw)
     out = {k: v for k, v in raw.items() if k not in ("params", "opt_state")}
     out["state_dict"] = flax_params_to_state_dict(params)
+    out["opt_state"] = None
+    if isinstance(raw.get("opt_state"), dict) and raw["opt_state"]:
+        out["opt_state"] = optax_state_to_torch(raw["opt_state"])
     return out
 
 
-def save_flax_checkpoint(path: str, state_dict: Dict[str, torch.Tensor], **fields) -> None:
-    blob = msgpack_serialize({"params": state_dict_to_flax_params(state_dict), **fields})
+def save_flax_checkpoint(path: str, state_dict: Dict[str, torch.Tensor], opt_state=None,
+                         accumulation_steps: int = 1, **fields) -> None:
+    """Write a ``.flax`` file the reference can load.  ``opt_state`` is a
+    ``DawnAdamW.state_dict()``; without it the field is an empty dict."""
+    tree = {"params": state_dict_to_flax_params(state_dict),
+            "opt_state": {} if opt_state is None else torch_opt_state_to_optax(opt_state, accumulation_steps),
+            **fields}
     with open(path, "wb") as f:
-        f.write(blob)
+        f.write(msgpack_serialize(tree))

@@ -116,6 +116,58 @@ def test_flax_msgpack_roundtrip_and_name_mapping(tmp_path):
     assert sd2["neuron_pool.qk_emb"].shape == sd["neuron_pool.qk_emb"].shape
 
 
+def test_optax_optimizer_state_converts_both_ways(tmp_path):
+    """A hand-built tree in the layout flax.serialization gives an optax chain
+    (tuple -> {"0",...}, NamedTuple -> field dict, EmptyState -> {}), with and
+    without the MultiSteps wrapper, resumes DawnAdamW with its moments and
+    step count; writing it back reproduces the tree."""
+    import numpy as np
+    m = _tiny()
+    names = [n for n, _ in m.named_parameters()]
+    rng = np.random.default_rng(0)
+    sd = m.state_dict()
+    mu = {n: torch.from_numpy(rng.standard_normal(tuple(sd[n].shape)).astype(np.float32)) for n in names}
+    nu = {n: torch.from_numpy(rng.random(tuple(sd[n].shape)).astype(np.float32)) for n in names}
+    acc = {n: torch.from_numpy(rng.standard_normal(tuple(sd[n].shape)).astype(np.float32)) for n in names}
+    chain = {"0": {}, "1": {"count": np.asarray(7, np.int32), "mu": fc.state_dict_to_flax_params(mu),
+                            "nu": fc.state_dict_to_flax_params(nu)},
+             "2": {"inner_state": {}}, "3": {"inner_state": {}}, "4": {"count": np.asarray(7, np.int32)}}
+    wrapped = {"mini_step": np.asarray(1, np.int32), "gradient_step": np.asarray(7, np.int32),
+               "inner_opt_state": chain, "acc_grads": fc.state_dict_to_flax_params(acc), "skip_state": {}}
+    # Dense kernels are stored [in, out] on the reference side
+    assert chain["1"]["mu"]["router"]["proj_attn"]["kernel"].shape == (16, 12)
+    for tree, k in ((chain, 1), (wrapped, 2)):
+        path = str(tmp_path / f"c{k}.flax")
+        open(path, "wb").write(fc.msgpack_serialize(
+            {"params": fc.state_dict_to_flax_params(sd), "opt_state": tree, "epoch": 0, "step": 7 * k + (k - 1),
+             "step_in_epoch": 3, "steps_per_epoch": 10, "best_val_loss": 2.5, "config": {}, "training_config": {}}))
+        blob = fc.load_flax_checkpoint(path)
+        st = blob["opt_state"]
+        assert st["count"] == 7 and st["micro"] == (1 if k == 2 else 0)
+        opt = DawnAdamW(m.named_parameters(), lr=1e-3, fused=False, accumulation_steps=k)
+        opt.load_state_dict(st)
+        assert opt.count == 7 and opt.micro == st["micro"]
+        for (n, _), a, b in zip(opt.named, opt.exp_avg, opt.exp_avg_sq):
+            assert torch.equal(a, mu[n]) and torch.equal(b, nu[n]), n
+        if k == 2:      # the running mean of one micro-step is that micro-step's gradient sum
+            for (n, _), a in zip(opt.named, opt._acc):
+                assert torch.allclose(a, acc[n]), n
+        back = fc.torch_opt_state_to_optax(opt.state_dict(), accumulation_steps=k)
+        flat_a, flat_b = fc.flatten_tree(tree), fc.flatten_tree(back)
+        assert set(flat_a) == set(flat_b)
+        for key in flat_a:
+            assert np.allclose(np.asarray(flat_a[key]), np.asarray(flat_b[key])), key
+    # the command-line converter carries the optimizer state through
+    from dawn_srw_b200.tools import convert_ckpt as cc
+    pt = str(tmp_path / "c.pt")
+    assert cc.main(["flax2pt", str(tmp_path / "c1.flax"), pt]) == 0
+    assert torch.load(pt, weights_only=False)["opt_state"]["count"] == 7
+    assert cc.main(["pt2flax", pt, str(tmp_path / "back.flax")]) == 0
+    again = fc.load_flax_checkpoint(str(tmp_path / "back.flax"))
+    assert again["opt_state"]["count"] == 7
+    assert torch.equal(again["opt_state"]["exp_avg"]["router.proj_attn.weight"], mu["router.proj_attn.weight"])
+
+
 def test_shard_consolidation(tmp_path):
     from dawn_srw_b200.parallel.topology import PoolShard
     full = _tiny()

@@ -166,3 +166,42 @@ def test_out_scale_and_route_accessors():
     assert torch.allclose(sc.grad, a.out.sum())
     listed = SRWResult(out=None, lb=a.lb, dead_penalty=a.dead_penalty, outs=[a.out[:, 0], a.out[:, 1]])
     assert torch.equal(listed.route(0), a.out[:, 0]) and torch.equal(listed.stacked(), a.out)
+
+
+def test_score_statistics_node_matches_autograd_of_the_plain_formula():
+    """tau / 1/sigma / column sums from the Gram matrix, forward and all gradients,
+    against autograd through explicit scores; a zero h row (router dropout, padded
+    rows) must give finite gradients."""
+    from dawn_srw_b200.ops.score_stats import score_stats
+    torch.manual_seed(3)
+    T, R, r, U = 37, 2, 16, 50
+    emb = torch.nn.functional.normalize(torch.randn(U, r), dim=-1)
+    h0 = torch.randn(T, R, r).bfloat16().float()
+    h0[5, 1] = 0.0
+    off0 = torch.randn(T, R) * 0.4
+    wt, wi, wh, wb = torch.randn(T, R), torch.randn(T, R), torch.randn(r), torch.randn(T, R, r).bfloat16().float()
+
+    def loss(tau, isd, hsum, hb):
+        return (tau * wt).sum() + (isd * wi).sum() * 1e-2 + (hsum * wh).sum() + (hb.float() * wb).sum()
+    # node under test
+    h, off = h0.clone().requires_grad_(True), off0.clone().requires_grad_(True)
+    ef = emb.clone().requires_grad_(True)
+    gram, esum = ef.t() @ ef, ef.sum(0)
+    loss(*score_stats(h, off, gram, esum, U)).backward()
+    got = [h.grad.clone(), off.grad.clone(), ef.grad.clone()]
+    # plain formula through the scores
+    h2, off2, ef2 = h0.clone().requires_grad_(True), off0.clone().requires_grad_(True), emb.clone().requires_grad_(True)
+    s = h2 @ ef2.t()                                                    # [T,R,U]
+    mu = s.mean(-1)
+    var = (s * s).mean(-1) - mu * mu
+    sd = torch.sqrt(var.clamp_min(1e-12)) + 1e-8
+    loss(mu + off2 * sd, 1.0 / sd, h2.sum(dim=(0, 1)), h2).backward()
+    want = [h2.grad, off2.grad, ef2.grad]
+    for name, a, b in zip(("dh", "doff", "demb"), got, want):
+        assert torch.isfinite(a).all(), name
+        # the zero row sits exactly at the variance floor, where the two formulations may
+        # legitimately differ; everywhere else they agree to fp32 round-off
+        if name == "dh":
+            a, b = a.clone(), b.clone()
+            a[5, 1], b[5, 1] = 0.0, 0.0
+        assert torch.allclose(a, b, rtol=2e-3, atol=2e-4), (name, (a - b).abs().max())

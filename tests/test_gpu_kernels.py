@@ -195,6 +195,37 @@ def test_srw_op_forward_backward_against_fp32_oracle(cb, version, dims):
     cb.check_status()
 
 
+@pytest.mark.parametrize("dims", [(300, 1, 128, 2600), (129, 2, 256, 6400), (64, 1, 384, 1000)])
+def test_score_statistics_kernels(cb, dims):
+    """tau, 1/sigma, column sums and all gradients of the Gram-matrix statistics:
+    engine GEMMs + row kernels against the same node in plain fp32 torch on the CPU."""
+    from dawn_srw_b200.ops.score_stats import score_stats
+    T, R, r, U = dims
+    torch.manual_seed(T)
+    emb = torch.nn.functional.normalize(torch.randn(U, r), dim=-1).bfloat16().float()
+    h0 = torch.randn(T, R, r).bfloat16().float()
+    h0[3, 0] = 0.0                                   # a zero row sits on the variance floor
+    off0 = torch.randn(T, R) * 0.4
+    wt, wi, wh = torch.randn(T, R), torch.randn(T, R) * 1e-2, torch.randn(r)
+    wb = torch.randn(T, R, r).bfloat16()
+    out = {}
+    for dev in ("cpu", "cuda"):
+        h, off = h0.to(dev).requires_grad_(True), off0.to(dev).requires_grad_(True)
+        gram = (emb.t() @ emb).to(dev).requires_grad_(True)
+        esum = emb.sum(0).to(dev).requires_grad_(True)
+        tau, isd, hsum, hb = score_stats(h, off, gram, esum, U)
+        ((tau * wt.to(dev)).sum() + (isd * wi.to(dev)).sum() + (hsum * wh.to(dev)).sum()
+         + (hb.float() * wb.to(dev).float()).sum()).backward()
+        out[dev] = [t.detach().cpu() for t in (tau, isd, hsum, hb.float(), h.grad, off.grad,
+                                               gram.grad, esum.grad)]
+    cb.check_status()
+    names = ("tau", "isd", "hsum", "hb", "dh", "doff", "dgram", "desum")
+    for n, a, b in zip(names, out["cuda"], out["cpu"]):
+        assert torch.isfinite(a).all(), n
+        tol = 2e-2 if n == "dgram" else 2e-3          # dG multiplies bf16-rounded d_var * h
+        assert _rel(a, b) < tol, (n, _rel(a, b))
+
+
 def test_layernorm_kernel(cb):
     from dawn_srw_b200.ops import reference as R
     dev = torch.device("cuda")

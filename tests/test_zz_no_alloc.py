@@ -88,6 +88,25 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
         prob = _problem(T, U, r, D, seed, dev)
         rc_a, raw_a, den_a = _run(lib, False, prob, gate, status)
         rc_s, raw_s, den_s = _run(lib, True, prob, gate, status)
+        # the contract in the name: once warm, a static call takes no device memory, neither
+        # from the driver nor from torch's allocator (its outputs are allocated before the
+        # measurement, exactly like the caller's own buffers would be)
+        raw2 = torch.empty_like(raw_s)
+        den2 = torch.empty_like(den_s)
+        torch.cuda.synchronize()
+        free0, alloc0 = torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev)
+        h, emb, x, read, write, tau, isd = prob
+        for _ in range(2):
+            rc = lib.dsb_srw_forward_static(
+                _ptr(h), _ll(h.stride(0)), _ptr(emb), _ll(emb.stride(0)), _ptr(x), _ll(x.stride(0)),
+                _ptr(read), _ll(read.stride(0)), _ptr(write), _ll(write.stride(0)), ctypes.c_int(T),
+                ctypes.c_int(U), ctypes.c_int(r), ctypes.c_int(D), _ptr(tau), _ptr(isd), _ptr(raw2),
+                _ll(raw2.stride(0)), _ptr(den2), ctypes.c_void_p(0), ctypes.c_void_p(0),
+                ctypes.byref(gate), _ptr(status), ctypes.c_void_p(0))
+            assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free0 and torch.cuda.memory_allocated(dev) == alloc0
+        assert torch.equal(raw2, raw_s)
         assert rc_a == 0 and rc_s == 0, lib.dsb_srw_forward_static_last_error()
         assert int(status.item()) == 0
         assert torch.isfinite(raw_s).all() and torch.isfinite(den_s).all()
@@ -121,3 +140,29 @@ def test_static_scratch_entry_point_refuses_oversized_problems():
     assert "needs" in msg and "static" in msg
     torch.cuda.synchronize()
     assert int(status.item()) == 0
+
+
+def test_static_scratch_entry_point_at_exactly_its_capacity():
+    """T = 4096 tokens x U = 8192 units needs exactly the 64 MiB the library
+    holds: accepted and correct; eight more (padded) units are refused."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = _lib()
+    T, U, r, D = 4096, 8192, 64, 128
+    assert lib.dsb_srw_forward_static_bytes_needed(T, U) == lib.dsb_srw_forward_static_capacity()
+    assert lib.dsb_srw_forward_static_bytes_needed(T, U + 1) > lib.dsb_srw_forward_static_capacity()
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    gate = DsbGate(1, 500.0, 0.5, 0.01, 1e-4, 10.0, 10.0, 0.01)
+    prob = _problem(T, U, r, D, 5, dev)
+    rc_a, raw_a, den_a = _run(lib, False, prob, gate, status)
+    rc_s, raw_s, den_s = _run(lib, True, prob, gate, status)
+    assert rc_a == 0 and rc_s == 0, lib.dsb_srw_forward_static_last_error()
+    assert int(status.item()) == 0
+    assert ((raw_s - raw_a).norm() / (raw_a.norm() + 1e-12)).item() < 1e-5
+    assert torch.allclose(den_s, den_a, rtol=1e-4, atol=1e-5)
+    null = ctypes.c_void_p(0)
+    rc = lib.dsb_srw_forward_static(null, _ll(8), null, _ll(8), null, _ll(8), null, _ll(8), null, _ll(8),
+                                    ctypes.c_int(T), ctypes.c_int(U + 1), ctypes.c_int(r),
+                                    ctypes.c_int(D), null, null, null, _ll(D), null, null, null,
+                                    ctypes.byref(gate), _ptr(status), null)
+    assert rc == 501
