@@ -50,6 +50,9 @@ def parse():
                     help="partitioned: reduce-scatter + AdamW on the owned slice + all-gather over "
                          "peer memory with sharded moments; auto = partitioned for --parallelism dp")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-shard-check", action="store_true",
+                    help="skip the one-off comparison of the sharded model's loss with the same "
+                         "model unsharded on rank 0 (runs before the warm-up, N > 1 only)")
     ap.add_argument("--profile", metavar="FILE",
                     help="after the timed runs, profile one more step with torch.profiler and "
                          "write the per-kernel device-time table of rank 0 to FILE")
@@ -138,6 +141,53 @@ class ClockSampler:
         return parse_clock_csv(text) or out
 
 
+def sharded_vs_unsharded(trainer, cfg, topo, dev, batch):
+    """Before anything is timed: the deterministic (no dropout) cross-entropy of the
+    sharded model on the global batch against the SAME model (same seed, so the same
+    weights) built unsharded on rank 0 and fed all ranks' sequences.  Returns the two
+    losses and their difference on rank 0 (None elsewhere)."""
+    import copy
+    import torch
+    import torch.distributed as dist
+    from dawn_srw_b200.parallel.topology import Topology
+    from dawn_srw_b200.train.trainer import Trainer
+    ids, mask = batch
+    labels = torch.where(mask == 1, ids, torch.full_like(ids, -100))
+    model = trainer.model
+    was_training = model.training
+    model.eval()
+    with torch.no_grad():
+        r = model(ids, labels=labels, attention_mask=mask, want_diag=False)
+        acc = torch.stack([r["loss"].double() * r["valid_count"], r["valid_count"].double()])
+    model.train(was_training)
+    dist.all_reduce(acc)
+    sharded = float(acc[0] / acc[1])
+    all_ids = [torch.empty_like(ids) for _ in range(topo.world)] if topo.is_main else None
+    all_mask = [torch.empty_like(mask) for _ in range(topo.world)] if topo.is_main else None
+    dist.gather(ids, all_ids, dst=0)
+    dist.gather(mask, all_mask, dst=0)
+    out = None
+    if topo.is_main:
+        cfg1 = copy.deepcopy(cfg)
+        cfg1.training.pool_shards, cfg1.training.seq_shard, cfg1.training.zero_pool_state = 1, False, False
+        cfg1.training.dp = 1
+        ref = Trainer(cfg1, topo=Topology(), device=dev, total_steps=10, build_data=False)
+        ref.model.eval()
+        tot = torch.zeros(2, dtype=torch.float64, device=dev)
+        with torch.no_grad():
+            for i_, m_ in zip(all_ids, all_mask):            # one rank's sequences at a time
+                lab = torch.where(m_ == 1, i_, torch.full_like(i_, -100))
+                rr = ref.model(i_, labels=lab, attention_mask=m_, want_diag=False)
+                tot += torch.stack([rr["loss"].double() * rr["valid_count"], rr["valid_count"].double()])
+        unsharded = float(tot[0] / tot[1])
+        del ref
+        torch.cuda.empty_cache()
+        out = {"sharded": sharded, "unsharded": unsharded, "abs_diff": abs(sharded - unsharded),
+               "ok": abs(sharded - unsharded) < 1e-2}
+    dist.barrier()
+    return out
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -197,6 +247,9 @@ def main():
         torch.cuda.synchronize()
 
     from dawn_srw_b200.ops import cuda_backend as CB
+    shard_check = None
+    if world > 1 and args.impl == "ours" and not args.no_shard_check:
+        shard_check = sharded_vs_unsharded(trainer, cfg, topo, dev, dev_batches[0])
     for i in range(args.warmup):
         trainer.train_step(*dev_batches[i % 4])
     barrier()
@@ -267,6 +320,8 @@ def main():
                        "optimizer": type(trainer.optimizer).__name__},
             "clocks": clocks, "gpu_launches": launches, "final_loss": loss_val,
         }
+        if shard_check is not None:
+            out["sharded_vs_unsharded_ce"] = shard_check
         if e2e:
             out["e2e"] = {"value": tokens_per_step * args.steps / e2e_s, "unit": "tokens/s",
                           "h2d_bytes_per_step": e2e[1], "d2h_bytes_per_step": e2e[2]}

@@ -202,12 +202,13 @@ class DAWN(nn.Module):
         h_qk = h_all[:, : 2 * r].reshape(T, 2, r)
         h_v = h_all[:, 2 * r:].reshape(T, 1, r)
         qk_scale, v_scale = self.pool_scale("qk"), self.pool_scale("v")
-        with trace("attn/srw_qk"):
-            res_qk = be.srw(xf, h_qk, tau_all[:, 0:2], pools["qk"], self.gate,
-                            pctx=self.pctx("qk"), want_diag=want_diag, out_scale=qk_scale)
-        with trace("attn/srw_v"):
-            res_v = be.srw(xf, h_v, tau_all[:, 2:3], pools["v"], self.gate,
-                           pctx=self.pctx("v"), want_diag=want_diag, out_scale=v_scale)
+        with trace("attn/srw_qkv"):
+            # the paired Q/K call and the V call read the same activations: one group
+            res_qk, res_v = be.srw_group(xf, [
+                dict(h=h_qk, tau_off=tau_all[:, 0:2], pool=pools["qk"], pctx=self.pctx("qk"),
+                     out_scale=qk_scale),
+                dict(h=h_v, tau_off=tau_all[:, 2:3], pool=pools["v"], pctx=self.pctx("v"),
+                     out_scale=v_scale)], self.gate, want_diag=want_diag)
         Q, K, V = res_qk.route(0), res_qk.route(1), res_v.route(0)
         dh = D // H
         to_heads = lambda t: t.reshape(B, S, H, dh).transpose(1, 2)
@@ -241,8 +242,9 @@ class DAWN(nn.Module):
             tau = be.linear(xf, rt.tau_know.weight, rt.tau_know.bias).float()         # [T,1]
         k_scale = self.pool_scale("know")
         with trace("know/srw"):
-            res = be.srw(xf, h.reshape(T, 1, self.d_route), tau, pools["know"], self.gate,
-                         pctx=self.pctx("know"), want_diag=want_diag, out_scale=k_scale)
+            (res,) = be.srw_group(xf, [dict(h=h.reshape(T, 1, self.d_route), tau_off=tau,
+                                            pool=pools["know"], pctx=self.pctx("know"),
+                                            out_scale=k_scale)], self.gate, want_diag=want_diag)
         out = res.route(0)
         raw = (out.detach() / k_scale) if want_diag else None     # pre-scale output, diagnostics only
         out_d = be.dropout(out, self.dropout_rate, training).reshape(B, S, D)

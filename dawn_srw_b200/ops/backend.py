@@ -96,6 +96,15 @@ class ReferenceBackend:
             res.out = res.out * out_scale
         return res
 
+    def srw_group(self, x, calls, spec: GateSpec, *, want_diag: bool = True):
+        """Several SRW calls on the same activations ``x`` (the Q/K and V calls of
+        an attention block).  ``calls``: dicts with the keyword arguments of
+        ``srw`` (h, tau_off, pool, pctx, out_scale, unit_mask).  Backends that can
+        share work between the calls override this; the default runs them in turn."""
+        return [self.srw(x, c["h"], c["tau_off"], c["pool"], spec, pctx=c.get("pctx"),
+                         want_diag=want_diag, unit_mask=c.get("unit_mask"),
+                         out_scale=c.get("out_scale")) for c in calls]
+
     def _srw(self, x, h, tau_off, pool, spec, pctx, want_diag, return_gates, unit_mask):
         return srw_pool_ref(
             x, h, tau_off, pool.emb, pool.read, pool.write, spec,

@@ -143,8 +143,20 @@ void srw_forward(const Tensor& h, const Tensor& emb, const Tensor& x, const Tens
 
 struct GatherHolder {
   std::vector<std::vector<const void*>> ptrs;
+  std::vector<std::vector<const void*>> stat_ptrs;
   DsbGather g;
 };
+// stat_lists: for every per-token float4 array, the n_ranks device pointers (as integers)
+void fill_gather_stats(GatherHolder& gh, const std::vector<std::vector<int64_t>>& stat_lists) {
+  TORCH_CHECK(stat_lists.size() <= 3, "at most three statistics arrays travel with a gather");
+  gh.stat_ptrs.resize(stat_lists.size());
+  gh.g.n_stats = static_cast<int>(stat_lists.size());
+  for (size_t s = 0; s < stat_lists.size(); ++s) {
+    TORCH_CHECK(static_cast<int>(stat_lists[s].size()) == gh.g.n_ranks);
+    for (auto p : stat_lists[s]) gh.stat_ptrs[s].push_back(reinterpret_cast<const void*>(p));
+    gh.g.stats[s] = gh.stat_ptrs[s].data();
+  }
+}
 // tensors: list of (peer pointer list, ld, cols) in the order x, h [, dy]
 void fill_gather(GatherHolder& gh, const std::vector<std::vector<int64_t>>& ptr_lists,
                  const std::vector<int64_t>& lds, const std::vector<int64_t>& cols, int64_t my_rank,
@@ -214,14 +226,19 @@ void srw_bwd_gate_gather(const Tensor& h_full, const Tensor& emb, const Tensor& 
 }
 
 // Forward gate kernel with optional extras: xr_out keeps the read scalars for
-// the backward pass; a non-empty ptr_lists (order x, h) fuses the all-gather of
-// the token operands (h / x are then this rank's full buffers).
+// the backward pass; `stats` (float32 [T, 4]: tau, 1/sigma, -, -) replaces tau /
+// inv_sigma; a non-empty ptr_lists fuses the all-gather of the listed bf16 tensors
+// (lds / cols per tensor; h and x are then views of this rank's full buffers) and
+// of the per-token statistics arrays in stat_lists.
 void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const Tensor& read,
-                     Tensor& p_out, c10::optional<Tensor> xr_out, const Tensor& tau,
-                     const Tensor& inv_sigma, Tensor& den_sum, c10::optional<Tensor> alive,
-                     c10::optional<Tensor> unit_mask, std::vector<double> gate, Tensor& status,
-                     std::vector<std::vector<int64_t>> ptr_lists, int64_t my_rank,
-                     int64_t rows_per_rank, c10::optional<Tensor> ready, int64_t epoch) {
+                     Tensor& p_out, c10::optional<Tensor> xr_out, c10::optional<Tensor> tau,
+                     c10::optional<Tensor> inv_sigma, c10::optional<Tensor> stats, Tensor& den_sum,
+                     c10::optional<Tensor> alive, c10::optional<Tensor> unit_mask,
+                     std::vector<double> gate, Tensor& status,
+                     std::vector<std::vector<int64_t>> ptr_lists, std::vector<int64_t> lds,
+                     std::vector<int64_t> cols, std::vector<std::vector<int64_t>> stat_lists,
+                     int64_t my_rank, int64_t rows_per_rank, c10::optional<Tensor> ready,
+                     int64_t epoch) {
   check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(x, "x");
   check_bf16_2d(read, "read"); check_bf16_2d(p_out, "p_out");
   const c10::cuda::CUDAGuard guard(x.device());
@@ -236,6 +253,12 @@ void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const 
     xr_p = xr_out->data_ptr();
     ldxr = xr_out->stride(0);
   }
+  const void* stats_p = nullptr;
+  if (stats.has_value() && stats->defined()) {
+    TORCH_CHECK(stats->is_cuda() && stats->scalar_type() == torch::kFloat32 &&
+                stats->is_contiguous() && stats->numel() >= static_cast<int64_t>(T) * 4);
+    stats_p = stats->data_ptr();
+  }
   unsigned char* alive_p = nullptr;
   if (alive.has_value() && alive->defined()) {
     TORCH_CHECK(alive->scalar_type() == torch::kUInt8 && alive->numel() >= U);
@@ -245,30 +268,32 @@ void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const 
   GatherHolder gh;
   const DsbGather* gp = nullptr;
   if (!ptr_lists.empty()) {
-    TORCH_CHECK(ptr_lists.size() == 2 && ready.has_value());
-    fill_gather(gh, ptr_lists, {x.stride(0), h.stride(0)}, {D, r}, my_rank, rows_per_rank, *ready,
-                epoch);
+    TORCH_CHECK(ptr_lists.size() == lds.size() && lds.size() == cols.size() && ready.has_value());
+    fill_gather(gh, ptr_lists, lds, cols, my_rank, rows_per_rank, *ready, epoch);
+    fill_gather_stats(gh, stat_lists);
     gp = &gh.g;
   }
   int rc = dsb_srw_fwd_gate_xr(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0),
                                x.data_ptr(), x.stride(0), read.data_ptr(), read.stride(0), T, U, r,
-                               D, p_out.data_ptr(), p_out.stride(0), xr_p, ldxr,
-                               tau.data_ptr<float>(), inv_sigma.data_ptr<float>(),
-                               den_sum.data_ptr<float>(), nullptr, alive_p, opt_f32(unit_mask), &g,
-                               gp, status.data_ptr<int>(), cur_stream());
+                               D, p_out.data_ptr(), p_out.stride(0), xr_p, ldxr, opt_f32(tau),
+                               opt_f32(inv_sigma), stats_p, den_sum.data_ptr<float>(), nullptr,
+                               alive_p, opt_f32(unit_mask), &g, gp, status.data_ptr<int>(),
+                               cur_stream());
   TORCH_CHECK(rc == 0, "dsb_srw_fwd_gate_xr failed with code ", rc);
 }
 
-// Backward gate step from saved read scalars.  Gathered tensors (optional), in
-// this order: h_full, dy_full[, x_full]; x_full is not an operand of this
-// kernel, it is only brought in for the GEMMs that follow.
+// Backward gate step from saved read scalars.  `stats` (float32 [T, 4]: tau,
+// 1/sigma, dden, -) replaces the three per-token arrays.  Gathered tensors
+// (optional): any bf16 full buffers (h, dy, and x for the GEMMs that follow).
 void srw_bwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& dy, const Tensor& write,
                      const Tensor& xr, Tensor& p_out, Tensor& dxr_out, Tensor& ds_out,
-                     const Tensor& tau, const Tensor& inv_sigma, const Tensor& dden,
-                     Tensor& dtau_sum, std::vector<double> gate, Tensor& status,
+                     c10::optional<Tensor> tau, c10::optional<Tensor> inv_sigma,
+                     c10::optional<Tensor> dden, c10::optional<Tensor> stats, Tensor& dtau_sum,
+                     std::vector<double> gate, Tensor& status,
                      std::vector<std::vector<int64_t>> ptr_lists, std::vector<int64_t> lds,
-                     std::vector<int64_t> cols, int64_t my_rank, int64_t rows_per_rank,
-                     c10::optional<Tensor> ready, int64_t epoch) {
+                     std::vector<int64_t> cols, std::vector<std::vector<int64_t>> stat_lists,
+                     int64_t my_rank, int64_t rows_per_rank, c10::optional<Tensor> ready,
+                     int64_t epoch) {
   check_bf16_2d(h, "h"); check_bf16_2d(emb, "emb"); check_bf16_2d(dy, "dy");
   check_bf16_2d(write, "write"); check_bf16_2d(xr, "xr");
   check_bf16_2d(p_out, "p_out"); check_bf16_2d(dxr_out, "dxr_out"); check_bf16_2d(ds_out, "ds_out");
@@ -277,21 +302,28 @@ void srw_bwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& dy, const
   TORCH_CHECK(dy.size(0) == T && write.size(0) == U && write.size(1) == D && h.size(1) == r);
   TORCH_CHECK(xr.size(0) == T && xr.size(1) >= U && p_out.size(0) == T && p_out.size(1) >= U);
   TORCH_CHECK(p_out.stride(0) == dxr_out.stride(0) && p_out.stride(0) == ds_out.stride(0));
+  const void* stats_p = nullptr;
+  if (stats.has_value() && stats->defined()) {
+    TORCH_CHECK(stats->is_cuda() && stats->scalar_type() == torch::kFloat32 &&
+                stats->is_contiguous() && stats->numel() >= static_cast<int64_t>(T) * 4);
+    stats_p = stats->data_ptr();
+  }
   DsbGate g = to_gate(gate);
   GatherHolder gh;
   const DsbGather* gp = nullptr;
   if (!ptr_lists.empty()) {
     TORCH_CHECK(ptr_lists.size() == lds.size() && lds.size() == cols.size() && ready.has_value());
     fill_gather(gh, ptr_lists, lds, cols, my_rank, rows_per_rank, *ready, epoch);
+    fill_gather_stats(gh, stat_lists);
     gp = &gh.g;
   }
   int rc = dsb_srw_bwd_gate_xr(h.data_ptr(), h.stride(0), emb.data_ptr(), emb.stride(0),
                                dy.data_ptr(), dy.stride(0), write.data_ptr(), write.stride(0),
                                xr.data_ptr(), xr.stride(0), T, U, r, D, p_out.data_ptr(),
                                dxr_out.data_ptr(), ds_out.data_ptr(), p_out.stride(0),
-                               tau.data_ptr<float>(), inv_sigma.data_ptr<float>(),
-                               dden.data_ptr<float>(), dtau_sum.data_ptr<float>(), &g, gp,
-                               status.data_ptr<int>(), cur_stream());
+                               opt_f32(tau), opt_f32(inv_sigma), opt_f32(dden), stats_p,
+                               dtau_sum.data_ptr<float>(), &g, gp, status.data_ptr<int>(),
+                               cur_stream());
   TORCH_CHECK(rc == 0, "dsb_srw_bwd_gate_xr failed with code ", rc);
 }
 
@@ -302,7 +334,7 @@ bool srw_wide_tiles(int64_t U) { return dsb_srw_wide_tiles(static_cast<int>(U)) 
 void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
                   std::vector<int64_t> out_ptrs, int64_t my_rank, int64_t rows_per_rank,
                   int64_t ldc, bool out_bf16, double alpha, c10::optional<Tensor> row_scale,
-                  Tensor& status) {
+                  Tensor& status, c10::optional<Tensor> aux_src, std::vector<int64_t> aux_ptrs) {
   check_bf16_2d(A, "A");
   check_bf16_2d(B, "B");
   const c10::cuda::CUDAGuard guard(A.device());
@@ -311,10 +343,16 @@ void gemm_scatter(const Tensor& A, bool a_mn, const Tensor& B, bool b_mn,
   const int64_t N = b_mn ? B.size(1) : B.size(0);
   std::vector<void*> outs;
   for (auto p : out_ptrs) outs.push_back(reinterpret_cast<void*>(p));
-  int rc = dsb_gemm_bf16_scatter(A.data_ptr(), a_mn, A.stride(0), B.data_ptr(), b_mn, B.stride(0),
-                                 M, N, K, outs.data(), static_cast<int>(outs.size()), my_rank,
-                                 rows_per_rank, ldc, out_bf16 ? 1 : 0, alpha, opt_f32(row_scale),
-                                 status.data_ptr<int>(), cur_stream());
+  std::vector<float*> auxd;
+  for (auto p : aux_ptrs) auxd.push_back(reinterpret_cast<float*>(p));
+  const float* aux = opt_f32(aux_src);
+  TORCH_CHECK(aux == nullptr || (auxd.size() == outs.size() && aux_src->numel() >= M));
+  int rc = dsb_gemm_bf16_scatter_aux(A.data_ptr(), a_mn, A.stride(0), B.data_ptr(), b_mn,
+                                     B.stride(0), M, N, K, outs.data(),
+                                     static_cast<int>(outs.size()), my_rank, rows_per_rank, ldc,
+                                     out_bf16 ? 1 : 0, alpha, opt_f32(row_scale), aux,
+                                     aux != nullptr ? auxd.data() : nullptr,
+                                     status.data_ptr<int>(), cur_stream());
   TORCH_CHECK(rc == 0, "dsb_gemm_bf16_scatter failed with code ", rc);
 }
 
@@ -329,6 +367,26 @@ Tensor sum_slabs(const Tensor& in, int64_t n_slabs, bool out_bf16) {
                          rows * cols, out.data_ptr(), out_bf16 ? 1 : 0, cur_stream());
   TORCH_CHECK(rc == 0, "dsb_sum_slabs failed with code ", rc);
   return out;
+}
+
+// Owner side of a route's fused reduce-scatter: [n_slabs * rows, cols] bf16 partial
+// outputs and [n_slabs * rows] fp32 partial denominators -> (scale * sum / max(den, 1), den).
+std::vector<Tensor> sum_slabs_div(const Tensor& in, int64_t n_slabs, const Tensor& den_in,
+                                  const Tensor& scale) {
+  TORCH_CHECK(in.is_cuda() && in.dim() == 2 && in.is_contiguous() && in.size(0) % n_slabs == 0 &&
+              in.scalar_type() == torch::kBFloat16);
+  const int64_t rows = in.size(0) / n_slabs, cols = in.size(1);
+  TORCH_CHECK(den_in.scalar_type() == torch::kFloat32 && den_in.is_contiguous() &&
+              den_in.numel() >= n_slabs * rows && scale.scalar_type() == torch::kFloat32 &&
+              scale.numel() == 1 && scale.is_cuda());
+  const c10::cuda::CUDAGuard guard(in.device());
+  auto out = torch::empty({rows, cols}, in.options().dtype(torch::kFloat32));
+  auto den = torch::empty({rows}, in.options().dtype(torch::kFloat32));
+  int rc = dsb_sum_slabs_div(in.data_ptr(), n_slabs, rows, cols, den_in.data_ptr<float>(),
+                             scale.data_ptr<float>(), out.data_ptr<float>(), den.data_ptr<float>(),
+                             cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_sum_slabs_div failed with code ", rc);
+  return {out, den};
 }
 
 void peer_barrier(const Tensor& pads_dev, int64_t rank, int64_t world, int64_t epoch,
@@ -616,6 +674,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("srw_wide_tiles", &srw_wide_tiles);
   m.def("gemm_scatter", &gemm_scatter);
   m.def("sum_slabs", &sum_slabs);
+  m.def("sum_slabs_div", &sum_slabs_div);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("ce_fwd", &ce_fwd);

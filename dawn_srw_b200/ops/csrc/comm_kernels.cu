@@ -214,6 +214,44 @@ __global__ void sum_slabs_kernel(const void* __restrict__ in, int n_slabs, long 
   }
 }
 
+// Owner side of the fused reduce-scatter of a route's output: sums the W partial
+// slabs (bf16) and the W partial denominators of its tokens and divides after the
+// reduction (the reference normalises before its all-reduce of bf16 outputs,
+// models/dawn_spatial_v41_exp.py:579-586; a per-row factor commutes with the sum).
+__global__ void sum_slabs_div_kernel(const __nv_bfloat16* __restrict__ in, int n_slabs, int rows,
+                                     int cols, const float* __restrict__ den_in,
+                                     const float* __restrict__ scale, float* __restrict__ out,
+                                     float* __restrict__ den_out) {
+  const int c8 = cols >> 3;
+  const long long n8 = static_cast<long long>(rows) * c8;
+  const long long slab = static_cast<long long>(rows) * cols;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const float sc = *scale;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += stride) {
+    const int row = static_cast<int>(i / c8);
+    const int cc = static_cast<int>(i - static_cast<long long>(row) * c8);
+    float den = 0.f;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int w = 0; w < n_slabs; ++w) {
+      den += den_in[static_cast<size_t>(w) * rows + row];
+      const uint4 v = reinterpret_cast<const uint4*>(in + w * slab)[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+    const float f = sc / fmaxf(den, 1.f);
+    float4* dst = reinterpret_cast<float4*>(out) + 2 * i;
+    dst[0] = make_float4(acc[0] * f, acc[1] * f, acc[2] * f, acc[3] * f);
+    dst[1] = make_float4(acc[4] * f, acc[5] * f, acc[6] * f, acc[7] * f);
+    if (cc == 0) den_out[row] = den;
+  }
+}
+
 }  // namespace dsb
 
 extern "C" int dsb_peer_barrier(unsigned int* const* pads_dev, int rank, int world,
@@ -280,5 +318,18 @@ extern "C" int dsb_sum_slabs(const void* in, int in_is_bf16, int n_slabs, long l
   else if (in_is_bf16) dsb::sum_slabs_kernel<true, false><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
   else if (out_is_bf16) dsb::sum_slabs_kernel<false, true><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
   else dsb::sum_slabs_kernel<false, false><<<grid, 256, 0, stream>>>(in, n_slabs, n, out);
+  return cudaGetLastError() == cudaSuccess ? 0 : 601;
+}
+
+extern "C" int dsb_sum_slabs_div(const void* in_bf16, int n_slabs, int rows, int cols,
+                                 const float* den_in, const float* scale, float* out,
+                                 float* den_out, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0 || n_slabs <= 0) return 0;
+  if ((cols & 7) || (reinterpret_cast<uintptr_t>(in_bf16) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return 603;
+  const long long n8 = static_cast<long long>(rows) * (cols >> 3);
+  dsb::sum_slabs_div_kernel<<<zero_grid(n8), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(in_bf16), n_slabs, rows, cols, den_in, scale, out, den_out);
   return cudaGetLastError() == cudaSuccess ? 0 : 601;
 }

@@ -67,6 +67,12 @@ struct alignas(64) GatherParams {
   int rows_per_rank;  // multiple of 128
   unsigned int* ready;  // [total_rows / 128] flags in local memory, compared with `epoch`
   unsigned int epoch;
+  // Per-token fp32 quadruples (thresholds, 1/sigma, denominator cotangents, ...) that travel
+  // with the rows: n_stats arrays of float4 [total_rows]; every rank has written its own
+  // block of stat_dst[s], the gather warp copies the peers' blocks with plain 16-byte loads.
+  int n_stats;
+  const float4* stat_src[kMaxGatherTensors][kMaxRanks];
+  float4* stat_dst[kMaxGatherTensors];
 };
 
 template <class EpiParams>
@@ -196,17 +202,26 @@ struct AccCtl {
 // `warp` is the epilogue warp index (0..kEpiWarps-1); its rows are
 // m0 + 32*(warp%4) + lane and, with 8 warps, its columns the (warp/4)-th half.
 
-// Registers per thread: the whole register file divided by the CTA's threads (one
-// CTA per SM), in allocation units of 8.  Stated explicitly because a bound derived
-// from the thread count alone is rounded to a coarser CTA size and leaves a sixth of
-// the file unused for the 10- and 11-warp configurations.
-constexpr int engine_max_regs(int threads) {
-  const int r = (65536 / threads) / 8 * 8;
-  return r > 255 ? 255 : r;
+// Threads per CTA.  With 8 epilogue warps the CTA is padded to three full warpgroups
+// (12 warps; warps 8.. are TMA, MMA, gather and idle) so that registers can be moved
+// between warpgroups: each SM sub-partition holds warps w, w+4 and w+8 and the kernel is
+// launched with 168 registers per thread.  The helper warpgroup gives most of its share
+// back (setmaxnreg.dec) and the two epilogue warpgroups, which keep 128 packed accumulator
+// values per thread, take it (setmaxnreg.inc).
+template <class Epi, bool kGather>
+constexpr int engine_threads() {
+  return Epi::kEpiWarps == 8 ? 384 : (Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32;
 }
+constexpr int kHelperRegs = 88;     // TMA / MMA / gather warps after setmaxnreg.dec
+constexpr int kEpilogueRegs = 208;  // epilogue warps after setmaxnreg.inc
+// Registers only move inside what the CTA was launched with: 168 per thread, i.e. 3 x 168 =
+// 504 per lane of a sub-partition.  A split that asks for more makes setmaxnreg.inc wait for
+// registers that never come, and that wait has no time limit.
+static_assert(2 * kEpilogueRegs + kHelperRegs <= 3 * 168, "register split exceeds the launch allocation");
+static_assert(kEpilogueRegs % 8 == 0 && kHelperRegs % 8 == 0, "setmaxnreg takes multiples of 8");
 
 template <int BN, class Epi, int kCtas, bool kGather = false>
-__global__ void __maxnreg__(engine_max_regs((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32))
+__global__ void __launch_bounds__(engine_threads<Epi, kGather>(), 1)
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   // kCtas == 2: the CTA pair of a 2-CTA cluster shares a 256-row tile.  Each CTA
   // stages its own 128 rows of A and BN/2 rows of B; the leader CTA (cluster
@@ -285,6 +300,10 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   // k-tiles of segment 0 handled by one split (the last split may get fewer)
   const int kt_per_split = (p.seg[0].k_tiles + k_splits - 1) / k_splits;
 
+  if (warp >= kEpiWarps) {
+  // ======================================================= helper warpgroup
+  if constexpr (kEpiWarps == 8)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kHelperRegs));
   if (warp == kTmaWarp) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -424,38 +443,59 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   } else if (kGather && warp == kGatherWarp) {
     // -------------------------------------------------------------- gather
     const GatherParams& g = p.gather;
-    if (lane == 0 && g.n_ranks > 1) {
+    if (g.n_ranks > 1) {
       const int cpr = g.rows_per_rank / 128;               // 128-row chunks per rank
       const int remote = (g.n_ranks - 1) * cpr;
       int slot = 0;
       uint32_t ph[2] = {0u, 0u};
       bool ok = true;
-      for (int rc = blockIdx.x; rc < remote && ok; rc += gridDim.x) {
+      for (int rc = blockIdx.x; rc < remote; rc += gridDim.x) {
         // nearer ranks first; every rank starts with a different peer
         const int owner = (g.my_rank + 1 + rc / cpr) % g.n_ranks;
         const int grow = owner * g.rows_per_rank + (rc % cpr) * 128;
-        for (int t = 0; t < g.n_tensors && ok; ++t) {
-          for (int c0 = 0; c0 < g.cols[t]; c0 += 64) {
-            bulk_wait_read<1>();   // the store that last used this bounce buffer has read it
-            uint8_t* b = gather_buf + slot * kGatherPieceBytes;
-            mbar_expect_tx(&gather_bar[slot], kGatherPieceBytes);
-            tma_load_2d(b, &g.src[t][owner], &gather_bar[slot], c0, grow);
-            if (!mbar_wait(&gather_bar[slot], ph[slot], abort_flag)) { ok = false; break; }
-            ph[slot] ^= 1u;
-            tma_store_2d(&g.dst[t], smem_u32(b), c0, grow);
-            bulk_commit();
-            slot ^= 1;
+        // per-token statistics of the chunk: 128 x 16 bytes per array, all lanes
+        for (int sidx = 0; sidx < g.n_stats; ++sidx) {
+          const float4* src = g.stat_src[sidx][owner] + grow;
+          float4* dst = g.stat_dst[sidx] + grow;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float4 v;
+            asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];"
+                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                         : "l"(src + lane + 32 * k)
+                         : "memory");
+            dst[lane + 32 * k] = v;
           }
         }
+        if (lane == 0) {
+          for (int t = 0; t < g.n_tensors && ok; ++t) {
+            for (int c0 = 0; c0 < g.cols[t]; c0 += 64) {
+              bulk_wait_read<1>();   // the store that last used this bounce buffer has read it
+              uint8_t* b = gather_buf + slot * kGatherPieceBytes;
+              mbar_expect_tx(&gather_bar[slot], kGatherPieceBytes);
+              tma_load_2d(b, &g.src[t][owner], &gather_bar[slot], c0, grow);
+              if (!mbar_wait(&gather_bar[slot], ph[slot], abort_flag)) { ok = false; break; }
+              ph[slot] ^= 1u;
+              tma_store_2d(&g.dst[t], smem_u32(b), c0, grow);
+              bulk_commit();
+              slot ^= 1;
+            }
+          }
+          if (ok) bulk_wait<0>();    // the whole chunk is in local memory
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
-        bulk_wait<0>();            // the whole chunk is in local memory
-        __threadfence();
-        flag_store_release(g.ready + grow / 128, g.epoch);
+        __threadfence();             // every lane's statistics stores, lane 0's tensor rows
+        __syncwarp();
+        if (lane == 0) flag_store_release(g.ready + grow / 128, g.epoch);
       }
-      bulk_wait<0>();
+      if (lane == 0) bulk_wait<0>();
     }
+  }
   } else {
     // ------------------------------------------------------------ epilogue
+    if constexpr (kEpiWarps == 8)
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs));
     int it = 0;
     bool ok = true;
     WarpStager stager{smem_u32(out_stage + warp * Epi::kOutBufs * kOutBufBytes), lane};

@@ -18,7 +18,8 @@ typedef struct DsbGate {
 // Fused all-gather of the token operands of a gate kernel over `n_ranks` GPUs.
 // Tensor t (0: x, 1: h, 2: dy) lives on every rank in a "full" bf16 buffer
 // [n_ranks * rows_per_rank, cols[t]] (ld[t] elements between rows) of which
-// the rank has filled only its own row block; bufs[t] is a HOST array with the
+// the rank has filled only its own row block (the tensors are generic: any bf16
+// operand of the kernel, or of the GEMMs that follow it); bufs[t] is a HOST array with the
 // n_ranks device pointers of those buffers (peer pointers for other ranks).
 // The kernel pulls the missing row blocks into bufs[t][my_rank] while it
 // computes.  `ready` is local device memory with one uint32 per 128 rows and
@@ -30,6 +31,10 @@ typedef struct DsbGather {
   int cols[3];
   unsigned int* ready;
   unsigned int epoch;
+  // optional: n_stats arrays of per-token float4 [n_ranks * rows_per_rank] that are gathered
+  // along with the rows; stats[s] is a HOST array with the n_ranks device pointers
+  int n_stats;
+  const void* const* stats[3];
 } DsbGather;
 
 // C[M,N] (=|+=) alpha * row_scale[m] * (A . B^T)[m,n] + bias[n]
@@ -85,27 +90,30 @@ int dsb_srw_wide_tiles(int U);
 
 // Forward gate kernel that can also keep the read scalars: xr_out (nullable)
 // receives bf16 xr = x.read^T [T, ldxr] next to p.  Needs dsb_srw_wide_tiles(U).
-// gather may be null.
+// gather may be null.  `stats` (nullable; wide kernels only) replaces tau / inv_sigma by
+// one float4 per token (tau, 1/sigma, -, -): the form in which a fused gather brings the
+// per-token constants in together with the rows (DsbGather.stats).
 int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
                         const void* x, long long ldx, const void* read, long long ldr, int T,
                         int U, int r, int D, void* p_out, long long ldp, void* xr_out,
-                        long long ldxr, const float* tau, const float* inv_sigma, float* den_sum,
-                        float* gate_sum, unsigned char* alive, const float* unit_mask,
-                        const DsbGate* gate, const DsbGather* gather /*host*/, int* status,
-                        cudaStream_t stream);
+                        long long ldxr, const float* tau, const float* inv_sigma,
+                        const void* stats, float* den_sum, float* gate_sum, unsigned char* alive,
+                        const float* unit_mask, const DsbGate* gate,
+                        const DsbGather* gather /*host*/, int* status, cudaStream_t stream);
 
 // Backward gate step from the read scalars the forward pass kept: one launch
 // computing S = h.emb^T and DP = dy.write^T, writing p = g*xr, dxr = DP*g and ds
 // (bf16 [T, ld_out]) and accumulating dtau_sum[T] -= sum_U ds.  No x / read
 // operands: xr is read back instead of recomputed.  With a gather, every tensor
-// it lists is pulled under its one epoch.
+// it lists is pulled under its one epoch.  `stats` (nullable): float4 (tau, 1/sigma, dden, -)
+// per token instead of the three arrays.
 int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
                         const void* dy, long long lddy, const void* write, long long ldw,
                         const void* xr, long long ldxr, int T, int U, int r, int D, void* p_out,
                         void* dxr_out, void* ds_out, long long ld_out, const float* tau,
-                        const float* inv_sigma, const float* dden, float* dtau_sum,
-                        const DsbGate* gate, const DsbGather* gather /*host*/, int* status,
-                        cudaStream_t stream);
+                        const float* inv_sigma, const float* dden, const void* stats,
+                        float* dtau_sum, const DsbGate* gate, const DsbGather* gather /*host*/,
+                        int* status, cudaStream_t stream);
 
 // One route of the SRW forward op (gate kernel + write GEMM).  `p_scratch` is
 // caller-provided scratch: bf16 [T, ldp] with ldp >= U and ldp % 8 == 0; its
@@ -127,6 +135,21 @@ int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, const void* B,
                           long long ldb, int M, int N, int K, void* const* outs, int n_ranks,
                           int my_rank, int rows_per_rank, long long ldc, int out_is_bf16,
                           float alpha, const float* row_scale, int* status, cudaStream_t stream);
+// Scatter GEMM that also sends one fp32 value per result row to the row's owner:
+// aux_dsts[j][my_rank * rows_per_rank + local row] = aux_src[row] (aux_dsts: HOST array of
+// n_ranks device pointers to fp32 [n_ranks * rows_per_rank] receive buffers).  Used for the
+// partial per-token denominators / threshold cotangents, which are then summed like the slabs.
+int dsb_gemm_bf16_scatter_aux(const void* A, int a_mn, long long lda, const void* B, int b_mn,
+                              long long ldb, int M, int N, int K, void* const* outs, int n_ranks,
+                              int my_rank, int rows_per_rank, long long ldc, int out_is_bf16,
+                              float alpha, const float* row_scale, const float* aux_src,
+                              float* const* aux_dsts, int* status, cudaStream_t stream);
+// Second half of the fused reduce-scatter of a route's output with the sum-normalisation
+// after the reduction: den[t] = sum_w den_in[w * rows + t];
+// out[t, :] = scale[0] * sum_w in[w][t, :] / max(den[t], 1)   (in bf16 [n_slabs * rows, cols],
+// cols a multiple of 8; out fp32 [rows, cols]; den_out fp32 [rows]; scale: device scalar).
+int dsb_sum_slabs_div(const void* in_bf16, int n_slabs, int rows, int cols, const float* den_in,
+                      const float* scale, float* out, float* den_out, cudaStream_t stream);
 // out[i] = sum_w in[w * n + i], w < n_slabs; in bf16 or fp32, out bf16 or fp32
 // (accumulated in fp32); n a multiple of 8, pointers 16-byte aligned.
 int dsb_sum_slabs(const void* in, int in_is_bf16, int n_slabs, long long n, void* out,

@@ -150,6 +150,11 @@ struct PlainEpi {
     // which remote reduce-adds (atomics) do not.
     int scatter_rows;
     int scatter_rank;
+    // With a scatter: an fp32 value per row of the result (a partial per-token sum such as
+    // the denominator) that goes to the row's owner too: aux_dst[owner][scatter_rank *
+    // scatter_rows + local row] = aux_src[row], written by the tiles of the first column block.
+    const float* aux_src;
+    float* aux_dst[kMaxOut];
   };
   template <int BN, class Ctl>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
@@ -159,6 +164,11 @@ struct PlainEpi {
     const uint32_t acc0 = ctl.wait(0);
     const int row = r0 + lane;
     const float scale = p.alpha * ((row < M && p.row_scale) ? p.row_scale[row] : 1.f);
+    if (p.scatter_rows > 0 && p.aux_src != nullptr && n0 == 0 && row < M) {
+      const int owner = r0 / p.scatter_rows;
+      p.aux_dst[owner][p.scatter_rank * p.scatter_rows + (row - owner * p.scatter_rows)] =
+          p.aux_src[row];
+    }
     int slab = 0;
     if (p.out_bf16) {
 #pragma unroll 1
@@ -231,6 +241,9 @@ struct PlainEpi {
 // Eight epilogue warps: warp w handles rows 32(w%4).. of the tile and the
 // (w/4)-th 64-column half, i.e. exactly one staged slab per tile.
 struct FwdGateParams {
+  // Per-token constants: either two arrays, or (wide kernels with a fused gather) one
+  // float4 per token (tau, 1/sigma, -, -) that the gather warps bring in with the rows.
+  const float4* stats;     // optional [T]
   const float* tau;        // [T]
   const float* inv_sigma;  // [T]
   float* den_sum;          // [T] += sum_U den_term
@@ -482,14 +495,25 @@ struct FwdGateEpiWide {
     if (r0 >= M || col0 >= N) { ctl.skip(); return; }  // warp-uniform
     const int row = r0 + lane;
     const bool row_ok = row < M;
-    const float tau = row_ok ? p.tau[row] : 0.f;
-    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
-    const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
     float den_acc = 0.f, g_acc = 0.f;
     const bool general = (col0 + 128 > N) || p.unit_mask != nullptr || p.alive != nullptr;
     // ---- phase 1: scores -> gate values (bf16 pairs in registers)
     uint32_t gp[64];
     const uint32_t acc_s = ctl.wait(0) + c;
+    // The row constants are read only now: with a fused gather they arrive together with
+    // the rows, which the completed score MMAs of this tile have consumed.
+    float tau = 0.f, isg = 1.f;
+    if (row_ok) {
+      if (p.stats != nullptr) {
+        const float4 sv = __ldcg(p.stats + row);
+        tau = sv.x;
+        isg = sv.y;
+      } else {
+        tau = p.tau[row];
+        isg = p.inv_sigma[row];
+      }
+    }
+    const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
     if (general) phase1<true>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
     else phase1<false>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
     ctl.release(0);   // the next tile's score MMAs may start
@@ -846,11 +870,15 @@ struct BwdGateEpiWide {
 // Everything after that works from registers and overlaps the next tile's MMAs:
 // gate coefficients (g, A1, A2) from the shifted score, then
 //   p = g * xr,   dxr = DP * g,   ds = A1 * (DP * xr) + A2 * dden,   dtau -= ds.
-// A thread reads the 128 xr values of its row straight from global memory, 16
-// at a time and one step ahead of their use (each lane covers whole 32-byte
-// sectors of its own row).  p may be written over xr in place: a thread's reads
-// of a chunk precede the store of the slab that contains it.
+// The xr rows of a slab are fetched into a staging buffer with 16-byte asynchronous
+// copies (8 lanes per row, i.e. full lines; a thread reading its own row straight
+// from global memory measured 1.7x slower for the whole kernel) and p is staged over
+// them chunk by chunk (a thread reads its chunk first), so p may also be written
+// over xr in place in global memory.  The first slab's fetch is issued before the
+// drains and is long complete when it is needed; the second slab's fetch waits for
+// the first slab's p store to leave the buffer and is the one exposed latency.
 struct BwdXrParams {
+  const float4* stats;     // optional [T]: (tau, 1/sigma, dden, -) per token, see FwdGateParams
   const float* tau;        // [T]
   const float* inv_sigma;  // [T]
   const float* dden;       // [T]
@@ -860,21 +888,30 @@ struct BwdXrParams {
   GateConsts gc;
 };
 
-__device__ __forceinline__ uint4 ld_global_v4_stream(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-
 template <int KIND>
 struct BwdGateEpiXr {
   static constexpr int kNumAcc = 2;
   static constexpr int kNumOut = 3;    // p, dxr, ds
-  static constexpr int kOutBufs = 3;   // one staged slab per output
+  static constexpr int kOutBufs = 3;   // 0: xr in, p out (in place); 1: dxr; 2: ds
   static constexpr int kEpiWarps = 8;
   __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
   using Params = BwdXrParams;
+
+  // Asynchronous fetch of one 32-row x 64-column xr slab into a staging buffer, in the
+  // swizzled layout of the TMA boxes: 8 lanes cover the 128 bytes of a row, so every
+  // request is a full line (a thread reading its own row would touch 32 lines per load).
+  __device__ static __forceinline__ void fetch_xr(const Params& p, uint32_t buf, int r0, int colS0,
+                                                  int M, int lane) {
+    const int ch = lane & 7;
+    const int colS = colS0 + ch * 8;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int rr = it * 4 + (lane >> 3);
+      const bool ok = r0 + rr < M && colS < p.ldxr;
+      const __nv_bfloat16* src = ok ? p.xr + static_cast<size_t>(r0 + rr) * p.ldxr + colS : p.xr;
+      cp_async_16(buf + rr * 128 + ((ch ^ (rr & 7)) << 4), src, ok ? 16 : 0);
+    }
+  }
 
   template <int BN, class Ctl>
   __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
@@ -886,24 +923,34 @@ struct BwdGateEpiXr {
     if (r0 >= M || col0 >= N) { ctl.skip(); return; }  // warp-uniform
     const int row = r0 + lane;
     const bool row_ok = row < M;
-    const float tau = row_ok ? p.tau[row] : 0.f;
-    const float isg = row_ok ? p.inv_sigma[row] : 1.f;
-    const float dden = row_ok ? p.dden[row] : 0.f;
-    const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
     const bool tail = col0 + 128 > N;
-    const __nv_bfloat16* xrow = p.xr + static_cast<size_t>(row_ok ? row : 0) * p.ldxr + col0;
-    // 16 xr values (two 16-byte loads) of chunk q; zeros outside the matrix
-    auto load_xr = [&](int q, uint4& u0, uint4& u1) {
-      const int cc = col0 + 16 * q;
-      u0 = (row_ok && cc < p.ldxr) ? ld_global_v4_stream(xrow + 16 * q) : make_uint4(0, 0, 0, 0);
-      u1 = (row_ok && cc + 8 < p.ldxr) ? ld_global_v4_stream(xrow + 16 * q + 8)
-                                       : make_uint4(0, 0, 0, 0);
-    };
+    const uint32_t b_x = st.buf(0), b_dxr = st.buf(1), b_ds = st.buf(2);
+
+    // xr of slab 0 starts moving now; it is needed only after both drains
+    st.wait_free<0>();                            // the previous tile's stores have read the buffers
+    fetch_xr(p, b_x, r0, col0, M, lane);
 
     // ---- drain S: shifted scores as fp16 pairs
     uint32_t zp[64];
+    float isg = 1.f, dden = 0.f;
     {
       const uint32_t acc_s = ctl.wait(0) + c;
+      // row constants, read once the tile's rows (and the statistics that travel with them
+      // under a fused gather) are known to be in place
+      float tau = 0.f;
+      if (row_ok) {
+        if (p.stats != nullptr) {
+          const float4 sv = __ldcg(p.stats + row);
+          tau = sv.x;
+          isg = sv.y;
+          dden = sv.z;
+        } else {
+          tau = p.tau[row];
+          isg = p.inv_sigma[row];
+          dden = p.dden[row];
+        }
+      }
+      const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
       float sb[2][16];
       tmem_ld16(acc_s, sb[0]);
 #pragma unroll
@@ -917,8 +964,6 @@ struct BwdGateEpiXr {
       }
       ctl.release(0);   // the next tile's score MMAs may start
     }
-    uint4 xa, xb;
-    load_xr(0, xa, xb);
     // ---- drain DP: bf16 pairs
     uint32_t dpp[64];
     {
@@ -936,55 +981,62 @@ struct BwdGateEpiXr {
       ctl.release(1);   // the next tile's MMAs may start
     }
 
-    // ---- outputs, from registers
+    // ---- outputs, from registers and the staged xr slab; nothing here holds the tensor core up
     float dtau_acc = 0.f;
-    const uint32_t b_p = st.buf(0), b_dxr = st.buf(1), b_ds = st.buf(2);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const int sl = q >> 2, k0 = 2 * (q & 3);
-      if ((q & 3) == 0) st.wait_free<0>();       // the previous slab's stores have read the buffers
-      const uint4 u0 = xa, u1 = xb;
-      if (q < 7) load_xr(q + 1, xa, xb);
-      const uint32_t xw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-      uint32_t pw[8], dxw[8], dsw[8];
+    for (int sl = 0; sl < 2; ++sl) {
+      cp_async_wait_all();                        // this slab's xr is in shared memory
+      __syncwarp();
+      if (sl == 1) st.wait_free<0>();             // slab 0's dxr / ds stores have read their buffers
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float2 zt = unpack_half2(zp[8 * q + j]);
-        const float2 dp =
-            __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dpp[8 * q + j]));
-        const float2 xr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[j]));
-        float a1x, a2x, a1y, a2y;
-        const float gx = gate_coeffs_shifted<KIND>(p.gc, zt.x, isg, a1x, a2x);
-        const float gy = gate_coeffs_shifted<KIND>(p.gc, zt.y, isg, a1y, a2y);
-        float dsx, dsy;
-        if constexpr (KIND == 2) {
-          dsx = fmaf(a1x, dp.x * xr.x, a2x * dden);
-          dsy = fmaf(a1y, dp.y * xr.y, a2y * dden);
-        } else {
-          dsx = a1x * fmaf(dp.x, xr.x, dden);
-          dsy = a1y * fmaf(dp.y, xr.y, dden);
+      for (int qq = 0; qq < 4; ++qq) {
+        const int q = 4 * sl + qq, k0 = 2 * qq;
+        const uint4 u0 = ld_shared_v4(b_x + lane * 128 + ((k0 ^ (lane & 7)) << 4));
+        const uint4 u1 = ld_shared_v4(b_x + lane * 128 + (((k0 + 1) ^ (lane & 7)) << 4));
+        const uint32_t xw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        uint32_t pw[8], dxw[8], dsw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 zt = unpack_half2(zp[8 * q + j]);
+          const float2 dp =
+              __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dpp[8 * q + j]));
+          const float2 xr = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[j]));
+          float a1x, a2x, a1y, a2y;
+          const float gx = gate_coeffs_shifted<KIND>(p.gc, zt.x, isg, a1x, a2x);
+          const float gy = gate_coeffs_shifted<KIND>(p.gc, zt.y, isg, a1y, a2y);
+          float dsx, dsy;
+          if constexpr (KIND == 2) {
+            dsx = fmaf(a1x, dp.x * xr.x, a2x * dden);
+            dsy = fmaf(a1y, dp.y * xr.y, a2y * dden);
+          } else {
+            dsx = a1x * fmaf(dp.x, xr.x, dden);
+            dsy = a1y * fmaf(dp.y, xr.y, dden);
+          }
+          if (tail) {
+            const int col = col0 + 16 * q + 2 * j;
+            if (col >= N) dsx = 0.f;
+            if (col + 1 >= N) dsy = 0.f;
+          }
+          dtau_acc -= dsx + dsy;
+          pw[j] = pack_bf16x2(gx * xr.x, gy * xr.y);
+          dxw[j] = pack_bf16x2(dp.x * gx, dp.y * gy);
+          dsw[j] = pack_bf16x2(dsx, dsy);
         }
-        if (tail) {
-          const int col = col0 + 16 * q + 2 * j;
-          if (col >= N) dsx = 0.f;
-          if (col + 1 >= N) dsy = 0.f;
-        }
-        dtau_acc -= dsx + dsy;
-        pw[j] = pack_bf16x2(gx * xr.x, gy * xr.y);
-        dxw[j] = pack_bf16x2(dp.x * gx, dp.y * gy);
-        dsw[j] = pack_bf16x2(dsx, dsy);
+        // p goes over the xr chunk this thread has just read
+        st.put(b_x, k0, pw[0], pw[1], pw[2], pw[3]);
+        st.put(b_x, k0 + 1, pw[4], pw[5], pw[6], pw[7]);
+        st.put(b_dxr, k0, dxw[0], dxw[1], dxw[2], dxw[3]);
+        st.put(b_dxr, k0 + 1, dxw[4], dxw[5], dxw[6], dxw[7]);
+        st.put(b_ds, k0, dsw[0], dsw[1], dsw[2], dsw[3]);
+        st.put(b_ds, k0 + 1, dsw[4], dsw[5], dsw[6], dsw[7]);
       }
-      st.put(b_p, k0, pw[0], pw[1], pw[2], pw[3]);
-      st.put(b_p, k0 + 1, pw[4], pw[5], pw[6], pw[7]);
-      st.put(b_dxr, k0, dxw[0], dxw[1], dxw[2], dxw[3]);
-      st.put(b_dxr, k0 + 1, dxw[4], dxw[5], dxw[6], dxw[7]);
-      st.put(b_ds, k0, dsw[0], dsw[1], dsw[2], dsw[3]);
-      st.put(b_ds, k0 + 1, dsw[4], dsw[5], dsw[6], dsw[7]);
-      if ((q & 3) == 3) {
-        const bool in_range = col0 + 64 * sl < N;
-        st.flush(&maps[0], b_p, col0 + 64 * sl, r0, false, in_range);
-        st.flush(&maps[1], b_dxr, col0 + 64 * sl, r0, false, in_range);
-        st.flush(&maps[2], b_ds, col0 + 64 * sl, r0, false, in_range);
+      const bool in_range = col0 + 64 * sl < N;
+      st.flush(&maps[0], b_x, col0 + 64 * sl, r0, false, in_range);      // p first: its buffer
+      st.flush(&maps[1], b_dxr, col0 + 64 * sl, r0, false, in_range);    // is wanted back soonest
+      st.flush(&maps[2], b_ds, col0 + 64 * sl, r0, false, in_range);
+      if (sl == 0) {
+        st.wait_free<2>();                        // the p store has read the buffer ...
+        fetch_xr(p, b_x, r0, col0 + 64, M, lane); // ... which takes the second slab's xr
       }
     }
     if (row_ok) atomicAdd(p.dtau_sum + row, dtau_acc);
@@ -1027,7 +1079,7 @@ static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t
   const int grid = kCtas * static_cast<int>(total < units ? total : units);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3((Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32);
+  cfg.blockDim = dim3(engine_threads<Epi, kGather>());
   cfg.dynamicSmemBytes = Smem::kTotalBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1094,6 +1146,15 @@ static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int*
       if (rc) return 710 + rc;
     }
     g->dst[t] = g->src[t][d->my_rank];
+  }
+  if (d->n_stats < 0 || d->n_stats > kMaxGatherTensors) return 704;
+  g->n_stats = d->n_stats;
+  for (int sidx = 0; sidx < d->n_stats; ++sidx) {
+    for (int j = 0; j < d->n_ranks; ++j) {
+      if (reinterpret_cast<uintptr_t>(d->stats[sidx][j]) & 15) return 705;
+      g->stat_src[sidx][j] = static_cast<const float4*>(d->stats[sidx][j]);
+    }
+    g->stat_dst[sidx] = const_cast<float4*>(g->stat_src[sidx][d->my_rank]);
   }
   *m_rot = d->my_rank * d->rows_per_rank / (2 * kBlockM);
   return 0;
@@ -1208,7 +1269,7 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   gp.status = status;
   rc = make_out_tmap(&gp.tma_out[0], C, M, N, ldc, c_is_bf16 ? 2 : 4);
   if (rc) return 300 + rc;
-  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, 0, 0};
+  gp.epi = {alpha, row_scale, bias, c_is_bf16, accumulate, 0, 0, nullptr, {}};
   if (accumulate && !c_is_bf16 && bias == nullptr) {
     // few output tiles but a long K (pool gradients of a small unit shard): cut K so
     // that every SM pair has work; the splits meet in the fp32 reduce-add epilogue
@@ -1239,8 +1300,8 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
                                 float* gate_sum, unsigned char* alive, const float* unit_mask,
                                 const DsbGate* gate, int* status, cudaStream_t stream) {
   return dsb_srw_fwd_gate_xr(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, nullptr, 0,
-                             tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, gate, nullptr,
-                             status, stream);
+                             tau, inv_sigma, nullptr, den_sum, gate_sum, alive, unit_mask, gate,
+                             nullptr, status, stream);
 }
 
 extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void* emb,
@@ -1252,8 +1313,8 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
                                        const DsbGate* gate, const DsbGather* gather, int* status,
                                        cudaStream_t stream) {
   return dsb_srw_fwd_gate_xr(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, nullptr, 0,
-                             tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, gate, gather,
-                             status, stream);
+                             tau, inv_sigma, nullptr, den_sum, gate_sum, alive, unit_mask, gate,
+                             gather, status, stream);
 }
 
 extern "C" int dsb_srw_wide_tiles(int U) {
@@ -1278,8 +1339,8 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
                                    const void* x, long long ldx, const void* read, long long ldr,
                                    int T, int U, int r, int D, void* p_out, long long ldp,
                                    void* xr_out, long long ldxr, const float* tau,
-                                   const float* inv_sigma, float* den_sum, float* gate_sum,
-                                   unsigned char* alive, const float* unit_mask,
+                                   const float* inv_sigma, const void* stats, float* den_sum,
+                                   float* gate_sum, unsigned char* alive, const float* unit_mask,
                                    const DsbGate* gate, const DsbGather* gather, int* status,
                                    cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
@@ -1289,6 +1350,8 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
   // 256-wide tiles (CTA pairs only) once the pool is wide enough to fill the machine with them
   const bool wide = dsb_srw_wide_tiles(U) != 0;
   if (xr_out != nullptr && !wide) return 704;   // only the wide kernel writes the read scalars
+  if (stats != nullptr && !wide) return 706;    // ... and reads per-token float4 statistics
+  if (stats == nullptr && (tau == nullptr || inv_sigma == nullptr)) return 707;
   const int brows = wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
@@ -1304,7 +1367,8 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
   rc = make_out_tmap(&gp.tma_out[0], p_out, T, U, ldp, 2);
   if (xr_out != nullptr) rc |= make_out_tmap(&gp.tma_out[1], xr_out, T, U, ldxr, 2);
   if (rc) return 300 + rc;
-  gp.epi = {tau, inv_sigma, den_sum, gate_sum, alive, unit_mask, make_gc(gate)};
+  gp.epi = {static_cast<const float4*>(stats), tau, inv_sigma, den_sum, gate_sum, alive, unit_mask,
+            make_gc(gate)};
   const bool fused = gather != nullptr && gather->n_ranks > 1;
   if (fused) {
     if (!use_cta_pairs()) return 702;
@@ -1334,10 +1398,12 @@ extern "C" int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb
                                    long long ldw, const void* xr, long long ldxr, int T, int U,
                                    int r, int D, void* p_out, void* dxr_out, void* ds_out,
                                    long long ld_out, const float* tau, const float* inv_sigma,
-                                   const float* dden, float* dtau_sum, const DsbGate* gate,
-                                   const DsbGather* gather, int* status, cudaStream_t stream) {
+                                   const float* dden, const void* stats, float* dtau_sum,
+                                   const DsbGate* gate, const DsbGather* gather, int* status,
+                                   cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   if (!dsb_srw_wide_tiles(U)) return 704;
+  if (stats == nullptr && (tau == nullptr || inv_sigma == nullptr || dden == nullptr)) return 707;
   if (xr == nullptr || ldxr < U || (ldxr & 7) != 0 || (reinterpret_cast<uintptr_t>(xr) & 15) != 0)
     return 705;
   GemmParams<BwdXrParams> gp;
@@ -1358,8 +1424,8 @@ extern "C" int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb
   rc |= make_out_tmap(&gp.tma_out[1], dxr_out, T, U, ld_out, 2);
   rc |= make_out_tmap(&gp.tma_out[2], ds_out, T, U, ld_out, 2);
   if (rc) return 300 + rc;
-  gp.epi = {tau, inv_sigma, dden, dtau_sum, reinterpret_cast<const __nv_bfloat16*>(xr), ldxr,
-            make_gc(gate)};
+  gp.epi = {static_cast<const float4*>(stats), tau, inv_sigma, dden, dtau_sum,
+            reinterpret_cast<const __nv_bfloat16*>(xr), ldxr, make_gc(gate)};
   const bool fused = gather != nullptr && gather->n_ranks > 1;
   if (fused) {
     rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
@@ -1470,6 +1536,18 @@ extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, con
                                      int rows_per_rank, long long ldc, int out_is_bf16,
                                      float alpha, const float* row_scale, int* status,
                                      cudaStream_t stream) {
+  return dsb_gemm_bf16_scatter_aux(A, a_mn, lda, B, b_mn, ldb, M, N, K, outs, n_ranks, my_rank,
+                                   rows_per_rank, ldc, out_is_bf16, alpha, row_scale, nullptr,
+                                   nullptr, status, stream);
+}
+
+extern "C" int dsb_gemm_bf16_scatter_aux(const void* A, int a_mn, long long lda, const void* B,
+                                         int b_mn, long long ldb, int M, int N, int K,
+                                         void* const* outs, int n_ranks, int my_rank,
+                                         int rows_per_rank, long long ldc, int out_is_bf16,
+                                         float alpha, const float* row_scale,
+                                         const float* aux_src, float* const* aux_dsts,
+                                         int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (n_ranks < 1 || n_ranks > kMaxOut || rows_per_rank % 32 != 0 || my_rank < 0 ||
       my_rank >= n_ranks || static_cast<long long>(n_ranks) * rows_per_rank != M)
@@ -1491,7 +1569,11 @@ extern "C" int dsb_gemm_bf16_scatter(const void* A, int a_mn, long long lda, con
   gp.M = M;
   gp.N = N;
   gp.status = status;
-  gp.epi = {alpha, row_scale, nullptr, out_is_bf16 ? 1 : 0, 0, rows_per_rank, my_rank};
+  gp.epi = {alpha, row_scale, nullptr, out_is_bf16 ? 1 : 0, 0, rows_per_rank, my_rank, nullptr, {}};
+  if (aux_src != nullptr && aux_dsts != nullptr) {
+    gp.epi.aux_src = aux_src;
+    for (int j = 0; j < n_ranks; ++j) gp.epi.aux_dst[j] = aux_dsts[j];
+  }
   // Every rank starts with the rows of a different owner (rank+1, rank+2, ..., itself last), so
   // at any moment the ranks store to distinct peers instead of all converging on one GPU.
   const int tile_m = (use_cta_pairs() ? 2 : 1) * kBlockM;

@@ -155,6 +155,10 @@ class _XrBudget:
 
 XR_BUDGET = _XrBudget()
 
+# trailing arguments of the gate-kernel bindings when no all-gather is fused in:
+# (ptr_lists, lds, cols, stat_lists, my_rank, rows_per_rank, ready, epoch)
+NO_GATHER = ([], [], [], [], 0, 0, None, 0)
+
 
 def _alloc_saved_xr(dev, T: int, Up: int, U: int, wanted: bool):
     """bf16 [T, Up] buffer for the read scalars of one route if the pool runs on
@@ -358,8 +362,8 @@ def _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den, hd, spec, U, xr=Non
         dxr = torch.empty_like(p)
         ds = torch.empty_like(p)
         count_launches(1)
-        e.srw_bwd_gate_xr(h_bf, emb, dy, write, xr, p, dxr, ds, tau, inv_sd, d_den, dtau,
-                          _gate_list(spec), status_word(dev), [], [], [], 0, 0, None, 0)
+        e.srw_bwd_gate_xr(h_bf, emb, dy, write, xr, p, dxr, ds, tau, inv_sd, d_den, None, dtau,
+                          _gate_list(spec), status_word(dev), *NO_GATHER)
     else:
         p = torch.empty(T, Up, dtype=torch.bfloat16, device=dev)
         dxr = torch.empty_like(p)
@@ -432,8 +436,8 @@ class _SRWRouteScaledFn(torch.autograd.Function):
         xr = _alloc_saved_xr(dev, T, Up, U, getattr(holder, "keep_xr", True) and unit_mask is None
                              and any(ctx.needs_input_grad))
         count_launches(2)
-        e.srw_fwd_gate_xr(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, xr, tau, inv_sd, den,
-                          alive, unit_mask, _gate_list(spec), status_word(dev), [], 0, 0, None, 0)
+        e.srw_fwd_gate_xr(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, xr, tau, inv_sd, None, den,
+                          alive, unit_mask, _gate_list(spec), status_word(dev), *NO_GATHER)
         rs = (scale.detach().float() / den.clamp(min=1.0)).contiguous()
         y = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32, row_scale=rs)
         ctx.save_for_backward(x_bf, h_bf, tau, inv_sd, y, den, rs, scale)
@@ -751,6 +755,123 @@ class CudaBackend:
                 res.out = res.out * out_scale
             return res
         return self._srw_local(x, h, tau_off, pool, spec, pctx, want_diag, unit_mask, out_scale)
+
+    def srw_group(self, x, calls, spec: GateSpec, *, want_diag: bool = True):
+        """Several SRW calls on the same ``x``.  Sequence- and pool-sharded calls on
+        the wide kernels run as ONE group through parallel/fused_group.py: ``x`` is
+        gathered once, two barriers per direction for the whole group, per-token
+        statistics and denominators travel inside the kernels (no library
+        collective).  Everything else runs call by call."""
+        if self._group_ok(x, calls, spec):
+            return self._srw_group_fused(x, calls, spec, want_diag)
+        return [self.srw(x, c["h"], c["tau_off"], c["pool"], spec, pctx=c.get("pctx"),
+                         want_diag=want_diag, unit_mask=c.get("unit_mask"),
+                         out_scale=c.get("out_scale")) for c in calls]
+
+    def _group_ok(self, x, calls, spec) -> bool:
+        if not self.fused_comm or not calls:
+            return False
+        from .gates import GATE_GELU_Z  # noqa: F401
+        pc0 = calls[0].get("pctx") or ParallelCtx()
+        nsh = C.group_size(pc0.shard_group)
+        if nsh <= 1 or nsh > 8 or not pc0.seq_sharded:
+            return False
+        n_routes = sum(c["h"].shape[1] for c in calls)
+        if n_routes > 3 or x.shape[0] % 256 != 0 or x.shape[1] % 64 != 0:
+            return False
+        for c in calls:
+            pc = c.get("pctx") or ParallelCtx()
+            if pc.shard_group is not pc0.shard_group or not pc.seq_sharded:
+                return False
+            if c["h"].shape[-1] % 64 != 0 or not ext().srw_wide_tiles(c["pool"].extra["U"]):
+                return False
+            if c.get("unit_mask") is not None and torch.is_grad_enabled():
+                return False            # masked (ablation) forwards have no backward on this path
+        return True
+
+    def _srw_group_fused(self, x, calls, spec, want_diag):
+        from ..parallel.fused_group import GroupShardComm, route_group
+        pc0 = calls[0]["pctx"]
+        grp = pc0.shard_group
+        nsh = C.group_size(grp)
+        Tl, D = x.shape
+        r = calls[0]["h"].shape[-1]
+        key = ("group", id(grp), Tl, D, r)
+        comm = self._comm.get(key)
+        if comm is None:
+            comm = self._comm[key] = GroupShardComm(grp, x.device, Tl, D, r)
+        x_bf = _bf16_2d(x)
+        hs, taus, isds, holders, units, anchors, scales, alives, masks, per_call = \
+            [], [], [], [], [], [], [], [], [], []
+        hsums = []
+        for c in calls:
+            pool, pctx = c["pool"], c["pctx"]
+            ex = pool.extra
+            U = ex["U"]
+            U_tot = pctx.n_total if pctx.n_total is not None else U * nsh
+            tau, inv_sd, hsum, h_bf3 = score_stats(c["h"], c["tau_off"], ex["gram"], ex["esum"], U_tot,
+                                                   ex["gram_split"])
+            Rr = h_bf3.shape[1]
+            hs.append(h_bf3)
+            taus.append(tau)
+            isds.append(inv_sd)
+            hsums.append(hsum)
+            anchors.append(ex["anchor"])
+            sc = c.get("out_scale")
+            if sc is None:
+                sc = torch.ones((), device=x.device)
+            elif not isinstance(sc, torch.Tensor):
+                sc = torch.full((), float(sc), device=x.device)
+            alive = torch.zeros(U, dtype=torch.uint8, device=x.device) if spec.has_dead_penalty else None
+            um = c.get("unit_mask")
+            um = None if um is None else um[:U].float().contiguous()
+            for _ in range(Rr):
+                holders.append(pool)
+                units.append(U)
+                scales.append(sc)
+                alives.append(alive)
+                masks.append(um)
+            per_call.append((Rr, U, U_tot, alive))
+        # per-unit mean scores need the column sums of h over ALL tokens of the group: one
+        # small all-reduce for every pool of the group
+        hsum_all = C.sum_over_shards(torch.stack(hsums), grp)
+        outs, dens = route_group(x_bf, torch.cat(hs, dim=1), torch.cat(taus, dim=1),
+                                 torch.cat(isds, dim=1), comm, spec, holders, units, anchors, scales,
+                                 alives, masks)
+        m_us, parts = [], []
+        for k, (c, (Rr, U, U_tot, alive)) in enumerate(zip(calls, per_call)):
+            hbar = hsum_all[k] / float(Tl * nsh * Rr)
+            m_u = _PoolMatVecFn.apply(hbar, anchors[k], c["pool"], U)
+            m_us.append(m_u)
+            parts.append(torch.stack([C.mean_over_group(m_u.sum(), c["pctx"].dp_group),
+                                      C.mean_over_group((m_u * m_u).sum(), c["pctx"].dp_group)]))
+        ns = C.sum_over_shards(torch.stack(parts), grp)          # [calls, 2], one all-reduce
+        results, i0 = [], 0
+        for k, (c, (Rr, U, U_tot, alive)) in enumerate(zip(calls, per_call)):
+            mean_score = ns[k, 0] / U_tot
+            var_score = ns[k, 1] / U_tot - mean_score ** 2
+            lb = var_score / (mean_score ** 2 + var_score + 1e-2)
+            dead_pen = x.new_zeros(())
+            if spec.has_dead_penalty:
+                # a unit is alive if any token of the whole batch gates it: every rank of the
+                # shard group sees all tokens of its own units, so only data-parallel replicas
+                # need to be combined
+                al = C.all_reduce_nograd(alive.float(), c["pctx"].dp_group, "max")
+                dead = (al < 0.5).float()
+                ms = C.mean_over_group(m_us[k], c["pctx"].dp_group)
+                dead_pen = C.sum_over_shards((torch.relu(-ms) * dead).sum(), grp)
+            o = outs[i0:i0 + Rr]
+            den = torch.stack(dens[i0:i0 + Rr], dim=1).clamp(min=1.0)
+            diag = {}
+            if want_diag:
+                with torch.no_grad():
+                    diag = self._srw_library(x.detach(), c["h"].detach(), c["tau_off"].detach(),
+                                             c["pool"], spec, c["pctx"], True, False,
+                                             c.get("unit_mask")).diag
+            results.append(SRWResult(out=o[0].unsqueeze(1) if Rr == 1 else None, lb=lb,
+                                     dead_penalty=dead_pen, diag=diag, den=den, outs=list(o)))
+            i0 += Rr
+        return results
 
     def _srw_local(self, x, h, tau_off, pool, spec, pctx, want_diag, unit_mask, out_scale):
         """Unsharded pools: statistics, then per route the gate kernel and the

@@ -112,7 +112,7 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         inv_den = (scale.detach().float() / den.clamp(min=1.0)).contiguous()   # pool scale folded in
         tgt = c.out_rs[c.next_rs("out")]
         e.gemm_scatter(p[:, :U], False, holder.write[:U], True, tgt.ptrs, c.rank, Tl, D, True, 1.0,
-                       inv_den, st)
+                       inv_den, st, None, [])
         c.ws.barrier()                                   # every rank's partial rows have landed
         out = e.sum_slabs(tgt.local, c.world, False)     # fp32 [Tl, D]
         CB.count_launches(1)
@@ -165,8 +165,8 @@ class _SRWRouteGatherFn(torch.autograd.Function):
         bi = c.next_rs("dx")
         dxt, dht = c.dx_rs[bi], c.dh_rs[bi]
         CB._LAUNCHES += 2
-        e.gemm_scatter(dxrv, False, read, True, dxt.ptrs, c.rank, Tl, D, True, 1.0, None, st)   # dxr . read
-        e.gemm_scatter(dsv, False, emb, True, dht.ptrs, c.rank, Tl, r, True, 1.0, None, st)     # ds . emb
+        e.gemm_scatter(dxrv, False, read, True, dxt.ptrs, c.rank, Tl, D, True, 1.0, None, st, None, [])   # dxr . read
+        e.gemm_scatter(dsv, False, emb, True, dht.ptrs, c.rank, Tl, r, True, 1.0, None, st, None, [])     # ds . emb
         c.ws.barrier()
         dx = e.sum_slabs(dxt.local, c.world, True)       # bf16 [Tl, D]
         dh32 = e.sum_slabs(dht.local, c.world, False)    # fp32 [Tl, r]

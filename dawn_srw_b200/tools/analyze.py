@@ -40,8 +40,28 @@ dict; the selection mirrors the SRW part of the reference's analysis CLI
   cross_suppress  effect of suppressing the most-used units of one pool on the loss and on the
                activity of the other pools
 
+  r1           Q / K specialisation of the shared pool (q_ratio thresholds 0.7 / 0.3)
+  r2           token-class selectivity of the knowledge units, specialists per class
+  r3           knowledge units by contrastive score (target text vs the rest)
+  r4           layer balance: attention vs knowledge output norm, averaged over the sample
+  r5           suppression sweep of the top contrastive units (1 / 3 / 5 / 10 %) vs random
+  rw_proj      read / write vectors against the token embeddings (what a unit reads / writes)
+  act_context  contexts in which the most-used knowledge units open most strongly
+  gate_mech    denominator statistics, floor activity, top-1 share of the gate mass
+  comp_expr    effective rank of the write vectors spanned by a token's active set
+  neuron_cluster  k-means clusters in emb / read / write space and their co-activation lift
+  deep         corrective (cos(r,w) < -0.5) vs neutral vs amplifying units: selection and gate share
+  op_space     diversity of the router projections, uniqueness of active sets, emb geometry
+  compose      knowledge output split into corrective / neutral / amplifying contributions
+  phase        phase boundary and baseline crossover from training logs (--dawn-log, --baseline-log)
+  combo        distinct active sets, reuse entropy
+  dom_supp     class-targeted vs random suppression with a selectivity index
+  rw_func      cos(read, write) bins against selection frequency and gate mass
+  tau_grad     gradient reaching the tau heads from the task loss vs from the auxiliary loss
+  rw_cov       alias for read_cov,write_cov
+
 All analyses run on one device through the model's public inference API
-(models/inference.py).
+(models/inference.py); the second half of the list lives in tools/analyze_ext.py.
 """
 from __future__ import annotations
 
@@ -508,10 +528,17 @@ SPATIAL_ONLY = {"health", "weights", "routing", "gate_dist", "utilization", "sel
                 "sel_trans", "gate_ci", "read_cov", "write_cov", "samples", "resid_dyn", "z_dist",
                 "addit", "cross_suppress"}
 
+from .analyze_ext import EXTRA_ANALYSES, NEEDS_GRAD  # noqa: E402  (second half of the suite)
+ANALYSES.update(EXTRA_ANALYSES)
+SPATIAL_ONLY |= set(EXTRA_ANALYSES) - {"phase"}
+# meta keys of the reference's CLI: rw_cov = read_cov + write_cov
+ALIASES = {"rw_cov": ["read_cov", "write_cov"]}
+
 
 def run(model, cfg, info, args) -> Dict:
     keys = [k for k in (args.only.split(",") if args.only else ANALYSES) if k]
-    skip = set(args.skip.split(",")) if args.skip else set()
+    keys = [kk for k in keys for kk in ALIASES.get(k, [k])]
+    skip = {kk for k in (args.skip.split(",") if args.skip else []) for kk in ALIASES.get(k, [k])}
     unknown = [k for k in keys if k not in ANALYSES]
     if unknown:
         raise SystemExit(f"unknown analysis key(s) {unknown}; choose from {sorted(ANALYSES)}")
@@ -520,8 +547,11 @@ def run(model, cfg, info, args) -> Dict:
     for k in keys:
         if k in skip or (k in SPATIAL_ONLY and not cfg.model.is_spatial):
             continue
-        with torch.no_grad():
+        if k in NEEDS_GRAD:
             results[k] = ANALYSES[k](ctx)
+        else:
+            with torch.no_grad():
+                results[k] = ANALYSES[k](ctx)
     return results
 
 
@@ -542,6 +572,13 @@ def main(argv=None):
     ap.add_argument("--top-k", type=int, default=50)
     ap.add_argument("--suppress-top", type=int, nargs="*", default=[16, 128])
     ap.add_argument("--compare-checkpoint")
+    ap.add_argument("--target-prompt", action="append",
+                    help="target text of the contrastive analyses r3 / r5 (needs the tokenizer)")
+    ap.add_argument("--p6-samples", type=int, default=32, help="token samples of comp_expr")
+    ap.add_argument("--dom-supp-levels", default="0.01,0.05",
+                    help="comma-separated suppression fractions of dom_supp")
+    ap.add_argument("--dawn-log", help="training metrics (JSONL or CSV) for the phase analysis")
+    ap.add_argument("--baseline-log", help="a baseline run's metrics for the crossover step")
     ap.add_argument("--output")
     ap.add_argument("--library", action="store_true")
     ap.add_argument("--device")

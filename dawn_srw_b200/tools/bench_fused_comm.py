@@ -151,7 +151,7 @@ def main(argv=None):
             outbf = torch.empty(Tl, D, dtype=bf, device=dev)
 
             def fused_rs():
-                e.gemm_scatter(p, False, write, True, tgt.ptrs, rank, Tl, D, True, 1.0, None, st)
+                e.gemm_scatter(p, False, write, True, tgt.ptrs, rank, Tl, D, True, 1.0, None, st, None, [])
                 ws.barrier()
                 e.sum_slabs(tgt.local, world, False)
 

@@ -100,14 +100,14 @@ def main(argv=None):
     for it in range(args.iters):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         ev[0].record()
-        e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau, isd, den, None, None, gl, st, [], 0, 0, None, 0)
+        e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau, isd, None, den, None, None, gl, st, *CB.NO_GATHER)
         ev[1].record()
         CB.gemm(p[:, :U], False, write, True, out=raw)
         ev[2].record()
         if keep:
             # p overwrites the kept read scalars in place, as in training
-            e.srw_bwd_gate_xr(h, emb, dy, write, xr, xr, dxr, ds, tau, isd, dden, dtau, gl, st,
-                              [], [], [], 0, 0, None, 0)
+            e.srw_bwd_gate_xr(h, emb, dy, write, xr, xr, dxr, ds, tau, isd, dden, None, dtau, gl, st,
+                              *CB.NO_GATHER)
         else:
             e.srw_bwd_gate(h, emb, x, read, dy, write, p, dxr, ds, tau, isd, dden, dtau, dsz, gl, st)
         ev[3].record()

@@ -4,7 +4,7 @@ profilers and device-timed per-range totals for the trainer's own report.
 Both are off by default and cost one dictionary lookup per range when off.
 
 * ``DAWN_NVTX=1`` (or ``enable(nvtx=True)``): every range pushes / pops an NVTX
-  range on CUDA, so Nsight tools show ``attn/srw_qk``, ``know/srw`` ... on the
+  range on CUDA, so Nsight tools show ``attn/srw_qkv``, ``know/srw`` ... on the
   timeline.
 * ``enable(timers=True)``: every range is bracketed by CUDA events on the
   current stream (``perf_counter`` on CPU); ``report()`` synchronises once and
@@ -43,7 +43,7 @@ def active() -> bool:
 
 @contextlib.contextmanager
 def trace(name: str):
-    """``with trace("attn/srw_qk"): ...``"""
+    """``with trace("attn/srw_qkv"): ...``"""
     if not (_STATE["nvtx"] or _STATE["timers"]):
         yield
         return

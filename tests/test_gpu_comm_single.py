@@ -34,7 +34,7 @@ def test_scatter_gemm_and_slab_sum_emulating_three_ranks(cb):
             A = torch.randn(M, K, device=dev, generator=g).bfloat16()
             B = torch.randn(N, K, device=dev, generator=g).bfloat16()
             rs = torch.rand(M, device=dev, generator=g) + 0.5
-            e.gemm_scatter(A, False, B, False, ptrs, rank, rows, N, dt == torch.bfloat16, 1.0, rs, st)
+            e.gemm_scatter(A, False, B, False, ptrs, rank, rows, N, dt == torch.bfloat16, 1.0, rs, st, None, [])
             want += (A.float() @ B.float().t()) * rs[:, None]
         for owner in range(W):
             assert not torch.isnan(recv[owner].float()).any()          # every slot row was written

@@ -131,7 +131,7 @@ def test_gate_kernels_with_kept_read_scalars(cb, kind, dims):
     e, st, gl = cb.ext(), cb.status_word(dev), cb._gate_list(spec)
     assert e.srw_wide_tiles(U)
     tau_c, isd_c = tau.squeeze(-1).contiguous(), (1 / sd).squeeze(-1).contiguous()
-    e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau_c, isd_c, den, None, None, gl, st, [], 0, 0, None, 0)
+    e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau_c, isd_c, None, den, None, None, gl, st, *cb.NO_GATHER)
     assert _rel(p[:, :U], g * xr_ref) < 6e-3 and _rel(xr[:, :U], xr_ref) < 4e-3
     assert _rel(den, dt.sum(-1)) < 1e-4
     dy = (rn(T, D) * 0.1).bfloat16()
@@ -141,8 +141,8 @@ def test_gate_kernels_with_kept_read_scalars(cb, kind, dims):
     ds_ref, dtau_ref, _ = gate_backward(spec, s, tau, sd, dp * xr_q, dden[:, None])
     dxr, ds = torch.zeros_like(p), torch.zeros_like(p)
     dtau = torch.zeros(T, device=dev)
-    e.srw_bwd_gate_xr(h, emb, dy, write, xr, xr, dxr, ds, tau_c, isd_c, dden, dtau, gl, st,
-                      [], [], [], 0, 0, None, 0)            # p overwrites xr in place
+    e.srw_bwd_gate_xr(h, emb, dy, write, xr, xr, dxr, ds, tau_c, isd_c, dden, None, dtau, gl, st,
+                      *cb.NO_GATHER)                        # p overwrites xr in place
     assert _rel(xr[:, :U], g * xr_q) < 6e-3 and _rel(dxr[:, :U], dp * g) < 6e-3
     assert _rel(ds[:, :U], ds_ref) < 8e-3 and _rel(dtau, dtau_ref.squeeze(-1)) < 4e-3
     cb.check_status()
@@ -210,9 +210,9 @@ def test_score_statistics_kernels(cb, dims):
     wb = torch.randn(T, R, r).bfloat16()
     out = {}
     for dev in ("cpu", "cuda"):
-        h, off = h0.to(dev).requires_grad_(True), off0.to(dev).requires_grad_(True)
-        gram = (emb.t() @ emb).to(dev).requires_grad_(True)
-        esum = emb.sum(0).to(dev).requires_grad_(True)
+        leaf = lambda t: t.detach().clone().to(dev).requires_grad_(True)
+        h, off = leaf(h0), leaf(off0)
+        gram, esum = leaf(emb.t() @ emb), leaf(emb.sum(0))
         tau, isd, hsum, hb = score_stats(h, off, gram, esum, U)
         ((tau * wt.to(dev)).sum() + (isd * wi.to(dev)).sum() + (hsum * wh.to(dev)).sum()
          + (hb.float() * wb.to(dev).float()).sum()).backward()

@@ -58,6 +58,34 @@ def test_analysis_cli_runs_every_key(tmp_path):
     assert len(res["intervene"]["suppressed"]) == 1
     assert -1.0 <= res["rw_align"]["know"]["cos_mean"] <= 1.0
     assert res["tau_dist"]["Know"]["std"] >= 0.0
+    # the rebuttal / interpretation / combinatorics half of the suite
+    assert abs(res["r1"]["q_specialised_frac"] + res["r1"]["k_specialised_frac"] + res["r1"]["shared_frac"] - 1.0) < 1e-5
+    assert len(res["r4"]["attn_share"]) == L and len(res["r5"]["levels"]) == 4
+    assert res["r3"]["top_units"] and res["combo"]["Know"]["unique_sets"] >= 1
+    assert 0.0 <= res["op_space"]["unique_active_sets_frac"] <= 1.0
+    assert len(res["rw_func"]["bins"]) == 10 and sum(b["units"] for b in res["rw_func"]["bins"]) == cfg.model.n_know
+    assert res["tau_grad"]["task_tau_grad_norm"] >= 0.0 and "skipped" in res["phase"]
+    assert set(res["deep"]["units"]) == {"corrective", "neutral", "amplifying"}
+    # every --only key of the reference's CLI is accepted (rw_cov expands to its two members)
+    ref_keys = ("info,val,health,generate,weights,routing,samples,gate_dist,utilization,r1,r2,r3,r4,r5,"
+                "rw_proj,act_context,layer_role,cross_suppress,gate_mech,comp_expr,neuron_cluster,cross_ref,"
+                "deep,op_space,intervene,compose,rw_align,resid_dyn,phase,drift,gate_ci,write_cov,read_cov,"
+                "rw_cov,sel_gini,sel_trans,combo,addit,dom_supp,rw_func,z_dist,tau_grad,pool_geom").split(",")
+    assert all(k in A.ANALYSES or k in A.ALIASES for k in ref_keys)
+    # phase dynamics from this framework's own metrics file
+    log = tmp_path / "m.jsonl"
+    log.write_text("\n".join(json.dumps({"type": "train", "step": s_, "ce_loss": 5.0 - 0.01 * s_,
+                                          "know_active": 0.7 if s_ < 50 else 0.1, "know_tau_mean": 0.01 * s_})
+                             for s_ in range(0, 100, 10)))
+    base = tmp_path / "b.jsonl"
+    base.write_text("\n".join(json.dumps({"type": "train", "step": s_, "ce_loss": 4.8 - 0.004 * s_})
+                              for s_ in range(0, 100, 10)))
+    assert A.main(["--checkpoint", path, "--synthetic", "--batch-size", "2", "--n-batches", "1",
+                   "--only", "phase,rw_cov", "--dawn-log", str(log), "--baseline-log", str(base),
+                   "--output", out_dir, "--device", "cpu"]) == 0
+    res2 = json.load(open(os.path.join(out_dir, "analysis.json")))
+    assert set(res2) == {"phase", "read_cov", "write_cov"}
+    assert res2["phase"]["phase_boundary_step"] == 50 and res2["phase"]["crossover_step"] == 40
     assert res["drift"]["know_emb"]["rel_l2"] == 0.0          # compared with itself
     assert 0.0 <= res["cross_ref"]["token_jaccard_mean"] <= 1.0
     assert len(res["layer_sim"]["Know"]["adjacent"]) == L - 1

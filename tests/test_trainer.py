@@ -165,7 +165,7 @@ def test_trace_ranges_cover_a_training_step():
         tracing.enable(timers=False)
     L = tr.cfg.model.n_layers
     assert rep["forward"][0] == 1 and rep["backward"][0] == 1 and rep["optimizer"][0] == 1
-    assert rep["attn/srw_qk"][0] == L and rep["know/srw"][0] == L and rep["lm_head_ce"][0] == 1
+    assert rep["attn/srw_qkv"][0] == L and rep["know/srw"][0] == L and rep["lm_head_ce"][0] == 1
     assert rep["forward"][1] >= rep["know/srw"][1] > 0
     assert "know/srw" in tracing.format_report(rep)
     tr.train_step(ids, mask)
