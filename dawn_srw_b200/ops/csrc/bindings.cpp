@@ -233,7 +233,8 @@ void srw_bwd_gate_gather(const Tensor& h_full, const Tensor& emb, const Tensor& 
 void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const Tensor& read,
                      Tensor& p_out, c10::optional<Tensor> xr_out, c10::optional<Tensor> tau,
                      c10::optional<Tensor> inv_sigma, c10::optional<Tensor> stats, Tensor& den_sum,
-                     c10::optional<Tensor> alive, c10::optional<Tensor> unit_mask,
+                     c10::optional<Tensor> diag, c10::optional<Tensor> alive,
+                     c10::optional<Tensor> unit_mask,
                      std::vector<double> gate, Tensor& status,
                      std::vector<std::vector<int64_t>> ptr_lists, std::vector<int64_t> lds,
                      std::vector<int64_t> cols, std::vector<std::vector<int64_t>> stat_lists,
@@ -264,6 +265,12 @@ void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const 
     TORCH_CHECK(alive->scalar_type() == torch::kUInt8 && alive->numel() >= U);
     alive_p = alive->data_ptr<unsigned char>();
   }
+  float* diag_p = nullptr;
+  if (diag.has_value() && diag->defined()) {
+    TORCH_CHECK(diag->is_cuda() && diag->scalar_type() == torch::kFloat32 && diag->is_contiguous() &&
+                diag->numel() >= static_cast<int64_t>(T) * 12 + 2);
+    diag_p = diag->data_ptr<float>();
+  }
   DsbGate g = to_gate(gate);
   GatherHolder gh;
   const DsbGather* gp = nullptr;
@@ -277,7 +284,7 @@ void srw_fwd_gate_xr(const Tensor& h, const Tensor& emb, const Tensor& x, const 
                                x.data_ptr(), x.stride(0), read.data_ptr(), read.stride(0), T, U, r,
                                D, p_out.data_ptr(), p_out.stride(0), xr_p, ldxr, opt_f32(tau),
                                opt_f32(inv_sigma), stats_p, den_sum.data_ptr<float>(), nullptr,
-                               alive_p, opt_f32(unit_mask), &g, gp, status.data_ptr<int>(),
+                               diag_p, alive_p, opt_f32(unit_mask), &g, gp, status.data_ptr<int>(),
                                cur_stream());
   TORCH_CHECK(rc == 0, "dsb_srw_fwd_gate_xr failed with code ", rc);
 }

@@ -93,12 +93,16 @@ int dsb_srw_wide_tiles(int U);
 // gather may be null.  `stats` (nullable; wide kernels only) replaces tau / inv_sigma by
 // one float4 per token (tau, 1/sigma, -, -): the form in which a fused gather brings the
 // per-token constants in together with the rows (DsbGather.stats).
+// `diag` (nullable; wide kernels only): zeroed fp32 [T * 12 + 2]; receives the routing
+// diagnostics as per-token sums over the units, 12 columns per token (gate sum, active,
+// strong, band, z / intensity sum, two narrower bands, sum g log g, sum s^3, sum s^4, gate
+// max, one spare), followed by two scalars (max intensity, count of capped intensities).
 int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb, long long lde,
                         const void* x, long long ldx, const void* read, long long ldr, int T,
                         int U, int r, int D, void* p_out, long long ldp, void* xr_out,
                         long long ldxr, const float* tau, const float* inv_sigma,
-                        const void* stats, float* den_sum, float* gate_sum, unsigned char* alive,
-                        const float* unit_mask, const DsbGate* gate,
+                        const void* stats, float* den_sum, float* gate_sum, float* diag,
+                        unsigned char* alive, const float* unit_mask, const DsbGate* gate,
                         const DsbGather* gather /*host*/, int* status, cudaStream_t stream);
 
 // Backward gate step from the read scalars the forward pass kept: one launch

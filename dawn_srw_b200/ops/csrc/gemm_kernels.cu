@@ -250,8 +250,62 @@ struct FwdGateParams {
   float* gate_sum;         // optional [T] += sum_U g
   unsigned char* alive;    // optional [U]: 1 if any token gates the unit >= dead_thr
   const float* unit_mask;  // optional [U] multiplier on the gate (ablation)
+  // Optional routing diagnostics (log steps; wide kernels only): per token kDiagCols fp32
+  // accumulators over the units, see DiagCol, and two scalars (max intensity, count of
+  // intensities at the cap) for the two-stage gate.  Zeroed by the caller.
+  float* diag;             // [T, kDiagCols]
+  float* diag_scalars;     // [2]
   GateConsts gc;
 };
+constexpr int kDiagCols = 12;
+enum DiagCol : int {
+  kDgGateSum = 0,   // sum_U g
+  kDgActive = 1,    // units counted active (g > 0; act > 0.5 for the two-stage gate)
+  kDgStrong = 2,    // g > 0.5 (act > 0.9)
+  kDgBand = 3,      // Phi(z) outside [0.05, 0.95]  (act inside (0.1, 0.9))
+  kDgZSum = 4,      // sum of positive z (sum of intensities)
+  kDgB075 = 5,      // 0 < z < 0.75  (act inside (0.05, 0.95))
+  kDgB030 = 6,      // 0 < z < 0.30  (act inside (0.2, 0.8))
+  kDgGLogG = 7,     // sum g log(g + 1e-8)
+  kDgS3 = 8,        // sum s^3
+  kDgS4 = 9,        // sum s^4
+  kDgGateMax = 10,  // max_U g (atomicMax on the bit pattern; g >= 0)
+};
+
+// Per-element contribution to the diagnostics.  `s` is the raw score, `zt` the shifted score
+// (see RowGate), `g` the gate value (after any unit mask), `dt` its denominator term.
+template <int KIND>
+__device__ __forceinline__ void diag_accumulate(const GateConsts& gc, float s, float zt, float g,
+                                                float dt, float (&d)[kDiagCols], float& int_max,
+                                                float& int_cap) {
+  d[kDgGateSum] += g;
+  d[kDgGLogG] = fmaf(g, __logf(g + 1e-8f), d[kDgGLogG]);
+  const float s2 = s * s;
+  d[kDgS3] = fmaf(s2, s, d[kDgS3]);
+  d[kDgS4] = fmaf(s2, s2, d[kDgS4]);
+  d[kDgGateMax] = fmaxf(d[kDgGateMax], g);
+  if constexpr (KIND == 0) {
+    d[kDgActive] += zt > 0.f ? 1.f : 0.f;
+  } else if constexpr (KIND == 1) {
+    d[kDgActive] += g > 0.f ? 1.f : 0.f;
+    d[kDgStrong] += g > 0.5f ? 1.f : 0.f;
+    d[kDgBand] += fabsf(zt) > 1.6448536f ? 1.f : 0.f;      // Phi(z) > 0.95 or < 0.05
+    d[kDgZSum] += fmaxf(zt, 0.f);
+    d[kDgB075] += (zt > 0.f && zt < 0.75f) ? 1.f : 0.f;
+    d[kDgB030] += (zt > 0.f && zt < 0.30f) ? 1.f : 0.f;
+  } else {
+    // act = sigmoid(sharp * zt): act > a  <=>  sharp * zt > log(a / (1 - a))
+    const float a = gc.sharp * zt;
+    d[kDgActive] += a > 0.f ? 1.f : 0.f;
+    d[kDgStrong] += a > 2.1972246f ? 1.f : 0.f;                 // 0.9
+    d[kDgBand] += fabsf(a) < 2.1972246f ? 1.f : 0.f;            // (0.1, 0.9)
+    d[kDgZSum] += dt;                                           // intensity
+    d[kDgB075] += fabsf(a) < 2.9444390f ? 1.f : 0.f;            // (0.05, 0.95)
+    d[kDgB030] += fabsf(a) < 1.3862944f ? 1.f : 0.f;            // (0.2, 0.8)
+    int_max = fmaxf(int_max, dt);
+    int_cap += dt >= gc.eps + gc.max_int - 1e-3f ? 1.f : 0.f;
+  }
+}
 template <int KIND>
 struct FwdGateEpi {
   static constexpr int kNumAcc = 2;
@@ -444,11 +498,19 @@ struct FwdGateEpiWide {
   __host__ __device__ static constexpr int acc_bufs(int) { return 1; }
   using Params = FwdGateParams;
 
-  template <bool kGeneral>
+  // kGeneral: column tail, unit mask or alive flags in play; kDiag: routing diagnostics wanted
+  // (then kGeneral too, so that padded columns are left out of the counts).
+  template <bool kGeneral, bool kDiag = false>
   __device__ static __forceinline__ void phase1(const Params& p, uint32_t acc_s, int col0, int N,
                                                 bool row_ok, RowGate rg, uint32_t (&gp)[64],
-                                                float& den_acc, float& g_acc, int lane) {
+                                                float& den_acc, float& g_acc, int lane, int row) {
     float sb[2][32];
+    float dg[kDiagCols];
+    float int_max = 0.f, int_cap = 0.f;
+    if constexpr (kDiag) {
+#pragma unroll
+      for (int k = 0; k < kDiagCols; ++k) dg[k] = 0.f;
+    }
     tmem_ld32(acc_s, sb[0]);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -460,7 +522,8 @@ struct FwdGateEpiWide {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         float g, dt;
-        gate_fwd_shifted<KIND>(p.gc, fmaf(s[j], rg.a, rg.b), g, dt);
+        const float zt = fmaf(s[j], rg.a, rg.b);
+        gate_fwd_shifted<KIND>(p.gc, zt, g, dt);
         if constexpr (kGeneral) {
           if (cbase + j >= N) { g = 0.f; dt = 0.f; }
           if (p.unit_mask != nullptr && cbase + j < N) {
@@ -469,6 +532,9 @@ struct FwdGateEpiWide {
             dt *= um;
           }
           if (row_ok && g >= p.gc.dead_thr) alive_bits |= 1u << j;
+        }
+        if constexpr (kDiag) {
+          if (cbase + j < N) diag_accumulate<KIND>(p.gc, s[j], zt, g, dt, dg, int_max, int_cap);
         }
         den_acc += dt;
         if constexpr (KIND == 2) g_acc += g;
@@ -482,6 +548,20 @@ struct FwdGateEpiWide {
       }
 #pragma unroll
       for (int j = 0; j < 16; ++j) gp[16 * q + j] = pack_bf16x2(s[2 * j], s[2 * j + 1]);
+    }
+    if constexpr (kDiag) {
+      if (row_ok) {
+        float* dst = p.diag + static_cast<size_t>(row) * kDiagCols;
+#pragma unroll
+        for (int k = 0; k < kDiagCols; ++k) {
+          if (k == kDgGateMax) atomicMax(reinterpret_cast<int*>(dst + k), __float_as_int(dg[k]));
+          else if (k < kDgGateMax) atomicAdd(dst + k, dg[k]);
+        }
+        if constexpr (KIND == 2) {
+          atomicMax(reinterpret_cast<int*>(p.diag_scalars), __float_as_int(int_max));
+          atomicAdd(p.diag_scalars + 1, int_cap);
+        }
+      }
     }
   }
 
@@ -514,8 +594,9 @@ struct FwdGateEpiWide {
       }
     }
     const RowGate rg = row_gate<KIND>(p.gc, tau, isg);
-    if (general) phase1<true>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
-    else phase1<false>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane);
+    if (p.diag != nullptr) phase1<true, true>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane, row);
+    else if (general) phase1<true>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane, row);
+    else phase1<false>(p, acc_s, col0, N, row_ok, rg, gp, den_acc, g_acc, lane, row);
     ctl.release(0);   // the next tile's score MMAs may start
     if constexpr (KIND != 2) g_acc = den_acc;
     // ---- drain XR into bf16 pairs and release it
@@ -1300,8 +1381,8 @@ extern "C" int dsb_srw_fwd_gate(const void* h, long long ldh, const void* emb, l
                                 float* gate_sum, unsigned char* alive, const float* unit_mask,
                                 const DsbGate* gate, int* status, cudaStream_t stream) {
   return dsb_srw_fwd_gate_xr(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, nullptr, 0,
-                             tau, inv_sigma, nullptr, den_sum, gate_sum, alive, unit_mask, gate,
-                             nullptr, status, stream);
+                             tau, inv_sigma, nullptr, den_sum, gate_sum, nullptr, alive, unit_mask,
+                             gate, nullptr, status, stream);
 }
 
 extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void* emb,
@@ -1313,8 +1394,8 @@ extern "C" int dsb_srw_fwd_gate_gather(const void* h, long long ldh, const void*
                                        const DsbGate* gate, const DsbGather* gather, int* status,
                                        cudaStream_t stream) {
   return dsb_srw_fwd_gate_xr(h, ldh, emb, lde, x, ldx, read, ldr, T, U, r, D, p_out, ldp, nullptr, 0,
-                             tau, inv_sigma, nullptr, den_sum, gate_sum, alive, unit_mask, gate,
-                             gather, status, stream);
+                             tau, inv_sigma, nullptr, den_sum, gate_sum, nullptr, alive, unit_mask,
+                             gate, gather, status, stream);
 }
 
 extern "C" int dsb_srw_wide_tiles(int U) {
@@ -1340,9 +1421,9 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
                                    int T, int U, int r, int D, void* p_out, long long ldp,
                                    void* xr_out, long long ldxr, const float* tau,
                                    const float* inv_sigma, const void* stats, float* den_sum,
-                                   float* gate_sum, unsigned char* alive, const float* unit_mask,
-                                   const DsbGate* gate, const DsbGather* gather, int* status,
-                                   cudaStream_t stream) {
+                                   float* gate_sum, float* diag, unsigned char* alive,
+                                   const float* unit_mask, const DsbGate* gate,
+                                   const DsbGather* gather, int* status, cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
   constexpr int BN = 128;
   GemmParams<FwdGateParams> gp;
@@ -1351,6 +1432,7 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
   const bool wide = dsb_srw_wide_tiles(U) != 0;
   if (xr_out != nullptr && !wide) return 704;   // only the wide kernel writes the read scalars
   if (stats != nullptr && !wide) return 706;    // ... and reads per-token float4 statistics
+  if (diag != nullptr && !wide) return 708;     // ... and accumulates routing diagnostics
   if (stats == nullptr && (tau == nullptr || inv_sigma == nullptr)) return 707;
   const int brows = wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
@@ -1368,6 +1450,7 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
   if (xr_out != nullptr) rc |= make_out_tmap(&gp.tma_out[1], xr_out, T, U, ldxr, 2);
   if (rc) return 300 + rc;
   gp.epi = {static_cast<const float4*>(stats), tau, inv_sigma, den_sum, gate_sum, alive, unit_mask,
+            diag, diag != nullptr ? diag + static_cast<size_t>(T) * kDiagCols : nullptr,
             make_gc(gate)};
   const bool fused = gather != nullptr && gather->n_ranks > 1;
   if (fused) {

@@ -426,7 +426,8 @@ class _SRWRouteScaledFn(torch.autograd.Function):
     Only for unsharded pools (the denominator is complete on this rank)."""
 
     @staticmethod
-    def forward(ctx, x_bf, h_bf, tau, inv_sd, anchor, holder, spec, U, alive, unit_mask, scale):
+    def forward(ctx, x_bf, h_bf, tau, inv_sd, anchor, holder, spec, U, alive, unit_mask, scale,
+                diag=None):
         e = ext()
         dev = x_bf.device
         T, D = x_bf.shape
@@ -437,7 +438,7 @@ class _SRWRouteScaledFn(torch.autograd.Function):
                              and any(ctx.needs_input_grad))
         count_launches(2)
         e.srw_fwd_gate_xr(h_bf, holder.emb[:U], x_bf, holder.read[:U], p, xr, tau, inv_sd, None, den,
-                          alive, unit_mask, _gate_list(spec), status_word(dev), *NO_GATHER)
+                          diag, alive, unit_mask, _gate_list(spec), status_word(dev), *NO_GATHER)
         rs = (scale.detach().float() / den.clamp(min=1.0)).contiguous()
         y = gemm(p[:, :U], False, holder.write[:U], True, out_dtype=torch.float32, row_scale=rs)
         ctx.save_for_backward(x_bf, h_bf, tau, inv_sd, y, den, rs, scale)
@@ -461,7 +462,7 @@ class _SRWRouteScaledFn(torch.autograd.Function):
         dx, dh, dtau, d_isd = _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den.contiguous(), hd,
                                                    spec, U, xr)
         return (dx, dh, dtau, d_isd, torch.zeros(1, device=dev), None, None, None, None, None,
-                d_scale)
+                d_scale, None)
 
 
 # ---------------------------------------------------------------------------
@@ -647,6 +648,33 @@ def grad_sq_norm(grads) -> torch.Tensor:
     return ext().grad_sq_norm([g.float().contiguous() for g in grads])
 
 
+DIAG_COLS = 12      # per-token accumulators the gate kernels keep on log steps (csrc: DiagCol)
+
+
+def diag_from_kernel(spec, dg, tau, inv_sd, tau_off, U_tot: int, alive, shard_group):
+    """Routing diagnostics of a pool-op call from the accumulators its gate kernels filled.
+    ``dg``: [R, T * DIAG_COLS + 2] fp32 (per token: gate sum, active, strong, band, z sum, two
+    narrower bands, sum g log g, sum s^3, sum s^4, gate max; then max intensity and the count
+    of capped intensities), partial over this rank's units for ALL T tokens; ``tau``,
+    ``inv_sd``, ``tau_off``: [T, R] for the same tokens.  The sums over the shard group are
+    taken here (log steps only)."""
+    from .srw_ref import finalize_diag
+    R, T = dg.shape[0], tau.shape[0]
+    cols = dg[:, : T * DIAG_COLS].reshape(R, T, DIAG_COLS).permute(1, 0, 2)       # [T,R,12]
+    col = lambda k: cols[..., k:k + 1].contiguous()
+    acc = {"active": col(1), "strong": col(2), "band": col(3), "zsum": col(4), "b075": col(5),
+           "b030": col(6), "glogg": col(7)}
+    gsum = C.all_reduce_nograd(col(0), shard_group, "sum")
+    den_sum = C.all_reduce_nograd(col(4), shard_group, "sum")      # two-stage gate: sum of intensities
+    sd = (1.0 / inv_sd).unsqueeze(-1)
+    tau3 = tau.unsqueeze(-1)
+    mu = tau3 - tau_off.unsqueeze(-1) * sd
+    scal = dg[:, T * DIAG_COLS:]
+    dead_cnt = (alive == 0).float().sum() if alive is not None else tau.new_zeros(())
+    return finalize_diag(spec, acc, col(10), col(8), col(9), gsum, den_sum, mu, sd, tau3, U_tot,
+                         dead_cnt, scal[:, 0].max(), scal[:, 1].sum(), shard_group)
+
+
 # ---------------------------------------------------------------------------
 class CudaBackend:
     name = "sm100a"
@@ -801,8 +829,9 @@ class CudaBackend:
         if comm is None:
             comm = self._comm[key] = GroupShardComm(grp, x.device, Tl, D, r)
         x_bf = _bf16_2d(x)
-        hs, taus, isds, holders, units, anchors, scales, alives, masks, per_call = \
-            [], [], [], [], [], [], [], [], [], []
+        hs, taus, isds, offs, holders, units, anchors, scales, alives, masks, diags, per_call = \
+            [], [], [], [], [], [], [], [], [], [], [], []
+        T_all = Tl * nsh
         hsums = []
         for c in calls:
             pool, pctx = c["pool"], c["pctx"]
@@ -815,6 +844,7 @@ class CudaBackend:
             hs.append(h_bf3)
             taus.append(tau)
             isds.append(inv_sd)
+            offs.append(c["tau_off"].detach().float())
             hsums.append(hsum)
             anchors.append(ex["anchor"])
             sc = c.get("out_scale")
@@ -831,13 +861,15 @@ class CudaBackend:
                 scales.append(sc)
                 alives.append(alive)
                 masks.append(um)
+                diags.append(torch.zeros(T_all * DIAG_COLS + 2, dtype=torch.float32, device=x.device)
+                             if want_diag else None)
             per_call.append((Rr, U, U_tot, alive))
         # per-unit mean scores need the column sums of h over ALL tokens of the group: one
         # small all-reduce for every pool of the group
         hsum_all = C.sum_over_shards(torch.stack(hsums), grp)
         outs, dens = route_group(x_bf, torch.cat(hs, dim=1), torch.cat(taus, dim=1),
                                  torch.cat(isds, dim=1), comm, spec, holders, units, anchors, scales,
-                                 alives, masks)
+                                 alives, masks, diags, torch.cat(offs, dim=1) if want_diag else None)
         m_us, parts = [], []
         for k, (c, (Rr, U, U_tot, alive)) in enumerate(zip(calls, per_call)):
             hbar = hsum_all[k] / float(Tl * nsh * Rr)
@@ -865,9 +897,12 @@ class CudaBackend:
             diag = {}
             if want_diag:
                 with torch.no_grad():
-                    diag = self._srw_library(x.detach(), c["h"].detach(), c["tau_off"].detach(),
-                                             c["pool"], spec, c["pctx"], True, False,
-                                             c.get("unit_mask")).diag
+                    # thresholds, 1/sigma and offsets of ALL tokens sit in the gathered
+                    # statistics buffers of this group's forward
+                    st_all = [comm.stats[comm._parity["gather"]][i0 + j].local for j in range(Rr)]
+                    pick = lambda k: torch.stack([t[:, k] for t in st_all], dim=1)
+                    diag = diag_from_kernel(spec, torch.stack(diags[i0:i0 + Rr]), pick(0), pick(1),
+                                            pick(3), U_tot, alive, grp)
             results.append(SRWResult(out=o[0].unsqueeze(1) if Rr == 1 else None, lb=lb,
                                      dead_penalty=dead_pen, diag=diag, den=den, outs=list(o)))
             i0 += Rr
@@ -899,10 +934,14 @@ class CudaBackend:
         else:
             scale = torch.full((), float(out_scale), device=x.device)
         outs, dens = [], []
+        # routing diagnostics ride in the gate kernel's epilogue (wide kernels); pools too
+        # small for those take the library path below
+        dg = torch.zeros(Rr, T * DIAG_COLS + 2, dtype=torch.float32, device=x.device) \
+            if want_diag and ext().srw_wide_tiles(U) else None
         for ri in range(Rr):
             y, den = _SRWRouteScaledFn.apply(x_bf, _bf16_2d(h_bf3[:, ri]), tau[:, ri].contiguous(),
                                              inv_sd[:, ri].contiguous(), anchor, pool, spec, U,
-                                             alive, um, scale)
+                                             alive, um, scale, None if dg is None else dg[ri])
             outs.append(y)
             dens.append(den)
         den = torch.stack(dens, dim=1).clamp(min=1.0)
@@ -915,9 +954,14 @@ class CudaBackend:
         diag = {}
         if want_diag:
             with torch.no_grad():
-                diag = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec,
-                                         ParallelCtx(None, pctx.dp_group, pctx.n_total, pctx.n_valid,
-                                                     False), True, False, unit_mask).diag
+                if dg is not None:
+                    diag = diag_from_kernel(spec, dg, tau.detach(), inv_sd.detach(), tau_off.detach(),
+                                            U_tot, alive, None)
+                else:
+                    diag = self._srw_library(x.detach(), h.detach(), tau_off.detach(), pool, spec,
+                                             ParallelCtx(None, pctx.dp_group, pctx.n_total,
+                                                         pctx.n_valid, False), True, False,
+                                             unit_mask).diag
         out = outs[0].unsqueeze(1) if Rr == 1 else None
         return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, den=den, outs=outs)
 

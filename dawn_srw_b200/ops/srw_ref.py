@@ -74,6 +74,59 @@ def _mm(a, b_t, dtype):
     return (a.to(dtype) @ b_t.to(dtype).t()).float()
 
 
+def finalize_diag(spec: GateSpec, acc: Dict[str, torch.Tensor], gmax, s3, s4, gsum, den_sum, mu, sd,
+                  tau, U_tot: int, dead_cnt, int_max, int_cap, shard_group) -> Dict[str, torch.Tensor]:
+    """Routing diagnostics of one pool-op call from per-token accumulators over this rank's
+    units (reference: models/dawn_spatial_v41_exp.py:519-534, 588-635).  ``acc`` holds
+    [T, R, 1] sums "active", "strong", "band", "zsum", "b075", "b030", "glogg"; ``gmax`` the
+    per-token gate maximum; ``s3`` / ``s4`` the raw third / fourth score moments' sums; ``gsum``
+    and ``den_sum`` are already summed over the shard group, the accumulators are summed here."""
+    T, R = mu.shape[0], mu.shape[1]
+    red = lambda t: C.all_reduce_nograd(t, shard_group, "sum")
+    active = red(acc["active"])
+    gmax_g = C.all_reduce_nograd(gmax, shard_group, "max")
+    s3g, s4g = red(s3), red(s4)
+    cube = s3g / U_tot
+    third = cube - 3.0 * mu * sd ** 2 - mu ** 3
+    quad = s4g / U_tot
+    fourth = quad - 4.0 * mu * cube + 6.0 * mu ** 2 * sd ** 2 + 3.0 * mu ** 4
+    glogg = red(acc["glogg"])
+    if spec.kind == GATE_TWO_STAGE:
+        adenom = active.clamp(min=1.0)
+        z_mean_active = gsum / (active + 1e-8)
+        gs_eps = gsum.clamp(min=1e-6)
+        ent = -torch.where(gsum > 1e-6, glogg, torch.zeros_like(glogg)) / gs_eps + torch.log(gs_eps)
+        ent = torch.where(torch.isfinite(ent), ent, torch.zeros_like(ent))
+        z_sum_out = den_sum.mean()
+    else:
+        adenom = active + 1e-8
+        z_mean_active = red(acc["zsum"]) / (active + 1e-8)
+        gs_eps = gsum + 1e-8
+        ent = -glogg / gs_eps + torch.log(gs_eps)
+        z_sum_out = red(acc["zsum"]).mean()
+    return {
+        "active_frac": (active / U_tot).mean(dim=1).squeeze(-1),     # [T]
+        "gate_max": gmax_g.mean(dim=1).squeeze(-1),                  # [T]
+        "score_std": sd.mean(),
+        "gate_sum": gsum.mean(),
+        "active_n_mean": active.mean(),
+        "strong": (red(acc["strong"]) / U_tot).mean(),
+        "phi_binary": (red(acc["band"]) / U_tot).mean(),
+        "z_mean_active": z_mean_active.mean(),
+        "tau_abs_mean": tau.mean(),
+        "z_lt_075": (red(acc["b075"]) / adenom).mean(),
+        "z_lt_030": (red(acc["b030"]) / adenom).mean(),
+        "score_skew": (third / (sd ** 3 + 1e-8)).mean(),
+        "active_per_token_std": active.std(unbiased=False),
+        "gate_entropy": ent.mean(),
+        "z_sum": z_sum_out,
+        "score_kurt": (fourth / (sd ** 4 + 1e-8)).mean(),
+        "dead_count": red(dead_cnt),
+        "int_max": C.all_reduce_nograd(int_max, shard_group, "max"),
+        "int_cap_frac": red(int_cap) / float(T * R * U_tot),
+    }
+
+
 def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
                  compute_dtype=torch.float32, chunk_size: Optional[int] = None,
                  n_valid: Optional[int] = None, n_total: Optional[int] = None,
@@ -226,52 +279,9 @@ def srw_pool_ref(x, h, tau_off, emb, read, write, spec: GateSpec, *,
     diag: Dict[str, torch.Tensor] = {}
     if want_diag:
         with torch.no_grad():
-            red = lambda t: C.all_reduce_nograd(t, shard_group, "sum")
-            active = red(acc["active"])
-            gmax_g = C.all_reduce_nograd(gmax, shard_group, "max")
-            gsum_d = gsum.detach()
-            s3g, s4g = red(s3), red(s4)
-            mu_d, sd_d = mu.detach(), sd.detach()
-            cube = s3g / U_tot
-            third = cube - 3.0 * mu_d * sd_d ** 2 - mu_d ** 3
-            quad = s4g / U_tot
-            fourth = quad - 4.0 * mu_d * cube + 6.0 * mu_d ** 2 * sd_d ** 2 + 3.0 * mu_d ** 4
-            glogg = red(acc["glogg"])
-            if spec.kind == GATE_TWO_STAGE:
-                adenom = active.clamp(min=1.0)
-                z_mean_active = gsum_d / (active + 1e-8)
-                gs_eps = gsum_d.clamp(min=1e-6)
-                ent = -torch.where(gsum_d > 1e-6, glogg, torch.zeros_like(glogg)) / gs_eps \
-                    + torch.log(gs_eps)
-                ent = torch.where(torch.isfinite(ent), ent, torch.zeros_like(ent))
-                z_sum_out = den_sum.detach().mean()
-            else:
-                adenom = active + 1e-8
-                z_mean_active = red(acc["zsum"]) / (active + 1e-8)
-                gs_eps = gsum_d + 1e-8
-                ent = -glogg / gs_eps + torch.log(gs_eps)
-                z_sum_out = red(acc["zsum"]).mean()
-            diag = {
-                "active_frac": (active / U_tot).mean(dim=1).squeeze(-1),     # [T]
-                "gate_max": gmax_g.mean(dim=1).squeeze(-1),                  # [T]
-                "score_std": sd_d.mean(),
-                "gate_sum": gsum_d.mean(),
-                "active_n_mean": active.mean(),
-                "strong": (red(acc["strong"]) / U_tot).mean(),
-                "phi_binary": (red(acc["band"]) / U_tot).mean(),
-                "z_mean_active": z_mean_active.mean(),
-                "tau_abs_mean": tau.detach().mean(),
-                "z_lt_075": (red(acc["b075"]) / adenom).mean(),
-                "z_lt_030": (red(acc["b030"]) / adenom).mean(),
-                "score_skew": (third / (sd_d ** 3 + 1e-8)).mean(),
-                "active_per_token_std": active.std(unbiased=False),
-                "gate_entropy": ent.mean(),
-                "z_sum": z_sum_out,
-                "score_kurt": (fourth / (sd_d ** 4 + 1e-8)).mean(),
-                "dead_count": red(dead_cnt),
-                "int_max": C.all_reduce_nograd(int_max, shard_group, "max"),
-                "int_cap_frac": red(int_cap) / float(T * R * U_tot),
-            }
+            diag = finalize_diag(spec, acc, gmax, s3, s4, gsum.detach(), den_sum.detach(), mu.detach(),
+                                 sd.detach(), tau.detach(), U_tot, dead_cnt, int_max, int_cap,
+                                 shard_group)
     gates = torch.cat(gates_out, dim=-1) if return_gates else None
     return SRWResult(out=out, lb=lb, dead_penalty=dead_pen, diag=diag, gates=gates,
                      den=den.squeeze(-1))

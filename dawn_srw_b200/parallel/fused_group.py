@@ -98,7 +98,7 @@ class _RouteGroupFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x_bf, h_all, tau, inv_sd, comm, spec, holders, units, n_anchor, alives, masks,
-                *rest):
+                diags, tau_off, *rest):
         from ..ops import cuda_backend as CB
         anchors, scales = rest[:n_anchor], rest[n_anchor:]
         c: GroupShardComm = comm
@@ -116,6 +116,8 @@ class _RouteGroupFn(torch.autograd.Function):
             s_loc = sf[i].local[c.rows]
             s_loc[:, 0].copy_(tau[:, i])
             s_loc[:, 1].copy_(inv_sd[:, i])
+            if tau_off is not None:                      # only the diagnostics read it back
+                s_loc[:, 3].copy_(tau_off[:, i])
         c.ws.barrier()                                   # every rank's rows are in place
         ob = c.flip("out")
         out_t, aux_t = c.out_rs[ob], c.aux_rs[ob]
@@ -134,7 +136,7 @@ class _RouteGroupFn(torch.autograd.Function):
             else:
                 gather = CB.NO_GATHER
             e.srw_fwd_gate_xr(h_i, hd.emb[:U], xf.local, hd.read[:U], p, xr, None, None, sf[i].local,
-                              den, alives[i], masks[i], gl, st, *gather)
+                              den, diags[i], alives[i], masks[i], gl, st, *gather)
             # un-normalised partial rows + partial denominators to the owners
             e.gemm_scatter(p[:, :U], False, hd.write[:U], True,
                            c.offset_ptrs(out_t, i * W * Tl * D), c.rank, Tl, D, True, 1.0, None, st,
@@ -193,7 +195,7 @@ class _RouteGroupFn(torch.autograd.Function):
             s_loc[:, 1].copy_(inv_sd[:, i])
             s_loc[:, 2].copy_(dden_l)
             d_scales.append((rowdot.sum() / scales[i].detach().float()).reshape(scales[i].shape)
-                            .to(scales[i].dtype) if ctx.needs_input_grad[11 + n_anchor + i] else None)
+                            .to(scales[i].dtype) if ctx.needs_input_grad[13 + n_anchor + i] else None)
         CB.count_launches(nR)
         c.ws.barrier()
         xb = c.flip("dx")
@@ -243,21 +245,26 @@ class _RouteGroupFn(torch.autograd.Function):
         d_tau = torch.stack(dtaus, dim=1)
         d_isd = torch.stack(d_isds, dim=1) if d_isds else None
         zeros = tuple(torch.zeros(1, device=dev) for _ in range(n_anchor))
-        return (dx, d_h, d_tau, d_isd, None, None, None, None, None, None, None) + zeros + \
-            tuple(d_scales)
+        return (dx, d_h, d_tau, d_isd, None, None, None, None, None, None, None, None, None) + \
+            zeros + tuple(d_scales)
 
 
 def route_group(x_bf, h_all, tau, inv_sd, comm, spec, holders: Sequence, units: Sequence[int],
                 anchors: Sequence[torch.Tensor], scales: Sequence[torch.Tensor],
-                alives: Sequence = None, masks: Sequence = None):
+                alives: Sequence = None, masks: Sequence = None, diags: Sequence = None,
+                tau_off=None):
     """One entry of holders / units / scales / alives / masks per ROUTE (a pool with two
     routes appears twice), one anchor per call.  ``alives``: uint8 [U] buffers that get a 1
     for every unit some token gates above the dead threshold (or None); ``masks``: fp32 [U]
-    multipliers on the gate (ablation; forward only).
+    multipliers on the gate (ablation; forward only); ``diags``: zeroed fp32 [T * 12 + 2]
+    buffers for the routing diagnostics of log steps (with ``tau_off`` [Tl, nR], which then
+    travels in the spare slot of the per-token statistics so that every rank can finalise them).
     -> (outs: list of [Tl, D] fp32, dens: list of [Tl])."""
     nR = h_all.shape[1]
     alives = tuple(alives) if alives is not None else (None,) * nR
     masks = tuple(masks) if masks is not None else (None,) * nR
+    diags = tuple(diags) if diags is not None else (None,) * nR
     res = _RouteGroupFn.apply(x_bf, h_all, tau, inv_sd, comm, spec, tuple(holders), tuple(units),
-                              len(anchors), alives, masks, *anchors, *scales)
+                              len(anchors), alives, masks, diags,
+                              None if tau_off is None else tau_off.detach(), *anchors, *scales)
     return list(res[:nR]), list(res[nR:])
