@@ -50,6 +50,9 @@ def parse():
                     help="partitioned: reduce-scatter + AdamW on the owned slice + all-gather over "
                          "peer memory with sharded moments; auto = partitioned for --parallelism dp")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--log-step", action="store_true",
+                    help="after the timed runs, also time steps that produce the full routing "
+                         "diagnostics (what a logging step of the trainer costs)")
     ap.add_argument("--no-shard-check", action="store_true",
                     help="skip the one-off comparison of the sharded model's loss with the same "
                          "model unsharded on rank 0 (runs before the warm-up, N > 1 only)")
@@ -283,6 +286,18 @@ def main():
         h2d = sum(x.numel() * x.element_size() for x in host_batches[0])
         e2e = (e2e_s, h2d, 4)
 
+    log_step = None
+    if args.log_step:
+        trainer.train_step(*dev_batches[0], want_diag=True)          # warm the diagnostic path
+        barrier()
+        l0, l1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0.record()
+        for i in range(2):
+            trainer.train_step(*dev_batches[i % 4], want_diag=True)
+        l1.record()
+        barrier()
+        log_step = l0.elapsed_time(l1) / 2
+
     if args.profile:
         from torch.profiler import ProfilerActivity, profile
         barrier()
@@ -320,6 +335,8 @@ def main():
                        "optimizer": type(trainer.optimizer).__name__},
             "clocks": clocks, "gpu_launches": launches, "final_loss": loss_val,
         }
+        if log_step is not None:
+            out["log_step"] = {"ms": log_step, "ratio_to_normal_step": log_step / ms_per_step}
         if shard_check is not None:
             out["sharded_vs_unsharded_ce"] = shard_check
         if e2e:

@@ -495,6 +495,44 @@ void ce_bwd(const Tensor& logits, const Tensor& labels, const Tensor& lse, const
                          dl.data_ptr(), dl.stride(0), cur_stream()) == 0);
 }
 
+// Fused tied LM head + cross-entropy statistics: returns (logits bf16 [T, V] view of a padded
+// buffer, lse, label_logit, argmax).
+std::vector<Tensor> lm_head_ce_fwd(const Tensor& x, const Tensor& emb, const Tensor& labels,
+                                   Tensor& status) {
+  check_bf16_2d(x, "x"); check_bf16_2d(emb, "emb");
+  TORCH_CHECK(labels.is_cuda() && labels.scalar_type() == torch::kInt64 && labels.is_contiguous() &&
+              labels.numel() == x.size(0) && x.size(1) == emb.size(1));
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = x.size(0), V = emb.size(0), K = x.size(1);
+  const int64_t ldl = (V + 7) / 8 * 8, n_tiles = (V + 255) / 256;
+  auto logits = torch::empty({T, ldl}, x.options());
+  auto partial = torch::empty({T, n_tiles, 4}, x.options().dtype(torch::kFloat32));
+  auto lse = torch::empty({T}, x.options().dtype(torch::kFloat32));
+  auto lab = torch::empty({T}, x.options().dtype(torch::kFloat32));
+  auto pred = torch::empty({T}, x.options().dtype(torch::kInt64));
+  int rc = dsb_lm_head_ce_fwd(x.data_ptr(), x.stride(0), emb.data_ptr(), emb.stride(0), T, V, K,
+                              reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                              logits.data_ptr(), ldl, partial.data_ptr(), lse.data_ptr<float>(),
+                              lab.data_ptr<float>(),
+                              reinterpret_cast<long long*>(pred.data_ptr<int64_t>()),
+                              status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_lm_head_ce_fwd failed with code ", rc);
+  return {logits, lse, lab, pred};
+}
+
+void lm_head_ce_bwd_inplace(Tensor& logits, int64_t V, const Tensor& labels, const Tensor& lse,
+                            const Tensor& scale) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == torch::kBFloat16 && logits.dim() == 2 &&
+              logits.is_contiguous() && labels.is_contiguous() && lse.is_contiguous() &&
+              scale.scalar_type() == torch::kFloat32 && scale.is_contiguous() &&
+              scale.numel() == logits.size(0));
+  const c10::cuda::CUDAGuard guard(logits.device());
+  int rc = dsb_lm_head_ce_bwd_inplace(logits.data_ptr(), logits.size(1), logits.size(0), V,
+                                      reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                                      lse.data_ptr<float>(), scale.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_lm_head_ce_bwd_inplace failed with code ", rc);
+}
+
 std::vector<Tensor> attention_fwd(const Tensor& q, const Tensor& k, const Tensor& v, int64_t H,
                                   double p_drop, int64_t seed, Tensor& status) {
   TORCH_CHECK(q.is_cuda() && q.dim() == 3 && q.scalar_type() == torch::kBFloat16 &&
@@ -685,6 +723,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("ce_fwd", &ce_fwd);
+  m.def("lm_head_ce_fwd", &lm_head_ce_fwd);
+  m.def("lm_head_ce_bwd_inplace", &lm_head_ce_bwd_inplace);
   m.def("ce_bwd", &ce_bwd);
   m.def("adamw_multi", &adamw_multi);
   m.def("embed_fwd", &embed_fwd);

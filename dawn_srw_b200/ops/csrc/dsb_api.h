@@ -159,6 +159,18 @@ int dsb_sum_slabs_div(const void* in_bf16, int n_slabs, int rows, int cols, cons
 int dsb_sum_slabs(const void* in, int in_is_bf16, int n_slabs, long long n, void* out,
                   int out_is_bf16, cudaStream_t stream);
 
+// Tied LM head with the softmax statistics taken in the GEMM epilogue (no fp32 logits):
+// logits_bf16 [M, ldl] = x[M, K] . emb[V, K]^T, lse / label_logit fp32 [M], argmax int64 [M];
+// `partial`: scratch of M * ceil(V / 256) * 16 bytes.  labels < 0: no label (label_logit 0).
+int dsb_lm_head_ce_fwd(const void* x, long long ldx, const void* emb, long long lde, int M, int V,
+                       int K, const long long* labels, void* logits_bf16, long long ldl,
+                       void* partial, float* lse, float* label_logit, long long* argmax,
+                       int* status, cudaStream_t stream);
+// In place: logits -> scale[row] * (softmax - onehot(label)) as bf16 (columns >= V zeroed).
+int dsb_lm_head_ce_bwd_inplace(void* logits_bf16, long long ldl, int M, int V,
+                               const long long* labels, const float* lse, const float* scale,
+                               cudaStream_t stream);
+
 // Bounded cross-GPU barrier over symmetric signal pads.  `pads_dev` is a DEVICE
 // array of `world` pointers to the ranks' pads (uint32); slots
 // [slot_base, slot_base + world) of every pad belong to this barrier stream.

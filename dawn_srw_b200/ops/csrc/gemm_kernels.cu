@@ -237,6 +237,144 @@ struct PlainEpi {
   }
 };
 
+// ------------------------------------------------- LM-head cross-entropy epilogue
+// Tied-embedding logits L = x . E^T (T x V, V = vocabulary) with the softmax
+// statistics taken while the tile is still in TMEM: per row and per 256-column
+// tile the epilogue emits (max, sum exp(l - max), arg-max, label logit) as one
+// float4 and stores the logits as bf16, so no fp32 [T, V] tensor ever exists (the
+// reference keeps the full fp32 logits, models/dawn_spatial_v41_exp.py:1642-1668).
+// A row kernel merges the per-tile partials into logsumexp / label logit / arg-max;
+// the backward pass turns the stored bf16 logits into d(loss)/d(logits) in place.
+struct CeFwdEpi {
+  static constexpr int kNumAcc = 1;
+  static constexpr int kNumOut = 1;
+  static constexpr int kOutBufs = 2;
+  static constexpr int kEpiWarps = 4;
+  __host__ __device__ static constexpr int acc_bufs(int) { return 2; }
+  struct Params {
+    const long long* labels;   // [M] label per row (< 0: no label)
+    float4* partial;           // [M, n_tiles]
+    int n_tiles;
+  };
+  template <int BN, class Ctl>
+  __device__ static void run(const Params& p, const CUtensorMap* maps, WarpStager& st, Ctl& ctl,
+                             int m0, int n0, int M, int N, int warp, int lane) {
+    const int r0 = m0 + warp * 32;
+    if (r0 >= M) { ctl.skip(); return; }
+    const uint32_t acc0 = ctl.wait(0);
+    const int row = r0 + lane;
+    const bool row_ok = row < M;
+    const int label = row_ok ? static_cast<int>(p.labels[row]) : -1;
+    float mx = -3.0e38f, sum = 0.f, lab_logit = 0.f;
+    int amax = n0;
+    int slab = 0;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 64, ++slab) {
+      const int col0 = n0 + c;
+      if (col0 >= N) break;
+      st.wait_free<1>();
+      const uint32_t buf = st.buf(slab & 1);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float v[32];
+        tmem_ld32(acc0 + c + 32 * half, v);
+        tmem_ld_wait();
+        const int cb = col0 + 32 * half;
+        // chunk maximum first, then one rescale of the running sum per chunk
+        float cm = -3.0e38f;
+        int ci = cb;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const bool in = cb + j < N;
+          if (in && v[j] > cm) { cm = v[j]; ci = cb + j; }
+          if (cb + j == label) lab_logit = v[j];
+        }
+        if (cm > mx) {
+          sum *= __expf(mx - cm);
+          mx = cm;
+          amax = ci;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (cb + j < N) sum += __expf(v[j] - mx);
+        stage_bf16_32(st, buf, 4 * half, v);
+      }
+      st.flush(&maps[0], buf, col0, r0, false, true);
+    }
+    ctl.release(0);
+    if (row_ok)
+      p.partial[static_cast<size_t>(row) * p.n_tiles + n0 / BN] =
+          make_float4(mx, sum, __int_as_float(amax), lab_logit);
+  }
+};
+
+// One warp per row: merge the per-tile partials.
+__global__ void ce_merge_kernel(const float4* __restrict__ partial, int n_tiles, int M,
+                                const long long* __restrict__ labels, float* __restrict__ lse,
+                                float* __restrict__ label_logit, long long* __restrict__ argmax) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float mx = -3.0e38f, sum = 0.f, lab = 0.f;
+  int am = 0x7fffffff;
+  for (int t = lane; t < n_tiles; t += 32) {
+    const float4 v = partial[static_cast<size_t>(row) * n_tiles + t];
+    const int ai = __float_as_int(v.z);
+    if (v.x > mx || (v.x == mx && ai < am)) {
+      sum = sum * __expf(mx - v.x) + v.y;
+      mx = v.x;
+      am = ai;
+    } else {
+      sum += v.y * __expf(v.x - mx);
+    }
+    lab += v.w;      // exactly one tile holds the label's column, the others contribute 0
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float omx = __shfl_xor_sync(0xffffffffu, mx, o);
+    const float osum = __shfl_xor_sync(0xffffffffu, sum, o);
+    const int oam = __shfl_xor_sync(0xffffffffu, am, o);
+    lab += __shfl_xor_sync(0xffffffffu, lab, o);
+    if (omx > mx || (omx == mx && oam < am)) {
+      sum = sum * __expf(mx - omx) + osum;
+      mx = omx;
+      am = oam;
+    } else {
+      sum += osum * __expf(omx - mx);
+    }
+  }
+  if (lane == 0) {
+    lse[row] = mx + __logf(sum);
+    label_logit[row] = labels[row] >= 0 ? lab : 0.f;
+    argmax[row] = am;
+  }
+}
+
+// In place on the stored bf16 logits: dl = scale[row] * (exp(l - lse) - [col == label]);
+// columns V.. of the padded row are zeroed.  One block per row.
+__global__ void ce_bwd_inplace_kernel(__nv_bfloat16* __restrict__ logits, long long ld, int V,
+                                      const long long* __restrict__ labels,
+                                      const float* __restrict__ lse,
+                                      const float* __restrict__ scale) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  const float l = lse[row], sc = scale[row];
+  const int lab = static_cast<int>(labels[row]);
+  for (int i = threadIdx.x * 8; i < ld; i += blockDim.x * 8) {
+    uint4 u = *reinterpret_cast<const uint4*>(lr + i);
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f = __bfloat1622float2(h2[e]);
+      const int c0 = i + 2 * e;
+      f.x = c0 < V ? sc * (__expf(f.x - l) - (c0 == lab ? 1.f : 0.f)) : 0.f;
+      f.y = c0 + 1 < V ? sc * (__expf(f.y - l) - (c0 + 1 == lab ? 1.f : 0.f)) : 0.f;
+      h2[e] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    *reinterpret_cast<uint4*>(lr + i) = u;
+  }
+}
+
 // ------------------------------------------------------ forward gate epilogue
 // Eight epilogue warps: warp w handles rows 32(w%4).. of the tile and the
 // (w/4)-th 64-column half, i.e. exactly one staged slab per tile.
@@ -1663,4 +1801,45 @@ extern "C" int dsb_gemm_bf16_scatter_aux(const void* A, int a_mn, long long lda,
   if (rows_per_rank % tile_m == 0)
     gp.m_rot = ((my_rank + 1) % n_ranks) * (rows_per_rank / tile_m);
   return launch_engine<BN, PlainEpi>(gp, stream);
+}
+
+// Tied LM head + cross-entropy statistics in one pass: logits_bf16 [M, ldl] = x . E^T as bf16
+// (ldl >= V, a multiple of 8), lse / label_logit fp32 [M], argmax int64 [M].  `partial` is
+// scratch of M * ceil(V / 256) float4.
+extern "C" int dsb_lm_head_ce_fwd(const void* x, long long ldx, const void* emb, long long lde,
+                                  int M, int V, int K, const long long* labels, void* logits_bf16,
+                                  long long ldl, void* partial, float* lse, float* label_logit,
+                                  long long* argmax, int* status, cudaStream_t stream) {
+  if (M <= 0 || V <= 0 || K <= 0) return 0;
+  constexpr int BN = 256;
+  GemmParams<CeFwdEpi::Params> gp;
+  memset(&gp, 0, sizeof(gp));
+  int rc = fill_operand(&gp.tma_a[0], {x, 0, ldx}, M, K, kBlockM);
+  if (rc) return 100 + rc;
+  rc = fill_operand(&gp.tma_b[0], {emb, 0, lde}, V, K, use_cta_pairs() ? BN / 2 : BN);
+  if (rc) return 200 + rc;
+  gp.seg[0] = {(K + kBlockK - 1) / kBlockK, 0, 0, 0};
+  gp.n_seg = 1;
+  gp.M = M;
+  gp.N = V;
+  gp.status = status;
+  rc = make_out_tmap(&gp.tma_out[0], logits_bf16, M, V, ldl, 2);
+  if (rc) return 300 + rc;
+  const int n_tiles = (V + BN - 1) / BN;
+  gp.epi = {labels, static_cast<float4*>(partial), n_tiles};
+  rc = launch_engine<BN, CeFwdEpi>(gp, stream);
+  if (rc) return rc;
+  ce_merge_kernel<<<(M + 7) / 8, 256, 0, stream>>>(static_cast<const float4*>(partial), n_tiles, M,
+                                                   labels, lse, label_logit, argmax);
+  return cudaGetLastError() == cudaSuccess ? 0 : 12;
+}
+
+extern "C" int dsb_lm_head_ce_bwd_inplace(void* logits_bf16, long long ldl, int M, int V,
+                                          const long long* labels, const float* lse,
+                                          const float* scale, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if ((ldl & 7) != 0 || (reinterpret_cast<uintptr_t>(logits_bf16) & 15) != 0) return 13;
+  ce_bwd_inplace_kernel<<<M, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(logits_bf16), ldl, V,
+                                               labels, lse, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 12;
 }

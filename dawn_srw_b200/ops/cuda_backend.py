@@ -467,49 +467,51 @@ class _SRWRouteScaledFn(torch.autograd.Function):
 
 # ---------------------------------------------------------------------------
 class _LMHeadCEFn(torch.autograd.Function):
-    """Tied-embedding cross entropy without keeping [T, V] logits: logits are
-    produced chunk by chunk on the tcgen05 engine, reduced to (lse, label
-    logit, argmax) and recomputed in backward."""
-    CHUNK = 8192
+    """Tied-embedding cross entropy with the softmax statistics taken in the logits
+    GEMM's epilogue: the kernel emits per-tile (max, sum exp, arg-max, label logit)
+    partials and bf16 logits, a row kernel merges the partials; no fp32 [T, V]
+    tensor exists.  Backward rewrites the bf16 logits in place into
+    ``d_nll * (softmax - onehot)`` and runs the two gradient GEMMs on them."""
+    CHUNK = 65536
 
     @staticmethod
     def forward(ctx, x, emb, labels, emb_bf):
         T = x.shape[0]
         xb = _bf16_2d(x)
-        lse = torch.empty(T, dtype=torch.float32, device=x.device)
-        lab = torch.empty(T, dtype=torch.float32, device=x.device)
-        pred = torch.empty(T, dtype=torch.long, device=x.device)
-        safe = labels.clamp(min=0)
+        e, st = ext(), status_word(x.device)
         V = emb_bf.shape[0]
-        e = ext()
+        lab_c = labels.contiguous()
+        parts = []
         for a in range(0, T, _LMHeadCEFn.CHUNK):
             b = min(a + _LMHeadCEFn.CHUNK, T)
-            lg = gemm(xb[a:b], False, emb_bf, False, out_dtype=torch.float32)
-            e.ce_fwd(lg, safe[a:b].contiguous(), V, lse[a:b], lab[a:b], pred[a:b])
-        ctx.save_for_backward(xb, emb_bf, labels, lse)
-        ctx.x_dtype = x.dtype
+            parts.append(e.lm_head_ce_fwd(xb[a:b], emb_bf, lab_c[a:b], st))
+        count_launches(2 * len(parts))
+        cat = lambda k: parts[0][k] if len(parts) == 1 else torch.cat([p_[k] for p_ in parts])
+        lse, lab, pred = cat(1), cat(2), cat(3)
+        ctx.save_for_backward(xb, emb_bf, lab_c, lse)
+        ctx.logits = [p_[0] for p_ in parts]          # bf16, consumed (in place) by backward
+        ctx.x_dtype, ctx.V = x.dtype, V
         ctx.mark_non_differentiable(pred)
         return lse - lab, pred
 
     @staticmethod
     def backward(ctx, d_nll, _d_pred):
         xb, emb_bf, labels, lse = ctx.saved_tensors
-        T = xb.shape[0]
-        V = emb_bf.shape[0]
+        logits, ctx.logits = ctx.logits, None
+        T, V = xb.shape[0], ctx.V
         dx = torch.empty(T, xb.shape[1], dtype=ctx.x_dtype, device=xb.device)
         demb = torch.zeros(V, emb_bf.shape[1], dtype=torch.float32, device=xb.device)
-        safe = labels.clamp(min=0)
         e = ext()
         scale = d_nll.float().contiguous()
-        ldo = _round_up(V, 8)
-        for a in range(0, T, _LMHeadCEFn.CHUNK):
+        for i, a in enumerate(range(0, T, _LMHeadCEFn.CHUNK)):
             b = min(a + _LMHeadCEFn.CHUNK, T)
-            lg = gemm(xb[a:b], False, emb_bf, False, out_dtype=torch.float32)
-            dl_buf = torch.empty(b - a, ldo, dtype=torch.bfloat16, device=xb.device)
-            e.ce_bwd(lg, safe[a:b].contiguous(), lse[a:b], scale[a:b], V, dl_buf)
-            dl = dl_buf[:, :V]
+            lg = logits[i]
+            e.lm_head_ce_bwd_inplace(lg, V, labels[a:b], lse[a:b], scale[a:b])
+            dl = lg[:, :V]
             gemm(dl, False, emb_bf, True, out=dx[a:b])                         # dl . E
             gemm(dl, True, xb[a:b], True, out=demb, accumulate=True)           # dl^T x
+            logits[i] = None
+        count_launches(len(logits))
         return dx, demb, None, None
 
 

@@ -100,7 +100,7 @@ def main(argv=None):
     for it in range(args.iters):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         ev[0].record()
-        e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau, isd, None, den, None, None, gl, st, *CB.NO_GATHER)
+        e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau, isd, None, den, None, None, None, gl, st, *CB.NO_GATHER)
         ev[1].record()
         CB.gemm(p[:, :U], False, write, True, out=raw)
         ev[2].record()

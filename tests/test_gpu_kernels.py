@@ -131,7 +131,7 @@ def test_gate_kernels_with_kept_read_scalars(cb, kind, dims):
     e, st, gl = cb.ext(), cb.status_word(dev), cb._gate_list(spec)
     assert e.srw_wide_tiles(U)
     tau_c, isd_c = tau.squeeze(-1).contiguous(), (1 / sd).squeeze(-1).contiguous()
-    e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau_c, isd_c, None, den, None, None, gl, st, *cb.NO_GATHER)
+    e.srw_fwd_gate_xr(h, emb, x, read, p, xr, tau_c, isd_c, None, den, None, None, None, gl, st, *cb.NO_GATHER)
     assert _rel(p[:, :U], g * xr_ref) < 6e-3 and _rel(xr[:, :U], xr_ref) < 4e-3
     assert _rel(den, dt.sum(-1)) < 1e-4
     dy = (rn(T, D) * 0.1).bfloat16()
@@ -224,6 +224,36 @@ def test_score_statistics_kernels(cb, dims):
         assert torch.isfinite(a).all(), n
         tol = 2e-2 if n == "dgram" else 2e-3          # dG multiplies bf16-rounded d_var * h
         assert _rel(a, b) < tol, (n, _rel(a, b))
+
+
+@pytest.mark.parametrize("version", ["spatial-r1-v3.9.4", "spatial-r1-v4.0.1", "spatial-r1-v4.1"])
+def test_routing_diagnostics_from_the_gate_epilogue(cb, version):
+    """On log steps the gate kernel accumulates the routing diagnostics itself; they must
+    agree with the same statistics computed by the torch restatement of the op."""
+    from dawn_srw_b200.ops.backend import ParallelCtx
+    from dawn_srw_b200.ops.gates import gate_spec_for
+    T, R, U, r, D = 300, 2, 1580, 64, 256
+    dev = torch.device("cuda")
+    torch.manual_seed(5)
+    spec = gate_spec_for(version)
+    be = cb.CudaBackend()
+    nz = torch.nn.functional.normalize
+    q = lambda t: t.bfloat16().float()
+    emb, read, write = (q(nz(torch.randn(U, d, device=dev), dim=-1)) for d in (r, D, D))
+    x, h = q(torch.randn(T, D, device=dev)), q(torch.randn(T, R, r, device=dev))
+    off = torch.randn(T, R, device=dev) * 0.3 - 0.3
+    with torch.no_grad():
+        pool = be.prepare_pool(emb, read, write, spec, ParallelCtx())
+        got = be.srw(x, h, off, pool, spec, pctx=ParallelCtx(), want_diag=True).diag
+        want = be._srw_library(x, h, off, pool, spec, ParallelCtx(), True, False, None).diag
+    cb.check_status()
+    assert set(got) == set(want)
+    loose = {"score_skew", "score_kurt", "gate_entropy"}     # higher moments / logs of bf16-level differences
+    for k in want:
+        a, b = got[k].float(), want[k].float()
+        scale = float(b.abs().max()) + 1e-3
+        err = float((a - b).abs().max()) / scale
+        assert err < (0.1 if k in loose else 2e-2), (k, err, a.flatten()[:4], b.flatten()[:4])
 
 
 def test_layernorm_kernel(cb):
