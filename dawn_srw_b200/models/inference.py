@@ -61,13 +61,27 @@ def _srw(model, be, x, h, tau, pools, name, *, return_gates=False, unit_mask=Non
                   return_gates=return_gates, unit_mask=unit_mask)
 
 
+def _fast_infer(model, be) -> bool:
+    """Forward-only kernels path: unsharded pools on a backend that has it."""
+    return hasattr(be, "srw_infer") and model.shard_group is None
+
+
 def _layer_qkv(model, be, normed, pools, masks=None, return_gates=False):
     """normed [T,D] -> Q,K,V [T,D] (+ gates)."""
     rt, r = model.router, model.d_route
     T = normed.shape[0]
-    h_all = be.linear(normed, rt.proj_attn.weight, rt.proj_attn.bias)
-    tau_all = be.linear(normed, rt.tau_attn.weight, rt.tau_attn.bias).float()
     m = masks or {}
+    if hasattr(be, "linear_cat") and not torch.is_grad_enabled():
+        h_all, tau_all = be.linear_cat(normed, (rt.proj_attn, rt.tau_attn))
+    else:
+        h_all = be.linear(normed, rt.proj_attn.weight, rt.proj_attn.bias)
+        tau_all = be.linear(normed, rt.tau_attn.weight, rt.tau_attn.bias).float()
+    if not m and not return_gates and _fast_infer(model, be):
+        q, k = be.srw_infer(normed, h_all[:, :2 * r].reshape(T, 2, r), tau_all[:, 0:2], pools["qk"],
+                            model.gate, n_total=model.n_qk, out_scale=model.pool_scale("qk"))
+        (v,) = be.srw_infer(normed, h_all[:, 2 * r:].reshape(T, 1, r), tau_all[:, 2:3], pools["v"],
+                            model.gate, n_total=model.n_v, out_scale=model.pool_scale("v"))
+        return q, k, v, None, None
     rq = _srw(model, be, normed, h_all[:, :2 * r].reshape(T, 2, r), tau_all[:, 0:2], pools, "qk",
               return_gates=return_gates, unit_mask=m.get("qk"))
     rv = _srw(model, be, normed, h_all[:, 2 * r:].reshape(T, 1, r), tau_all[:, 2:3], pools, "v",
@@ -79,8 +93,15 @@ def _layer_qkv(model, be, normed, pools, masks=None, return_gates=False):
 def _know(model, be, normed, pools, masks=None, return_gates=False):
     rt = model.router
     T = normed.shape[0]
-    h = be.linear(normed, rt.proj_know.weight, rt.proj_know.bias)
-    tau = be.linear(normed, rt.tau_know.weight, rt.tau_know.bias).float()
+    if hasattr(be, "linear_cat") and not torch.is_grad_enabled():
+        h, tau = be.linear_cat(normed, (rt.proj_know, rt.tau_know))
+    else:
+        h = be.linear(normed, rt.proj_know.weight, rt.proj_know.bias)
+        tau = be.linear(normed, rt.tau_know.weight, rt.tau_know.bias).float()
+    if not masks and not return_gates and _fast_infer(model, be):
+        (out,) = be.srw_infer(normed, h.reshape(T, 1, model.d_route), tau, pools["know"], model.gate,
+                              n_total=model.n_know, out_scale=model.pool_scale("know"))
+        return out, None
     res = _srw(model, be, normed, h.reshape(T, 1, model.d_route), tau, pools, "know",
                return_gates=return_gates, unit_mask=(masks or {}).get("know"))
     return res.route(0) * model.pool_scale("know"), res
@@ -202,6 +223,86 @@ def decode_step(model, token: torch.Tensor, cache_k, cache_v, length: int):
     return be.logits(x, model.token_emb.weight)[:, 0], cache_k, cache_v, length + 1
 
 
+class DecodeSession:
+    """KV-cache decoding with the whole per-token step captured in a CUDA graph.
+
+    One decoded token is about forty small launches per layer (LayerNorm, router
+    GEMMs, statistics, three gate kernels, three split-K write GEMMs, cache
+    attention, O projection, ...).  At batch 1 the kernels of the 400M model stream
+    about 12 GB of pool weights per token, i.e. a couple of milliseconds of HBM
+    time, which is less than the time the host needs to issue those launches one
+    by one; a graph replays them in one submission.  For that the step must have
+    static shapes and addresses: the position is a device scalar (position
+    embedding by ``index_select``, cache write by ``index_copy_``, attention over
+    the whole cache under a position mask), the token ids arrive in a fixed buffer.
+
+    ``session = DecodeSession(model, cache_k, cache_v, length)`` after ``prefill``;
+    ``logits = session.step(tokens)`` per new token.  On CPU, for the dense baseline
+    or with ``use_graph=False`` it runs the same step eagerly."""
+
+    def __init__(self, model, cache_k, cache_v, length: int, use_graph: Optional[bool] = None):
+        self.model, self.cache_k, self.cache_v = model, cache_k, cache_v
+        dev = cache_k.device
+        self.B = cache_k.shape[1]
+        self.length = int(length)
+        self.tok = torch.zeros(self.B, dtype=torch.long, device=dev)
+        self.pos = torch.full((1,), self.length, dtype=torch.long, device=dev)
+        self.be = _be(model, dev)
+        self.pools = None if _is_dense(model) else _pools(model, self.be)
+        if use_graph is None:
+            use_graph = dev.type == "cuda" and not _is_dense(model) and _fast_infer(model, self.be)
+        self.graph, self.out = None, None
+        self.use_graph = bool(use_graph)
+
+    @torch.no_grad()
+    def _step_static(self):
+        m, be, pools = self.model, self.be, self.pools
+        B, H, D = self.B, m.n_heads, m.d_model
+        dh = D // H
+        x = (m.token_emb.weight.index_select(0, self.tok)
+             + m.pos_emb.weight.index_select(0, self.pos)).float().reshape(B, 1, D)
+        n_valid = self.pos + 1                                   # cache positions in use
+        for li, blk in enumerate(m.layers):
+            n = be.layer_norm(x, blk.norm1.weight, blk.norm1.bias).reshape(B, D)
+            q, k, v, _, _ = _layer_qkv(m, be, n, pools)
+            self.cache_k[li].index_copy_(2, self.pos, k.reshape(B, H, 1, dh).to(self.cache_k.dtype))
+            self.cache_v[li].index_copy_(2, self.pos, v.reshape(B, H, 1, dh).to(self.cache_v.dtype))
+            o = R.cached_attention(q.reshape(B, H, 1, dh), self.cache_k[li], self.cache_v[li], n_valid)
+            x = x + be.linear(o.reshape(B, D), blk.attn.expand_O.weight, None).reshape(B, 1, D)
+            n = be.layer_norm(x, blk.norm2.weight, blk.norm2.bias).reshape(B, D)
+            ko, _ = _know(m, be, n, pools)
+            x = x + ko.reshape(B, 1, D)
+        x = be.layer_norm(x, m.norm.weight, m.norm.bias)
+        return be.logits(x, m.token_emb.weight)[:, 0]
+
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B] -> logits [B, V] of the next position."""
+        if self.length >= self.model.max_seq_len:
+            raise ValueError("KV cache is full")
+        if not self.use_graph:
+            lg, self.cache_k, self.cache_v, self.length = decode_step(
+                self.model, tokens, self.cache_k, self.cache_v, self.length)
+            return lg
+        self.tok.copy_(tokens)
+        self.pos.fill_(self.length)
+        if self.graph is None:
+            # warm up on a side stream (lazy initialisation must not happen during capture),
+            # then capture; the warm-up writes the same cache slot the replay writes again
+            side = torch.cuda.Stream(device=self.tok.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step_static()
+            torch.cuda.current_stream().wait_stream(side)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.out = self._step_static()
+        self.graph.replay()
+        self.length += 1
+        return self.out.clone()
+
+
 def sample_token(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0,
                  top_p: float = 0.0, generator=None) -> torch.Tensor:
     if temperature <= 0:
@@ -221,28 +322,37 @@ def sample_token(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0,
 
 @torch.no_grad()
 def generate(model, input_ids: torch.Tensor, max_new_tokens: int = 32, temperature: float = 1.0,
-             top_k: int = 0, top_p: float = 0.0, stop_ids: Iterable[int] = (), generator=None
-             ) -> Tuple[torch.Tensor, Dict[str, float]]:
+             top_k: int = 0, top_p: float = 0.0, stop_ids: Iterable[int] = (), generator=None,
+             use_graph: Optional[bool] = None) -> Tuple[torch.Tensor, Dict[str, float]]:
     """KV-cache sampling (reference sampler: scripts/analysis/standalone/
     spatial_analysis.py:444-546).  Returns the full sequences and tokens/s."""
     import time
     model.eval()
     logits, ck, cv, length = prefill(model, input_ids)
+    session = DecodeSession(model, ck, cv, length, use_graph=use_graph)
     out = [input_ids]
     nxt = sample_token(logits[:, -1], temperature, top_k, top_p, generator)
     stop = set(int(s) for s in stop_ids)
-    t0, n = time.perf_counter(), 0
+    sync = torch.cuda.synchronize if input_ids.is_cuda else (lambda: None)
+    t0, n, t1 = time.perf_counter(), 0, None
     for _ in range(max_new_tokens):
         out.append(nxt[:, None])
         n += 1
-        if length >= model.max_seq_len or (stop and all(int(t) in stop for t in nxt)):
+        if session.length >= model.max_seq_len or (stop and all(int(t) in stop for t in nxt)):
             break
-        lg, ck, cv, length = decode_step(model, nxt, ck, cv, length)
+        lg = session.step(nxt)
         nxt = sample_token(lg, temperature, top_k, top_p, generator)
-    if input_ids.is_cuda:
-        torch.cuda.synchronize()
-    dt = max(time.perf_counter() - t0, 1e-9)
-    return torch.cat(out, dim=1), {"new_tokens": n, "tokens_per_sec": n * input_ids.shape[0] / dt}
+        if t1 is None:                 # the first step carries the graph capture
+            sync()
+            t1 = time.perf_counter()
+    sync()
+    t2 = time.perf_counter()
+    B = input_ids.shape[0]
+    stats = {"new_tokens": n, "tokens_per_sec": n * B / max(t2 - t0, 1e-9),
+             "first_step_s": (t1 - t0) if t1 is not None else 0.0, "graph": session.use_graph}
+    if t1 is not None and n > 2:
+        stats["steady_tokens_per_sec"] = (n - 2) * B / max(t2 - t1, 1e-9)
+    return torch.cat(out, dim=1), stats
 
 
 @torch.no_grad()

@@ -650,6 +650,28 @@ std::vector<Tensor> score_stats_fwd(const Tensor& hg, const Tensor& h, const Ten
   return {tau, isd, mu, sd, hsum};
 }
 
+// Route-major tau, isd [R*T] and bf16(h) [R*T, r] for a handful of rows (one launch).
+std::vector<Tensor> score_stats_rows(const Tensor& h, const Tensor& off, const Tensor& gram,
+                                     const Tensor& esum, double inv_u) {
+  TORCH_CHECK(h.is_cuda() && h.dim() == 3 && h.scalar_type() == torch::kFloat32 && h.stride(2) == 1);
+  const int T = h.size(0), R = h.size(1), r = h.size(2);
+  TORCH_CHECK(off.is_cuda() && off.dim() == 2 && off.scalar_type() == torch::kFloat32 &&
+              off.size(0) == T && off.size(1) == R);
+  TORCH_CHECK(gram.scalar_type() == torch::kFloat32 && gram.is_contiguous() && gram.dim() == 2 &&
+              gram.size(0) == r && gram.size(1) == r && esum.scalar_type() == torch::kFloat32 &&
+              esum.is_contiguous() && esum.numel() == r);
+  const c10::cuda::CUDAGuard guard(h.device());
+  auto o = gram.options();
+  auto tau = torch::empty({R * T}, o), isd = torch::empty({R * T}, o);
+  auto hb = torch::empty({R * T, r}, o.dtype(torch::kBFloat16));
+  int rc = dsb_score_stats_rows(h.data_ptr<float>(), h.stride(0), h.stride(1), off.data_ptr<float>(),
+                                off.stride(0), off.stride(1), gram.data_ptr<float>(),
+                                esum.data_ptr<float>(), inv_u, T, R, r, tau.data_ptr<float>(),
+                                isd.data_ptr<float>(), hb.data_ptr(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_score_stats_rows failed with code ", rc);
+  return {tau, isd, hb};
+}
+
 // dh fp32 [N, r], w bf16 [N, r] (row stride padded to 8), d_off [N], d_esum [r].
 std::vector<Tensor> score_stats_bwd(c10::optional<Tensor> d_tau, c10::optional<Tensor> d_isd,
                                     c10::optional<Tensor> d_hsum, c10::optional<Tensor> d_hb,
@@ -736,6 +758,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grad_sq_norm", &grad_sq_norm);
   m.def("score_stats_fwd", &score_stats_fwd);
   m.def("score_stats_bwd", &score_stats_bwd);
+  m.def("score_stats_rows", &score_stats_rows);
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
   m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);
   m.def("peer_barrier", &peer_barrier);

@@ -132,8 +132,16 @@ struct WarpStager {
   // (c0, r0).  Always commits a group so waits can count slabs.
   __device__ __forceinline__ void flush(const CUtensorMap* map, uint32_t buf_addr, int c0, int r0,
                                         bool reduce_add, bool issue) const {
+    publish();
+    store(map, buf_addr, c0, r0, reduce_add, issue);
+  }
+  // The two halves of flush(), for staging several slabs behind one fence.
+  __device__ __forceinline__ void publish() const {
     fence_proxy_async_smem();
     __syncwarp();
+  }
+  __device__ __forceinline__ void store(const CUtensorMap* map, uint32_t buf_addr, int c0, int r0,
+                                        bool reduce_add, bool issue) const {
     if (lane == 0) {
       if (issue) {
         if (reduce_add) tma_reduce_add_2d(map, buf_addr, c0, r0);

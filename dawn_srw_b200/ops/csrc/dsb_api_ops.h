@@ -47,6 +47,13 @@ int dsb_route_bwd_prologue(const float* dy, const float* y, const float* row_sca
 int dsb_score_stats_fwd(const float* hg, const void* h_bf16, long long ldh, const float* esum,
                         const float* off, float inv_u, int N, int r, float* tau, float* isd,
                         float* mu, float* sd, float* hsum, cudaStream_t stream);
+// The same statistics for a handful of rows in one launch (generation), from fp32 h [T, R, r]
+// (strides h_st, h_sr in elements, unit inner stride), off [T, R] (strides o_st, o_sr) and the
+// fp32 Gram matrix.  Output rows are route-major: row ri * T + t; hb is bf16(h) [R * T, r].
+int dsb_score_stats_rows(const float* h, long long h_st, long long h_sr, const float* off,
+                         long long o_st, long long o_sr, const float* gram, const float* esum,
+                         float inv_u, int T, int R, int r, float* tau, float* isd, void* hb_bf16,
+                         cudaStream_t stream);
 // Backward of the above.  d_tau, d_isd [N], d_hsum [r], d_hb (bf16 [N, r] cotangent of the
 // bf16 copy of h) may be null.  Writes dh fp32 [N, r] (all terms summed), w = bf16(d_var * h)
 // [N, ldw] (operand of dG = w^T h * inv_u), d_off [N]; accumulates d_esum [r] (zero it first).

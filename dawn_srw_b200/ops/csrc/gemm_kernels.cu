@@ -754,19 +754,7 @@ struct FwdGateEpiWide {
       ctl.release(1);   // the next tile's read MMAs may start
     }
     // ---- phase 2: p = g * xr from registers; nothing here holds the tensor core up
-#pragma unroll
-    for (int sl = 0; sl < 2; ++sl) {
-      const bool in_range = col0 + 64 * sl < N;   // warp-uniform
-      uint32_t b_p, b_x;
-      if constexpr (kSaveXr) {
-        b_p = st.buf(0);
-        b_x = st.buf(1);
-        st.wait_free<0>();                        // both buffers have been read by their stores
-      } else {
-        b_p = st.buf(sl);
-        b_x = 0;
-        st.wait_free<1>();
-      }
+    auto put_p = [&](int sl, uint32_t b) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {               // 16-byte chunk k of the slab: 8 columns
         uint32_t pw[4];
@@ -779,13 +767,39 @@ struct FwdGateEpiWide {
               __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xp[idx]));
           pw[e] = pack_bf16x2(gf.x * xf.x, gf.y * xf.y);
         }
-        st.put(b_p, k, pw[0], pw[1], pw[2], pw[3]);
-        if constexpr (kSaveXr)
-          st.put(b_x, k, xp[32 * sl + 4 * k], xp[32 * sl + 4 * k + 1], xp[32 * sl + 4 * k + 2],
-                 xp[32 * sl + 4 * k + 3]);
+        st.put(b, k, pw[0], pw[1], pw[2], pw[3]);
       }
-      st.flush(&maps[0], b_p, col0 + 64 * sl, r0, false, in_range);
-      if constexpr (kSaveXr) st.flush(&maps[1], b_x, col0 + 64 * sl, r0, false, in_range);
+    };
+    auto put_x = [&](int sl, uint32_t b) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        st.put(b, k, xp[32 * sl + 4 * k], xp[32 * sl + 4 * k + 1], xp[32 * sl + 4 * k + 2],
+               xp[32 * sl + 4 * k + 3]);
+    };
+    const bool in0 = col0 < N, in1 = col0 + 64 < N;   // warp-uniform
+    if constexpr (!kSaveXr) {
+#pragma unroll
+      for (int sl = 0; sl < 2; ++sl) {
+        st.wait_free<1>();
+        put_p(sl, st.buf(sl));
+        st.flush(&maps[0], st.buf(sl), col0 + 64 * sl, r0, false, sl == 0 ? in0 : in1);
+      }
+    } else {
+      // Two fences per tile: both read-scalar slabs behind one, both p slabs
+      // behind the other.
+      st.wait_free<0>();
+      put_x(0, st.buf(0));
+      put_x(1, st.buf(1));
+      st.publish();
+      st.store(&maps[1], st.buf(0), col0, r0, false, in0);
+      st.store(&maps[1], st.buf(1), col0 + 64, r0, false, in1);
+      st.wait_free<1>();
+      put_p(0, st.buf(0));
+      st.wait_free<0>();
+      put_p(1, st.buf(1));
+      st.publish();
+      st.store(&maps[0], st.buf(0), col0, r0, false, in0);
+      st.store(&maps[0], st.buf(1), col0 + 64, r0, false, in1);
     }
     if (row_ok) {
       atomicAdd(p.den_sum + row, den_acc);
@@ -1292,7 +1306,9 @@ static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t
   gp.m_tiles = (gp.M + kBlockM * kCtas - 1) / (kBlockM * kCtas);
   gp.n_tiles = (gp.N + BN - 1) / BN;
   gp.n_fastest = gp.n_tiles <= gp.m_tiles ? 1 : 0;
-  const long long total = static_cast<long long>(gp.m_tiles) * gp.n_tiles;
+  // work items of the persistent loop: output tiles times the K splits of each
+  const long long total =
+      static_cast<long long>(gp.m_tiles) * gp.n_tiles * (gp.k_splits > 1 ? gp.k_splits : 1);
   if (total <= 0) return 0;
   const int units = sm_count() / kCtas;
   const int grid = kCtas * static_cast<int>(total < units ? total : units);
@@ -1477,9 +1493,11 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   GemmParams<PlainEpi::Params> gp;
   memset(&gp, 0, sizeof(gp));
   const int BN = (block_n & 0xffff) == 128 ? 128 : 256;
+  // up to 128 rows fit one CTA's tile: no pairs, so twice as many workers share N and K
+  const bool pairs = use_cta_pairs() && M > kBlockM;
   int rc = fill_operand(&gp.tma_a[0], {A, a_mn, lda}, M, K, kBlockM);
   if (rc) return 100 + rc;
-  rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, use_cta_pairs() ? BN / 2 : BN);
+  rc = fill_operand(&gp.tma_b[0], {B, b_mn, ldb}, N, K, pairs ? BN / 2 : BN);
   if (rc) return 200 + rc;
   gp.seg[0] = {(K + kBlockK - 1) / kBlockK, 0, a_mn, b_mn};
   gp.n_seg = 1;
@@ -1492,19 +1510,33 @@ extern "C" int dsb_gemm_bf16(const void* A, int a_mn, long long lda, const void*
   if (accumulate && !c_is_bf16 && bias == nullptr) {
     // few output tiles but a long K (pool gradients of a small unit shard): cut K so
     // that every SM pair has work; the splits meet in the fp32 reduce-add epilogue
-    const int tm = use_cta_pairs() ? 2 * kBlockM : kBlockM;
+    const int tm = pairs ? 2 * kBlockM : kBlockM;
     const long long tiles = static_cast<long long>((M + tm - 1) / tm) * ((N + BN - 1) / BN);
-    const int units = sm_count() / (use_cta_pairs() ? 2 : 1);
+    const int units = sm_count() / (pairs ? 2 : 1);
     const int k_tiles = gp.seg[0].k_tiles;
     if (tiles < 2 * units && k_tiles >= 64) {
-      int want = static_cast<int>((3 * units + tiles - 1) / tiles);
-      const int max_by_k = k_tiles / 32;
-      if (want > max_by_k) want = max_by_k;
+      // tiles * splits should fill a whole number of waves (1..3) of SM pairs; a
+      // longer wave count is taken only if it fills the machine 5 % better
+      // every split reduce-adds a whole output tile: long splits unless the output is a few rows
+      const int max_by_k = k_tiles / (M <= tm ? 8 : 32);
+      int want = 1;
+      double best = static_cast<double>(tiles) / ((tiles + units - 1) / units * units);
+      for (int w = 1; w <= 3; ++w) {
+        int s = static_cast<int>(static_cast<long long>(w) * units / tiles);
+        if (s > max_by_k) s = max_by_k;
+        if (s < 2) continue;
+        const long long items = tiles * s;
+        const double fill = static_cast<double>(items) / ((items + units - 1) / units * units);
+        if (fill > best + 0.05) { best = fill; want = s; }
+      }
       if (want > 1) gp.k_splits = want;
     }
   }
-  return BN == 128 ? launch_engine<128, PlainEpi>(gp, stream)
-                   : launch_engine<256, PlainEpi>(gp, stream);
+  if (!pairs)
+    return BN == 128 ? launch_engine_impl<128, PlainEpi, 1>(gp, stream)
+                     : launch_engine_impl<256, PlainEpi, 1>(gp, stream);
+  return BN == 128 ? launch_engine_impl<128, PlainEpi, 2>(gp, stream)
+                   : launch_engine_impl<256, PlainEpi, 2>(gp, stream);
 }
 
 static GateConsts make_gc(const DsbGate* g) {
@@ -1572,7 +1604,11 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
   if (stats != nullptr && !wide) return 706;    // ... and reads per-token float4 statistics
   if (diag != nullptr && !wide) return 708;     // ... and accumulates routing diagnostics
   if (stats == nullptr && (tau == nullptr || inv_sigma == nullptr)) return 707;
-  const int brows = wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
+  // A handful of token rows (decoding): a CTA pair would spend a 256-row tile on them, so
+  // single CTAs take 128 x 256 tiles and twice as many of them stream the pool.
+  const bool solo = wide && T <= kBlockM && xr_out == nullptr && diag == nullptr &&
+                    !(gather != nullptr && gather->n_ranks > 1);
+  const int brows = solo ? 256 : wide ? 128 : (use_cta_pairs() ? BN / 2 : BN);
   int rc = fill_operand(&gp.tma_a[0], {h, 0, ldh}, T, r, kBlockM);
   rc |= fill_operand(&gp.tma_b[0], {emb, 0, lde}, U, r, brows);
   rc |= fill_operand(&gp.tma_a[1], {x, 0, ldx}, T, D, kBlockM);
@@ -1595,6 +1631,11 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
     if (!use_cta_pairs()) return 702;
     rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
     if (rc) return rc;
+  }
+  if (solo) {
+    if (gate->kind == 0) return launch_engine_impl<256, FwdGateEpiWide<0, false>, 1>(gp, stream);
+    if (gate->kind == 1) return launch_engine_impl<256, FwdGateEpiWide<1, false>, 1>(gp, stream);
+    return launch_engine_impl<256, FwdGateEpiWide<2, false>, 1>(gp, stream);
   }
   if (wide) {
     return xr_out != nullptr ? launch_fwd_wide<true>(gp, gate->kind, fused, stream)

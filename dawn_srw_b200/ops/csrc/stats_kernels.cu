@@ -142,6 +142,72 @@ __global__ void score_stats_bwd_kernel(const float* __restrict__ d_tau, const fl
   for (int j = threadIdx.x; j < r; j += blockDim.x) atomicAdd(d_esum + j, s_sum[j]);
 }
 
+constexpr int kRowGroups = 8;      // thread groups that share the rows of G
+constexpr int kRowThreads = 128;   // threads of a group: one column of G each (strided)
+
+// A handful of rows (decoding): the whole statistic in one launch, fp32 throughout.
+// Block n handles token t = n % T of route ri = n / T (route-major output rows, the
+// order in which the routes of one pool are stacked into one gate-kernel call).
+// Thread j owns column j of the symmetric G: consecutive threads read consecutive
+// addresses of every row of G.
+__global__ void score_stats_rows_kernel(const float* __restrict__ h, long long h_st, long long h_sr,
+                                        const float* __restrict__ off, long long o_st, long long o_sr,
+                                        const float* __restrict__ gram, const float* __restrict__ esum,
+                                        float inv_u, int T, int r, float* __restrict__ tau,
+                                        float* __restrict__ isd, __nv_bfloat16* __restrict__ hb) {
+  __shared__ float s_h[kMaxR];
+  __shared__ float s_part[kRowGroups][kMaxR];
+  __shared__ float s_red[2][32];
+  const int n = blockIdx.x, t = n % T, ri = n / T;
+  const float* hr = h + t * h_st + ri * h_sr;
+  for (int j = threadIdx.x; j < r; j += blockDim.x) {
+    const __nv_bfloat16 q = __float2bfloat16(hr[j]);     // the gate kernels see bf16(h)
+    hb[static_cast<size_t>(n) * r + j] = q;
+    s_h[j] = __bfloat162float(q);
+  }
+  __syncthreads();
+  // (G h)_j: the rows of G are dealt to kRowGroups thread groups, eight independent
+  // accumulators per thread keep the loads in flight
+  const int grp = threadIdx.x / kRowThreads, tj = threadIdx.x % kRowThreads;
+  const int rows_per = (r + kRowGroups - 1) / kRowGroups;
+  const int i0 = grp * rows_per, i1 = min(r, i0 + rows_per);
+  for (int j = tj; j < r; j += kRowThreads) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    int i = i0;
+    for (; i + 8 <= i1; i += 8) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        a[k] = fmaf(gram[static_cast<size_t>(i + k) * r + j], s_h[i + k], a[k]);
+    }
+    for (; i < i1; ++i) a[0] = fmaf(gram[static_cast<size_t>(i) * r + j], s_h[i], a[0]);
+    s_part[grp][j] = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+  }
+  __syncthreads();
+  float m2 = 0.f, m1 = 0.f;
+  for (int j = threadIdx.x; j < r; j += blockDim.x) {
+    float acc = 0.f;
+#pragma unroll
+    for (int g = 0; g < kRowGroups; ++g) acc += s_part[g][j];
+    m2 = fmaf(acc, s_h[j], m2);
+    m1 = fmaf(esum[j], s_h[j], m1);
+  }
+  m2 = warp_sum(m2);
+  m1 = warp_sum(m1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { s_red[0][warp] = m2; s_red[1][warp] = m1; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    m2 = warp_sum(lane < nw ? s_red[0][lane] : 0.f) * inv_u;
+    const float mu = warp_sum(lane < nw ? s_red[1][lane] : 0.f) * inv_u;
+    if (lane == 0) {
+      const float sd = sqrtf(fmaxf(m2 - mu * mu, kVarFloor)) + kSdEps;
+      tau[n] = fmaf(off[t * o_st + ri * o_sr], sd, mu);
+      isd[n] = 1.f / sd;
+    }
+  }
+}
+
 int stats_grid(int N) {
   const int blocks = (N + 7) / 8;
   return blocks < 148 * 4 ? (blocks < 1 ? 1 : blocks) : 148 * 4;
@@ -174,5 +240,17 @@ extern "C" int dsb_score_stats_bwd(const float* d_tau, const float* d_isd, const
       d_tau, d_isd, d_hsum, static_cast<const __nv_bfloat16*>(d_hb_bf16), off, mu, sd, hg,
       static_cast<const __nv_bfloat16*>(h_bf16), ldh, esum,
       inv_u, N, r, dh, static_cast<__nv_bfloat16*>(w_bf16), ldw, d_off, d_esum);
+  return cudaGetLastError() == cudaSuccess ? 0 : 802;
+}
+
+extern "C" int dsb_score_stats_rows(const float* h, long long h_st, long long h_sr, const float* off,
+                                    long long o_st, long long o_sr, const float* gram,
+                                    const float* esum, float inv_u, int T, int R, int r, float* tau,
+                                    float* isd, void* hb_bf16, cudaStream_t stream) {
+  if (T <= 0 || R <= 0) return 0;
+  if (r <= 0 || r > kMaxR) return 801;
+  score_stats_rows_kernel<<<T * R, kRowGroups * kRowThreads, 0, stream>>>(h, h_st, h_sr, off, o_st, o_sr, gram, esum, inv_u,
+                                                     T, r, tau, isd,
+                                                     static_cast<__nv_bfloat16*>(hb_bf16));
   return cudaGetLastError() == cudaSuccess ? 0 : 802;
 }

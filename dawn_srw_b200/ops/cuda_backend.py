@@ -38,7 +38,7 @@ from . import build as _build
 from . import reference as R
 from .backend import ParallelCtx, PreparedPool
 from .gates import GATE_GELU_Z, GateSpec
-from .score_stats import score_stats
+from .score_stats import score_stats, score_stats_rows
 from .srw_ref import SRWResult, srw_pool_ref
 from ..parallel import collectives as C
 
@@ -717,6 +717,33 @@ class CudaBackend:
             return y[:, :n]
         return _LinearFn.apply(x, w, b, self._w(w), torch.float32)
 
+    @torch.no_grad()
+    def linear_cat(self, x, layers):
+        """Forward-only: several ``nn.Linear`` layers on the same input as ONE GEMM over
+        their concatenated (and 8-padded) weights; the bf16 weight and the bias are cached
+        until a parameter changes.  Returns one output view per layer."""
+        key = tuple((l.weight.data_ptr(), l.weight._version,
+                     0 if l.bias is None else l.bias._version) for l in layers)
+        cache = self.__dict__.setdefault("_cat_cache", {})
+        hit = cache.get(id(layers[0]))
+        if hit is None or hit[0] != key:
+            ws, bs, cuts, n0 = [], [], [], 0
+            for l in layers:
+                n = l.weight.shape[0]
+                ws.append(l.weight.detach().float())
+                bs.append(l.bias.detach().float() if l.bias is not None
+                          else torch.zeros(n, device=l.weight.device))
+                cuts.append((n0, n0 + n))
+                n0 += n
+            pad = _round_up(n0, 8) - n0
+            w = F.pad(torch.cat(ws, 0), (0, 0, 0, pad)).to(torch.bfloat16).contiguous()
+            b = F.pad(torch.cat(bs, 0), (0, pad)).contiguous()
+            hit = (key, w, b, cuts)
+            cache[id(layers[0])] = hit
+        _, w, b, cuts = hit
+        y = gemm(_bf16_2d(x), False, w, False, out_dtype=torch.float32, bias=b)
+        return [y[:, a:e] for a, e in cuts]
+
     def embed(self, ids, tok, pos):
         if tok.shape[1] % 4 != 0 or tok.dtype != torch.float32:
             return R.embed(ids, tok, pos)
@@ -785,6 +812,61 @@ class CudaBackend:
                 res.out = res.out * out_scale
             return res
         return self._srw_local(x, h, tau_off, pool, spec, pctx, want_diag, unit_mask, out_scale)
+
+    @torch.no_grad()
+    def srw_infer(self, x, h, tau_off, pool: CudaPool, spec: GateSpec, *, n_total=None,
+                  out_scale=None):
+        """Forward-only SRW call for generation (unsharded pools): no load-balance or dead-unit
+        statistics, nothing kept for a backward pass, and the write GEMM cuts its long K = U
+        into splits that meet in the fp32 reduce-add epilogue, so that with a handful of token
+        rows (decoding: T = batch) every SM pair still streams a share of the pool instead of
+        five row tiles streaming all of it (reference: _srw_inference,
+        models/dawn_spatial_v41_exp.py:1713-1739).  Returns the per-route outputs [T, D] fp32,
+        normalised and scaled."""
+        ex = pool.extra
+        U = ex["U"]
+        U_tot = n_total if n_total is not None else U
+        T, Rr, r = h.shape
+        e, dev = ext(), x.device
+        st = status_word(dev)
+        x_bf = _bf16_2d(x)
+        Up = _round_up(U, 8)
+        D = x.shape[1]
+        if out_scale is None:
+            scale = 1.0
+        else:
+            scale = out_scale.detach().float() if isinstance(out_scale, torch.Tensor) else float(out_scale)
+        gl = _gate_list(spec)
+        wide = bool(e.srw_wide_tiles(U))
+        # Routes of one pool are independent token rows as far as the kernels care: with few
+        # tokens (decoding) they are stacked into one call, so the pool is streamed once.
+        stack = Rr * T <= 128
+        if stack:
+            tau, inv_sd, h_rm = score_stats_rows(h, tau_off, ex["gram"], ex["esum"], U_tot)
+            calls = [(h_rm, x_bf.repeat(Rr, 1) if Rr > 1 else x_bf, tau, inv_sd)]
+        else:
+            tau, inv_sd, _, h_bf3 = score_stats(h, tau_off, ex["gram"], ex["esum"], U_tot,
+                                                ex["gram_split"])
+            calls = [(_bf16_2d(h_bf3[:, ri]), x_bf, tau[:, ri].contiguous(), inv_sd[:, ri].contiguous())
+                     for ri in range(Rr)]
+        outs = []
+        for h_r, x_r, tau_r, isd_r in calls:
+            Tr = h_r.shape[0]
+            p = torch.empty(Tr, Up, dtype=torch.bfloat16, device=dev)
+            work = torch.zeros(Tr * (D + 1), dtype=torch.float32, device=dev)   # y and den, one fill
+            y, den = work[:Tr * D].view(Tr, D), work[Tr * D:]
+            if wide:
+                e.srw_fwd_gate_xr(h_r, pool.emb[:U], x_r, pool.read[:U], p, None, tau_r, isd_r, None,
+                                  den, None, None, None, gl, st, *NO_GATHER)
+            else:
+                e.srw_fwd_gate(h_r, pool.emb[:U], x_r, pool.read[:U], p, tau_r, isd_r, den, None, None,
+                               None, gl, st)
+            gemm(p[:, :U], False, pool.write[:U], True, out=y, accumulate=True)
+            outs.append(y * (scale / den.clamp(min=1.0)).unsqueeze(-1))
+        count_launches(len(calls))
+        if stack:
+            return list(outs[0].reshape(Rr, T, D).unbind(0))
+        return outs
 
     def srw_group(self, x, calls, spec: GateSpec, *, want_diag: bool = True):
         """Several SRW calls on the same ``x``.  Sequence- and pool-sharded calls on

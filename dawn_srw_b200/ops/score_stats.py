@@ -111,3 +111,26 @@ class _ScoreStatsFn(torch.autograd.Function):
 def score_stats(h, tau_off, gram, esum, n_units: int, gram_split=None):
     """-> (tau [T,R], inv_sigma [T,R], hsum [r], h_bf [T,R,r]); see the module docstring."""
     return _ScoreStatsFn.apply(h, tau_off, gram, esum, 1.0 / float(n_units), gram_split)
+
+
+@torch.no_grad()
+def score_stats_rows(h, tau_off, gram, esum, n_units: int):
+    """Forward-only statistics of a handful of rows (generation) in one launch:
+    h [T, R, r], tau_off [T, R] -> route-major (row ``ri * T + t``) tau [R*T],
+    inv_sigma [R*T] and the bf16 copy of h [R*T, r]."""
+    T, Rr, r = h.shape
+    inv_u = 1.0 / float(n_units)
+    if h.is_cuda:
+        from . import cuda_backend as CB
+        hf = h if h.dtype == torch.float32 and h.stride(2) == 1 else h.float().contiguous()
+        off = tau_off if tau_off.dtype == torch.float32 else tau_off.float()
+        tau, isd, hb = CB.ext().score_stats_rows(hf, off, gram.detach().float().contiguous(),
+                                                 esum.detach().float().contiguous(), inv_u)
+        CB.count_launches(1)
+        return tau, isd, hb
+    hb = h.detach().to(torch.bfloat16).transpose(0, 1).reshape(Rr * T, r)
+    hf = hb.float()
+    mu = (hf @ esum.float()) * inv_u
+    m2 = ((hf @ gram.float()) * hf).sum(-1) * inv_u
+    sd = torch.sqrt((m2 - mu * mu).clamp_min(VAR_FLOOR)) + SD_EPS
+    return mu + tau_off.float().t().reshape(-1) * sd, 1.0 / sd, hb

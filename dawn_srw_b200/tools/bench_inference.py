@@ -51,7 +51,10 @@ def run(model, vocab: int, batch: int, seq_len: int, warmup: int, iters: int, ne
         prompt = ids[:, : max(1, min(8, seq_len - new_tokens))]
         generate(model, prompt, max_new_tokens=2)                      # warm-up
         _, stats = generate(model, prompt, max_new_tokens=new_tokens, temperature=1.0, top_k=50)
-        rec["decode_tokens_per_sec"] = stats["tokens_per_sec"]
+        rec["decode_tokens_per_sec"] = stats.get("steady_tokens_per_sec", stats["tokens_per_sec"])
+        rec["decode_tokens_per_sec_with_first_step"] = stats["tokens_per_sec"]
+        rec["decode_first_step_ms"] = 1e3 * stats["first_step_s"]
+        rec["decode_graph"] = stats["graph"]
         rec["decode_new_tokens"] = stats["new_tokens"]
     return rec
 

@@ -58,6 +58,71 @@ def test_gemm_epilogue_options(cb):
     cb.check_status()
 
 
+@pytest.mark.parametrize("M", [1, 32, 128])
+def test_engine_gemm_with_few_rows(cb, M):
+    """Up to 128 rows: single-CTA tiles, and the long K of a decode-step write GEMM is cut
+    into splits that meet in the reduce-add epilogue."""
+    dev = torch.device("cuda")
+    torch.manual_seed(M)
+    for K, N in ((6400, 1280), (20000, 384), (72, 520)):
+        A = torch.randn(M, K, device=dev).bfloat16()
+        Bt = torch.randn(K, N, device=dev).bfloat16()         # stored [K, N]: MN-major operand
+        ref = A.float() @ Bt.float()
+        y = torch.full((M, N), 0.25, device=dev)
+        cb.gemm(A, False, Bt, True, out=y, accumulate=True)
+        assert _rel(y, ref + 0.25) < 1e-5
+        out = cb.gemm(A, False, Bt.t().contiguous(), False, out_dtype=torch.bfloat16)
+        assert _rel(out, ref) < 5e-3
+    cb.check_status()
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("T", [1, 7, 128])
+def test_forward_gate_kernel_with_few_rows(cb, kind, T):
+    """Decode shapes run the 256-wide gate kernel on single CTAs (128 x 256 tiles)."""
+    from dawn_srw_b200.ops.gates import GateSpec, gate_forward
+    dev = torch.device("cuda")
+    torch.manual_seed(10 * T + kind)
+    U, r, D = 3001, 128, 384
+    spec = GateSpec(kind=kind)
+    nz = torch.nn.functional.normalize
+    h, x = torch.randn(T, r, device=dev).bfloat16(), torch.randn(T, D, device=dev).bfloat16()
+    emb, read = (nz(torch.randn(U, d, device=dev), dim=-1).bfloat16() for d in (r, D))
+    s = h.float() @ emb.float().t()
+    mu, sd = s.mean(-1, keepdim=True), s.std(-1, unbiased=False, keepdim=True) + 1e-8
+    tau = mu + 0.3 * sd
+    g, dt, _ = gate_forward(spec, s, tau, sd)
+    Up = (U + 7) // 8 * 8
+    p = torch.zeros(T, Up, device=dev, dtype=torch.bfloat16)
+    den = torch.zeros(T, device=dev)
+    e, st, gl = cb.ext(), cb.status_word(dev), cb._gate_list(spec)
+    e.srw_fwd_gate_xr(h, emb, x, read, p, None, tau.squeeze(-1).contiguous(),
+                      (1 / sd).squeeze(-1).contiguous(), None, den, None, None, None, gl, st,
+                      *cb.NO_GATHER)
+    assert _rel(p[:, :U], g * (x.float() @ read.float().t())) < 6e-3
+    assert _rel(den, dt.sum(-1)) < 1e-4
+    cb.check_status()
+
+
+def test_score_statistics_of_a_few_rows(cb):
+    """The one-launch statistics kernel of the generation path against fp32 torch."""
+    from dawn_srw_b200.ops.score_stats import score_stats_rows
+    dev = torch.device("cuda")
+    torch.manual_seed(3)
+    T, R, r, U = 5, 2, 256, 3000
+    emb = torch.nn.functional.normalize(torch.randn(U, r, device=dev), dim=-1)
+    gram, esum = emb.t() @ emb, emb.sum(0)
+    big = torch.randn(T, 3 * r + 8, device=dev)
+    h = big[:, :2 * r].view(T, R, r)                          # strided view, as the router emits it
+    off = torch.randn(T, 3, device=dev)[:, :2]
+    tau, isd, hb = score_stats_rows(h, off, gram, esum, U)
+    hq = h.bfloat16().float().transpose(0, 1).reshape(R * T, r)
+    s = hq @ emb.t()
+    mu, sd = s.mean(-1), s.std(-1, unbiased=False) + 1e-8
+    assert torch.equal(hb.float(), hq)
+    assert _rel(isd, 1 / sd) < 1e-4 and _rel(tau, mu + off.t().reshape(-1) * sd) < 1e-4
+
+
 @pytest.mark.parametrize("kind", [0, 1, 2])
 @pytest.mark.parametrize("dims", [(256, 384, 128, 384), (300, 1580, 128, 384), (130, 197, 64, 256),
                                   (300, 2504, 128, 384), (520, 4099, 64, 256), (260, 777, 64, 256)])   # U >= 512: 256-wide tiles
@@ -67,6 +132,7 @@ def test_gate_kernels(cb, kind, dims):
     dev = torch.device("cuda")
     spec = GateSpec(kind=kind)
     nz = torch.nn.functional.normalize
+    torch.manual_seed(T + U + kind)
     h = torch.randn(T, r, device=dev).bfloat16()
     emb = nz(torch.randn(U, r, device=dev), dim=-1).bfloat16()
     x = torch.randn(T, D, device=dev).bfloat16()
@@ -95,7 +161,7 @@ def test_gate_kernels(cb, kind, dims):
     dtau, dsz = torch.zeros(T, device=dev), torch.zeros(T, device=dev)
     e.srw_bwd_gate(h, emb, x, read, dy, write, pb, dxr, ds, tau_c, isd_c, dden, dtau, dsz, gl, st)
     assert _rel(pb[:, :U], g * xr) < 6e-3 and _rel(dxr[:, :U], dp * g) < 6e-3
-    assert _rel(ds[:, :U], ds_ref) < 8e-3 and _rel(dtau, dtau_ref.squeeze(-1)) < 4e-3  # gate coefficients are held as bf16
+    assert _rel(ds[:, :U], ds_ref) < 1e-2 and _rel(dtau, dtau_ref.squeeze(-1)) < 4e-3  # gate coefficients are held as bf16
     if kind == 1:
         # the sigma-path reduction is recovered from ds.emb and dtau instead of a kernel output
         dh = ds[:, :U].float() @ emb.float()
@@ -494,6 +560,36 @@ def test_tiny_model_matches_reference_backend_and_trains(cb):
     # diagnostics path on the CUDA backend
     r = m2(ids, labels=ids, want_diag=True)
     assert "know_active" in r and 0.0 <= float(r["know_active"]) <= 1.0
+    cb.check_status()
+
+
+def test_graph_captured_decoding_matches_eager_and_prefill(cb):
+    """The per-token step replayed from a CUDA graph gives the logits of the eager step,
+    and both agree with a full-sequence forward over the same tokens."""
+    from dawn_srw_b200.models import inference as I
+    from dawn_srw_b200.models.dawn import DAWN
+    dev = torch.device("cuda")
+    m = DAWN(vocab_size=1000, d_model=128, n_layers=2, n_heads=4, max_seq_len=64, d_route=64, n_qk=200,
+             n_v=264, n_know=1100, model_version="spatial-r1-v4.0.1", dropout_rate=0.0,
+             router_dropout=0.0, backend=cb.CudaBackend()).to(dev).eval()
+    g = torch.Generator(device=dev).manual_seed(3)
+    ids = torch.randint(1, 1000, (3, 12), device=dev, generator=g)
+    more = torch.randint(1, 1000, (3, 5), device=dev, generator=g)
+    logits_p, ck, cv, n = I.prefill(m, ids)
+    sess_g = I.DecodeSession(m, ck.clone(), cv.clone(), n, use_graph=True)
+    sess_e = I.DecodeSession(m, ck.clone(), cv.clone(), n, use_graph=False)
+    got_g, got_e = [], []
+    for t in range(more.shape[1]):
+        got_g.append(sess_g.step(more[:, t]))
+        got_e.append(sess_e.step(more[:, t]))
+    assert sess_g.graph is not None and sess_g.length == n + more.shape[1]
+    full = I.prefill(m, torch.cat([ids, more], dim=1))[0]          # [B, S, V]
+    for t in range(more.shape[1]):
+        assert _rel(got_g[t], got_e[t]) < 1e-3
+        assert _rel(got_g[t], full[:, n + t]) < 2e-2
+    out_g, _ = I.generate(m, ids, max_new_tokens=6, temperature=0.0, use_graph=True)
+    out_e, _ = I.generate(m, ids, max_new_tokens=6, temperature=0.0, use_graph=False)
+    assert torch.equal(out_g, out_e)
     cb.check_status()
 
 
