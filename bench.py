@@ -46,6 +46,10 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=512)
     ap.add_argument("--batch-per-gpu", type=int, default=0, help="sequences per GPU per step")
     ap.add_argument("--parallelism", default="pool", choices=["pool", "dp"])
+    ap.add_argument("--pool-shards", type=int, default=0,
+                    help="with --parallelism pool: unit shards per pool (a divisor of --gpus); the "
+                         "remaining factor is data parallel (e.g. --gpus 8 --pool-shards 4 = dp2 x pool4). "
+                         "0 = all GPUs shard the pools")
     ap.add_argument("--optimizer", default="auto", choices=["auto", "partitioned", "replicated"],
                     help="partitioned: reduce-scatter + AdamW on the owned slice + all-gather over "
                          "peer memory with sharded moments; auto = partitioned for --parallelism dp")
@@ -208,6 +212,10 @@ def main():
             raise SystemExit(f"--gpus {args.gpus} needs a torchrun launch with {args.gpus} ranks "
                              f"(WORLD_SIZE={world})")
     pool_shards = world if (args.parallelism == "pool" and world > 1) else 1
+    if pool_shards > 1 and args.pool_shards:
+        if world % args.pool_shards != 0:
+            raise SystemExit(f"--pool-shards {args.pool_shards} does not divide {world} GPUs")
+        pool_shards = args.pool_shards
     topo = init_topology(pool_shards=pool_shards, seq_shard=True)
     dev = torch.device("cuda", topo.local_rank)
     torch.cuda.set_device(dev)
@@ -329,7 +337,8 @@ def main():
             "data": "synthetic uniform tokens, random init", "impl": args.impl,
             "config": {"model": f"DAWN-SRW {args.model} ({cfg.model.model_version})",
                        "global_batch": t.batch_size, "seq_len": args.seq_len,
-                       "parallelism": (f"pool{pool_shards}+seqshard" if pool_shards > 1 else f"dp{world}"),
+                       "parallelism": ((f"dp{world // pool_shards}x" if pool_shards < world else "")
+                                       + f"pool{pool_shards}+seqshard" if pool_shards > 1 else f"dp{world}"),
                        "l2": "inputs and weights per step exceed the 126 MB L2 (no flush needed)",
                        "layer_recompute": False,
                        "optimizer": type(trainer.optimizer).__name__},

@@ -92,6 +92,7 @@ class TrainingConfig:
     dp: int = 0
     seq_shard: bool = True
     zero_pool_state: bool = False
+    fsdp: bool = False                   # dense baseline: Linear weights sharded by rows over the data-parallel ranks
     overlap_grad_reduce: bool = True     # replicated-parameter gradients are all-reduced during backward
     n_chunks_know: int = 0
     n_chunks_qk: int = 0

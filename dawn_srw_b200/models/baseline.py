@@ -17,6 +17,7 @@ import torch.nn.functional as F
 import torch.utils.checkpoint as ckpt
 
 from ..ops.backend import default_backend
+from ..parallel.fsdp import sharded_linear
 from .dawn import _LN
 
 
@@ -94,15 +95,16 @@ class VanillaTransformer(nn.Module):
         n = be.layer_norm(x, lyr.norm1.weight, lyr.norm1.bias).reshape(B * S, D)
         heads = lambda t: t.reshape(B, S, H, D // H).transpose(1, 2)
         a = lyr.attn
-        q = heads(be.linear(n, a.q_proj.weight, a.q_proj.bias))
-        k = heads(be.linear(n, a.k_proj.weight, a.k_proj.bias))
-        v = heads(be.linear(n, a.v_proj.weight, a.v_proj.bias))
+        lin = lambda t, layer: sharded_linear(be, t, layer)     # gathers row-sharded weights
+        q = heads(lin(n, a.q_proj))
+        k = heads(lin(n, a.k_proj))
+        v = heads(lin(n, a.v_proj))
         o = be.attention(q, k, v, self.dropout_rate, training).transpose(1, 2).reshape(B * S, D)
-        x = x + be.linear(o, a.o_proj.weight, None).reshape(B, S, D)
+        x = x + lin(o, a.o_proj).reshape(B, S, D)
         n = be.layer_norm(x, lyr.norm2.weight, lyr.norm2.bias).reshape(B * S, D)
-        hdn = F.gelu(be.linear(n, lyr.ffn.w_up.weight, lyr.ffn.w_up.bias), approximate="tanh")
+        hdn = F.gelu(lin(n, lyr.ffn.w_up), approximate="tanh")
         hdn = be.dropout(hdn, self.dropout_rate, training)
-        return x + be.linear(hdn, lyr.ffn.w_down.weight, lyr.ffn.w_down.bias).reshape(B, S, D)
+        return x + lin(hdn, lyr.ffn.w_down).reshape(B, S, D)
 
     def forward(self, input_ids, labels=None, attention_mask=None, *, want_diag=False,
                 deterministic: Optional[bool] = None) -> Dict[str, Any]:

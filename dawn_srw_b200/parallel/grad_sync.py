@@ -15,6 +15,10 @@ partial sums:
   every rank of its shard group: they arrive through the all-reduced /
   all-gathered output gradient).
 
+* weights sharded by rows over the data-parallel ranks (parallel/fsdp.py, dense
+  baseline) arrive already summed by their reduce-scatter -> only divided by
+  the world size; their squared norm is summed over that group.
+
 Small tensors are packed into one flat bucket per reduction; pool tensors are
 reduced in place.  The squared global norm counts each parameter once: pool
 slices are summed over the shard group, replicated parameters are taken from
@@ -59,7 +63,7 @@ class GradSync:
             return
         self._overlap, self._bucket_bytes = True, int(bucket_bytes)
         for n, p in named_params:
-            if p.requires_grad and not self._is_pool(n):
+            if p.requires_grad and not self._is_pool(n) and not self._is_rowsharded(p):
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad_ready))
 
     def detach(self) -> None:
@@ -113,12 +117,17 @@ class GradSync:
     def _is_pool(self, name: str) -> bool:
         return wd_group_of(name) == "pool"
 
+    @staticmethod
+    def _is_rowsharded(p) -> bool:
+        return getattr(p, "_fsdp_rows", None) is not None
+
     def reduce(self, named, grads: List[torch.Tensor]) -> List[torch.Tensor]:
         t = self.topo
         if t.world == 1:
             return grads
         done = self._finish_overlapped(named, grads) if self._overlap else set()
-        small = [g for (n, _), g in zip(named, grads) if not self._is_pool(n) and id(g) not in done]
+        small = [g for (n, p), g in zip(named, grads)
+                 if not self._is_pool(n) and not self._is_rowsharded(p) and id(g) not in done]
         if small:
             flat = torch.cat([g.reshape(-1).float() for g in small])
             dist.all_reduce(flat, group=t.world_group)
@@ -128,8 +137,10 @@ class GradSync:
                 g.copy_(flat[off: off + g.numel()].view_as(g))
                 off += g.numel()
         pool_div = float(t.world)
-        for (n, _), g in zip(named, grads):
-            if self._is_pool(n):
+        for (n, p), g in zip(named, grads):
+            if self._is_rowsharded(p):
+                g /= pool_div
+            elif self._is_pool(n):
                 if t.pool_shards == 1:
                     dist.all_reduce(g, group=t.world_group)
                 elif t.dp > 1:
@@ -139,12 +150,19 @@ class GradSync:
 
     def global_sq_norm(self, named, grads: List[torch.Tensor]) -> torch.Tensor:
         t = self.topo
-        rep = [g.float().square().sum() for (n, _), g in zip(named, grads) if not self._is_pool(n)]
-        pool = [g.float().square().sum() for (n, _), g in zip(named, grads) if self._is_pool(n)]
+        sq = lambda g: g.float().square().sum()
+        rep = [sq(g) for (n, p), g in zip(named, grads) if not self._is_pool(n) and not self._is_rowsharded(p)]
+        pool = [sq(g) for (n, _), g in zip(named, grads) if self._is_pool(n)]
+        rows = [(sq(g), p._fsdp_group) for (_, p), g in zip(named, grads) if self._is_rowsharded(p)]
         dev = grads[0].device
         rep_s = torch.stack(rep).sum() if rep else torch.zeros((), device=dev)
         pool_s = torch.stack(pool).sum() if pool else torch.zeros((), device=dev)
         if t.pool_shards > 1:
             pool_s = pool_s.clone()
             dist.all_reduce(pool_s, group=t.shard_group)
-        return rep_s + pool_s
+        total = rep_s + pool_s
+        if rows:
+            rows_s = torch.stack([v for v, _ in rows]).sum()
+            dist.all_reduce(rows_s, group=rows[0][1])
+            total = total + rows_s
+        return total

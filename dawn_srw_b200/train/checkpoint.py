@@ -183,12 +183,15 @@ def consolidate(paths: List[str], pool_sizes: Dict[str, int], out_path: str) -> 
     count = len(blobs)
     from ..parallel.topology import PoolShard
     merged = dict(blobs[0])
+    row_blocks = blobs[0].get("fsdp_rows") or {}     # dense weights stored as per-rank row blocks
 
     def merge_tree(trees):
         out = {}
         for k, v in trees[0].items():
             m = re.search(r"(qk|v|know)_(emb|read|write)$", k)
-            if m and isinstance(v, torch.Tensor) and v.dim() == 2:
+            if k in row_blocks and isinstance(v, torch.Tensor) and v.dim() == 2:
+                out[k] = torch.cat([t[k] for t in trees], 0)[: row_blocks[k]]
+            elif m and isinstance(v, torch.Tensor) and v.dim() == 2:
                 n = pool_sizes[m.group(1)]
                 rows = []
                 for i, t in enumerate(trees):
@@ -205,5 +208,6 @@ def consolidate(paths: List[str], pool_sizes: Dict[str, int], out_path: str) -> 
             os0[key] = merge_tree([b["opt_state"][key] for b in blobs])
         merged["opt_state"] = os0
     merged["shard"] = {"index": 0, "count": 1}
+    merged.pop("fsdp_rows", None)
     torch.save(merged, out_path)
     return out_path

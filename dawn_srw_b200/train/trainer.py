@@ -69,6 +69,11 @@ class Trainer:
         self.model = build_model_from_config(cfg, pool_shard=shard, backend=self.backend).to(self.device)
         self.model.set_parallel(shard_group=self.topo.shard_group, dp_group=self.topo.dp_group,
                                 seq_sharded=self.topo.seq_shard)
+        self.fsdp = bool(t.fsdp) and self.is_baseline and self.topo.world > 1
+        if self.fsdp:
+            # every rank built the same full weights (same seed); keep this rank's rows only
+            from ..parallel.fsdp import shard_dense_weights
+            shard_dense_weights(self.model, self.topo.world_group)
         self.steps_per_epoch = len(self.train_loader) if self.train_loader is not None else 0
         k = max(1, t.gradient_accumulation_steps)
         if total_steps is None:
@@ -81,7 +86,7 @@ class Trainer:
         self.total_steps = total_steps
         warm = int(total_steps * t.warmup_ratio)
         self.schedule = lambda s: warmup_cosine(s, t.lr, warm, total_steps)
-        if t.zero_pool_state and self.topo.world > 1:
+        if t.zero_pool_state and self.topo.world > 1 and not self.fsdp:
             # replicated parameters: reduce-scatter + AdamW on the owned slice + all-gather,
             # moments sharded over the replicas
             from ..parallel.zero import PartitionedAdamW
@@ -215,27 +220,39 @@ class Trainer:
         if hasattr(self.backend, "finish_run"):
             self.backend.finish_run()
         t = self.topo
-        writes = t.is_main or (t.pool_shards > 1 and t.dp_index == 0)
+        writes = t.is_main or (t.pool_shards > 1 and t.dp_index == 0) or self.fsdp
         if hasattr(self.optimizer, "gather_state"):
             self.optimizer.gather_state()       # collective: sharded moments -> per-parameter form
         path = None
         if writes:
+            si, sc = self._ckpt_shard()
+            extra = None
+            if self.fsdp:     # which tensors hold row blocks, and of how many rows (for consolidate)
+                extra = {"fsdp_rows": {n: p._fsdp_rows for n, p in self.model.named_parameters()
+                                       if getattr(p, "_fsdp_rows", None) is not None}}
             path = ckpt.save_checkpoint(
                 os.path.join(self.run_dir, name), self.model, self.optimizer, epoch=self.epoch,
                 step=self.global_step, step_in_epoch=self.step_in_epoch,
                 steps_per_epoch=self.steps_per_epoch, best_val_loss=self.best_val_loss,
                 config=self.cfg.model_dict(), training_config=self.cfg.training_dict(),
-                shard_index=t.shard_index, shard_count=t.pool_shards)
+                shard_index=si, shard_count=sc, extra=extra)
         if t.is_main and name.startswith("checkpoint_step"):
             ckpt.cleanup_old(self.run_dir, self.cfg.training.keep_last_checkpoints)
         return path
 
+    def _ckpt_shard(self):
+        """(index, count) of this rank's checkpoint file: pool shards, or the row
+        blocks of a row-sharded dense model (one file per rank)."""
+        if self.fsdp:
+            return self.topo.rank, self.topo.world
+        return self.topo.shard_index, self.topo.pool_shards
+
     def resume(self, path: str) -> None:
         err = None
         try:
+            si, sc = self._ckpt_shard()
             blob = ckpt.load_checkpoint(path, self.model, self.optimizer,
-                                        shard_index=self.topo.shard_index,
-                                        shard_count=self.topo.pool_shards)
+                                        shard_index=si, shard_count=sc)
         except Exception as e:       # missing / unreadable shard file on this rank
             err, blob = e, None
         if self.topo.world > 1:

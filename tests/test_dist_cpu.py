@@ -254,3 +254,60 @@ def test_diversity_sample_of_a_sharded_pool_matches_the_global_sample():
             assert torch.equal(r["rows"], want_rows.detach())
             assert abs(r["div"] - float(ref)) < 1e-6
             assert torch.allclose(r["grad"], full.grad[r["lo"]:r["hi"]], atol=1e-6)
+
+
+def _dense_trainer_worker(rank, world, fsdp, ckpt_dir=None):
+    import os
+    from dawn_srw_b200.parallel.fsdp import full_state_dict
+    from dawn_srw_b200.parallel.topology import init_topology
+    from dawn_srw_b200.train.trainer import Trainer
+    topo = init_topology(backend="gloo")
+    cfg = tiny_config(version="baseline", max_steps=3, fsdp=fsdp)
+    cfg.model.d_ff = 99                       # 99 rows over 2 ranks: blocks of 50 with one padding row
+    tr = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10, run_dir=ckpt_dir)
+    for i in range(3):
+        ids, mask = tr.train_loader.batch(i)
+        m = tr.train_step(ids, mask)
+    out = {"gn": float(m["grad_norm"]), "loss": float(m["total_loss"]), "fsdp": tr.fsdp,
+           "local": sum(p.numel() for p in tr.model.parameters())}
+    out["sd"] = {n: v.detach().clone() for n, v in full_state_dict(tr.model).items()}
+    if ckpt_dir is not None:
+        os.makedirs(ckpt_dir, exist_ok=True)
+        tr.save("checkpoint_step3.pt")
+        torch.distributed.barrier()
+        tr2 = Trainer(cfg, topo=topo, device=torch.device("cpu"), total_steps=10, run_dir=ckpt_dir)
+        tr2.resume(os.path.join(ckpt_dir, "checkpoint_step3.pt"))
+        for t_ in (tr, tr2):
+            ids, mask = t_.train_loader.batch(7)
+            t_.train_step(ids, mask)
+        out["resume_diff"] = max(float((a.detach() - b.detach()).abs().max()) for (_, a), (_, b) in zip(
+            tr.model.named_parameters(), tr2.model.named_parameters()))
+    return out
+
+
+def test_row_sharded_dense_baseline_matches_replicated_training(tmp_path):
+    """Linear weights of the dense baseline split by rows over the data-parallel ranks
+    (gathered for each GEMM, gradients reduce-scattered): same losses, gradient norm and
+    parameters as replicated data-parallel training; checkpoints are one file per rank
+    and consolidate into the ordinary layout."""
+    import glob
+    from dawn_srw_b200.train import checkpoint as ck
+    a = run_ranks(_dense_trainer_worker, 2, False)
+    b = run_ranks(_dense_trainer_worker, 2, True, str(tmp_path / "run"))
+    assert not a[0]["fsdp"] and b[0]["fsdp"]
+    assert b[0]["local"] < 0.75 * a[0]["local"]              # a rank holds half of the layer weights
+    for r in range(2):
+        assert abs(a[r]["gn"] - b[r]["gn"]) < 1e-5 and abs(a[r]["loss"] - b[r]["loss"]) < 1e-5
+        assert b[r]["resume_diff"] == 0.0
+    for n in a[0]["sd"]:
+        assert a[0]["sd"][n].shape == b[0]["sd"][n].shape, n
+        assert torch.equal(b[0]["sd"][n], b[1]["sd"][n]), n
+        if n.endswith("k_proj.bias"):
+            continue      # softmax ignores a key bias: its gradient is rounding noise, which Adam normalises to +-lr
+        assert torch.allclose(a[0]["sd"][n], b[0]["sd"][n], atol=2e-6), n
+    files = sorted(glob.glob(str(tmp_path / "run" / "checkpoint_step3.shard*of2.pt")))
+    assert len(files) == 2
+    merged = torch.load(ck.consolidate(files, {}, str(tmp_path / "full.pt")), weights_only=False)
+    for n, v in merged["params"].items():
+        assert v.shape == a[0]["sd"][n].shape, n
+    assert merged["opt_state"]["exp_avg"]["layers.0.ffn.w_up.weight"].shape == (99, 64)

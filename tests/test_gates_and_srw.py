@@ -205,3 +205,19 @@ def test_score_statistics_node_matches_autograd_of_the_plain_formula():
             a, b = a.clone(), b.clone()
             a[5, 1], b[5, 1] = 0.0, 0.0
         assert torch.allclose(a, b, rtol=2e-3, atol=2e-4), (name, (a - b).abs().max())
+
+
+def test_forward_only_row_statistics_agree_with_the_autograd_node():
+    """The generation path's route-major statistics (rows ri * T + t) are the node's
+    values in another order."""
+    from dawn_srw_b200.ops.score_stats import score_stats, score_stats_rows
+    torch.manual_seed(4)
+    T, R, r, U = 6, 2, 16, 40
+    emb = torch.nn.functional.normalize(torch.randn(U, r), dim=-1)
+    gram, esum = emb.t() @ emb, emb.sum(0)
+    h, off = torch.randn(T, R, r), torch.randn(T, R) * 0.3
+    tau, isd, _, hb = score_stats(h, off, gram, esum, U)
+    tau2, isd2, hb2 = score_stats_rows(h, off, gram, esum, U)
+    assert torch.allclose(tau2, tau.t().reshape(-1), atol=1e-6)
+    assert torch.allclose(isd2, isd.t().reshape(-1), rtol=1e-6)
+    assert torch.equal(hb2, hb.transpose(0, 1).reshape(R * T, r))
