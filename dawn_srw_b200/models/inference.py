@@ -262,12 +262,18 @@ class DecodeSession:
         x = (m.token_emb.weight.index_select(0, self.tok)
              + m.pos_emb.weight.index_select(0, self.pos)).float().reshape(B, 1, D)
         n_valid = self.pos + 1                                   # cache positions in use
+        fused_attn = (hasattr(be, "decode_attention") and self.cache_k.is_cuda
+                      and self.cache_k.dtype == torch.float32 and self.cache_k[0].is_contiguous()
+                      and dh <= 128)
         for li, blk in enumerate(m.layers):
             n = be.layer_norm(x, blk.norm1.weight, blk.norm1.bias).reshape(B, D)
             q, k, v, _, _ = _layer_qkv(m, be, n, pools)
-            self.cache_k[li].index_copy_(2, self.pos, k.reshape(B, H, 1, dh).to(self.cache_k.dtype))
-            self.cache_v[li].index_copy_(2, self.pos, v.reshape(B, H, 1, dh).to(self.cache_v.dtype))
-            o = R.cached_attention(q.reshape(B, H, 1, dh), self.cache_k[li], self.cache_v[li], n_valid)
+            if fused_attn:
+                o = be.decode_attention(q, k, v, self.cache_k[li], self.cache_v[li], self.pos, H)
+            else:
+                self.cache_k[li].index_copy_(2, self.pos, k.reshape(B, H, 1, dh).to(self.cache_k.dtype))
+                self.cache_v[li].index_copy_(2, self.pos, v.reshape(B, H, 1, dh).to(self.cache_v.dtype))
+                o = R.cached_attention(q.reshape(B, H, 1, dh), self.cache_k[li], self.cache_v[li], n_valid)
             x = x + be.linear(o.reshape(B, D), blk.attn.expand_O.weight, None).reshape(B, 1, D)
             n = be.layer_norm(x, blk.norm2.weight, blk.norm2.bias).reshape(B, D)
             ko, _ = _know(m, be, n, pools)

@@ -650,6 +650,76 @@ std::vector<Tensor> score_stats_fwd(const Tensor& hg, const Tensor& h, const Ten
   return {tau, isd, mu, sd, hsum};
 }
 
+// SRW pool op for up to four token rows in one streaming pass (decoding).
+// -> out fp32 [N, D] (normalised and scaled), den fp32 [N]
+std::vector<Tensor> srw_rows(const Tensor& h, const Tensor& x, const Tensor& tau, const Tensor& isd,
+                             const Tensor& emb, const Tensor& read, const Tensor& write,
+                             c10::optional<Tensor> unit_mask, std::vector<double> gate, double scale,
+                             c10::optional<Tensor> scale_t) {
+  check_bf16_2d(h, "h"); check_bf16_2d(x, "x"); check_bf16_2d(emb, "emb");
+  check_bf16_2d(read, "read"); check_bf16_2d(write, "write");
+  const int N = h.size(0), r = h.size(1), D = x.size(1), U = emb.size(0);
+  TORCH_CHECK(h.is_contiguous() && x.is_contiguous() && x.size(0) == N && emb.size(1) == r &&
+              read.size(0) == U && read.size(1) == D && write.size(0) == U && write.size(1) == D);
+  TORCH_CHECK(N >= 1 && N <= dsb_srw_rows_max(D), "srw_rows: too many rows for this d_model");
+  TORCH_CHECK(tau.scalar_type() == torch::kFloat32 && tau.is_contiguous() && tau.numel() == N &&
+              isd.scalar_type() == torch::kFloat32 && isd.is_contiguous() && isd.numel() == N);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int NR = N <= 1 ? 1 : N <= 2 ? 2 : 4;
+  const int blocks = dsb_srw_rows_blocks(N, D);
+  auto o = tau.options();
+  auto part = torch::empty({static_cast<int64_t>(blocks) * NR * (D + 1)}, o);
+  auto out = torch::empty({N, D}, o), den = torch::empty({N}, o);
+  DsbGate g = to_gate(gate);
+  const float* sp = nullptr;
+  if (scale_t.has_value() && scale_t->defined()) {
+    TORCH_CHECK(scale_t->is_cuda() && scale_t->scalar_type() == torch::kFloat32 && scale_t->numel() == 1);
+    sp = scale_t->data_ptr<float>();
+  }
+  float* part_p = part.data_ptr<float>();
+  int rc = dsb_srw_rows(h.data_ptr(), x.data_ptr(), tau.data_ptr<float>(), isd.data_ptr<float>(),
+                        emb.data_ptr(), emb.stride(0), read.data_ptr(), read.stride(0),
+                        write.data_ptr(), write.stride(0), opt_f32(unit_mask), N, U, r, D, &g,
+                        static_cast<float>(scale), sp, part_p,
+                        part_p + static_cast<size_t>(blocks) * NR * D, out.data_ptr<float>(),
+                        den.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_srw_rows failed with code ", rc);
+  return {out, den};
+}
+
+// y = x . W^T + bias for up to four rows (SIMT, one pass over W).
+void gemv_rows(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& y) {
+  check_bf16_2d(x, "x"); check_bf16_2d(w, "w");
+  TORCH_CHECK(x.is_contiguous() && x.size(1) == w.size(1) && y.is_cuda() && y.dim() == 2 &&
+              y.scalar_type() == torch::kFloat32 && y.stride(1) == 1 && y.size(0) == x.size(0) &&
+              y.size(1) == w.size(0));
+  const c10::cuda::CUDAGuard guard(x.device());
+  int rc = dsb_gemv_rows(x.data_ptr(), w.data_ptr(), w.stride(0), opt_f32(bias), y.data_ptr<float>(),
+                         y.stride(0), x.size(0), w.size(0), x.size(1), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_gemv_rows failed with code ", rc);
+}
+
+// Decode-time attention of one new token per sequence over the KV cache (which it extends).
+Tensor kv_decode_attention(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& cache_k,
+                           Tensor& cache_v, const Tensor& pos, int64_t H) {
+  auto ok = [](const Tensor& t) { return t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(); };
+  TORCH_CHECK(ok(q) && ok(k) && ok(v) && ok(cache_k) && ok(cache_v) && q.dim() == 2);
+  const int B = q.size(0), D = q.size(1);
+  TORCH_CHECK(D % H == 0 && k.sizes() == q.sizes() && v.sizes() == q.sizes());
+  const int dh = D / H;
+  TORCH_CHECK(cache_k.dim() == 4 && cache_k.size(0) == B && cache_k.size(1) == H &&
+              cache_k.size(3) == dh && cache_v.sizes() == cache_k.sizes());
+  TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == torch::kInt64 && pos.numel() == 1);
+  const c10::cuda::CUDAGuard guard(q.device());
+  auto out = torch::empty_like(q);
+  int rc = dsb_kv_decode_attention(q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(),
+                                   cache_k.data_ptr<float>(), cache_v.data_ptr<float>(),
+                                   reinterpret_cast<const long long*>(pos.data_ptr<int64_t>()), B, H, dh,
+                                   cache_k.size(2), out.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_kv_decode_attention failed with code ", rc);
+  return out;
+}
+
 // Route-major tau, isd [R*T] and bf16(h) [R*T, r] for a handful of rows (one launch).
 std::vector<Tensor> score_stats_rows(const Tensor& h, const Tensor& off, const Tensor& gram,
                                      const Tensor& esum, double inv_u) {
@@ -759,6 +829,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("score_stats_fwd", &score_stats_fwd);
   m.def("score_stats_bwd", &score_stats_bwd);
   m.def("score_stats_rows", &score_stats_rows);
+  m.def("srw_rows", &srw_rows);
+  m.def("gemv_rows", &gemv_rows);
+  m.def("kv_decode_attention", &kv_decode_attention);
+  m.def("srw_rows_max", [](int64_t D) { return dsb_srw_rows_max(static_cast<int>(D)); });
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);
   m.def("srw_bwd_gate_gather", &srw_bwd_gate_gather);
   m.def("peer_barrier", &peer_barrier);

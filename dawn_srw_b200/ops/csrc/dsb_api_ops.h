@@ -63,6 +63,33 @@ int dsb_score_stats_bwd(const float* d_tau, const float* d_isd, const float* d_h
                         float inv_u, int N, int r, float* dh, void* w_bf16, long long ldw,
                         float* d_off, float* d_esum, cudaStream_t stream);
 
+// SRW pool op for a handful of token rows (decoding): one streaming pass over the pool.
+// h [N, r], x [N, D] bf16 contiguous (row n of x belongs to row n of h), tau / isd [N];
+// emb / read / write bf16 with row strides in elements (multiples of 8); unit_mask [U] or null.
+// out[n, :] = (sum_u bf16(g * <x_n, r_u>) w_u) * scale / max(sum_u den_term, 1), fp32 [N, D];
+// scale_ptr (device scalar) overrides scale when not null; den_out [N] may be null.
+// part / den_part: scratch of dsb_srw_rows_blocks(N, D) * NR * D and * NR floats, NR = N rounded
+// up to 1, 2 or 4.  N <= dsb_srw_rows_max(D) (4 up to d_model 1280, 2 up to 2048, else 0).
+int dsb_srw_rows_max(int D);
+int dsb_srw_rows_blocks(int N, int D);
+struct DsbGate;
+int dsb_srw_rows(const void* h, const void* x, const float* tau, const float* isd, const void* emb,
+                 long long lde, const void* read, long long ldr, const void* write, long long ldw,
+                 const float* unit_mask, int N, int U, int r, int D, const struct DsbGate* gate,
+                 float scale, const float* scale_ptr, float* part, float* den_part, float* out,
+                 float* den_out, cudaStream_t stream);
+
+// One decoded token: k, v [B, H*dh] are appended to the fp32 caches [B, H, s_max, dh] at
+// position pos[0] (device scalar), out [B, H*dh] = softmax(q K^T / sqrt(dh)) V over 0..pos.
+int dsb_kv_decode_attention(const float* q, const float* k, const float* v, float* cache_k,
+                            float* cache_v, const long long* pos, int B, int H, int dh, int s_max,
+                            float* out, cudaStream_t stream);
+
+// y[t, n] = <x_t, W_n> + bias[n] for N <= 4 rows (decoding): x bf16 [N, K] contiguous, W bf16
+// [n_out, ldw], bias fp32 [n_out] or null, y fp32 [N, ldy]; K % 8 == 0, K <= 8192.
+int dsb_gemv_rows(const void* x, const void* w, long long ldw, const float* bias, float* y,
+                  long long ldy, int N, int n_out, int K, cudaStream_t stream);
+
 // Causal self-attention (tcgen05 kernels).  q, k, v, out, d_out: bf16 [B, S, H*dh]
 // (head h in columns [h*dh, (h+1)*dh)); dh a multiple of 16, at most 128.
 // lse, delta: fp32 [B, H, S] (delta is scratch filled by the backward call).

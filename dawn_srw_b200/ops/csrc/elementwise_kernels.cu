@@ -20,6 +20,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // One warp per row.  x fp32 [T, D]; y bf16 [T, D]; mean/rstd fp32 [T].
+// kRegs > 0: the row (D <= 32 * kRegs) is read once and kept in registers, all
+// loads in flight together; kRegs == 0: three passes over the row for any D.
+template <int kRegs>
 __global__ void ln_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
                               const float* __restrict__ b, __nv_bfloat16* __restrict__ y,
                               float* __restrict__ mean, float* __restrict__ rstd, int T, int D,
@@ -28,15 +31,86 @@ __global__ void ln_fwd_kernel(const float* __restrict__ x, const float* __restri
   const int lane = threadIdx.x & 31;
   if (row >= T) return;
   const float* xr = x + static_cast<size_t>(row) * D;
-  float s = 0.f;
-  for (int i = lane; i < D; i += 32) s += xr[i];
-  const float mu = warp_sum(s) / D;
-  float q = 0.f;
-  for (int i = lane; i < D; i += 32) { const float d = xr[i] - mu; q += d * d; }
-  const float rs = rsqrtf(warp_sum(q) / D + eps);
   __nv_bfloat16* yr = y + static_cast<size_t>(row) * D;
-  for (int i = lane; i < D; i += 32) yr[i] = __float2bfloat16((xr[i] - mu) * rs * w[i] + b[i]);
-  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+  if constexpr (kRegs > 0) {
+    float v[kRegs];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kRegs; ++k) {
+      const int i = lane + 32 * k;
+      v[k] = i < D ? xr[i] : 0.f;
+      s += v[k];
+    }
+    const float mu = warp_sum(s) / D;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < kRegs; ++k) {
+      const float d = lane + 32 * k < D ? v[k] - mu : 0.f;
+      q += d * d;
+    }
+    const float rs = rsqrtf(warp_sum(q) / D + eps);
+#pragma unroll
+    for (int k = 0; k < kRegs; ++k) {
+      const int i = lane + 32 * k;
+      if (i < D) yr[i] = __float2bfloat16((v[k] - mu) * rs * w[i] + b[i]);
+    }
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+  } else {
+    float s = 0.f;
+    for (int i = lane; i < D; i += 32) s += xr[i];
+    const float mu = warp_sum(s) / D;
+    float q = 0.f;
+    for (int i = lane; i < D; i += 32) { const float d = xr[i] - mu; q += d * d; }
+    const float rs = rsqrtf(warp_sum(q) / D + eps);
+    for (int i = lane; i < D; i += 32) yr[i] = __float2bfloat16((xr[i] - mu) * rs * w[i] + b[i]);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+  }
+}
+
+// A few rows only (decoding): one block of 256 threads per row, the row in
+// registers (D <= 256 * 8), two block reductions.
+__global__ void __launch_bounds__(256) ln_fwd_block_kernel(
+    const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+    __nv_bfloat16* __restrict__ y, float* __restrict__ mean, float* __restrict__ rstd, int D,
+    float eps) {
+  __shared__ float s_red[2][8];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* xr = x + static_cast<size_t>(row) * D;
+  float v[8];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = tid + 256 * k;
+    v[k] = i < D ? xr[i] : 0.f;
+    s += v[k];
+  }
+  s = warp_sum(s);
+  if (lane == 0) s_red[0][warp] = s;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += s_red[0][k];
+  const float mu = tot / D;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float d = tid + 256 * k < D ? v[k] - mu : 0.f;
+    q += d * d;
+  }
+  q = warp_sum(q);
+  if (lane == 0) s_red[1][warp] = q;
+  __syncthreads();
+  tot = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) tot += s_red[1][k];
+  const float rs = rsqrtf(tot / D + eps);
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * D;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int i = tid + 256 * k;
+    if (i < D) yr[i] = __float2bfloat16((v[k] - mu) * rs * w[i] + b[i]);
+  }
+  if (tid == 0) { mean[row] = mu; rstd[row] = rs; }
 }
 
 // LayerNorm backward in two kernels.  (1) dx: one warp per row, two passes over
@@ -330,9 +404,17 @@ extern "C" int dsb_layernorm_fwd(const float* x, const float* w, const float* b,
                                  float* mean, float* rstd, int T, int D, float eps,
                                  cudaStream_t stream) {
   if (T <= 0) return 0;
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(y_bf16);
+  if (T <= 296 && D <= 2048) {   // few rows: a block per row instead of a warp per row
+    ln_fwd_block_kernel<<<T, 256, 0, stream>>>(x, w, b, y, mean, rstd, D, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
+  }
   const int warps = 8;
-  ln_fwd_kernel<<<(T + warps - 1) / warps, warps * 32, 0, stream>>>(
-      x, w, b, reinterpret_cast<__nv_bfloat16*>(y_bf16), mean, rstd, T, D, eps);
+  const dim3 grid((T + warps - 1) / warps), block(warps * 32);
+  if (D <= 32 * 16) ln_fwd_kernel<16><<<grid, block, 0, stream>>>(x, w, b, y, mean, rstd, T, D, eps);
+  else if (D <= 32 * 40) ln_fwd_kernel<40><<<grid, block, 0, stream>>>(x, w, b, y, mean, rstd, T, D, eps);
+  else if (D <= 32 * 64) ln_fwd_kernel<64><<<grid, block, 0, stream>>>(x, w, b, y, mean, rstd, T, D, eps);
+  else ln_fwd_kernel<0><<<grid, block, 0, stream>>>(x, w, b, y, mean, rstd, T, D, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 

@@ -190,6 +190,12 @@ def gemm(a, a_mn, b, b_mn, *, out=None, out_dtype=torch.float32, accumulate=Fals
         block_n = 128 if N <= 128 else 256
     global _LAUNCHES
     _LAUNCHES += 1
+    if (M <= 4 and not a_mn and not b_mn and not accumulate and alpha == 1.0 and row_scale is None
+            and out.dtype == torch.float32 and a.is_contiguous() and a.shape[1] % 8 == 0
+            and a.shape[1] <= 8192):
+        # a handful of rows (decoding): one SIMT pass over the weights instead of a 128-row MMA tile
+        ext().gemv_rows(a, b, bias, out)
+        return out
     ext().gemm(a, a_mn, b, b_mn, out, accumulate, float(alpha), row_scale, bias, block_n,
                status_word(a.device))
     return out
@@ -744,6 +750,16 @@ class CudaBackend:
         y = gemm(_bf16_2d(x), False, w, False, out_dtype=torch.float32, bias=b)
         return [y[:, a:e] for a, e in cuts]
 
+    @torch.no_grad()
+    def decode_attention(self, q, k, v, cache_k, cache_v, pos, n_heads: int):
+        """One new token per sequence: q, k, v [B, D] fp32; k and v are written into the
+        fp32 caches [B, H, S_max, dh] at the device-scalar position ``pos`` and the token
+        attends over positions 0..pos.  One launch (the position stays on the device, so
+        the call can be captured in a graph).  Returns [B, D] fp32."""
+        f = lambda t: t.float().contiguous()
+        count_launches(1)
+        return ext().kv_decode_attention(f(q), f(k), f(v), cache_k, cache_v, pos, int(n_heads))
+
     def embed(self, ids, tok, pos):
         if tok.shape[1] % 4 != 0 or tok.dtype != torch.float32:
             return R.embed(ids, tok, pos)
@@ -841,6 +857,15 @@ class CudaBackend:
         # Routes of one pool are independent token rows as far as the kernels care: with few
         # tokens (decoding) they are stacked into one call, so the pool is streamed once.
         stack = Rr * T <= 128
+        if Rr * T <= e.srw_rows_max(D):
+            # one to four rows: a single streaming pass over the pool (SIMT, bound by HBM)
+            tau, inv_sd, h_rm = score_stats_rows(h, tau_off, ex["gram"], ex["esum"], U_tot)
+            x_rm = (x_bf.repeat(Rr, 1) if Rr > 1 else x_bf).contiguous()
+            sc_t = scale.reshape(1) if isinstance(scale, torch.Tensor) else None
+            out, _ = e.srw_rows(h_rm, x_rm, tau, inv_sd, pool.emb[:U], pool.read[:U], pool.write[:U],
+                                None, _gate_list(spec), 1.0 if sc_t is not None else float(scale), sc_t)
+            count_launches(2)
+            return list(out.reshape(Rr, T, D).unbind(0))
         if stack:
             tau, inv_sd, h_rm = score_stats_rows(h, tau_off, ex["gram"], ex["esum"], U_tot)
             calls = [(h_rm, x_bf.repeat(Rr, 1) if Rr > 1 else x_bf, tau, inv_sd)]

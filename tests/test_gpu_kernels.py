@@ -104,6 +104,74 @@ def test_forward_gate_kernel_with_few_rows(cb, kind, T):
     cb.check_status()
 
 
+@pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("N,D,r", [(1, 1280, 256), (2, 1280, 256), (3, 384, 128), (4, 1024, 256),
+                                   (2, 2048, 384)])
+def test_streaming_pool_op_for_a_few_rows(cb, kind, N, D, r):
+    """The SIMT decode kernel (one pass over the pool, normalisation and scale applied by its
+    second kernel) against the fp32 formula with p rounded to bf16."""
+    from dawn_srw_b200.ops.gates import GateSpec, gate_forward
+    dev = torch.device("cuda")
+    torch.manual_seed(100 * N + kind)
+    U = 5003
+    spec = GateSpec(kind=kind)
+    nz = torch.nn.functional.normalize
+    h, x = torch.randn(N, r, device=dev).bfloat16(), torch.randn(N, D, device=dev).bfloat16()
+    Up = (U + 7) // 8 * 8
+    emb, read, write = (torch.zeros(Up, d, device=dev, dtype=torch.bfloat16) for d in (r, D, D))
+    for t, d in ((emb, r), (read, D), (write, D)):
+        t[:U] = nz(torch.randn(U, d, device=dev), dim=-1).bfloat16()
+    s = h.float() @ emb[:U].float().t()
+    mu, sd = s.mean(-1, keepdim=True), s.std(-1, unbiased=False, keepdim=True) + 1e-8
+    tau = mu + 0.8 * sd                                   # most units of the relu-type gates are off
+    g, dt, _ = gate_forward(spec, s, tau, sd)
+    p = (g * (x.float() @ read[:U].float().t())).bfloat16().float()
+    scale = torch.tensor(1.7, device=dev)
+    ref = (p @ write[:U].float()) * (scale / dt.sum(-1).clamp(min=1.0))[:, None]
+    e = cb.ext()
+    out, den = e.srw_rows(h, x, tau.squeeze(-1).contiguous(), (1 / sd).squeeze(-1).contiguous(),
+                          emb[:U], read[:U], write[:U], None, cb._gate_list(spec), 1.0, scale.reshape(1))
+    assert _rel(den, dt.sum(-1)) < 1e-4
+    assert _rel(out, ref) < 3e-3
+    out2, _ = e.srw_rows(h, x, tau.squeeze(-1).contiguous(), (1 / sd).squeeze(-1).contiguous(),
+                         emb[:U], read[:U], write[:U], None, cb._gate_list(spec), 1.7, None)
+    assert _rel(out, out2) < 1e-5       # the blocks' partial sums meet in a different order
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+def test_few_row_gemv_path_of_the_gemm_wrapper(cb, M):
+    dev = torch.device("cuda")
+    torch.manual_seed(M)
+    for K, N in ((1280, 776), (384, 30522), (2048, 1283)):
+        x = torch.randn(M, K, device=dev).bfloat16()
+        Np = (N + 7) // 8 * 8
+        w = torch.randn(Np, K, device=dev).bfloat16()[:N]
+        bias = torch.randn(N, device=dev)
+        ref = x.float() @ w.float().t() + bias
+        out = cb.gemm(x, False, w, False, out_dtype=torch.float32, bias=bias)
+        assert out.shape == (M, N) and _rel(out, ref) < 1e-5
+    cb.check_status()
+
+
+def test_decode_attention_kernel_extends_the_cache_and_matches_torch(cb):
+    from dawn_srw_b200.ops import reference as R
+    dev = torch.device("cuda")
+    torch.manual_seed(11)
+    B, H, dh, S = 3, 4, 80, 96
+    ck, cv = torch.randn(B, H, S, dh, device=dev), torch.randn(B, H, S, dh, device=dev)
+    be = cb.CudaBackend()
+    for pos in (0, 5, S - 1):
+        q, k, v = (torch.randn(B, H * dh, device=dev) for _ in range(3))
+        ck2, cv2 = ck.clone(), cv.clone()
+        ck2[:, :, pos] = k.view(B, H, dh)
+        cv2[:, :, pos] = v.view(B, H, dh)
+        ref = R.cached_attention(q.view(B, H, 1, dh), ck2, cv2, pos + 1).reshape(B, H * dh)
+        c1, c2 = ck.clone(), cv.clone()
+        out = be.decode_attention(q, k, v, c1, c2, torch.tensor([pos], device=dev), H)
+        assert torch.equal(c1, ck2) and torch.equal(c2, cv2)
+        assert _rel(out, ref) < 1e-5
+
+
 def test_score_statistics_of_a_few_rows(cb):
     """The one-launch statistics kernel of the generation path against fp32 torch."""
     from dawn_srw_b200.ops.score_stats import score_stats_rows
@@ -325,7 +393,7 @@ def test_routing_diagnostics_from_the_gate_epilogue(cb, version):
 def test_layernorm_kernel(cb):
     from dawn_srw_b200.ops import reference as R
     dev = torch.device("cuda")
-    for T, D in ((300, 384), (129, 1280)):
+    for T, D in ((300, 384), (129, 1280), (1, 1280), (5, 2048), (1500, 2048), (40, 4096)):
         x = (torch.randn(T, D, device=dev) * 3 + 1).requires_grad_(True)
         w = torch.randn(D, device=dev).requires_grad_(True)
         b = torch.randn(D, device=dev).requires_grad_(True)
