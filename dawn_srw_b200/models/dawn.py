@@ -217,7 +217,7 @@ class DAWN(nn.Module):
             o = o.transpose(1, 2).reshape(T, D)
         with trace("attn/expand_O"):
             out = be.linear(o, blk.attn.expand_O.weight, None)
-        out_d = be.dropout(out, self.dropout_rate, training).reshape(B, S, D)
+        out_d = out.reshape(B, S, D)       # dropout is applied with the residual add (_layer)
         tau_relu = torch.relu(tau_all).mean()
         lb = (res_qk.lb + res_v.lb) / 3.0
         if self.gate.tau_reg_in_aux:
@@ -247,7 +247,7 @@ class DAWN(nn.Module):
                                             out_scale=k_scale)], self.gate, want_diag=want_diag)
         out = res.route(0)
         raw = (out.detach() / k_scale) if want_diag else None     # pre-scale output, diagnostics only
-        out_d = be.dropout(out, self.dropout_rate, training).reshape(B, S, D)
+        out_d = out.reshape(B, S, D)       # dropout is applied with the residual add (_layer)
         tau_relu = torch.relu(tau).mean()
         if self.gate.tau_reg_in_aux:
             aux, tau_reg = res.lb + 0.01 * tau_relu, None
@@ -344,10 +344,10 @@ class DAWN(nn.Module):
         side outputs (aux, dead penalty, tau offsets, tau_reg) of both halves."""
         normed = be.layer_norm(x, blk.norm1.weight, blk.norm1.bias)
         a_out, a_ex = self._attn(be, normed, pools, blk, training, want_diag, m)
-        x = x + a_out
+        x = be.dropout_add(x, a_out, self.dropout_rate, training)
         normed = be.layer_norm(x, blk.norm2.weight, blk.norm2.bias)
         k_out, k_ex = self._know(be, normed, pools, training, want_diag, m)
-        x = x + k_out
+        x = be.dropout_add(x, k_out, self.dropout_rate, training)
         return (x,) + tuple(a_ex) + tuple(k_ex)
 
     def forward(self, input_ids, labels=None, attention_mask=None, *, want_diag: bool = True,

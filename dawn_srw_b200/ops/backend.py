@@ -61,6 +61,9 @@ class ReferenceBackend:
     def dropout(self, x, p, training):
         return R.dropout(x, p, training)
 
+    def dropout_add(self, res, x, p, training):
+        return res + R.dropout(x, p, training)
+
     def attention(self, q, k, v, dropout_p, training):
         if self.compute_dtype == torch.float32 or not q.is_cuda:
             return R.causal_attention(q, k, v, dropout_p, training)

@@ -687,6 +687,24 @@ std::vector<Tensor> srw_rows(const Tensor& h, const Tensor& x, const Tensor& tau
   return {out, den};
 }
 
+// res + dropout(x) (res optional) with a counter-based mask; see dsb_dropout.
+Tensor dropout(c10::optional<Tensor> res, const Tensor& x, int64_t seed, double p) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.is_contiguous() &&
+              x.numel() % 4 == 0, "dropout: fp32 contiguous tensor with a multiple of 4 elements");
+  const float* rp = nullptr;
+  if (res.has_value() && res->defined()) {
+    TORCH_CHECK(res->is_cuda() && res->scalar_type() == torch::kFloat32 && res->is_contiguous() &&
+                res->numel() == x.numel());
+    rp = res->data_ptr<float>();
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty_like(x);
+  int rc = dsb_dropout(rp, x.data_ptr<float>(), y.data_ptr<float>(), x.numel(),
+                       static_cast<unsigned long long>(seed), static_cast<float>(p), cur_stream());
+  TORCH_CHECK(rc == 0, "dsb_dropout failed with code ", rc);
+  return y;
+}
+
 // y = x . W^T + bias for up to four rows (SIMT, one pass over W).
 void gemv_rows(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, Tensor& y) {
   check_bf16_2d(x, "x"); check_bf16_2d(w, "w");
@@ -831,6 +849,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("score_stats_rows", &score_stats_rows);
   m.def("srw_rows", &srw_rows);
   m.def("gemv_rows", &gemv_rows);
+  m.def("dropout", &dropout);
   m.def("kv_decode_attention", &kv_decode_attention);
   m.def("srw_rows_max", [](int64_t D) { return dsb_srw_rows_max(static_cast<int>(D)); });
   m.def("srw_fwd_gate_gather", &srw_fwd_gate_gather);

@@ -73,7 +73,21 @@ struct alignas(64) GatherParams {
   int n_stats;
   const float4* stat_src[kMaxGatherTensors][kMaxRanks];
   float4* stat_dst[kMaxGatherTensors];
+  // Raw views of the same buffers for the register-copy gather (kGather == 2): base
+  // pointers and the row stride in 16-byte units.
+  const uint4* src_ptr[kMaxGatherTensors][kMaxRanks];
+  uint4* dst_ptr[kMaxGatherTensors];
+  long long ld16[kMaxGatherTensors];
 };
+// Gather modes of the engine kernel (template parameter kGather):
+//   0  none
+//   1  TMA load from the peer -> two 16 KB bounce buffers in shared memory -> TMA store.
+//      Highest copy rate per CTA, but the 32 KB cost the operand ring one stage.
+//   2  two warps copy through registers (16-byte loads from the peer, 16-byte stores into
+//      the local buffer, eight in flight per lane): no shared memory, so the ring keeps
+//      all its stages; the copy rate is lower and suits kernels that run long enough to
+//      hide it (large unit shards).
+constexpr int kGatherNone = 0, kGatherBounce = 1, kGatherRegs = 2;
 
 template <class EpiParams>
 struct alignas(64) GemmParams {
@@ -86,6 +100,9 @@ struct alignas(64) GemmParams {
   int m_tiles, n_tiles;
   int n_fastest;  // tile raster: 1 = consecutive tiles walk N first
   int m_rot;      // tile rows are visited starting from this m-tile (own rows first)
+  int m_first;    // > 0 with an M-fastest raster: the first m_first (rotated) tile rows - this
+                  // rank's own rows - are swept completely before the others, so a fused
+                  // gather has that long to land the peers' rows
   int k_splits;   // > 1: the K range of segment 0 is cut into this many tiles that all
                   // reduce-add into the same output (accumulating fp32 epilogues only)
   GatherParams gather;
@@ -96,12 +113,12 @@ struct alignas(64) GemmParams {
 constexpr int kOutBufBytes = 4096;  // one staged slab: 32 rows x 128 bytes
 
 constexpr int kGatherPieceBytes = 128 * 64 * 2;   // 128 rows x 64 bf16
-template <int BN, int kOutBufsPerWarp, int kEpiWarps = 4, bool kGather = false>
+template <int BN, int kOutBufsPerWarp, int kEpiWarps = 4, int kGather = 0>
 struct EngineSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KB
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kGatherBytes = kGather ? 2 * kGatherPieceBytes : 0;
+  static constexpr int kGatherBytes = kGather == kGatherBounce ? 2 * kGatherPieceBytes : 0;
   static constexpr int kOutBytes = kEpiWarps * kOutBufsPerWarp * kOutBufBytes + kGatherBytes;
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 512 /*barriers*/;
@@ -216,7 +233,7 @@ struct AccCtl {
 // launched with 168 registers per thread.  The helper warpgroup gives most of its share
 // back (setmaxnreg.dec) and the two epilogue warpgroups, which keep 128 packed accumulator
 // values per thread, take it (setmaxnreg.inc).
-template <class Epi, bool kGather>
+template <class Epi, int kGather>
 constexpr int engine_threads() {
   return Epi::kEpiWarps == 8 ? 384 : (Epi::kEpiWarps + 2 + (kGather ? 1 : 0)) * 32;
 }
@@ -228,7 +245,31 @@ constexpr int kEpilogueRegs = 208;  // epilogue warps after setmaxnreg.inc
 static_assert(2 * kEpilogueRegs + kHelperRegs <= 3 * 168, "register split exceeds the launch allocation");
 static_assert(kEpilogueRegs % 8 == 0 && kHelperRegs % 8 == 0, "setmaxnreg takes multiples of 8");
 
-template <int BN, class Epi, int kCtas, bool kGather = false>
+// (m-tile, n-tile) of the t2-th output tile of the raster described by the launch parameters.
+template <class P>
+__device__ __forceinline__ void tile_coords(const P& p, int t2, int& mt, int& nt) {
+  if (p.n_fastest) {
+    mt = t2 / p.n_tiles;
+    nt = t2 - mt * p.n_tiles;
+  } else if (p.m_first > 0 && p.m_first < p.m_tiles) {
+    const int first = p.m_first * p.n_tiles;
+    if (t2 < first) {
+      nt = t2 / p.m_first;
+      mt = t2 - nt * p.m_first;
+    } else {
+      const int rest = p.m_tiles - p.m_first, t3 = t2 - first;
+      nt = t3 / rest;
+      mt = p.m_first + (t3 - nt * rest);
+    }
+  } else {
+    nt = t2 / p.m_tiles;
+    mt = t2 - nt * p.m_tiles;
+  }
+  mt += p.m_rot;
+  if (mt >= p.m_tiles) mt -= p.m_tiles;
+}
+
+template <int BN, class Epi, int kCtas, int kGather = 0>
 __global__ void __launch_bounds__(engine_threads<Epi, kGather>(), 1)
 gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   // kCtas == 2: the CTA pair of a 2-CTA cluster shares a 256-row tile.  Each CTA
@@ -279,7 +320,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], kCtas * kEpiWarps);   // one elected arrive per epilogue warp
     }
-    if (kGather) { mbar_init(&gather_bar[0], 1); mbar_init(&gather_bar[1], 1); }
+    if (kGather == kGatherBounce) { mbar_init(&gather_bar[0], 1); mbar_init(&gather_bar[1], 1); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -318,19 +359,29 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      constexpr int kSeenWords = 32;      // 1024 row blocks of 128 rows
+      uint32_t seen[kSeenWords];          // gathered row blocks whose flag this CTA has seen
+      if (kGather) {
+#pragma unroll
+        for (int i = 0; i < kSeenWords; ++i) seen[i] = 0u;
+      }
       for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride) {
         const int ks = tile / mn_tiles, t2 = tile - ks * mn_tiles;
-        int mt = p.n_fastest ? t2 / p.n_tiles : t2 % p.m_tiles;
-        const int nt = p.n_fastest ? t2 % p.n_tiles : t2 / p.m_tiles;
-        mt += p.m_rot;
-        if (mt >= p.m_tiles) mt -= p.m_tiles;
+        int mt, nt;
+        tile_coords(p, t2, mt, nt);
         const int m0 = mt * kTileM + static_cast<int>(rank) * kBlockM;
         const int n0 = nt * BN + static_cast<int>(rank) * kBRows;
         if (kGather && p.gather.n_ranks > 1 && m0 < p.M &&
             m0 / p.gather.rows_per_rank != p.gather.my_rank) {
-          // rows of another rank: wait until the gather warps have landed them here
-          if (!flag_wait_ge(p.gather.ready + m0 / 128, p.gather.epoch, abort_flag)) { ok = false; break; }
-          fence_proxy_async_global();
+          // rows of another rank: wait until the gather warps have landed them here; a block
+          // seen once needs no second system-scope acquire
+          const int blk = m0 / 128;
+          const bool known = blk < 32 * kSeenWords && ((seen[blk >> 5] >> (blk & 31)) & 1u);
+          if (!known) {
+            if (!flag_wait_ge(p.gather.ready + blk, p.gather.epoch, abort_flag)) { ok = false; break; }
+            fence_proxy_async_global();
+            if (blk < 32 * kSeenWords) seen[blk >> 5] |= 1u << (blk & 31);
+          }
         }
         for (int s = 0; s < p.n_seg && ok; ++s) {
           const GemmSeg sg = p.seg[s];
@@ -448,8 +499,58 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
         }
       }
     }
-  } else if (kGather && warp == kGatherWarp) {
-    // -------------------------------------------------------------- gather
+  } else if (kGather == kGatherRegs &&
+             (warp == kGatherWarp || (kEpiWarps == 8 && warp == kGatherWarp + 1))) {
+    // ------------------------------------------- gather through registers
+    const GatherParams& g = p.gather;
+    if (g.n_ranks > 1) {
+      constexpr int kGW = kEpiWarps == 8 ? 2 : 1;          // gather warps per CTA
+      const int cpr = g.rows_per_rank / 128;               // 128-row chunks per rank
+      const int remote = (g.n_ranks - 1) * cpr;
+      for (int rc = blockIdx.x * kGW + (warp - kGatherWarp); rc < remote; rc += gridDim.x * kGW) {
+        const int owner = (g.my_rank + 1 + rc / cpr) % g.n_ranks;
+        const int grow = owner * g.rows_per_rank + (rc % cpr) * 128;
+        for (int sidx = 0; sidx < g.n_stats; ++sidx) {
+          const float4* src = g.stat_src[sidx][owner] + grow;
+          float4* dst = g.stat_dst[sidx] + grow;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float4 v;
+            asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];"
+                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                         : "l"(src + lane + 32 * k)
+                         : "memory");
+            dst[lane + 32 * k] = v;
+          }
+        }
+        for (int t = 0; t < g.n_tensors; ++t) {
+          const int vpr = g.cols[t] >> 3;                  // 16-byte vectors per row
+          const int total = 128 * vpr;                     // a multiple of 256 (cols % 64 == 0)
+          const uint4* src = g.src_ptr[t][owner] + static_cast<size_t>(grow) * g.ld16[t];
+          uint4* dst = g.dst_ptr[t] + static_cast<size_t>(grow) * g.ld16[t];
+          for (int v0 = 0; v0 < total; v0 += 256) {
+            uint4 q[8];
+            size_t off[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int v = v0 + lane + 32 * k;
+              off[k] = static_cast<size_t>(v / vpr) * g.ld16[t] + (v % vpr);
+              asm volatile("ld.global.cv.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(q[k].x), "=r"(q[k].y), "=r"(q[k].z), "=r"(q[k].w)
+                           : "l"(src + off[k])
+                           : "memory");
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) dst[off[k]] = q[k];
+          }
+        }
+        __threadfence();             // every lane's stores are visible before the flag
+        __syncwarp();
+        if (lane == 0) flag_store_release(g.ready + grow / 128, g.epoch);
+      }
+    }
+  } else if (kGather == kGatherBounce && warp == kGatherWarp) {
+    // ------------------------------- gather through shared-memory bounce buffers
     const GatherParams& g = p.gather;
     if (g.n_ranks > 1) {
       const int cpr = g.rows_per_rank / 128;               // 128-row chunks per rank
@@ -509,10 +610,8 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     WarpStager stager{smem_u32(out_stage + warp * Epi::kOutBufs * kOutBufBytes), lane};
     for (int tile = first_tile; tile < total_tiles && ok; tile += tile_stride, ++it) {
       const int t2 = tile % mn_tiles;
-      int mt = p.n_fastest ? t2 / p.n_tiles : t2 % p.m_tiles;
-      const int nt = p.n_fastest ? t2 % p.n_tiles : t2 / p.m_tiles;
-      mt += p.m_rot;
-      if (mt >= p.m_tiles) mt -= p.m_tiles;
+      int mt, nt;
+      tile_coords(p, t2, mt, nt);
       Ctl ctl{acc_full, acc_empty, tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16), it,
               lane, abort_flag, true};
       Epi::template run<BN>(p.epi, p.tma_out, stager, ctl,

@@ -41,6 +41,12 @@ int dsb_offdiag_abs(const float* sim, long long ld, int m, void* sgn_bf16, long 
 int dsb_route_bwd_prologue(const float* dy, const float* y, const float* row_scale,
                            void* dy_bf16, float* rowdot, int T, int D, cudaStream_t stream);
 
+// y = res + dropout(x) (res may be null: y = dropout(x)); fp32, n % 4 == 0.  An element is kept
+// (and scaled by 1 / (1 - p)) iff a hash of (seed, its index) is >= p * 2^32, so the gradient
+// of x is the same call with res = null on the incoming gradient.
+int dsb_dropout(const float* res, const float* x, float* y, long long n, unsigned long long seed,
+                float p, cudaStream_t stream);
+
 // Per-token score statistics from hg = h . (E^T E) (fp32 [N, r]) and bf16 h [N, ldh]:
 //   mu = <h, esum> * inv_u,  var = <hg, h> * inv_u - mu^2,  sd = sqrt(max(var, 1e-12)) + 1e-8,
 //   tau = mu + off * sd,  isd = 1 / sd;  hsum[r] += column sums of h (hsum may be null).

@@ -497,3 +497,61 @@ extern "C" int dsb_route_bwd_prologue(const float* dy, const float* y, const flo
       dy, y, row_scale, reinterpret_cast<__nv_bfloat16*>(dy_bf16), rowdot, T, D);
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
+
+// ------------------------------------------------------------------ dropout
+// Keep-mask dropout scaled by 1 / keep, optionally fused with the residual add
+// that follows it (y = res + dropout(x)).  The mask is a counter-based hash of
+// (seed, element index): nothing is stored, the backward kernel regenerates it.
+// (The reference draws from the JAX key stream, models/dawn_spatial_v41_exp.py:
+// 308-318; same distribution, different bits.)
+namespace {
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+// element 4*i4 + k of the tensor is kept iff its 32 hash bits are >= thresh
+__device__ __forceinline__ void keep4(uint64_t seed, long long i4, uint32_t thresh, float scale,
+                                      float (&m)[4]) {
+  const uint64_t a = mix64(seed + static_cast<uint64_t>(2 * i4) * 0x9E3779B97F4A7C15ull);
+  const uint64_t b = mix64(seed + static_cast<uint64_t>(2 * i4 + 1) * 0x9E3779B97F4A7C15ull);
+  m[0] = static_cast<uint32_t>(a) >= thresh ? scale : 0.f;
+  m[1] = static_cast<uint32_t>(a >> 32) >= thresh ? scale : 0.f;
+  m[2] = static_cast<uint32_t>(b) >= thresh ? scale : 0.f;
+  m[3] = static_cast<uint32_t>(b >> 32) >= thresh ? scale : 0.f;
+}
+
+__global__ void dropout_kernel(const float4* __restrict__ res, const float4* __restrict__ x,
+                               float4* __restrict__ y, long long n4, uint64_t seed, uint32_t thresh,
+                               float scale) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float m[4];
+    keep4(seed, i, thresh, scale, m);
+    const float4 v = x[i];
+    float4 o = make_float4(v.x * m[0], v.y * m[1], v.z * m[2], v.w * m[3]);
+    if (res != nullptr) {
+      const float4 r = res[i];
+      o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+    }
+    y[i] = o;
+  }
+}
+
+}  // namespace
+
+extern "C" int dsb_dropout(const float* res, const float* x, float* y, long long n,
+                           unsigned long long seed, float p, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((n & 3) || !(p >= 0.f && p < 1.f)) return 2;
+  const long long n4 = n >> 2;
+  const uint32_t thresh = static_cast<uint32_t>(static_cast<double>(p) * 4294967296.0);
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dropout_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const float4*>(res), reinterpret_cast<const float4*>(x),
+      reinterpret_cast<float4*>(y), n4, seed, thresh, 1.f / (1.f - p));
+  return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}

@@ -1208,7 +1208,7 @@ static int fill_operand(CUtensorMap* map, const OperandDesc& o, long long rows, 
 }
 
 // kCtas == 2 launches 2-CTA clusters (one SM pair per 256-row tile).
-template <int BN, class Epi, int kCtas, bool kGather = false>
+template <int BN, class Epi, int kCtas, int kGather = 0>
 static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
   using Smem = EngineSmem<BN / kCtas, Epi::kOutBufs, Epi::kEpiWarps, kGather>;
   auto kern = gemm_engine_kernel<BN, Epi, kCtas, kGather>;
@@ -1222,6 +1222,9 @@ static int launch_engine_impl(GemmParams<typename Epi::Params>& gp, cudaStream_t
   gp.m_tiles = (gp.M + kBlockM * kCtas - 1) / (kBlockM * kCtas);
   gp.n_tiles = (gp.N + BN - 1) / BN;
   gp.n_fastest = gp.n_tiles <= gp.m_tiles ? 1 : 0;
+  gp.m_first = 0;
+  if (kGather != 0 && gp.gather.n_ranks > 1 && !gp.n_fastest)
+    gp.m_first = gp.gather.rows_per_rank / (kBlockM * kCtas);   // own rows first, then the peers'
   // work items of the persistent loop: output tiles times the K splits of each
   const long long total =
       static_cast<long long>(gp.m_tiles) * gp.n_tiles * (gp.k_splits > 1 ? gp.k_splits : 1);
@@ -1270,9 +1273,23 @@ static int launch_engine(GemmParams<typename Epi::Params>& gp, cudaStream_t stre
 }
 
 // Gate kernels with the all-gather of their token operands fused in (CTA pairs only).
+// `regs`: copy through registers (no shared-memory bounce buffers, the operand ring keeps all
+// its stages) - for launches that run long enough to hide the lower copy rate.
 template <int BN, class Epi>
-static int launch_engine_gather(GemmParams<typename Epi::Params>& gp, cudaStream_t stream) {
-  return launch_engine_impl<BN, Epi, 2, true>(gp, stream);
+static int launch_engine_gather(GemmParams<typename Epi::Params>& gp, cudaStream_t stream,
+                                bool regs = false) {
+  if (regs) return launch_engine_impl<BN, Epi, 2, kGatherRegs>(gp, stream);
+  return launch_engine_impl<BN, Epi, 2, kGatherBounce>(gp, stream);
+}
+
+// Local units from which a gate kernel's own run time hides a register-copy gather.
+static bool gather_through_registers(int units) {
+  static int thr = -1;
+  if (thr < 0) {
+    const char* e = getenv("DSB_GATHER_REGS_MIN_UNITS");
+    thr = e ? atoi(e) : 4096;
+  }
+  return units >= thr;
 }
 
 static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int* m_rot) {
@@ -1297,6 +1314,13 @@ static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int*
       if (rc) return 710 + rc;
     }
     g->dst[t] = g->src[t][d->my_rank];
+    if (d->ld[t] % 8 != 0) return 702;
+    g->ld16[t] = d->ld[t] / 8;
+    for (int j = 0; j < d->n_ranks; ++j) {
+      if (reinterpret_cast<uintptr_t>(d->bufs[t][j]) & 15) return 703;
+      g->src_ptr[t][j] = static_cast<const uint4*>(d->bufs[t][j]);
+    }
+    g->dst_ptr[t] = const_cast<uint4*>(g->src_ptr[t][d->my_rank]);
   }
   if (d->n_stats < 0 || d->n_stats > kMaxGatherTensors) return 704;
   g->n_stats = d->n_stats;
@@ -1492,9 +1516,10 @@ namespace dsb {
 template <bool kSaveXr>
 static int launch_fwd_wide(GemmParams<FwdGateParams>& gp, int kind, bool fused, cudaStream_t stream) {
   if (fused) {
-    if (kind == 0) return launch_engine_gather<256, FwdGateEpiWide<0, kSaveXr>>(gp, stream);
-    if (kind == 1) return launch_engine_gather<256, FwdGateEpiWide<1, kSaveXr>>(gp, stream);
-    return launch_engine_gather<256, FwdGateEpiWide<2, kSaveXr>>(gp, stream);
+    const bool regs = gather_through_registers(gp.N);
+    if (kind == 0) return launch_engine_gather<256, FwdGateEpiWide<0, kSaveXr>>(gp, stream, regs);
+    if (kind == 1) return launch_engine_gather<256, FwdGateEpiWide<1, kSaveXr>>(gp, stream, regs);
+    return launch_engine_gather<256, FwdGateEpiWide<2, kSaveXr>>(gp, stream, regs);
   }
   if (kind == 0) return launch_engine_impl<256, FwdGateEpiWide<0, kSaveXr>, 2>(gp, stream);
   if (kind == 1) return launch_engine_impl<256, FwdGateEpiWide<1, kSaveXr>, 2>(gp, stream);
@@ -1608,9 +1633,10 @@ extern "C" int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb
   if (fused) {
     rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
     if (rc) return rc;
-    if (gate->kind == 0) return launch_engine_gather<256, BwdGateEpiXr<0>>(gp, stream);
-    if (gate->kind == 1) return launch_engine_gather<256, BwdGateEpiXr<1>>(gp, stream);
-    return launch_engine_gather<256, BwdGateEpiXr<2>>(gp, stream);
+    const bool regs = gather_through_registers(U);
+    if (gate->kind == 0) return launch_engine_gather<256, BwdGateEpiXr<0>>(gp, stream, regs);
+    if (gate->kind == 1) return launch_engine_gather<256, BwdGateEpiXr<1>>(gp, stream, regs);
+    return launch_engine_gather<256, BwdGateEpiXr<2>>(gp, stream, regs);
   }
   if (gate->kind == 0) return launch_engine_impl<256, BwdGateEpiXr<0>, 2>(gp, stream);
   if (gate->kind == 1) return launch_engine_impl<256, BwdGateEpiXr<1>, 2>(gp, stream);

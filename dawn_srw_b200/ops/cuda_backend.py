@@ -237,6 +237,23 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db, None, None
 
 
+class _DropoutFn(torch.autograd.Function):
+    """y = res + dropout(x) (``res`` may be None).  The keep mask is a hash of
+    (seed, element index): nothing is saved but the seed, backward regenerates it."""
+    @staticmethod
+    def forward(ctx, res, x, p):
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item())        # CPU generator: no device sync
+        ctx.seed, ctx.p, ctx.has_res = seed, p, res is not None
+        count_launches(1)
+        return ext().dropout(None if res is None else res.contiguous(), x.contiguous(), seed, p)
+
+    @staticmethod
+    def backward(ctx, dy):
+        count_launches(1)
+        dx = ext().dropout(None, dy.contiguous(), ctx.seed, ctx.p) if ctx.needs_input_grad[1] else None
+        return (dy if ctx.has_res else None), dx, None
+
+
 class _LayerNormFn(torch.autograd.Function):
     """LayerNorm (eps 1e-6, population variance) with bf16 output: the only
     consumers of a normed activation are bf16 GEMM operands."""
@@ -258,8 +275,32 @@ class _LayerNormFn(torch.autograd.Function):
 
 
 # ---------------------------------------------------------------------------
+class _PoolTensors:
+    """bf16 compute copies of a pool and the fp32 gradient accumulators of the current step."""
+    __slots__ = ("emb", "read", "write", "g_emb", "g_read", "g_write", "__weakref__")
+
+    def __init__(self):
+        self.emb = self.read = self.write = None
+        self.g_emb = self.g_read = self.g_write = None
+
+
+def _on_tensors(name):
+    return property(lambda self: getattr(self.tensors, name),
+                    lambda self, v: setattr(self.tensors, name, v))
+
+
 class CudaPool(PreparedPool):
-    pass
+    """A prepared pool.  Its tensors live on a separate ``tensors`` object: the preparation
+    node of the autograd graph (which the pool reaches through ``extra['anchor']``) keeps
+    only that object, not the pool, so pool -> anchor -> graph node -> pool is not a cycle.
+    Such a cycle runs through the C++ graph, where Python's collector cannot see it, and
+    every forward pass that is not followed by a backward pass would leak its pools."""
+    emb, read, write = _on_tensors("emb"), _on_tensors("read"), _on_tensors("write")
+    g_emb, g_read, g_write = _on_tensors("g_emb"), _on_tensors("g_read"), _on_tensors("g_write")
+
+    def __init__(self):
+        self.tensors = _PoolTensors()
+        self.extra = None
 
 
 class _PoolPrepFn(torch.autograd.Function):
@@ -766,7 +807,20 @@ class CudaBackend:
         return _EmbedFn.apply(ids, tok, pos)
 
     def dropout(self, x, p, training):
-        return R.dropout(x, p, training)
+        if not training or p == 0.0:
+            return x
+        if not x.is_cuda or x.dtype != torch.float32 or x.numel() % 4 != 0:
+            return R.dropout(x, p, training)
+        return _DropoutFn.apply(None, x, float(p))
+
+    def dropout_add(self, res, x, p, training):
+        """res + dropout(x): one kernel forward (and one for the gradient of x)."""
+        if not training or p == 0.0:
+            return res + x
+        if (not x.is_cuda or x.dtype != torch.float32 or res.dtype != torch.float32
+                or x.numel() % 4 != 0 or res.shape != x.shape):
+            return res + R.dropout(x, p, training)
+        return _DropoutFn.apply(res, x, float(p))
 
     def attention(self, q, k, v, dropout_p, training):
         """q, k, v [B, H, S, dh] (head-major views of token-major projections)."""
@@ -804,9 +858,9 @@ class CudaBackend:
     def prepare_pool(self, emb, read, write, spec: GateSpec, pctx: Optional[ParallelCtx] = None):
         pctx = pctx or ParallelCtx()
         U = pctx.n_valid if pctx.n_valid is not None else emb.shape[0]
-        pool = CudaPool(None, None, None)
+        pool = CudaPool()
         pool.keep_xr = self.keep_xr
-        anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, pool, spec.normalize_pool, U)
+        anchor, gram, esum = _PoolPrepFn.apply(emb, read, write, pool.tensors, spec.normalize_pool, U)
         gram = C.sum_over_shards(gram, pctx.shard_group)
         esum = C.sum_over_shards(esum, pctx.shard_group)
         from .score_stats import split_bf16

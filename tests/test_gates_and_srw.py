@@ -221,3 +221,25 @@ def test_forward_only_row_statistics_agree_with_the_autograd_node():
     assert torch.allclose(tau2, tau.t().reshape(-1), atol=1e-6)
     assert torch.allclose(isd2, isd.t().reshape(-1), rtol=1e-6)
     assert torch.equal(hb2, hb.transpose(0, 1).reshape(R * T, r))
+
+
+def test_prepared_pool_is_freed_without_a_backward_pass():
+    """A forward pass with gradients enabled that is never followed by backward (an
+    exception, a skipped non-finite step) must not keep its prepared pools alive: the
+    preparation node of the graph does not point back at the pool."""
+    import gc
+    import weakref
+    from dawn_srw_b200.ops.backend import ParallelCtx
+    from dawn_srw_b200.ops.cuda_backend import CudaBackend
+    from dawn_srw_b200.ops.gates import gate_spec_for
+    spec = gate_spec_for("spatial-r1-v4.0.1")
+    be = CudaBackend()
+    emb, read, write = (torch.randn(50, d, requires_grad=True) for d in (16, 32, 32))
+    refs = []
+    for _ in range(3):
+        pool = be.prepare_pool(emb, read, write, spec, ParallelCtx())
+        assert pool.emb.dtype == torch.bfloat16 and pool.g_write is not None
+        refs.append(weakref.ref(pool.tensors))
+        del pool
+    gc.collect()
+    assert all(r() is None for r in refs)

@@ -408,6 +408,31 @@ def test_layernorm_kernel(cb):
         assert _rel(x.grad, x2.grad) < 1e-4 and _rel(w.grad, w2.grad) < 1e-4 and _rel(b.grad, b2.grad) < 1e-4
 
 
+def test_dropout_with_residual_add_and_regenerated_mask(cb):
+    dev = torch.device("cuda")
+    torch.manual_seed(5)
+    be = cb.CudaBackend()
+    res = torch.randn(512, 1280, device=dev)
+    x = (torch.rand(512, 1280, device=dev) + 0.5).requires_grad_(True)      # no zeros: the mask is y != res
+    p = 0.1
+    y = be.dropout_add(res, x, p, True)
+    kept = (y - res) != 0
+    frac = kept.float().mean().item()
+    assert abs(frac - (1 - p)) < 5e-3, frac
+    assert torch.allclose((y - res)[kept], (x.detach() / (1 - p))[kept], rtol=1e-5, atol=1e-6)
+    # rows and columns are not correlated: every column keeps about 90 %
+    assert (kept.float().mean(0) - (1 - p)).abs().max() < 0.08
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    assert torch.allclose(x.grad, gy * kept / (1 - p), rtol=1e-5, atol=1e-6)   # same mask, regenerated
+    # a second call draws another mask; evaluation is the identity
+    y2 = be.dropout_add(res, x.detach(), p, True)
+    assert ((y2 - res) != 0).ne(kept).any()
+    assert torch.equal(be.dropout_add(res, x.detach(), p, False), res + x.detach())
+    z = be.dropout(x.detach(), 0.25, True)
+    assert abs((z != 0).float().mean().item() - 0.75) < 5e-3
+
+
 def test_lm_head_cross_entropy(cb):
     from dawn_srw_b200.ops import reference as R
     dev = torch.device("cuda")

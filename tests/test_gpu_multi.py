@@ -248,9 +248,13 @@ def _group_vs_oracle(rank, world, version, n_qk, n_v):
     ("spatial-r1-v4.0.1", 4100, 5000),      # every shard runs the 256-wide kernels up to 8 ranks
     ("spatial-r1-v3.9.4", 4100, 5000),
     ("spatial-r1-v4.1", 4100, 5000),        # dead-unit penalty on the fused path
+    ("spatial-r1-v4.0.1+regs", 4100, 5000), # peers' rows copied through registers instead of bounce buffers
 ])
-def test_sharded_route_group_matches_single_process_fp32_oracle(world, version, n_qk, n_v):
+def test_sharded_route_group_matches_single_process_fp32_oracle(world, version, n_qk, n_v, monkeypatch):
     _need(world)
+    if version.endswith("+regs"):
+        version = version[: -len("+regs")]
+        monkeypatch.setenv("DSB_GATHER_REGS_MIN_UNITS", "1")      # the spawned ranks inherit it
     outs = _spawn(_group_vs_oracle, world, version, n_qk, n_v)
     sharp = ("demb", "dh", "doff")     # flow through d(gate)/d(score): bf16 rounding moves scores across the kink
     for o in outs:
