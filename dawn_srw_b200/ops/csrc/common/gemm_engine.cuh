@@ -81,8 +81,9 @@ struct alignas(64) GatherParams {
 };
 // Gather modes of the engine kernel (template parameter kGather):
 //   0  none
-//   1  TMA load from the peer -> two 16 KB bounce buffers in shared memory -> TMA store.
-//      Highest copy rate per CTA, but the 32 KB cost the operand ring one stage.
+//   1  TMA load from the peer -> a ring of four 8 KB bounce buffers in shared memory -> TMA
+//      store, three loads in flight.  Highest copy rate per CTA, but the 32 KB cost the
+//      operand ring one stage.
 //   2  two warps copy through registers (16-byte loads from the peer, 16-byte stores into
 //      the local buffer, eight in flight per lane): no shared memory, so the ring keeps
 //      all its stages; the copy rate is lower and suits kernels that run long enough to
@@ -112,13 +113,14 @@ struct alignas(64) GemmParams {
 
 constexpr int kOutBufBytes = 4096;  // one staged slab: 32 rows x 128 bytes
 
-constexpr int kGatherPieceBytes = 128 * 64 * 2;   // 128 rows x 64 bf16
+constexpr int kGatherPieceBytes = 64 * 64 * 2;    // 64 rows x 64 bf16
+constexpr int kGatherSlots = 4;                   // bounce buffers of the ring
 template <int BN, int kOutBufsPerWarp, int kEpiWarps = 4, int kGather = 0>
 struct EngineSmem {
   static constexpr int kABytes = kBlockM * kBlockK * 2;  // 16 KB
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kGatherBytes = kGather == kGatherBounce ? 2 * kGatherPieceBytes : 0;
+  static constexpr int kGatherBytes = kGather == kGatherBounce ? kGatherSlots * kGatherPieceBytes : 0;
   static constexpr int kOutBytes = kEpiWarps * kOutBufsPerWarp * kOutBufBytes + kGatherBytes;
   static constexpr int kMaxSmem = 227 * 1024;
   static constexpr int kBudget = kMaxSmem - kOutBytes - 1024 /*align slack*/ - 512 /*barriers*/;
@@ -301,7 +303,7 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
   uint64_t* acc_empty = bars + 2 * kStages + 6;    // [kMaxSeg][2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint64_t* gather_bar = bars + 2 * kStages + 14;  // [2]
+  uint64_t* gather_bar = bars + 2 * kStages + 14;  // [kGatherSlots]
   uint8_t* gather_buf = out_stage + kEpiWarps * Epi::kOutBufs * kOutBufBytes;
 
   const int warp = threadIdx.x >> 5;
@@ -320,7 +322,9 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], kCtas * kEpiWarps);   // one elected arrive per epilogue warp
     }
-    if (kGather == kGatherBounce) { mbar_init(&gather_bar[0], 1); mbar_init(&gather_bar[1], 1); }
+    if (kGather == kGatherBounce) {
+      for (int i = 0; i < kGatherSlots; ++i) mbar_init(&gather_bar[i], 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -551,52 +555,82 @@ gemm_engine_kernel(const __grid_constant__ GemmParams<typename Epi::Params> p) {
     }
   } else if (kGather == kGatherBounce && warp == kGatherWarp) {
     // ------------------------------- gather through shared-memory bounce buffers
+    // A ring of kGatherSlots pieces (64 rows x 64 columns): up to kGatherSlots - 1 loads
+    // from the peer are in flight while landed pieces are stored to local memory.
     const GatherParams& g = p.gather;
     if (g.n_ranks > 1) {
       const int cpr = g.rows_per_rank / 128;               // 128-row chunks per rank
       const int remote = (g.n_ranks - 1) * cpr;
-      int slot = 0;
-      uint32_t ph[2] = {0u, 0u};
+      int strips = 0;                                      // 64-column strips over all tensors
+      for (int t = 0; t < g.n_tensors; ++t) strips += g.cols[t] >> 6;
+      const int ppc = 2 * strips;                          // pieces per chunk
+      const int my_chunks = (remote > static_cast<int>(blockIdx.x))
+                                ? (remote - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1
+                                : 0;
+      const int total = my_chunks * ppc;
+      // piece q -> (owner row block, tensor, column, row half)
+      auto locate = [&](int q, int& t, int& c0, int& grow, int& owner) {
+        const int rc = static_cast<int>(blockIdx.x) + (q / ppc) * static_cast<int>(gridDim.x);
+        owner = (g.my_rank + 1 + rc / cpr) % g.n_ranks;   // nearer ranks first, a different peer per rank
+        grow = owner * g.rows_per_rank + (rc % cpr) * 128;
+        int w = q % ppc;
+        const int half = w & 1;
+        w >>= 1;
+        t = 0;
+        while (w >= (g.cols[t] >> 6)) { w -= g.cols[t] >> 6; ++t; }
+        c0 = w << 6;
+        grow += 64 * half;
+      };
+      auto issue_load = [&](int q) {
+        int t, c0, grow, owner;
+        locate(q, t, c0, grow, owner);
+        const int slot = q % kGatherSlots;
+        mbar_expect_tx(&gather_bar[slot], kGatherPieceBytes);
+        tma_load_2d(gather_buf + slot * kGatherPieceBytes, &g.src[t][owner], &gather_bar[slot], c0, grow);
+      };
       bool ok = true;
-      for (int rc = blockIdx.x; rc < remote; rc += gridDim.x) {
-        // nearer ranks first; every rank starts with a different peer
-        const int owner = (g.my_rank + 1 + rc / cpr) % g.n_ranks;
-        const int grow = owner * g.rows_per_rank + (rc % cpr) * 128;
-        // per-token statistics of the chunk: 128 x 16 bytes per array, all lanes
-        for (int sidx = 0; sidx < g.n_stats; ++sidx) {
-          const float4* src = g.stat_src[sidx][owner] + grow;
-          float4* dst = g.stat_dst[sidx] + grow;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            float4 v;
-            asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];"
-                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                         : "l"(src + lane + 32 * k)
-                         : "memory");
-            dst[lane + 32 * k] = v;
-          }
-        }
+      if (lane == 0)
+        for (int q = 0; q < kGatherSlots - 1 && q < total; ++q) issue_load(q);
+      for (int done = 0; done < total && ok; ++done) {
+        int t, c0, grow, owner;
+        locate(done, t, c0, grow, owner);
         if (lane == 0) {
-          for (int t = 0; t < g.n_tensors && ok; ++t) {
-            for (int c0 = 0; c0 < g.cols[t]; c0 += 64) {
-              bulk_wait_read<1>();   // the store that last used this bounce buffer has read it
-              uint8_t* b = gather_buf + slot * kGatherPieceBytes;
-              mbar_expect_tx(&gather_bar[slot], kGatherPieceBytes);
-              tma_load_2d(b, &g.src[t][owner], &gather_bar[slot], c0, grow);
-              if (!mbar_wait(&gather_bar[slot], ph[slot], abort_flag)) { ok = false; break; }
-              ph[slot] ^= 1u;
-              tma_store_2d(&g.dst[t], smem_u32(b), c0, grow);
-              bulk_commit();
-              slot ^= 1;
+          const int slot = done % kGatherSlots;
+          ok = mbar_wait(&gather_bar[slot], static_cast<uint32_t>(done / kGatherSlots) & 1u, abort_flag);
+          if (ok) {
+            tma_store_2d(&g.dst[t], smem_u32(gather_buf + slot * kGatherPieceBytes), c0, grow);
+            bulk_commit();
+            const int nxt = done + kGatherSlots - 1;
+            if (nxt < total) {
+              bulk_wait_read<1>();   // the store that last used the next load's slot has read it
+              issue_load(nxt);
             }
           }
-          if (ok) bulk_wait<0>();    // the whole chunk is in local memory
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
-        __threadfence();             // every lane's statistics stores, lane 0's tensor rows
-        __syncwarp();
-        if (lane == 0) flag_store_release(g.ready + grow / 128, g.epoch);
+        if (done % ppc == ppc - 1) {
+          // last piece of a chunk: copy its per-token statistics (all lanes), wait for the
+          // chunk's stores, publish the block
+          const int crow = grow - 64;                      // the last piece is a second half
+          for (int sidx = 0; sidx < g.n_stats; ++sidx) {
+            const float4* src = g.stat_src[sidx][owner] + crow;
+            float4* dst = g.stat_dst[sidx] + crow;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float4 v;
+              asm volatile("ld.global.cv.v4.f32 {%0,%1,%2,%3}, [%4];"
+                           : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                           : "l"(src + lane + 32 * k)
+                           : "memory");
+              dst[lane + 32 * k] = v;
+            }
+          }
+          if (lane == 0) bulk_wait<0>();                   // the chunk's rows are in local memory
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) flag_store_release(g.ready + crow / 128, g.epoch);
+        }
       }
       if (lane == 0) bulk_wait<0>();
     }

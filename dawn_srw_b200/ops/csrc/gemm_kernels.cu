@@ -1310,7 +1310,7 @@ static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int*
     if (d->cols[t] % 64 != 0) return 701;
     g->cols[t] = d->cols[t];
     for (int j = 0; j < d->n_ranks; ++j) {
-      int rc = make_tmap_bf16(&g->src[t][j], d->bufs[t][j], d->cols[t], total_rows, d->ld[t], 64, 128);
+      int rc = make_tmap_bf16(&g->src[t][j], d->bufs[t][j], d->cols[t], total_rows, d->ld[t], 64, 64);
       if (rc) return 710 + rc;
     }
     g->dst[t] = g->src[t][d->my_rank];

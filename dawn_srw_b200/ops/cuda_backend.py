@@ -277,11 +277,12 @@ class _LayerNormFn(torch.autograd.Function):
 # ---------------------------------------------------------------------------
 class _PoolTensors:
     """bf16 compute copies of a pool and the fp32 gradient accumulators of the current step."""
-    __slots__ = ("emb", "read", "write", "g_emb", "g_read", "g_write", "__weakref__")
+    __slots__ = ("emb", "read", "write", "g_emb", "g_read", "g_write", "emb_f", "__weakref__")
 
     def __init__(self):
         self.emb = self.read = self.write = None
         self.g_emb = self.g_read = self.g_write = None
+        self.emb_f = None          # fp32 copy of emb for the per-unit mat-vecs (made on first use)
 
 
 def _on_tensors(name):
@@ -372,6 +373,15 @@ class _PoolPrepFn(torch.autograd.Function):
         return out + (None, None, None)
 
 
+def _emb_f32(holder):
+    """fp32 copy of the prepared (bf16) embedding rows, made once per prepared pool: every
+    layer's mat-vec, forward and backward, uses it."""
+    t = holder.tensors if hasattr(holder, "tensors") else holder
+    if t.emb_f is None:
+        t.emb_f = t.emb.float()
+    return t.emb_f
+
+
 class _PoolMatVecFn(torch.autograd.Function):
     """m[u] = emb_c[u] . v  (per-unit mean score).  The emb gradient is added
     into the pool's shared accumulator."""
@@ -379,14 +389,14 @@ class _PoolMatVecFn(torch.autograd.Function):
     def forward(ctx, v, anchor, holder, U):
         ctx.holder, ctx.U = holder, U
         ctx.save_for_backward(v)
-        return holder.emb[:U].float() @ v
+        return _emb_f32(holder)[:U] @ v
 
     @staticmethod
     def backward(ctx, dm):
         (v,) = ctx.saved_tensors
         hd, U = ctx.holder, ctx.U
         hd.g_emb[:U].addr_(dm, v)
-        return hd.emb[:U].float().t() @ dm, torch.zeros_like(dm[:1]), None, None
+        return _emb_f32(hd)[:U].t() @ dm, torch.zeros_like(dm[:1]), None, None
 
 
 def _route_backward_core(x_bf, h_bf, tau, inv_sd, dy, d_den, hd, spec, U, xr=None):
@@ -832,7 +842,8 @@ class CudaBackend:
         p = float(dropout_p) if training else 0.0
         seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if p > 0.0 else 0
         o = causal_attention(tok(q), tok(k), tok(v), H, p, seed)
-        return o.view(B, S, H, dh).transpose(1, 2).float()
+        # bf16, as the kernel writes it: the only consumer is the bf16 operand of the O projection
+        return o.view(B, S, H, dh).transpose(1, 2)
 
     def lm_head_ce(self, x, tok_emb, labels):
         B, S, D = x.shape
