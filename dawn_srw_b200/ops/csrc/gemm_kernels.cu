@@ -1180,9 +1180,10 @@ struct BwdGateEpiXr {
         st.put(b_ds, k0 + 1, dsw[4], dsw[5], dsw[6], dsw[7]);
       }
       const bool in_range = col0 + 64 * sl < N;
-      st.flush(&maps[0], b_x, col0 + 64 * sl, r0, false, in_range);      // p first: its buffer
-      st.flush(&maps[1], b_dxr, col0 + 64 * sl, r0, false, in_range);    // is wanted back soonest
-      st.flush(&maps[2], b_ds, col0 + 64 * sl, r0, false, in_range);
+      st.publish();                               // one proxy fence for the three slabs
+      st.store(&maps[0], b_x, col0 + 64 * sl, r0, false, in_range);      // p first: its buffer
+      st.store(&maps[1], b_dxr, col0 + 64 * sl, r0, false, in_range);    // is wanted back soonest
+      st.store(&maps[2], b_ds, col0 + 64 * sl, r0, false, in_range);
       if (sl == 0) {
         st.wait_free<2>();                        // the p store has read the buffer ...
         fetch_xr(p, b_x, r0, col0 + 64, M, lane); // ... which takes the second slab's xr
