@@ -50,6 +50,10 @@ def parse():
                     help="with --parallelism pool: unit shards per pool (a divisor of --gpus); the "
                          "remaining factor is data parallel (e.g. --gpus 8 --pool-shards 4 = dp2 x pool4). "
                          "0 = all GPUs shard the pools")
+    ap.add_argument("--shard-pools", default="",
+                    help="comma-separated pools that are split over the pool shards (default: all "
+                         "of qk,v,know); the others are kept whole on every rank, e.g. "
+                         "--shard-pools know")
     ap.add_argument("--optimizer", default="auto", choices=["auto", "partitioned", "replicated"],
                     help="partitioned: reduce-scatter + AdamW on the owned slice + all-gather over "
                          "peer memory with sharded moments; auto = partitioned for --parallelism dp")
@@ -227,6 +231,8 @@ def main():
     t = cfg.training
     t.batch_size = bpg * world
     t.pool_shards, t.seq_shard = pool_shards, True
+    if args.shard_pools and pool_shards > 1:
+        t.shard_pools = [n.strip() for n in args.shard_pools.split(",") if n.strip()]
     t.log_interval = 0
     opt_mode = args.optimizer
     if opt_mode == "auto":
@@ -338,7 +344,9 @@ def main():
             "config": {"model": f"DAWN-SRW {args.model} ({cfg.model.model_version})",
                        "global_batch": t.batch_size, "seq_len": args.seq_len,
                        "parallelism": ((f"dp{world // pool_shards}x" if pool_shards < world else "")
-                                       + f"pool{pool_shards}+seqshard" if pool_shards > 1 else f"dp{world}"),
+                                       + f"pool{pool_shards}"
+                                       + (f"[{','.join(t.shard_pools)} only]" if t.shard_pools else "")
+                                       + "+seqshard" if pool_shards > 1 else f"dp{world}"),
                        "l2": "inputs and weights per step exceed the 126 MB L2 (no flush needed)",
                        "layer_recompute": False,
                        "optimizer": type(trainer.optimizer).__name__},

@@ -14,7 +14,7 @@ import dataclasses
 import json
 import warnings
 from dataclasses import dataclass, field
-from typing import Any, Dict, Optional
+from typing import Any, Dict, List, Optional
 
 import yaml
 
@@ -92,6 +92,7 @@ class TrainingConfig:
     dp: int = 0
     seq_shard: bool = True
     zero_pool_state: bool = False
+    shard_pools: Optional[List[str]] = None   # pools split over pool_shards ranks (None: all); the rest are replicated
     fsdp: bool = False                   # dense baseline: Linear weights sharded by rows over the data-parallel ranks
     overlap_grad_reduce: bool = True     # replicated-parameter gradients are all-reduced during backward
     n_chunks_know: int = 0

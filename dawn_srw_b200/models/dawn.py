@@ -53,24 +53,37 @@ class NeuronPool(nn.Module):
     ``PoolShard`` each rank stores only its (padded) slice of unit rows."""
 
     def __init__(self, n_qk, n_v, n_know, d_model, d_route, spec: GateSpec,
-                 shard: Optional[PoolShard] = None, gen=None):
+                 shard: Optional[PoolShard] = None, gen=None, sharded_names=None):
         super().__init__()
         self.sizes = {"qk": n_qk, "v": n_v, "know": n_know}
         self.shard = shard or PoolShard(0, 1)
+        # Pools named here are split over the shard group; the others are kept whole on every
+        # rank (small pools: no per-layer traffic, one gradient all-reduce per step instead).
+        self.sharded_names = set(POOLS if sharded_names is None else sharded_names)
+        unknown = self.sharded_names - set(POOLS)
+        if unknown:
+            raise ValueError(f"unknown pool names {sorted(unknown)}; pools are {POOLS}")
         for name, n in self.sizes.items():
-            lo, hi, padded = self.shard.slice_of(n)
+            lo, hi, padded = self.shard_of(name).slice_of(n)
+            replicated = self.shard.count > 1 and name not in self.sharded_names
             for kind, dim in (("emb", d_route), ("read", d_model), ("write", d_model)):
                 full = _unit_rows(n, dim, gen)
                 local = torch.zeros(padded, dim)
                 local[: hi - lo] = full[lo:hi]
-                self.register_parameter(f"{name}_{kind}", nn.Parameter(local))
+                prm = nn.Parameter(local)
+                if replicated:
+                    prm._pool_replicated = True      # gradient: all-reduced over every rank
+                self.register_parameter(f"{name}_{kind}", prm)
         if spec.learnable_scale:
             for name in POOLS:
                 self.register_parameter(
                     f"{name}_scale", nn.Parameter(torch.full((1,), math.sqrt(d_model))))
 
+    def shard_of(self, name: str) -> PoolShard:
+        return self.shard if name in self.sharded_names else PoolShard(0, 1)
+
     def n_valid(self, name: str) -> int:
-        lo, hi, _ = self.shard.slice_of(self.sizes[name])
+        lo, hi, _ = self.shard_of(name).slice_of(self.sizes[name])
         return hi - lo
 
     def tensors(self, name: str):
@@ -127,7 +140,8 @@ class DAWN(nn.Module):
                  d_route=128, n_qk=1580, n_v=2600, n_know=25200, dropout_rate=0.1,
                  router_dropout=0.1, gradient_checkpointing=False,
                  model_version="spatial-r1-v4.1", gate: Optional[GateSpec] = None,
-                 pool_shard: Optional[PoolShard] = None, seed: int = 0, backend=None):
+                 pool_shard: Optional[PoolShard] = None, seed: int = 0, backend=None,
+                 sharded_pools=None):
         super().__init__()
         if d_model % n_heads != 0:
             raise ValueError(f"d_model ({d_model}) must be divisible by n_heads ({n_heads})")
@@ -143,18 +157,21 @@ class DAWN(nn.Module):
         self.pos_emb = nn.Embedding(max_seq_len, d_model)
         nn.init.normal_(self.token_emb.weight, std=0.02, generator=gen)
         nn.init.normal_(self.pos_emb.weight, std=0.02, generator=gen)
-        self.neuron_pool = NeuronPool(n_qk, n_v, n_know, d_model, d_route, self.gate, pool_shard, gen)
+        self.neuron_pool = NeuronPool(n_qk, n_v, n_know, d_model, d_route, self.gate, pool_shard, gen,
+                                      sharded_names=sharded_pools)
         self.router = Router(d_model, d_route, gen)
         self.layers = nn.ModuleList([DAWNBlock(d_model, gen) for _ in range(n_layers)])
         self.norm = _LN(d_model)
         self.backend = backend
         self.shard_group = None       # process group over which pool units are split
         self.dp_group = None          # data-parallel group (LB / dead statistics)
+        self.world_group = None       # every rank of the job (replicated pools under sharding)
         self.seq_sharded = False
 
     # ------------------------------------------------------------------
-    def set_parallel(self, shard_group=None, dp_group=None, seq_sharded=False):
+    def set_parallel(self, shard_group=None, dp_group=None, seq_sharded=False, world_group=None):
         self.shard_group, self.dp_group, self.seq_sharded = shard_group, dp_group, seq_sharded
+        self.world_group = world_group
 
     def _backend(self, device):
         if self.backend is None:
@@ -180,6 +197,13 @@ class DAWN(nn.Module):
         return math.sqrt(float(self.d_model))
 
     def pctx(self, name: str) -> ParallelCtx:
+        if self.shard_group is not None and name not in self.neuron_pool.sharded_names:
+            # a pool kept whole on every rank: the op runs on this rank's own tokens; its
+            # per-unit statistics are averaged over all ranks that see different tokens
+            n = self.neuron_pool.sizes[name]
+            peers = self.world_group if self.seq_sharded else self.dp_group
+            return ParallelCtx(shard_group=None, dp_group=peers, n_total=n, n_valid=n,
+                               seq_sharded=False)
         return ParallelCtx(shard_group=self.shard_group, dp_group=self.dp_group,
                            n_total=self.neuron_pool.sizes[name],
                            n_valid=self.neuron_pool.n_valid(name), seq_sharded=self.seq_sharded)

@@ -47,7 +47,7 @@ MODEL_REGISTRY: Dict[str, ModelSpec] = {
 }
 
 
-def build_model_from_config(cfg: Config, *, pool_shard=None, backend=None):
+def build_model_from_config(cfg: Config, *, pool_shard=None, backend=None, sharded_pools=None):
     version = cfg.model.model_version
     if version not in MODEL_REGISTRY:
         raise ValueError(f"Unknown model_version: {version!r}. Known: {sorted(MODEL_REGISTRY)}")
@@ -55,6 +55,8 @@ def build_model_from_config(cfg: Config, *, pool_shard=None, backend=None):
     kw = spec.build_kwargs(cfg)
     if spec.supports_sharded and pool_shard is not None:
         kw["pool_shard"] = pool_shard
+        if sharded_pools is not None:
+            kw["sharded_pools"] = list(sharded_pools)
     kw["backend"] = backend
     return spec.cls(**kw)
 

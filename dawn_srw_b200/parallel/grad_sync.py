@@ -15,6 +15,8 @@ partial sums:
   every rank of its shard group: they arrive through the all-reduced /
   all-gathered output gradient).
 
+* pool tensors that stay whole on every rank while other pools are sharded
+  (``training.shard_pools``) behave like replicated parameters: sum over the world;
 * weights sharded by rows over the data-parallel ranks (parallel/fsdp.py, dense
   baseline) arrive already summed by their reduce-scatter -> only divided by
   the world size; their squared norm is summed over that group.
@@ -118,6 +120,11 @@ class GradSync:
         return wd_group_of(name) == "pool"
 
     @staticmethod
+    def _is_replicated_pool(p) -> bool:
+        """A pool tensor kept whole on every rank although other pools are sharded."""
+        return getattr(p, "_pool_replicated", False)
+
+    @staticmethod
     def _is_rowsharded(p) -> bool:
         return getattr(p, "_fsdp_rows", None) is not None
 
@@ -141,7 +148,7 @@ class GradSync:
             if self._is_rowsharded(p):
                 g /= pool_div
             elif self._is_pool(n):
-                if t.pool_shards == 1:
+                if t.pool_shards == 1 or self._is_replicated_pool(p):
                     dist.all_reduce(g, group=t.world_group)
                 elif t.dp > 1:
                     dist.all_reduce(g, group=t.dp_group)
@@ -152,7 +159,10 @@ class GradSync:
         t = self.topo
         sq = lambda g: g.float().square().sum()
         rep = [sq(g) for (n, p), g in zip(named, grads) if not self._is_pool(n) and not self._is_rowsharded(p)]
-        pool = [sq(g) for (n, _), g in zip(named, grads) if self._is_pool(n)]
+        # replicated pools count once (the local copy), like any replicated parameter
+        rep += [sq(g) for (n, p), g in zip(named, grads) if self._is_pool(n) and self._is_replicated_pool(p)]
+        pool = [sq(g) for (n, p), g in zip(named, grads)
+                if self._is_pool(n) and not self._is_replicated_pool(p)]
         rows = [(sq(g), p._fsdp_group) for (_, p), g in zip(named, grads) if self._is_rowsharded(p)]
         dev = grads[0].device
         rep_s = torch.stack(rep).sum() if rep else torch.zeros((), device=dev)

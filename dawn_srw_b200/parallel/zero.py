@@ -80,7 +80,7 @@ class PartitionedAdamW:
         buckets: Dict[Tuple[str, str], _Bucket] = {}
         for n, p in self.named:
             wdg = wd_group_of(n)
-            if wdg == "pool" and topo.pool_shards > 1:
+            if wdg == "pool" and topo.pool_shards > 1 and not getattr(p, "_pool_replicated", False):
                 kind, group, gsize, grank = "dp", topo.dp_group, topo.dp, topo.dp_index
             else:
                 kind, group, gsize, grank = "world", topo.world_group, topo.world, topo.rank

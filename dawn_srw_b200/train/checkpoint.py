@@ -184,6 +184,7 @@ def consolidate(paths: List[str], pool_sizes: Dict[str, int], out_path: str) -> 
     from ..parallel.topology import PoolShard
     merged = dict(blobs[0])
     row_blocks = blobs[0].get("fsdp_rows") or {}     # dense weights stored as per-rank row blocks
+    sharded_pools = blobs[0].get("sharded_pools")    # None: every pool is split over the shards
 
     def merge_tree(trees):
         out = {}
@@ -191,7 +192,8 @@ def consolidate(paths: List[str], pool_sizes: Dict[str, int], out_path: str) -> 
             m = re.search(r"(qk|v|know)_(emb|read|write)$", k)
             if k in row_blocks and isinstance(v, torch.Tensor) and v.dim() == 2:
                 out[k] = torch.cat([t[k] for t in trees], 0)[: row_blocks[k]]
-            elif m and isinstance(v, torch.Tensor) and v.dim() == 2:
+            elif (m and isinstance(v, torch.Tensor) and v.dim() == 2
+                  and (sharded_pools is None or m.group(1) in sharded_pools)):
                 n = pool_sizes[m.group(1)]
                 rows = []
                 for i, t in enumerate(trees):
@@ -209,5 +211,6 @@ def consolidate(paths: List[str], pool_sizes: Dict[str, int], out_path: str) -> 
         merged["opt_state"] = os0
     merged["shard"] = {"index": 0, "count": 1}
     merged.pop("fsdp_rows", None)
+    merged.pop("sharded_pools", None)
     torch.save(merged, out_path)
     return out_path

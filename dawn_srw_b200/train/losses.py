@@ -126,7 +126,7 @@ def total_loss(result: Dict[str, Any], model, tcfg, step: int, *, is_baseline: b
             n = pool.n_valid(name)
             for k in ("emb", "read", "write"):
                 w = getattr(pool, f"{name}_{k}")[:n]
-                if sharded:
+                if sharded and name in pool.sharded_names:
                     # the statistic is defined on a sample of the whole pool, not of a shard
                     w = global_strided_sample(w, pool.sizes[name], pool.shard, shard_group)
                 tensors.append(w)

@@ -66,9 +66,10 @@ class Trainer:
                 seed=cfg.seed)
             m.vocab_size = vocab
         shard = self.topo.pool_shard if self.topo.pool_shards > 1 else None
-        self.model = build_model_from_config(cfg, pool_shard=shard, backend=self.backend).to(self.device)
+        self.model = build_model_from_config(cfg, pool_shard=shard, backend=self.backend,
+                                             sharded_pools=t.shard_pools).to(self.device)
         self.model.set_parallel(shard_group=self.topo.shard_group, dp_group=self.topo.dp_group,
-                                seq_sharded=self.topo.seq_shard)
+                                seq_sharded=self.topo.seq_shard, world_group=self.topo.world_group)
         self.fsdp = bool(t.fsdp) and self.is_baseline and self.topo.world > 1
         if self.fsdp:
             # every rank built the same full weights (same seed); keep this rank's rows only
@@ -227,6 +228,8 @@ class Trainer:
         if writes:
             si, sc = self._ckpt_shard()
             extra = None
+            if t.pool_shards > 1 and self.cfg.training.shard_pools is not None:
+                extra = {"sharded_pools": list(self.cfg.training.shard_pools)}
             if self.fsdp:     # which tensors hold row blocks, and of how many rows (for consolidate)
                 extra = {"fsdp_rows": {n: p._fsdp_rows for n, p in self.model.named_parameters()
                                        if getattr(p, "_fsdp_rows", None) is not None}}
