@@ -273,3 +273,31 @@ def test_prefetching_loader_yields_the_same_batches_and_propagates_errors(tmp_pa
             return super().rows(lo, hi)
     with pytest.raises(OSError):
         list(BinDataLoader(Broken(64, 8, 100), 8, prefetch=2))
+
+
+def test_consolidate_keeps_replicated_pools_whole(tmp_path):
+    """Shard files of a hybrid layout (only the Know pool split): the Know rows are
+    concatenated with the padding dropped, the QK pool is taken as it is."""
+    import torch
+    from dawn_srw_b200.parallel.topology import PoolShard
+    from dawn_srw_b200.train import checkpoint as ck
+    n_know, n_qk = 21, 10
+    know = torch.arange(n_know * 4, dtype=torch.float32).reshape(n_know, 4)
+    qk = torch.randn(n_qk, 4)
+    paths = []
+    for k in range(2):
+        lo, hi, padded = PoolShard(k, 2).slice_of(n_know)
+        rows = torch.zeros(padded, 4)
+        rows[: hi - lo] = know[lo:hi]
+        blob = {"params": {"neuron_pool.know_emb": rows, "neuron_pool.qk_emb": qk.clone(),
+                           "norm.weight": torch.ones(4)},
+                "opt_state": None, "step": 3, "shard": {"index": k, "count": 2},
+                "sharded_pools": ["know"]}
+        path = str(tmp_path / f"checkpoint_step3.shard{k}of2.pt")
+        torch.save(blob, path)
+        paths.append(path)
+    merged = torch.load(ck.consolidate(paths, {"know": n_know, "qk": n_qk, "v": 0}, str(tmp_path / "full.pt")),
+                        weights_only=False)
+    assert torch.equal(merged["params"]["neuron_pool.know_emb"], know)
+    assert torch.equal(merged["params"]["neuron_pool.qk_emb"], qk)
+    assert "sharded_pools" not in merged and merged["shard"] == {"index": 0, "count": 1}
