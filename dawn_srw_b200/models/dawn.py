@@ -202,6 +202,10 @@ class DAWN(nn.Module):
             # per-unit statistics are averaged over all ranks that see different tokens
             n = self.neuron_pool.sizes[name]
             peers = self.world_group if self.seq_sharded else self.dp_group
+            if self.seq_sharded and self.world_group is not None:
+                import torch.distributed as dist
+                if dist.get_world_size(self.shard_group) == dist.get_world_size(self.world_group):
+                    peers = self.shard_group     # same ranks; this group has the peer-memory all-reduce
             return ParallelCtx(shard_group=None, dp_group=peers, n_total=n, n_valid=n,
                                seq_sharded=False)
         return ParallelCtx(shard_group=self.shard_group, dp_group=self.dp_group,
