@@ -1284,13 +1284,16 @@ static int launch_engine_gather(GemmParams<typename Epi::Params>& gp, cudaStream
 }
 
 // Local units from which a gate kernel's own run time hides a register-copy gather.
-static bool gather_through_registers(int units) {
+static bool gather_through_registers(int units, const GatherParams& g) {
   static int thr = -1;
   if (thr < 0) {
     const char* e = getenv("DSB_GATHER_REGS_MIN_UNITS");
     thr = e ? atoi(e) : 4096;
   }
-  return units >= thr;
+  // ... or little to copy (one route's h rows): not worth a stage of the operand ring
+  int cols = 0;
+  for (int t = 0; t < g.n_tensors; ++t) cols += g.cols[t];
+  return units >= thr || cols <= 512;
 }
 
 static int fill_gather(GatherParams* g, const DsbGather* d, int total_rows, int* m_rot) {
@@ -1517,7 +1520,7 @@ namespace dsb {
 template <bool kSaveXr>
 static int launch_fwd_wide(GemmParams<FwdGateParams>& gp, int kind, bool fused, cudaStream_t stream) {
   if (fused) {
-    const bool regs = gather_through_registers(gp.N);
+    const bool regs = gather_through_registers(gp.N, gp.gather);
     if (kind == 0) return launch_engine_gather<256, FwdGateEpiWide<0, kSaveXr>>(gp, stream, regs);
     if (kind == 1) return launch_engine_gather<256, FwdGateEpiWide<1, kSaveXr>>(gp, stream, regs);
     return launch_engine_gather<256, FwdGateEpiWide<2, kSaveXr>>(gp, stream, regs);
@@ -1541,10 +1544,13 @@ extern "C" int dsb_srw_fwd_gate_xr(const void* h, long long ldh, const void* emb
   GemmParams<FwdGateParams> gp;
   memset(&gp, 0, sizeof(gp));
   // 256-wide tiles (CTA pairs only) once the pool is wide enough to fill the machine with them
-  const bool wide = dsb_srw_wide_tiles(U) != 0;
-  if (xr_out != nullptr && !wide) return 704;   // only the wide kernel writes the read scalars
-  if (stats != nullptr && !wide) return 706;    // ... and reads per-token float4 statistics
-  if (diag != nullptr && !wide) return 708;     // ... and accumulates routing diagnostics
+  // A caller that asks for what only the wide kernel does (read scalars out, per-token float4
+  // statistics in, routing diagnostics) gets it for any unit count: in a sharded group every
+  // rank must take the same path although the last rank may hold fewer than 512 units.
+  const bool wide_only = xr_out != nullptr || stats != nullptr || diag != nullptr;
+  const bool wide = dsb_srw_wide_tiles(U) != 0 ||
+                    (wide_only && use_cta_pairs() && use_wide_gate());
+  if (wide_only && !wide) return 704;
   if (stats == nullptr && (tau == nullptr || inv_sigma == nullptr)) return 707;
   // A handful of token rows (decoding): a CTA pair would spend a 256-row tile on them, so
   // single CTAs take 128 x 256 tiles and twice as many of them stream the pool.
@@ -1606,7 +1612,7 @@ extern "C" int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb
                                    const DsbGate* gate, const DsbGather* gather, int* status,
                                    cudaStream_t stream) {
   if (T <= 0 || U <= 0) return 0;
-  if (!dsb_srw_wide_tiles(U)) return 704;
+  if (!(use_cta_pairs() && use_wide_gate())) return 704;   // any unit count: see the forward entry
   if (stats == nullptr && (tau == nullptr || inv_sigma == nullptr || dden == nullptr)) return 707;
   if (xr == nullptr || ldxr < U || (ldxr & 7) != 0 || (reinterpret_cast<uintptr_t>(xr) & 15) != 0)
     return 705;
@@ -1634,7 +1640,7 @@ extern "C" int dsb_srw_bwd_gate_xr(const void* h, long long ldh, const void* emb
   if (fused) {
     rc = fill_gather(&gp.gather, gather, T, &gp.m_rot);
     if (rc) return rc;
-    const bool regs = gather_through_registers(U);
+    const bool regs = gather_through_registers(U, gp.gather);
     if (gate->kind == 0) return launch_engine_gather<256, BwdGateEpiXr<0>>(gp, stream, regs);
     if (gate->kind == 1) return launch_engine_gather<256, BwdGateEpiXr<1>>(gp, stream, regs);
     return launch_engine_gather<256, BwdGateEpiXr<2>>(gp, stream, regs);

@@ -985,7 +985,13 @@ class CudaBackend:
             pc = c.get("pctx") or ParallelCtx()
             if pc.shard_group is not pc0.shard_group or not pc.seq_sharded:
                 return False
-            if c["h"].shape[-1] % 64 != 0 or not ext().srw_wide_tiles(c["pool"].extra["U"]):
+            if c["h"].shape[-1] % 64 != 0:
+                return False
+            # the same answer on every rank: judge by the padded rows per rank and by what the
+            # last rank holds, not by this rank's own unit count
+            per = c["pool"].emb.shape[0]
+            n_total = pc.n_total if pc.n_total is not None else per * nsh
+            if per < 512 or n_total - (nsh - 1) * per < 8:
                 return False
             if c.get("unit_mask") is not None and torch.is_grad_enabled():
                 return False            # masked (ablation) forwards have no backward on this path

@@ -249,6 +249,7 @@ def _group_vs_oracle(rank, world, version, n_qk, n_v):
     ("spatial-r1-v3.9.4", 4100, 5000),
     ("spatial-r1-v4.1", 4100, 5000),        # dead-unit penalty on the fused path
     ("spatial-r1-v4.0.1+regs", 4100, 5000), # peers' rows copied through registers instead of bounce buffers
+    ("spatial-r1-v4.0.1", 1030, 1100),      # 2 ranks: 520 padded rows each, the last rank holds 510 (< 512) units
 ])
 def test_sharded_route_group_matches_single_process_fp32_oracle(world, version, n_qk, n_v, monkeypatch):
     _need(world)
