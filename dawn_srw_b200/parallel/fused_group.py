@@ -38,6 +38,9 @@ from ..ops.gates import GATE_GELU_Z
 from .symm import SymmWorkspace
 
 MAX_ROUTES = 3
+# From this many ranks on, every kernel of a group gathers its own rows; below it the first
+# kernel gathers for all (measured: 2 ranks 780 vs 794 ms per 400M step in favour of the latter).
+kSpreadGatherRanks = int(__import__("os").environ.get("DSB_SPREAD_GATHER_RANKS", "4"))
 
 
 class GroupShardComm:
@@ -130,13 +133,20 @@ class _RouteGroupFn(torch.autograd.Function):
             xr = torch.empty(T, Up, dtype=torch.bfloat16, device=dev) if keep else None
             den = torch.zeros(T, dtype=torch.float32, device=dev)
             h_i = hf.local[:, i * r:(i + 1) * r]
-            # every kernel brings in what it needs and nobody has brought yet: the first one x
-            # and its own h rows, the others only their h rows and statistics - the copies of
-            # a group are spread over its kernels instead of all waiting on the first
-            ptrs, lds, cols = [c.offset_ptrs(hf, i * r)], [hf.local.stride(0)], [r]
-            if i == 0:
-                ptrs, lds, cols = [xf.ptrs] + ptrs, [xf.local.stride(0)] + lds, [D] + cols
-            gather = (ptrs, lds, cols, [sf[i].ptrs], c.rank, Tl, c.ready, c.next_epoch())
+            if W >= kSpreadGatherRanks:
+                # every kernel brings in what it needs and nobody has brought yet: the first
+                # one x and its own h rows, the others only their h rows and statistics - the
+                # copies of a group are spread over its kernels instead of all waiting on the
+                # first (with many ranks the first kernel is far shorter than its gather)
+                ptrs, lds, cols = [c.offset_ptrs(hf, i * r)], [hf.local.stride(0)], [r]
+                if i == 0:
+                    ptrs, lds, cols = [xf.ptrs] + ptrs, [xf.local.stride(0)] + lds, [D] + cols
+                gather = (ptrs, lds, cols, [sf[i].ptrs], c.rank, Tl, c.ready, c.next_epoch())
+            elif i == 0:                                 # few ranks: the first kernel brings everything in
+                gather = ([xf.ptrs, hf.ptrs], [xf.local.stride(0), hf.local.stride(0)], [D, nR * r],
+                          [sf[j].ptrs for j in range(nR)], c.rank, Tl, c.ready, c.next_epoch())
+            else:
+                gather = CB.NO_GATHER
             e.srw_fwd_gate_xr(h_i, hd.emb[:U], xf.local, hd.read[:U], p, xr, None, None, sf[i].local,
                               den, diags[i], alives[i], masks[i], gl, st, *gather)
             # un-normalised partial rows + partial denominators to the owners
@@ -210,12 +220,20 @@ class _RouteGroupFn(torch.autograd.Function):
             dtau = torch.zeros(T, dtype=torch.float32, device=dev)
             h_i = hf.local[:, i * r:(i + 1) * r]
             dy_i = dyf.local[:, i * D:(i + 1) * D]
-            # as in forward: each kernel gathers its own dy and h rows, the first one x as well
-            ptrs = [c.offset_ptrs(hf, i * r), c.offset_ptrs(dyf, i * D)]
-            lds, cols = [hf.local.stride(0), dyf.local.stride(0)], [r, D]
-            if i == 0:
-                ptrs, lds, cols = [xf.ptrs] + ptrs, [xf.local.stride(0)] + lds, [D] + cols
-            gather = (ptrs, lds, cols, [sf[i].ptrs], c.rank, Tl, c.ready, c.next_epoch())
+            if W >= kSpreadGatherRanks:
+                # as in forward: each kernel gathers its own dy and h rows, the first one x too
+                ptrs = [c.offset_ptrs(hf, i * r), c.offset_ptrs(dyf, i * D)]
+                lds, cols = [hf.local.stride(0), dyf.local.stride(0)], [r, D]
+                if i == 0:
+                    ptrs, lds, cols = [xf.ptrs] + ptrs, [xf.local.stride(0)] + lds, [D] + cols
+                gather = (ptrs, lds, cols, [sf[i].ptrs], c.rank, Tl, c.ready, c.next_epoch())
+            elif i == 0:
+                gather = ([xf.ptrs, hf.ptrs, dyf.ptrs],
+                          [xf.local.stride(0), hf.local.stride(0), dyf.local.stride(0)],
+                          [D, nR * r, nR * D], [sf[j].ptrs for j in range(nR)], c.rank, Tl, c.ready,
+                          c.next_epoch())
+            else:
+                gather = CB.NO_GATHER
             e.srw_bwd_gate_xr(h_i, emb, dy_i, write, p, p, dxr, ds, None, None, None, sf[i].local, dtau,
                               gl, st, *gather)
             pv, dxrv, dsv = p[:, :U], dxr[:, :U], ds[:, :U]

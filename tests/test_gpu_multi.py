@@ -256,6 +256,7 @@ def test_sharded_route_group_matches_single_process_fp32_oracle(world, version, 
     if version.endswith("+regs"):
         version = version[: -len("+regs")]
         monkeypatch.setenv("DSB_GATHER_REGS_MIN_UNITS", "1")      # the spawned ranks inherit it
+        monkeypatch.setenv("DSB_SPREAD_GATHER_RANKS", "2")         # and every kernel of a group gathers its own rows
     outs = _spawn(_group_vs_oracle, world, version, n_qk, n_v)
     sharp = ("demb", "dh", "doff")     # flow through d(gate)/d(score): bf16 rounding moves scores across the kink
     for o in outs:
