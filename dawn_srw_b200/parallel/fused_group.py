@@ -39,8 +39,10 @@ from .symm import SymmWorkspace
 
 MAX_ROUTES = 3
 # From this many ranks on, every kernel of a group gathers its own rows; below it the first
-# kernel gathers for all (measured: 2 ranks 780 vs 794 ms per 400M step in favour of the latter).
-kSpreadGatherRanks = int(__import__("os").environ.get("DSB_SPREAD_GATHER_RANKS", "4"))
+# kernel gathers for all.  Measured per 400M step: 2 ranks 780 vs 794 ms and 4 ranks 812 vs 837 ms
+# in favour of the single gather (the other kernels keep their full operand ring), 8 ranks 902 vs
+# 878 ms in favour of the spread one (1.35 GB would otherwise arrive in one 0.46 ms kernel).
+kSpreadGatherRanks = int(__import__("os").environ.get("DSB_SPREAD_GATHER_RANKS", "8"))
 
 
 class GroupShardComm:
