@@ -793,27 +793,43 @@ std::vector<Tensor> score_stats_bwd(c10::optional<Tensor> d_tau, c10::optional<T
 void adamw_multi(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> exp_avg,
                  std::vector<Tensor> exp_avg_sq, const Tensor& clip_scale, double lr, double b1,
                  double b2, double eps, double wd, double bc1, double bc2) {
-  for (size_t i = 0; i < params.size(); ++i) {
-    auto& p = params[i];
-    TORCH_CHECK(p.is_cuda() && p.scalar_type() == torch::kFloat32 && p.is_contiguous() &&
-                grads[i].is_contiguous() && grads[i].scalar_type() == torch::kFloat32);
-    const c10::cuda::CUDAGuard guard(p.device());
-    TORCH_CHECK(dsb_adamw(p.data_ptr<float>(), grads[i].data_ptr<float>(),
-                          exp_avg[i].data_ptr<float>(), exp_avg_sq[i].data_ptr<float>(), p.numel(),
-                          clip_scale.data_ptr<float>(), lr, b1, b2, eps, wd, bc1, bc2,
-                          cur_stream()) == 0);
+  if (params.empty()) return;
+  const size_t k = params.size();
+  TORCH_CHECK(grads.size() == k && exp_avg.size() == k && exp_avg_sq.size() == k);
+  std::vector<float*> p(k), m(k), v(k);
+  std::vector<const float*> g(k);
+  std::vector<long long> n(k);
+  for (size_t i = 0; i < k; ++i) {
+    auto ok = [](const Tensor& t) { return t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(); };
+    TORCH_CHECK(ok(params[i]) && ok(grads[i]) && ok(exp_avg[i]) && ok(exp_avg_sq[i]) &&
+                grads[i].numel() == params[i].numel() && exp_avg[i].numel() == params[i].numel() &&
+                exp_avg_sq[i].numel() == params[i].numel() && params[i].device() == params[0].device());
+    p[i] = params[i].data_ptr<float>();
+    g[i] = grads[i].data_ptr<float>();
+    m[i] = exp_avg[i].data_ptr<float>();
+    v[i] = exp_avg_sq[i].data_ptr<float>();
+    n[i] = params[i].numel();
   }
+  const c10::cuda::CUDAGuard guard(params[0].device());
+  TORCH_CHECK(dsb_adamw_multi(p.data(), g.data(), m.data(), v.data(), n.data(), static_cast<int>(k),
+                              clip_scale.data_ptr<float>(), lr, b1, b2, eps, wd, bc1, bc2,
+                              cur_stream()) == 0);
 }
 
 Tensor grad_sq_norm(std::vector<Tensor> grads) {
   TORCH_CHECK(!grads.empty());
   const c10::cuda::CUDAGuard guard(grads[0].device());
   auto out = torch::zeros({}, grads[0].options().dtype(torch::kFloat32));
-  for (auto& g : grads) {
-    TORCH_CHECK(g.scalar_type() == torch::kFloat32 && g.is_contiguous());
-    TORCH_CHECK(dsb_sqnorm_accumulate(g.data_ptr<float>(), g.numel(), out.data_ptr<float>(),
-                                      cur_stream()) == 0);
+  std::vector<const float*> g(grads.size());
+  std::vector<long long> n(grads.size());
+  for (size_t i = 0; i < grads.size(); ++i) {
+    TORCH_CHECK(grads[i].is_cuda() && grads[i].scalar_type() == torch::kFloat32 &&
+                grads[i].is_contiguous() && grads[i].device() == grads[0].device());
+    g[i] = grads[i].data_ptr<float>();
+    n[i] = grads[i].numel();
   }
+  TORCH_CHECK(dsb_sqnorm_multi(g.data(), n.data(), static_cast<int>(grads.size()),
+                               out.data_ptr<float>(), cur_stream()) == 0);
   return out;
 }
 

@@ -27,6 +27,13 @@ int dsb_adamw(float* p, const float* g, float* m, float* v, long long n, const f
               cudaStream_t stream);
 // out[0] += sum(g^2)
 int dsb_sqnorm_accumulate(const float* g, long long n, float* out, cudaStream_t stream);
+// The same two operations over lists of tensors (host arrays of device pointers and element
+// counts) in one launch per 160 tensors: a block takes a 64 K-element chunk of one tensor.
+int dsb_adamw_multi(float* const* p, const float* const* g, float* const* m, float* const* v,
+                    const long long* n, int count, const float* clip_scale, float lr, float b1,
+                    float b2, float eps, float wd, float bc1, float bc2, cudaStream_t stream);
+int dsb_sqnorm_multi(const float* const* g, const long long* n, int count, float* out,
+                     cudaStream_t stream);
 
 // out[t, :] = tok[ids[t], :] + pos[t % S, :]  (fp32, D % 4 == 0; ids clamped to [0, V)).
 int dsb_embed_fwd(const long long* ids, const float* tok, const float* pos, float* out, int T, int S,

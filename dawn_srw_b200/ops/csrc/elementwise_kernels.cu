@@ -555,3 +555,129 @@ extern "C" int dsb_dropout(const float* res, const float* x, float* y, long long
       reinterpret_cast<float4*>(y), n4, seed, thresh, 1.f / (1.f - p));
   return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
+
+// ----------------------------------------------------- multi-tensor launches
+// AdamW and the squared gradient norm over a whole list of tensors in one launch
+// each: a block takes one 64 K-element chunk of one tensor; the chunk -> tensor
+// map is a prefix table in the kernel parameters (binary search, 8 steps).
+namespace {
+
+constexpr int kMultiMax = 160;                 // tensors per launch
+constexpr long long kMultiChunk = 1 << 16;     // elements per block
+
+struct MultiTable {
+  const float* g[kMultiMax];
+  float* p[kMultiMax];
+  float* m[kMultiMax];
+  float* v[kMultiMax];
+  long long n[kMultiMax];
+  int first_chunk[kMultiMax + 1];
+  int count;
+};
+
+__device__ __forceinline__ int chunk_owner(const MultiTable& t, int chunk) {
+  int lo = 0, hi = t.count - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (t.first_chunk[mid] <= chunk) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(256) adamw_multi_kernel(const __grid_constant__ MultiTable t,
+                                                          const float* __restrict__ clip_scale,
+                                                          float lr, float b1, float b2, float eps,
+                                                          float wd, float bc1, float bc2) {
+  const int ti = chunk_owner(t, blockIdx.x);
+  const long long off = static_cast<long long>(blockIdx.x - t.first_chunk[ti]) * kMultiChunk;
+  const long long n = min(kMultiChunk, t.n[ti] - off);
+  float* __restrict__ p = t.p[ti] + off;
+  const float* __restrict__ g = t.g[ti] + off;
+  float* __restrict__ m = t.m[ti] + off;
+  float* __restrict__ v = t.v[ti] + off;
+  const float cs = *clip_scale;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const float gi = g[i] * cs;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float pi = p[i];
+    const float upd = (mi / bc1) / (sqrtf(vi / bc2) + eps) + wd * pi;
+    p[i] = pi - lr * upd;
+  }
+}
+
+__global__ void __launch_bounds__(256) sqnorm_multi_kernel(const __grid_constant__ MultiTable t,
+                                                           float* __restrict__ out) {
+  const int ti = chunk_owner(t, blockIdx.x);
+  const long long off = static_cast<long long>(blockIdx.x - t.first_chunk[ti]) * kMultiChunk;
+  const long long n = min(kMultiChunk, t.n[ti] - off);
+  const float* __restrict__ g = t.g[ti] + off;
+  float s = 0.f;
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+    const float x = g[i];
+    s = fmaf(x, x, s);
+  }
+  s = warp_sum(s);
+  __shared__ float sh[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sh[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int k = 0; k < 8; ++k) tot += sh[k];
+    atomicAdd(out, tot);
+  }
+}
+
+// Fills `t` with tensors [i0, i0 + cnt) of the lists; returns the number of chunks.
+int fill_table(MultiTable& t, const float* const* g, float* const* p, float* const* m, float* const* v,
+               const long long* n, int i0, int cnt) {
+  int chunks = 0, k = 0;
+  for (int i = i0; i < i0 + cnt; ++i) {
+    if (n[i] <= 0) continue;
+    t.g[k] = g[i];
+    t.p[k] = p != nullptr ? p[i] : nullptr;
+    t.m[k] = m != nullptr ? m[i] : nullptr;
+    t.v[k] = v != nullptr ? v[i] : nullptr;
+    t.n[k] = n[i];
+    t.first_chunk[k] = chunks;
+    chunks += static_cast<int>((n[i] + kMultiChunk - 1) / kMultiChunk);
+    ++k;
+  }
+  t.first_chunk[k] = chunks;
+  t.count = k;
+  return chunks;
+}
+
+}  // namespace
+
+extern "C" int dsb_adamw_multi(float* const* p, const float* const* g, float* const* m, float* const* v,
+                               const long long* n, int count, const float* clip_scale, float lr,
+                               float b1, float b2, float eps, float wd, float bc1, float bc2,
+                               cudaStream_t stream) {
+  for (int i0 = 0; i0 < count; i0 += kMultiMax) {
+    MultiTable t;
+    const int cnt = count - i0 < kMultiMax ? count - i0 : kMultiMax;
+    const int chunks = fill_table(t, g, p, m, v, n, i0, cnt);
+    if (chunks == 0) continue;
+    adamw_multi_kernel<<<chunks, 256, 0, stream>>>(t, clip_scale, lr, b1, b2, eps, wd, bc1, bc2);
+    if (cudaGetLastError() != cudaSuccess) return 1;
+  }
+  return 0;
+}
+
+extern "C" int dsb_sqnorm_multi(const float* const* g, const long long* n, int count, float* out,
+                                cudaStream_t stream) {
+  for (int i0 = 0; i0 < count; i0 += kMultiMax) {
+    MultiTable t;
+    const int cnt = count - i0 < kMultiMax ? count - i0 : kMultiMax;
+    const int chunks = fill_table(t, g, nullptr, nullptr, nullptr, n, i0, cnt);
+    if (chunks == 0) continue;
+    sqnorm_multi_kernel<<<chunks, 256, 0, stream>>>(t, out);
+    if (cudaGetLastError() != cudaSuccess) return 1;
+  }
+  return 0;
+}

@@ -605,8 +605,9 @@ def test_fused_adamw_and_grad_norm(cb):
     from dawn_srw_b200.train.optimizer import DawnAdamW
     dev = torch.device("cuda")
     torch.manual_seed(0)
-    shapes = [(130, 70), (70,), (1000, 33)]
-    names = ["router.proj_know.weight", "router.proj_know.bias", "neuron_pool.know_read"]
+    shapes = [(130, 70), (70,), (1000, 33), (300, 701), (3,)]      # one tensor spans several 64 K chunks
+    names = ["router.proj_know.weight", "router.proj_know.bias", "neuron_pool.know_read",
+             "layers.0.attn.expand_O.weight", "router.tau_attn.bias"]
     pa = [torch.nn.Parameter(torch.randn(*s, device=dev)) for s in shapes]
     pb = [torch.nn.Parameter(p.detach().clone()) for p in pa]
     oa = DawnAdamW(list(zip(names, pa)), lr=1e-2, fused=True)
